@@ -1,0 +1,71 @@
+/* CPU checker interface -- TEST INFRASTRUCTURE ONLY.
+ *
+ * Two libraries export this interface: the plain-C restatement (prefix fmo_,
+ * fm_oracle.c) and the harness around the reference project's own CPU code
+ * (prefix fmr_, ref_harness.c).  Both run the reference semantics of one
+ * decode step in fp32:
+ *
+ *   full attention (metal_infer/layer_forward.h:556-735):
+ *     per-head q/k RMS-norm (optional) -> partial RoPE at `pos` -> append k,v
+ *     at row `*len` -> *len += 1 -> softmax(q.K/sqrt(D)) V over rows [0,*len)
+ *     -> multiply by sigmoid(gate).
+ *   GatedDeltaNet (metal_infer/layer_forward.h:886-1025):
+ *     depthwise causal conv (width 4) + SiLU -> shift conv state -> q,k
+ *     RMS-normalise and scale -> decay / beta -> delta-rule recurrence on the
+ *     per-head [dv][dk] state -> gated RMS-norm with SiLU(z).
+ *
+ * Only tests, the smoke check and the bench's CPU-baseline leg may load these
+ * libraries.
+ */
+#ifndef FM_ORACLE_H
+#define FM_ORACLE_H
+#include <stdint.h>
+
+typedef struct {
+    int num_attn_heads;      /* 32 */
+    int num_kv_heads;        /* 2  */
+    int head_dim;            /* 256 */
+    int rotary_dim;          /* 64 */
+    float rope_theta;        /* 1e7 */
+    float rms_norm_eps;      /* 1e-6 */
+    int rope_scaling_mode;   /* 0 none, 1 linear, 2 NTK, 3 YaRN */
+    float rope_scale_factor; /* 1.0 */
+    int max_seq_len;         /* original context length (YaRN wavelength bounds) */
+    int linear_num_v_heads;  /* 64 */
+    int linear_num_k_heads;  /* 16 */
+    int linear_key_dim;      /* 128 */
+    int linear_value_dim;    /* 128 */
+    int conv_kernel_size;    /* 4 */
+} FmoDims;
+
+#define FMO_API(prefix)                                                                         \
+    /* One decode step. k_cache/v_cache: [capacity][kv_heads*head_dim] fp32, *len rows valid.   \
+       q, gate: [heads*head_dim] (already de-interleaved); k, v: [kv_heads*head_dim].           \
+       q_norm_w/k_norm_w: bf16 [head_dim] or NULL. out: [heads*head_dim].                       \
+       threads > 1 runs the per-head loop on that many OpenMP threads (same arithmetic).        \
+       Returns 0, or -1 on cache overflow (nothing written). */                                 \
+    int prefix##attn_step(const FmoDims *d, float *k_cache, float *v_cache, int *len,           \
+                          int capacity, const float *q, const float *gate, const float *k,      \
+                          const float *v, const uint16_t *q_norm_w, const uint16_t *k_norm_w,   \
+                          int pos, float *out, int threads);                                    \
+    /* n consecutive steps at positions start_pos.. (token-major inputs with leading [n]). */   \
+    int prefix##attn_run(const FmoDims *d, float *k_cache, float *v_cache, int *len,            \
+                         int capacity, const float *q, const float *gate, const float *k,       \
+                         const float *v, const uint16_t *q_norm_w, const uint16_t *k_norm_w,    \
+                         int start_pos, int n, float *out, int threads);                        \
+    /* One GatedDeltaNet step. conv_state: [(ks-1)][conv_dim]; ssm_state: [Hv][dv][dk].          \
+       qkv: [conv_dim] = q(Hk*dk) | k(Hk*dk) | v(Hv*dv); z: [Hv*dv]; beta, alpha: [Hv].          \
+       conv_w: bf16 [conv_dim][ks]; A_log: fp32 [Hv] or NULL; dt_bias: bf16 [Hv] or NULL;        \
+       norm_w: bf16 [dv] or NULL. out: [Hv*dv]. */                                              \
+    int prefix##gdn_step(const FmoDims *d, float *conv_state, float *ssm_state,                 \
+                         const float *qkv, const float *z, const float *beta,                   \
+                         const float *alpha, const uint16_t *conv_w, const float *A_log,        \
+                         const uint16_t *dt_bias, const uint16_t *norm_w, float *out,           \
+                         int threads);                                                          \
+    int prefix##gdn_run(const FmoDims *d, float *conv_state, float *ssm_state,                  \
+                        const float *qkv, const float *z, const float *beta,                    \
+                        const float *alpha, const uint16_t *conv_w, const float *A_log,         \
+                        const uint16_t *dt_bias, const uint16_t *norm_w, int n, float *out,     \
+                        int threads);
+
+#endif

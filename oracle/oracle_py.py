@@ -1,0 +1,123 @@
+"""ctypes binding of the CPU checkers -- TEST INFRASTRUCTURE ONLY.
+
+Importable from tests/, the smoke check and the bench's CPU-baseline leg;
+never from the product package.  ``Oracle("port")`` is the plain-C
+restatement, ``Oracle("reference")`` the reference project's own CPU code
+(present only when ``oracle/_ref/libfm_ref.so`` was built).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from pathlib import Path
+
+import numpy as np
+
+HERE = Path(__file__).resolve().parent
+
+
+class FmoDims(C.Structure):
+    _fields_ = [
+        ("num_attn_heads", C.c_int), ("num_kv_heads", C.c_int), ("head_dim", C.c_int),
+        ("rotary_dim", C.c_int), ("rope_theta", C.c_float), ("rms_norm_eps", C.c_float),
+        ("rope_scaling_mode", C.c_int), ("rope_scale_factor", C.c_float), ("max_seq_len", C.c_int),
+        ("linear_num_v_heads", C.c_int), ("linear_num_k_heads", C.c_int),
+        ("linear_key_dim", C.c_int), ("linear_value_dim", C.c_int), ("conv_kernel_size", C.c_int),
+    ]
+
+
+def make_dims(**kw) -> FmoDims:
+    d = dict(num_attn_heads=32, num_kv_heads=2, head_dim=256, rotary_dim=64, rope_theta=1e7,
+             rms_norm_eps=1e-6, rope_scaling_mode=0, rope_scale_factor=1.0, max_seq_len=262144,
+             linear_num_v_heads=64, linear_num_k_heads=16, linear_key_dim=128,
+             linear_value_dim=128, conv_kernel_size=4)
+    d.update(kw)
+    return FmoDims(**d)
+
+
+def _f32(a):
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    return a, a.ctypes.data_as(C.POINTER(C.c_float))
+
+
+def _u16(a):
+    if a is None:
+        return None, None
+    a = np.ascontiguousarray(a, dtype=np.uint16)
+    return a, a.ctypes.data_as(C.POINTER(C.c_uint16))
+
+
+def ref_available() -> bool:
+    return (HERE / "_ref" / "libfm_ref.so").exists()
+
+
+class Oracle:
+    def __init__(self, kind: str = "port"):
+        if kind == "reference":
+            path, self.prefix = HERE / "_ref" / "libfm_ref.so", "fmr_"
+        elif kind == "port":
+            path, self.prefix = HERE / "libfm_oracle.so", "fmo_"
+            if not path.exists():
+                import importlib.util
+                spec = importlib.util.spec_from_file_location("build_oracle", HERE / "build_oracle.py")
+                mod = importlib.util.module_from_spec(spec)
+                spec.loader.exec_module(mod)
+                mod.build_port()
+        else:
+            raise ValueError(kind)
+        self.kind = kind
+        self.lib = C.CDLL(str(path))
+        for name in ("attn_step", "attn_run", "gdn_step", "gdn_run"):
+            getattr(self.lib, self.prefix + name).restype = C.c_int
+
+    # -- full attention ------------------------------------------------------
+    def attn_run(self, dims: FmoDims, k_cache, v_cache, length: int, q, gate, k, v,
+                 q_norm_w=None, k_norm_w=None, start_pos=None, threads: int = 1):
+        """Run n decode steps. k_cache / v_cache are float32 [capacity][kv_dim] arrays updated in
+        place. Returns (out [n][q_dim], new length)."""
+        assert k_cache.dtype == np.float32 and k_cache.flags.c_contiguous
+        assert v_cache.dtype == np.float32 and v_cache.flags.c_contiguous
+        q, qp = _f32(q); gate, gp = _f32(gate); k, kp = _f32(k); v, vp = _f32(v)
+        n = q.shape[0] if q.ndim == 2 else 1
+        qd = dims.num_attn_heads * dims.head_dim
+        out = np.empty((n, qd), np.float32)
+        ln = C.c_int(length)
+        _a, qn = _u16(q_norm_w); _b, kn = _u16(k_norm_w)
+        if start_pos is None:
+            start_pos = length
+        rc = getattr(self.lib, self.prefix + "attn_run")(
+            C.byref(dims), k_cache.ctypes.data_as(C.POINTER(C.c_float)),
+            v_cache.ctypes.data_as(C.POINTER(C.c_float)), C.byref(ln), C.c_int(k_cache.shape[0]),
+            qp, gp, kp, vp, qn, kn, C.c_int(start_pos), C.c_int(n),
+            out.ctypes.data_as(C.POINTER(C.c_float)), C.c_int(threads))
+        if rc != 0:
+            raise RuntimeError("KV cache overflow in oracle")
+        return out, ln.value
+
+    # -- GatedDeltaNet -------------------------------------------------------
+    def gdn_run(self, dims: FmoDims, conv_state, ssm_state, qkv, z, beta, alpha, conv_w, A_log,
+                dt_bias, norm_w, threads: int = 1):
+        """Run n steps; conv_state / ssm_state float32 arrays updated in place. Returns out."""
+        for a in (conv_state, ssm_state):
+            assert a.dtype == np.float32 and a.flags.c_contiguous
+        qkv, qp = _f32(qkv); z, zp = _f32(z); beta, bp = _f32(beta); alpha, ap = _f32(alpha)
+        n = qkv.shape[0] if qkv.ndim == 2 else 1
+        vd = dims.linear_num_v_heads * dims.linear_value_dim
+        out = np.empty((n, vd), np.float32)
+        _a, cw = _u16(conv_w); _b, db = _u16(dt_bias); _c, nw = _u16(norm_w)
+        if A_log is not None:
+            A_log, alp = _f32(A_log)
+        else:
+            alp = None
+        getattr(self.lib, self.prefix + "gdn_run")(
+            C.byref(dims), conv_state.ctypes.data_as(C.POINTER(C.c_float)),
+            ssm_state.ctypes.data_as(C.POINTER(C.c_float)), qp, zp, bp, ap, cw, alp, db, nw,
+            C.c_int(n), out.ctypes.data_as(C.POINTER(C.c_float)), C.c_int(threads))
+        return out
+
+
+def host_threads() -> int:
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
