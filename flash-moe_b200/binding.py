@@ -1,0 +1,201 @@
+"""ctypes binding of libfm_b200.so (the C-ABI of include/fm_attn.h) for tests and benches.
+
+The product is the shared library; this module only turns numpy arrays / torch tensors into the
+pointers the C-ABI takes.  There is no fallback: if the library is missing, importing fails.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+import numpy as np
+
+HERE = Path(__file__).resolve().parent
+LIB_PATH = HERE / "libfm_b200.so"
+
+FM_OK, FM_ERR_INVALID, FM_ERR_CAPACITY, FM_ERR_NOMEM, FM_ERR_CUDA, FM_ERR_TIMEOUT, FM_ERR_UNSUPPORTED = range(7)
+FM_PTR_DEVICE, FM_PTR_HOST = 0, 1
+
+EXPORTS = [
+    "fm_default_config", "fm_create", "fm_destroy", "fm_last_error", "fm_set_stream",
+    "fm_set_pointer_mode", "fm_synchronize", "fm_reset", "fm_kv_len", "fm_kv_append_rope",
+    "fm_attn_decode", "fm_attn_decode_partial", "fm_attn_merge_gate", "fm_attn_prefill",
+    "fm_gdn_decode", "fm_gdn_prefill", "fm_kv_export", "fm_kv_import", "fm_state_export",
+    "fm_state_import", "fm_launch_count",
+]
+
+
+class FmConfig(C.Structure):
+    _fields_ = [
+        ("num_attn_heads", C.c_int), ("num_kv_heads", C.c_int), ("head_dim", C.c_int),
+        ("rotary_dim", C.c_int), ("rope_theta", C.c_float), ("rms_norm_eps", C.c_float),
+        ("rope_scaling_mode", C.c_int), ("rope_scale_factor", C.c_float),
+        ("rope_orig_max_pos", C.c_int), ("num_full_layers", C.c_int),
+        ("linear_num_v_heads", C.c_int), ("linear_num_k_heads", C.c_int),
+        ("linear_key_dim", C.c_int), ("linear_value_dim", C.c_int), ("conv_kernel_size", C.c_int),
+        ("num_linear_layers", C.c_int),
+        ("max_seqs", C.c_int), ("max_seq_len", C.c_int), ("page_size", C.c_int),
+        ("kv_pool_pages", C.c_int64), ("max_batch_tokens", C.c_int),
+        ("seq_shard_rank", C.c_int), ("seq_shard_count", C.c_int), ("device", C.c_int),
+    ]
+
+
+class FmError(RuntimeError):
+    def __init__(self, status: int, text: str):
+        super().__init__(f"fm status {status}: {text}")
+        self.status = status
+        self.text = text
+
+
+def load_library() -> C.CDLL:
+    if not LIB_PATH.exists():
+        raise ImportError(f"{LIB_PATH} is not built: run `python flash-moe_b200/build.py` "
+                          "(there is no CPU or PyTorch fallback for this library)")
+    lib = C.CDLL(str(LIB_PATH))
+    lib.fm_last_error.restype = C.c_char_p
+    lib.fm_last_error.argtypes = [C.c_void_p]
+    lib.fm_launch_count.restype = C.c_int64
+    lib.fm_launch_count.argtypes = [C.c_void_p]
+    lib.fm_destroy.restype = None
+    lib.fm_destroy.argtypes = [C.c_void_p]
+    lib.fm_default_config.restype = None
+    return lib
+
+
+def _ptr(a):
+    """Pointer of a numpy array, a torch tensor, or None."""
+    if a is None:
+        return None
+    if isinstance(a, np.ndarray):
+        assert a.flags.c_contiguous
+        return C.c_void_p(a.ctypes.data)
+    # torch tensor
+    assert a.is_contiguous()
+    return C.c_void_p(a.data_ptr())
+
+
+def _ints(a):
+    arr = np.ascontiguousarray(np.atleast_1d(np.asarray(a)), dtype=np.int32)
+    return arr, arr.ctypes.data_as(C.POINTER(C.c_int))
+
+
+def default_config(**kw) -> FmConfig:
+    lib = load_library()
+    cfg = FmConfig()
+    lib.fm_default_config(C.byref(cfg))
+    for k, v in kw.items():
+        if not hasattr(cfg, k):
+            raise AttributeError(k)
+        setattr(cfg, k, v)
+    return cfg
+
+
+class Context:
+    """One FmCtx.  Arrays given to the methods must match the pointer mode: numpy (host) arrays in
+    FM_PTR_HOST mode, CUDA torch tensors in FM_PTR_DEVICE mode."""
+
+    def __init__(self, cfg: FmConfig | None = None, host_pointers: bool = False, **kw):
+        self.lib = load_library()
+        self.cfg = cfg if cfg is not None else default_config(**kw)
+        h = C.c_void_p()
+        st = self.lib.fm_create(C.byref(self.cfg), C.byref(h))
+        if st != FM_OK:
+            raise FmError(st, self.lib.fm_last_error(None).decode())
+        self.h = h
+        if host_pointers:
+            self.set_pointer_mode(FM_PTR_HOST)
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.lib.fm_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _check(self, st):
+        if st != FM_OK:
+            raise FmError(st, self.lib.fm_last_error(self.h).decode())
+
+    def last_error(self) -> str:
+        return self.lib.fm_last_error(self.h).decode()
+
+    def set_stream(self, stream_ptr: int):
+        self._check(self.lib.fm_set_stream(self.h, C.c_void_p(stream_ptr)))
+
+    def set_pointer_mode(self, mode: int):
+        self._check(self.lib.fm_set_pointer_mode(self.h, C.c_int(mode)))
+
+    def synchronize(self):
+        self._check(self.lib.fm_synchronize(self.h))
+
+    def reset(self, seq: int = -1):
+        self._check(self.lib.fm_reset(self.h, C.c_int(seq)))
+
+    def kv_len(self, fa_idx: int, seq: int = 0) -> int:
+        return self.lib.fm_kv_len(self.h, C.c_int(fa_idx), C.c_int(seq))
+
+    def launch_count(self) -> int:
+        return self.lib.fm_launch_count(self.h)
+
+    def kv_append_rope(self, fa_idx, seq, pos, k, v, k_norm_w=None):
+        s, sp = _ints(seq); p, pp = _ints(pos)
+        self._check(self.lib.fm_kv_append_rope(self.h, C.c_int(fa_idx), sp, pp, C.c_int(len(s)),
+                                               _ptr(k), _ptr(v), _ptr(k_norm_w)))
+
+    def attn_decode(self, fa_idx, seq, pos, out, q_proj_out=None, q=None, gate=None, k=None, v=None,
+                    q_norm_w=None, k_norm_w=None):
+        s, sp = _ints(seq); p, pp = _ints(pos)
+        self._check(self.lib.fm_attn_decode(self.h, C.c_int(fa_idx), sp, pp, C.c_int(len(s)),
+                                            _ptr(q_proj_out), _ptr(q), _ptr(gate), _ptr(k), _ptr(v),
+                                            _ptr(q_norm_w), _ptr(k_norm_w), _ptr(out)))
+
+    def attn_decode_partial(self, fa_idx, seq, pos, o_part, ml_part, q_proj_out=None, q=None, k=None,
+                            v=None, q_norm_w=None, k_norm_w=None):
+        s, sp = _ints(seq); p, pp = _ints(pos)
+        self._check(self.lib.fm_attn_decode_partial(self.h, C.c_int(fa_idx), sp, pp, C.c_int(len(s)),
+                                                    _ptr(q_proj_out), _ptr(q), _ptr(k), _ptr(v),
+                                                    _ptr(q_norm_w), _ptr(k_norm_w), _ptr(o_part),
+                                                    _ptr(ml_part)))
+
+    def attn_merge_gate(self, nparts, o_parts, ml_parts, batch, out, q_proj_out=None, gate=None):
+        self._check(self.lib.fm_attn_merge_gate(self.h, C.c_int(nparts), _ptr(o_parts), _ptr(ml_parts),
+                                                _ptr(q_proj_out), _ptr(gate), C.c_int(batch), _ptr(out)))
+
+    def attn_prefill(self, fa_idx, seq, start_pos, n, out, q_proj_out=None, q=None, gate=None, k=None,
+                     v=None, q_norm_w=None, k_norm_w=None):
+        self._check(self.lib.fm_attn_prefill(self.h, C.c_int(fa_idx), C.c_int(seq), C.c_int(start_pos),
+                                             C.c_int(n), _ptr(q_proj_out), _ptr(q), _ptr(gate), _ptr(k),
+                                             _ptr(v), _ptr(q_norm_w), _ptr(k_norm_w), _ptr(out)))
+
+    def gdn_decode(self, li, seq, qkv, z, beta, alpha, out, conv_w=None, A_log=None, dt_bias=None,
+                   norm_w=None):
+        s, sp = _ints(seq)
+        self._check(self.lib.fm_gdn_decode(self.h, C.c_int(li), sp, C.c_int(len(s)), _ptr(qkv), _ptr(z),
+                                           _ptr(beta), _ptr(alpha), _ptr(conv_w), _ptr(A_log),
+                                           _ptr(dt_bias), _ptr(norm_w), _ptr(out)))
+
+    def gdn_prefill(self, li, seq, n, qkv, z, beta, alpha, out, conv_w=None, A_log=None, dt_bias=None,
+                    norm_w=None, chunk=0):
+        self._check(self.lib.fm_gdn_prefill(self.h, C.c_int(li), C.c_int(seq), C.c_int(n), C.c_int(chunk),
+                                            _ptr(qkv), _ptr(z), _ptr(beta), _ptr(alpha), _ptr(conv_w),
+                                            _ptr(A_log), _ptr(dt_bias), _ptr(norm_w), _ptr(out)))
+
+    def kv_export(self, fa_idx, seq, k, v, max_rows) -> int:
+        n = C.c_int(0)
+        self._check(self.lib.fm_kv_export(self.h, C.c_int(fa_idx), C.c_int(seq), _ptr(k), _ptr(v),
+                                          C.c_int(max_rows), C.byref(n)))
+        return n.value
+
+    def kv_import(self, fa_idx, seq, k, v, length):
+        self._check(self.lib.fm_kv_import(self.h, C.c_int(fa_idx), C.c_int(seq), _ptr(k), _ptr(v),
+                                          C.c_int(length)))
+
+    def state_export(self, li, seq, conv, ssm):
+        self._check(self.lib.fm_state_export(self.h, C.c_int(li), C.c_int(seq), _ptr(conv), _ptr(ssm)))
+
+    def state_import(self, li, seq, conv, ssm):
+        self._check(self.lib.fm_state_import(self.h, C.c_int(li), C.c_int(seq), _ptr(conv), _ptr(ssm)))

@@ -1,0 +1,363 @@
+// Split-KV decode attention over the paged bf16 KV store, and the log-sum-exp merge with the fused
+// sigmoid output gate.
+//
+// Math of metal_infer/layer_forward.h:631-735 (scores = q.K/sqrt(D), max-subtracted softmax,
+// weighted sum of V, times sigmoid(gate)), re-organised for a GPU:
+//   * one CTA per (split of the sequence, KV head, sequence); the query heads that share the KV
+//     head (up to 16) form the M dimension of bf16 tensor-core MMAs, so K and V are read from HBM
+//     exactly once per step instead of once per query head;
+//   * K/V pages (64 rows x 256 dims, 32 KB contiguous each) stream through a 3-stage shared-memory
+//     ring filled by 16-byte asynchronous copies;
+//   * online softmax in the exp2 domain with warp-shuffle row maxima; the running maximum is only
+//     advanced when a row's maximum grew by more than 2^8, which keeps the rescaling of the
+//     accumulators off the common path;
+//   * q and the softmax weights enter the MMAs as two bf16 terms (hi + lo), which keeps ~16
+//     mantissa bits: K and V are exact in bf16, so the result tracks the fp32 reference to ~1e-4;
+//   * each CTA writes an un-normalised partial (O, max, sum); a second kernel merges the partials
+//     and applies the gate.
+#include "fm_device.cuh"
+#include "fm_internal.h"
+
+namespace fm {
+
+constexpr int kD = 256;          // head dim the kernel is built for
+constexpr int kPage = 64;        // rows per page
+constexpr int kStages = 3;
+constexpr int kTileBytes = kPage * kD * 2;  // one K or V tile: 32 KB
+constexpr int kDecThreads = 128;
+constexpr int kQBytes = 16 * kD * 2;        // 16 heads x 256 bf16
+constexpr int kDecSmem = 2 * kQBytes + kStages * 2 * kTileBytes;
+
+__device__ __forceinline__ void load_tile_async(uint32_t dst, const __nv_bfloat16 *src, int tid) {
+    // 64 rows x 32 chunks of 16 B; consecutive threads take consecutive chunks (coalesced 512 B / warp)
+#pragma unroll
+    for (int i = 0; i < (kPage * 32) / kDecThreads; i++) {
+        const int c = tid + i * kDecThreads;
+        const int row = c >> 5, ch = c & 31;
+        cp_async16(dst + swz_row512(row, ch), reinterpret_cast<const char *>(src) + (size_t)c * 16);
+    }
+}
+
+__global__ void __launch_bounds__(kDecThreads, 1)
+attn_decode_kernel(KvView kv, RopeParams rope, TokSpec toks, int H, const float *__restrict__ q_proj_out,
+                   const float *__restrict__ q_in, const uint16_t *__restrict__ qnw, float eps,
+                   float *__restrict__ part_o, float *__restrict__ part_ml, int nsplits) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    const uint32_t s_qhi = smem_u32(smem);
+    const uint32_t s_qlo = s_qhi + kQBytes;
+    const uint32_t s_kv = s_qlo + kQBytes;  // stage s: K at s_kv + s*2*kTileBytes, V right after
+    unsigned char *kv_raw = smem + 2 * kQBytes;
+
+    const int split = blockIdx.x, kvh = blockIdx.y, tok = blockIdx.z;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int group = H / kv.Hkv;  // query heads per KV head (<= 16)
+
+    int seq, pos, row_new;
+    tok_get(toks, tok, seq, pos, row_new);
+    const int L = row_new + 1;  // rows attended, the new one included
+
+    // ---- which page slots this CTA walks ----
+    const int gpages = (L + kPage - 1) / kPage;
+    const int nslots = gpages > kv.shard_rank ? (gpages - kv.shard_rank + kv.shard_count - 1) / kv.shard_count : 0;
+    const int per = (nslots + nsplits - 1) / nsplits;
+    const int slot_begin = split * per;
+    const int slot_end = min(nslots, slot_begin + per);
+    const int ntiles = max(0, slot_end - slot_begin);
+    const int *ptab = kv.page_table + (size_t)seq * kv.max_slots;
+    const size_t page_elems = (size_t)2 * kv.Hkv * kPage * kD;
+
+    auto issue = [&](int t) {
+        if (t < ntiles) {
+            const int page = ptab[slot_begin + t];
+            const __nv_bfloat16 *base = kv.pool + (size_t)page * page_elems;
+            const uint32_t dst = s_kv + (uint32_t)(t % kStages) * 2 * kTileBytes;
+            load_tile_async(dst, base + (size_t)kvh * kPage * kD, tid);
+            load_tile_async(dst + kTileBytes, base + (size_t)(kv.Hkv + kvh) * kPage * kD, tid);
+        }
+        cp_async_commit();
+    };
+    issue(0);
+    issue(1);
+
+    // ---- q: RMS-norm, partial RoPE, scale, split into two bf16 terms -> shared memory ----
+    // stage 2 of the ring is free until the first loop iteration: use it as fp32 scratch
+    {
+        float *scratch = reinterpret_cast<float *>(kv_raw + 2 * 2 * kTileBytes);  // [16][256]
+        const float qscale = rope.logit_scale * kLog2e;
+        const int half = rope.rotary_dim / 2;
+        for (int r = warp; r < 16; r += 4) {
+            float x[8];
+            if (r < group) {
+                const int head = kvh * group + r;
+                const float *src = q_proj_out ? q_proj_out + ((size_t)tok * H + head) * 2 * kD
+                                              : q_in + ((size_t)tok * H + head) * kD;
+                const float4 a = *reinterpret_cast<const float4 *>(src + lane * 8);
+                const float4 b = *reinterpret_cast<const float4 *>(src + lane * 8 + 4);
+                x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w;
+                x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+                if (qnw != nullptr) {
+                    float ss = 0.f;
+#pragma unroll
+                    for (int j = 0; j < 8; j++) ss += x[j] * x[j];
+                    ss = warp_sum(ss);
+                    const float inv = 1.0f / sqrtf(ss / kD + eps);
+#pragma unroll
+                    for (int j = 0; j < 8; j++) x[j] = x[j] * inv * bf16_bits_to_float(qnw[lane * 8 + j]);
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; j++) x[j] = 0.f;
+            }
+            float *srow = scratch + r * kD;
+#pragma unroll
+            for (int j = 0; j < 8; j++) srow[lane * 8 + j] = x[j];
+            __syncwarp();
+            if (r < group) {
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    const int d = lane * 8 + j;
+                    if (d < rope.rotary_dim) {
+                        const int i = d < half ? d : d - half;
+                        const float ang = ((float)pos / rope.pos_div) * rope.inv_freq[i];
+                        const float c = cosf(ang), s = sinf(ang);
+                        x[j] = d < half ? x[j] * c - srow[d + half] * s : srow[d - half] * s + x[j] * c;
+                    }
+                }
+            }
+            uint32_t hi[4], lo[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) split_pack_bf16(x[2 * j] * qscale, x[2 * j + 1] * qscale, hi[j], lo[j]);
+            const uint32_t off = swz_row512(r, lane);
+            asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};\n" ::"r"(s_qhi + off), "r"(hi[0]), "r"(hi[1]), "r"(hi[2]), "r"(hi[3]));
+            asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};\n" ::"r"(s_qlo + off), "r"(lo[0]), "r"(lo[1]), "r"(lo[2]), "r"(lo[3]));
+        }
+    }
+
+    // ---- main loop ----
+    float o[32][4];
+#pragma unroll
+    for (int i = 0; i < 32; i++) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    float m_ref[2] = {kNegBig, kNegBig};  // rows lane/4 and lane/4 + 8
+    float l_sum[2] = {0.f, 0.f};
+
+    const int lm = lane >> 3, lr = lane & 7;  // ldmatrix: matrix index and row within it
+    for (int t = 0; t < ntiles; t++) {
+        cp_async_wait<1>();
+        __syncthreads();  // tile t landed for everyone; everyone is done with tile t-1 (and with q)
+        issue(t + 2);
+
+        const int gpage = (slot_begin + t) * kv.shard_count + kv.shard_rank;
+        const int p0 = gpage * kPage + warp * 16;  // first row of this warp's 16
+        if (p0 >= L) continue;
+        const uint32_t sk = s_kv + (uint32_t)(t % kStages) * 2 * kTileBytes;
+        const uint32_t sv = sk + kTileBytes;
+
+        // S = Q K^T for 16 heads x 16 rows
+        float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+        for (int kk = 0; kk < kD / 16; kk++) {
+            uint32_t ah[4], al[4], b[4];
+            const uint32_t qoff = swz_row512(lr + (lm & 1) * 8, 2 * kk + (lm >> 1));
+            ldmatrix_x4(ah[0], ah[1], ah[2], ah[3], s_qhi + qoff);
+            ldmatrix_x4(al[0], al[1], al[2], al[3], s_qlo + qoff);
+            ldmatrix_x4(b[0], b[1], b[2], b[3], sk + swz_row512(warp * 16 + (lm >> 1) * 8 + lr, 2 * kk + (lm & 1)));
+            mma_bf16(s[0], ah[0], ah[1], ah[2], ah[3], b[0], b[1]);
+            mma_bf16(s[1], ah[0], ah[1], ah[2], ah[3], b[2], b[3]);
+            mma_bf16(s[0], al[0], al[1], al[2], al[3], b[0], b[1]);
+            mma_bf16(s[1], al[0], al[1], al[2], al[3], b[2], b[3]);
+        }
+        // mask rows beyond the sequence
+        if (p0 + 16 > L) {
+#pragma unroll
+            for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const int p = p0 + nt * 8 + 2 * (lane & 3) + (e & 1);
+                    if (p >= L) s[nt][e] = kNegBig;
+                }
+        }
+        // row maxima (rows g and g+8), shared by the 4 lanes of a quad
+        float mx[2];
+        mx[0] = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+        mx[1] = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+        }
+        const bool grow = (mx[0] > m_ref[0] + 8.f) || (mx[1] > m_ref[1] + 8.f);
+        if (__any_sync(0xffffffffu, grow)) {
+            float corr[2];
+#pragma unroll
+            for (int r = 0; r < 2; r++) {
+                const float mn = fmaxf(m_ref[r], mx[r]);
+                corr[r] = fast_exp2(m_ref[r] - mn);
+                m_ref[r] = mn;
+                l_sum[r] *= corr[r];
+            }
+#pragma unroll
+            for (int i = 0; i < 32; i++) {
+                o[i][0] *= corr[0]; o[i][1] *= corr[0];
+                o[i][2] *= corr[1]; o[i][3] *= corr[1];
+            }
+        }
+        // weights, as two bf16 terms
+        uint32_t ph[4], pl[4];
+        {
+            float p[2][4];
+#pragma unroll
+            for (int nt = 0; nt < 2; nt++) {
+                p[nt][0] = fast_exp2(s[nt][0] - m_ref[0]);
+                p[nt][1] = fast_exp2(s[nt][1] - m_ref[0]);
+                p[nt][2] = fast_exp2(s[nt][2] - m_ref[1]);
+                p[nt][3] = fast_exp2(s[nt][3] - m_ref[1]);
+            }
+            l_sum[0] += p[0][0] + p[0][1] + p[1][0] + p[1][1];
+            l_sum[1] += p[0][2] + p[0][3] + p[1][2] + p[1][3];
+            split_pack_bf16(p[0][0], p[0][1], ph[0], pl[0]);
+            split_pack_bf16(p[0][2], p[0][3], ph[1], pl[1]);
+            split_pack_bf16(p[1][0], p[1][1], ph[2], pl[2]);
+            split_pack_bf16(p[1][2], p[1][3], ph[3], pl[3]);
+        }
+        // O += P V
+#pragma unroll
+        for (int nn = 0; nn < kD / 16; nn++) {
+            uint32_t b[4];
+            ldmatrix_x4_trans(b[0], b[1], b[2], b[3], sv + swz_row512(warp * 16 + (lm & 1) * 8 + lr, 2 * nn + (lm >> 1)));
+            mma_bf16(o[2 * nn], ph[0], ph[1], ph[2], ph[3], b[0], b[1]);
+            mma_bf16(o[2 * nn + 1], ph[0], ph[1], ph[2], ph[3], b[2], b[3]);
+            mma_bf16(o[2 * nn], pl[0], pl[1], pl[2], pl[3], b[0], b[1]);
+            mma_bf16(o[2 * nn + 1], pl[0], pl[1], pl[2], pl[3], b[2], b[3]);
+        }
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+
+    // ---- merge the four warps through shared memory (the ring is free now) ----
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+        l_sum[r] += __shfl_xor_sync(0xffffffffu, l_sum[r], 1);
+        l_sum[r] += __shfl_xor_sync(0xffffffffu, l_sum[r], 2);
+    }
+    float *s_o = reinterpret_cast<float *>(kv_raw);                 // [4][16][256]
+    float *s_ml = reinterpret_cast<float *>(kv_raw + 4 * 16 * kD * 4);  // [4][16][2]
+    {
+        const int g = lane >> 2, tq = lane & 3;
+        if (tq == 0) {
+            s_ml[(warp * 16 + g) * 2 + 0] = m_ref[0];
+            s_ml[(warp * 16 + g) * 2 + 1] = l_sum[0];
+            s_ml[(warp * 16 + g + 8) * 2 + 0] = m_ref[1];
+            s_ml[(warp * 16 + g + 8) * 2 + 1] = l_sum[1];
+        }
+        float *wo = s_o + (size_t)warp * 16 * kD;
+#pragma unroll
+        for (int i = 0; i < 32; i++) {
+            *reinterpret_cast<float2 *>(wo + g * kD + i * 8 + 2 * tq) = make_float2(o[i][0], o[i][1]);
+            *reinterpret_cast<float2 *>(wo + (g + 8) * kD + i * 8 + 2 * tq) = make_float2(o[i][2], o[i][3]);
+        }
+    }
+    __syncthreads();
+    for (int r = warp; r < group; r += 4) {
+        float mw[4], M = kNegBig;
+#pragma unroll
+        for (int w = 0; w < 4; w++) {
+            mw[w] = s_ml[(w * 16 + r) * 2];
+            M = fmaxf(M, mw[w]);
+        }
+        float f[4], lt = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; w++) {
+            f[w] = fast_exp2(mw[w] - M);
+            lt += f[w] * s_ml[(w * 16 + r) * 2 + 1];
+        }
+        const int head = kvh * group + r;
+        const size_t prow = ((size_t)tok * H + head) * nsplits + split;
+        float *dst = part_o + prow * kD;
+#pragma unroll
+        for (int j = 0; j < kD / 128; j++) {
+            const int d = (j * 32 + lane) * 4;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int w = 0; w < 4; w++) {
+                const float4 v = *reinterpret_cast<const float4 *>(s_o + ((size_t)w * 16 + r) * kD + d);
+                acc.x += f[w] * v.x; acc.y += f[w] * v.y; acc.z += f[w] * v.z; acc.w += f[w] * v.w;
+            }
+            *reinterpret_cast<float4 *>(dst + d) = acc;
+        }
+        if (lane == 0) {
+            part_ml[prow * 2 + 0] = M;
+            part_ml[prow * 2 + 1] = lt;
+        }
+    }
+}
+
+int launch_attn_decode(const KvView &kv, const RopeParams &rope, const TokSpec &toks, int H,
+                       const float *q_proj_out, const float *q, const uint16_t *q_norm_w, float eps,
+                       float *part_o, float *part_ml, int nsplits, cudaStream_t st) {
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmem) != cudaSuccess)
+            return -1;
+        configured = true;
+    }
+    dim3 grid(nsplits, kv.Hkv, toks.n);
+    attn_decode_kernel<<<grid, kDecThreads, kDecSmem, st>>>(kv, rope, toks, H, q_proj_out, q, q_norm_w, eps,
+                                                            part_o, part_ml, nsplits);
+    return cudaGetLastError() == cudaSuccess ? 1 : -1;
+}
+
+// ---- merge of partial results + sigmoid gate -------------------------------------------------
+// grid (H, tokens), block D/4 threads (one float4 each).
+// Final mode (out != nullptr && ml_out == nullptr): out = sum_j w_j O_j / sum_j w_j l_j * sigmoid(gate)
+// Partial mode (ml_out != nullptr): out = sum_j w_j O_j (relative to the merged maximum), ml_out = (M, l)
+__global__ void attn_merge_kernel(const float *__restrict__ part_o, const float *__restrict__ part_ml,
+                                  int nparts, long long ps_o, long long ps_ml, long long ts_o,
+                                  long long ts_ml, long long hs_o, long long hs_ml, int H, int D,
+                                  const float *__restrict__ q_proj_out, const float *__restrict__ gate,
+                                  float *__restrict__ out, float *__restrict__ ml_out) {
+    const int head = blockIdx.x, tok = blockIdx.y, d = threadIdx.x * 4;
+    const float *o0 = part_o + tok * ts_o + head * hs_o;
+    const float *ml0 = part_ml + tok * ts_ml + head * hs_ml;
+    float M = kNegBig;
+    for (int j = 0; j < nparts; j++) M = fmaxf(M, ml0[j * ps_ml]);
+    float lt = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int j = 0; j < nparts; j++) {
+        const float w = fast_exp2(ml0[j * ps_ml] - M);
+        lt += w * ml0[j * ps_ml + 1];
+        const float4 v = *reinterpret_cast<const float4 *>(o0 + j * ps_o + d);
+        acc.x += w * v.x; acc.y += w * v.y; acc.z += w * v.z; acc.w += w * v.w;
+    }
+    float *dst = out + ((size_t)tok * H + head) * D + d;
+    if (ml_out != nullptr) {
+        *reinterpret_cast<float4 *>(dst) = acc;
+        if (threadIdx.x == 0) {
+            ml_out[((size_t)tok * H + head) * 2 + 0] = M;
+            ml_out[((size_t)tok * H + head) * 2 + 1] = lt;
+        }
+        return;
+    }
+    const float inv = lt > 0.f ? 1.0f / lt : 0.f;
+    const float *gsrc = q_proj_out ? q_proj_out + ((size_t)tok * H + head) * 2 * D + D + d
+                                   : gate + ((size_t)tok * H + head) * D + d;
+    const float4 g = *reinterpret_cast<const float4 *>(gsrc);
+    float4 r;
+    r.x = acc.x * inv * (1.0f / (1.0f + __expf(-g.x)));
+    r.y = acc.y * inv * (1.0f / (1.0f + __expf(-g.y)));
+    r.z = acc.z * inv * (1.0f / (1.0f + __expf(-g.z)));
+    r.w = acc.w * inv * (1.0f / (1.0f + __expf(-g.w)));
+    *reinterpret_cast<float4 *>(dst) = r;
+}
+
+int launch_attn_merge(const float *part_o, const float *part_ml, int nparts, long long ps_o,
+                      long long ps_ml, long long ts_o, long long ts_ml, long long hs_o,
+                      long long hs_ml, int ntok, int H, int D, const float *q_proj_out,
+                      const float *gate, float *out, float *ml_out, cudaStream_t st) {
+    if (ntok <= 0) return 0;
+    dim3 grid(H, ntok);
+    attn_merge_kernel<<<grid, D / 4, 0, st>>>(part_o, part_ml, nparts, ps_o, ps_ml, ts_o, ts_ml, hs_o,
+                                              hs_ml, H, D, q_proj_out, gate, out, ml_out);
+    return cudaGetLastError() == cudaSuccess ? 1 : -1;
+}
+
+}  // namespace fm

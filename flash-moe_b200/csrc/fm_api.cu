@@ -1,0 +1,788 @@
+// C-ABI layer: context, paged-KV page allocator, pointer-mode staging, argument checks, and the
+// host-side sequencing of the kernels for each entry point of include/fm_attn.h.
+#include <math.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <algorithm>
+#include <new>
+
+#include "fm_internal.h"
+
+using namespace fm;
+
+static std::string g_create_error;
+
+static fm_status fail(FmCtx *ctx, fm_status st, const char *fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    if (ctx) ctx->err = buf; else g_create_error = buf;
+    return st;
+}
+
+#define FM_CUDA(ctx, call)                                                                          \
+    do {                                                                                            \
+        cudaError_t e__ = (call);                                                                   \
+        if (e__ != cudaSuccess)                                                                     \
+            return fail(ctx, FM_ERR_CUDA, "%s failed: %s", #call, cudaGetErrorString(e__));         \
+    } while (0)
+
+static fm_status launched(FmCtx *ctx, int n, const char *what) {
+    if (n < 0) return fail(ctx, FM_ERR_CUDA, "%s launch failed: %s", what, cudaGetErrorString(cudaGetLastError()));
+    ctx->launches += n;
+    return FM_OK;
+}
+
+extern "C" void fm_default_config(FmConfig *c) {
+    memset(c, 0, sizeof *c);
+    c->num_attn_heads = 32; c->num_kv_heads = 2; c->head_dim = 256; c->rotary_dim = 64;
+    c->rope_theta = 1e7f; c->rms_norm_eps = 1e-6f;
+    c->rope_scaling_mode = 0; c->rope_scale_factor = 1.0f; c->rope_orig_max_pos = 262144;
+    c->num_full_layers = 15;
+    c->linear_num_v_heads = 64; c->linear_num_k_heads = 16; c->linear_key_dim = 128;
+    c->linear_value_dim = 128; c->conv_kernel_size = 4; c->num_linear_layers = 45;
+    c->max_seqs = 1; c->max_seq_len = 8192; c->page_size = 64; c->kv_pool_pages = 0;
+    c->max_batch_tokens = 64;
+    c->seq_shard_rank = 0; c->seq_shard_count = 1; c->device = 0;
+}
+
+// RoPE frequency of pair i under the scaling modes of metal_infer/layer_forward.h:22-63, evaluated
+// on the host in fp32 with the same expressions so that device angles equal the CPU path's.
+static float rope_inv_freq(const FmConfig &c, int i) {
+    const float base = c.rope_theta;
+    const int rot = c.rotary_dim;
+    const float s = c.rope_scale_factor;
+    const float expo = (float)(2 * i) / rot;
+    if (c.rope_scaling_mode == 0 || s <= 1.0f || c.rope_scaling_mode == 1) return 1.0f / powf(base, expo);
+    const float base_ntk = base * powf(s, (float)rot / (rot - 2));
+    if (c.rope_scaling_mode == 2) return 1.0f / powf(base_ntk, expo);
+    const float f_orig = 1.0f / powf(base, expo), f_ntk = 1.0f / powf(base_ntk, expo);
+    const float wavelength = 2.0f * M_PI / f_orig;
+    const float lo = (float)c.rope_orig_max_pos, hi = lo / 32.0f;
+    if (wavelength < hi) return f_orig;
+    if (wavelength > lo) return f_ntk;
+    const float ramp = (wavelength - hi) / (lo - hi);
+    return f_orig * (1.0f - ramp) + f_ntk * ramp;
+}
+
+static size_t stage_need(const FmConfig &c) {
+    // largest set of host tensors one call moves: prefill q_proj_out + k + v + out, or the
+    // GatedDeltaNet inputs + output
+    const size_t n = (size_t)c.max_batch_tokens;
+    const size_t attn = n * ((size_t)c.num_attn_heads * c.head_dim * 3 + (size_t)c.num_kv_heads * c.head_dim * 2) * 4;
+    const size_t conv_dim = 2 * (size_t)c.linear_num_k_heads * c.linear_key_dim + (size_t)c.linear_num_v_heads * c.linear_value_dim;
+    const size_t gdn = n * (conv_dim + 2 * (size_t)c.linear_num_v_heads * c.linear_value_dim + 2 * (size_t)c.linear_num_v_heads) * 4;
+    return std::max(attn, gdn) + (1 << 20);
+}
+
+extern "C" fm_status fm_create(const FmConfig *cfg, FmCtx **out) {
+    if (!cfg || !out) return fail(nullptr, FM_ERR_INVALID, "fm_create: null argument");
+    *out = nullptr;
+    const FmConfig &c = *cfg;
+    const bool has_attn = c.num_full_layers > 0, has_gdn = c.num_linear_layers > 0;
+    if (c.max_seqs < 1 || c.max_batch_tokens < 1 || c.seq_shard_count < 1 || c.seq_shard_rank < 0 ||
+        c.seq_shard_rank >= c.seq_shard_count)
+        return fail(nullptr, FM_ERR_INVALID, "fm_create: bad max_seqs / max_batch_tokens / sequence sharding");
+    if (has_attn) {
+        if (c.head_dim != 256) return fail(nullptr, FM_ERR_UNSUPPORTED, "fm_create: head_dim %d (kernels are built for 256)", c.head_dim);
+        if (c.page_size != 64) return fail(nullptr, FM_ERR_UNSUPPORTED, "fm_create: page_size %d (kernels are built for 64)", c.page_size);
+        if (c.num_kv_heads < 1 || c.num_attn_heads % c.num_kv_heads != 0 || c.num_attn_heads / c.num_kv_heads > 16)
+            return fail(nullptr, FM_ERR_UNSUPPORTED, "fm_create: %d query heads per KV head (1..16 supported)",
+                        c.num_kv_heads ? c.num_attn_heads / c.num_kv_heads : 0);
+        if (c.rotary_dim < 0 || c.rotary_dim > 128 || c.rotary_dim % 2 != 0 || c.rotary_dim > c.head_dim)
+            return fail(nullptr, FM_ERR_UNSUPPORTED, "fm_create: rotary_dim %d (even, <= 128)", c.rotary_dim);
+        if (c.max_seq_len < 1) return fail(nullptr, FM_ERR_INVALID, "fm_create: max_seq_len %d", c.max_seq_len);
+    }
+    if (has_gdn) {
+        if (c.linear_key_dim != 128 || c.linear_value_dim != 128 || c.conv_kernel_size != 4)
+            return fail(nullptr, FM_ERR_UNSUPPORTED, "fm_create: GatedDeltaNet dims %dx%d conv %d (built for 128x128, conv 4)",
+                        c.linear_key_dim, c.linear_value_dim, c.conv_kernel_size);
+        if (c.linear_num_k_heads < 1 || c.linear_num_v_heads % c.linear_num_k_heads != 0)
+            return fail(nullptr, FM_ERR_INVALID, "fm_create: v heads must be a multiple of k heads");
+    }
+    int ndev = 0;
+    if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0)
+        return fail(nullptr, FM_ERR_CUDA, "fm_create: no CUDA device (this library has no CPU path)");
+    if (c.device < 0 || c.device >= ndev) return fail(nullptr, FM_ERR_INVALID, "fm_create: device %d of %d", c.device, ndev);
+
+    FmCtx *ctx = new (std::nothrow) FmCtx();
+    if (!ctx) return fail(nullptr, FM_ERR_NOMEM, "fm_create: out of host memory");
+    ctx->cfg = c;
+#define CREATE_CUDA(call)                                                                               \
+    do {                                                                                                \
+        cudaError_t e__ = (call);                                                                       \
+        if (e__ != cudaSuccess) {                                                                       \
+            fm_status st__ = fail(nullptr, e__ == cudaErrorMemoryAllocation ? FM_ERR_NOMEM : FM_ERR_CUDA, \
+                                  "fm_create: %s failed: %s", #call, cudaGetErrorString(e__));          \
+            fm_destroy(ctx);                                                                            \
+            return st__;                                                                                \
+        }                                                                                               \
+    } while (0)
+    CREATE_CUDA(cudaSetDevice(c.device));
+    cudaDeviceProp prop;
+    CREATE_CUDA(cudaGetDeviceProperties(&prop, c.device));
+    ctx->sm_count = prop.multiProcessorCount;
+    if (prop.major < 10) {
+        fm_destroy(ctx);
+        return fail(nullptr, FM_ERR_UNSUPPORTED, "fm_create: device is sm_%d%d; this library is built for sm_100a only", prop.major, prop.minor);
+    }
+
+    if (has_attn) {
+        ctx->rope.rotary_dim = c.rotary_dim;
+        for (int i = 0; i < c.rotary_dim / 2; i++) ctx->rope.inv_freq[i] = rope_inv_freq(c, i);
+        ctx->rope.pos_div = (c.rope_scaling_mode == 1 && c.rope_scale_factor > 1.0f) ? c.rope_scale_factor : 1.0f;
+        float yarn = 1.0f;
+        if (c.rope_scaling_mode == 3 && c.rope_scale_factor > 1.0f) yarn = sqrtf(0.1f * logf(c.rope_scale_factor) + 1.0f);
+        ctx->rope.logit_scale = (1.0f / sqrtf((float)c.head_dim)) * yarn;
+
+        const int gpages = (c.max_seq_len + c.page_size - 1) / c.page_size;
+        ctx->max_slots = (gpages + c.seq_shard_count - 1) / c.seq_shard_count;
+        ctx->page_elems = (size_t)2 * c.num_kv_heads * c.page_size * c.head_dim;
+        ctx->pool_pages = c.kv_pool_pages > 0 ? c.kv_pool_pages
+                                              : (int64_t)ctx->max_slots * c.max_seqs * c.num_full_layers;
+        CREATE_CUDA(cudaMalloc(&ctx->pool, (size_t)ctx->pool_pages * ctx->page_elems * sizeof(__nv_bfloat16)));
+        // zero so that rows past a sequence's end hold finite values (they meet zero weights)
+        CREATE_CUDA(cudaMemset(ctx->pool, 0, (size_t)ctx->pool_pages * ctx->page_elems * sizeof(__nv_bfloat16)));
+        const size_t nent = (size_t)c.num_full_layers * c.max_seqs * ctx->max_slots;
+        ctx->h_page_table.assign(nent, -1);
+        CREATE_CUDA(cudaMalloc(&ctx->d_page_table, nent * sizeof(int)));
+        CREATE_CUDA(cudaMemset(ctx->d_page_table, 0, nent * sizeof(int)));
+        ctx->free_pages.resize((size_t)ctx->pool_pages);
+        for (int64_t i = 0; i < ctx->pool_pages; i++) ctx->free_pages[(size_t)i] = (int)(ctx->pool_pages - 1 - i);
+        ctx->kv_len.assign((size_t)c.num_full_layers * c.max_seqs, 0);
+
+        // split partials: at most ~2 CTAs per SM plus one per (KV head, sequence), 16 head rows each
+        ctx->max_splits = std::max(1, ctx->sm_count);
+        const size_t rows = ((size_t)2 * ctx->sm_count + (size_t)c.num_kv_heads * c.max_batch_tokens) * 16 + 64;
+        CREATE_CUDA(cudaMalloc(&ctx->d_part_o, rows * c.head_dim * sizeof(float)));
+        CREATE_CUDA(cudaMalloc(&ctx->d_part_ml, rows * 2 * sizeof(float)));
+        CREATE_CUDA(cudaMalloc(&ctx->d_pf_o, (size_t)c.max_batch_tokens * c.num_attn_heads * c.head_dim * sizeof(float)));
+        CREATE_CUDA(cudaMalloc(&ctx->d_pf_ml, (size_t)c.max_batch_tokens * c.num_attn_heads * 2 * sizeof(float)));
+    }
+    if (has_gdn) {
+        ctx->conv_dim = 2 * c.linear_num_k_heads * c.linear_key_dim + c.linear_num_v_heads * c.linear_value_dim;
+        // conv history kept as a ring of ks rows (see gdn_decode.cu) + the token count that indexes it
+        const size_t conv_n = (size_t)c.num_linear_layers * c.max_seqs * c.conv_kernel_size * ctx->conv_dim;
+        const size_t ssm_n = (size_t)c.num_linear_layers * c.max_seqs * c.linear_num_v_heads * c.linear_value_dim * c.linear_key_dim;
+        CREATE_CUDA(cudaMalloc(&ctx->d_conv_state, conv_n * sizeof(float)));
+        CREATE_CUDA(cudaMalloc(&ctx->d_ssm_state, ssm_n * sizeof(float)));
+        CREATE_CUDA(cudaMemset(ctx->d_conv_state, 0, conv_n * sizeof(float)));
+        CREATE_CUDA(cudaMemset(ctx->d_ssm_state, 0, ssm_n * sizeof(float)));
+        ctx->gdn_steps.assign((size_t)c.num_linear_layers * c.max_seqs, 0);
+        GdnDims g{c.linear_num_v_heads, c.linear_num_k_heads, c.linear_key_dim, c.linear_value_dim, c.conv_kernel_size, ctx->conv_dim, c.rms_norm_eps};
+        ctx->work_bytes = gdn_prefill_work_bytes(g, c.max_batch_tokens, 64);
+        if (ctx->work_bytes) CREATE_CUDA(cudaMalloc(&ctx->d_work, ctx->work_bytes));
+    }
+    ctx->stage_bytes = stage_need(c);
+    CREATE_CUDA(cudaMallocHost(&ctx->h_stage, ctx->stage_bytes));
+    CREATE_CUDA(cudaMalloc(&ctx->d_stage, ctx->stage_bytes));
+    CREATE_CUDA(cudaDeviceSynchronize());
+#undef CREATE_CUDA
+    *out = ctx;
+    return FM_OK;
+}
+
+extern "C" void fm_destroy(FmCtx *ctx) {
+    if (!ctx) return;
+    cudaSetDevice(ctx->cfg.device);
+    cudaDeviceSynchronize();
+    cudaFree(ctx->pool); cudaFree(ctx->d_page_table); cudaFree(ctx->d_conv_state); cudaFree(ctx->d_ssm_state);
+    cudaFree(ctx->d_part_o); cudaFree(ctx->d_part_ml); cudaFree(ctx->d_pf_o); cudaFree(ctx->d_pf_ml); cudaFree(ctx->d_work);
+    cudaFree(ctx->d_stage);
+    if (ctx->h_stage) cudaFreeHost(ctx->h_stage);
+    delete ctx;
+}
+
+extern "C" const char *fm_last_error(const FmCtx *ctx) { return ctx ? ctx->err.c_str() : g_create_error.c_str(); }
+
+extern "C" fm_status fm_set_stream(FmCtx *ctx, void *s) {
+    if (!ctx) return FM_ERR_INVALID;
+    ctx->stream = (cudaStream_t)s;
+    return FM_OK;
+}
+extern "C" fm_status fm_set_pointer_mode(FmCtx *ctx, int mode) {
+    if (!ctx) return FM_ERR_INVALID;
+    if (mode != FM_PTR_DEVICE && mode != FM_PTR_HOST) return fail(ctx, FM_ERR_INVALID, "fm_set_pointer_mode: mode %d", mode);
+    ctx->ptr_mode = mode;
+    return FM_OK;
+}
+extern "C" fm_status fm_synchronize(FmCtx *ctx) {
+    if (!ctx) return FM_ERR_INVALID;
+    FM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return FM_OK;
+}
+extern "C" int64_t fm_launch_count(const FmCtx *ctx) { return ctx ? ctx->launches : 0; }
+
+// ---- KV bookkeeping ---------------------------------------------------------------------------
+static inline size_t lidx(const FmCtx *ctx, int layer, int seq) { return (size_t)layer * ctx->cfg.max_seqs + seq; }
+
+static KvView kv_view(const FmCtx *ctx, int fa_idx) {
+    KvView v;
+    v.pool = ctx->pool;
+    v.page_table = ctx->d_page_table + (size_t)fa_idx * ctx->cfg.max_seqs * ctx->max_slots;
+    v.max_slots = ctx->max_slots;
+    v.page_size = ctx->cfg.page_size;
+    v.Hkv = ctx->cfg.num_kv_heads;
+    v.D = ctx->cfg.head_dim;
+    v.shard_rank = ctx->cfg.seq_shard_rank;
+    v.shard_count = ctx->cfg.seq_shard_count;
+    return v;
+}
+
+// Makes sure the locally-held pages covering rows [0, new_len) of (layer, seq) exist.
+static fm_status ensure_pages(FmCtx *ctx, int fa_idx, int seq, int new_len) {
+    const FmConfig &c = ctx->cfg;
+    if (new_len > c.max_seq_len)
+        return fail(ctx, FM_ERR_CAPACITY, "KV cache overflow (pos=%d >= cap=%d)", new_len - 1, c.max_seq_len);
+    const int gpages = (new_len + c.page_size - 1) / c.page_size;
+    const int nslots = gpages > c.seq_shard_rank ? (gpages - c.seq_shard_rank + c.seq_shard_count - 1) / c.seq_shard_count : 0;
+    int *tab = &ctx->h_page_table[((size_t)fa_idx * c.max_seqs + seq) * ctx->max_slots];
+    int first_new = -1, need = 0;
+    for (int s = 0; s < nslots; s++)
+        if (tab[s] < 0) { if (first_new < 0) first_new = s; need++; }
+    if (need == 0) return FM_OK;
+    if ((size_t)need > ctx->free_pages.size())
+        return fail(ctx, FM_ERR_CAPACITY, "KV page pool exhausted (%d more pages needed, %zu free)", need, ctx->free_pages.size());
+    for (int s = first_new; s < nslots; s++)
+        if (tab[s] < 0) { tab[s] = ctx->free_pages.back(); ctx->free_pages.pop_back(); }
+    int *dtab = ctx->d_page_table + ((size_t)fa_idx * c.max_seqs + seq) * ctx->max_slots;
+    // pageable-source copies are staged by the runtime before the call returns, so `tab` may change later
+    FM_CUDA(ctx, cudaMemcpyAsync(dtab + first_new, tab + first_new, (size_t)(nslots - first_new) * sizeof(int),
+                                 cudaMemcpyHostToDevice, ctx->stream));
+    return FM_OK;
+}
+
+extern "C" int fm_kv_len(const FmCtx *ctx, int fa_idx, int seq) {
+    if (!ctx || fa_idx < 0 || fa_idx >= ctx->cfg.num_full_layers || seq < 0 || seq >= ctx->cfg.max_seqs) return -1;
+    return ctx->kv_len[lidx(ctx, fa_idx, seq)];
+}
+
+extern "C" fm_status fm_reset(FmCtx *ctx, int seq) {
+    if (!ctx) return FM_ERR_INVALID;
+    const FmConfig &c = ctx->cfg;
+    if (seq < -1 || seq >= c.max_seqs) return fail(ctx, FM_ERR_INVALID, "fm_reset: seq %d", seq);
+    FM_CUDA(ctx, cudaSetDevice(c.device));
+    const int s0 = seq < 0 ? 0 : seq, s1 = seq < 0 ? c.max_seqs : seq + 1;
+    for (int l = 0; l < c.num_full_layers; l++)
+        for (int s = s0; s < s1; s++) {
+            int *tab = &ctx->h_page_table[((size_t)l * c.max_seqs + s) * ctx->max_slots];
+            for (int i = 0; i < ctx->max_slots; i++)
+                if (tab[i] >= 0) { ctx->free_pages.push_back(tab[i]); tab[i] = -1; }
+            ctx->kv_len[lidx(ctx, l, s)] = 0;
+        }
+    for (int l = 0; l < c.num_linear_layers; l++)
+        for (int s = s0; s < s1; s++) {
+            const size_t cn = (size_t)c.conv_kernel_size * ctx->conv_dim;
+            const size_t sn = (size_t)c.linear_num_v_heads * c.linear_value_dim * c.linear_key_dim;
+            FM_CUDA(ctx, cudaMemsetAsync(ctx->d_conv_state + lidx(ctx, l, s) * cn, 0, cn * sizeof(float), ctx->stream));
+            FM_CUDA(ctx, cudaMemsetAsync(ctx->d_ssm_state + lidx(ctx, l, s) * sn, 0, sn * sizeof(float), ctx->stream));
+            ctx->gdn_steps[lidx(ctx, l, s)] = 0;
+        }
+    return FM_OK;
+}
+
+// ---- pointer-mode staging ---------------------------------------------------------------------
+// In host-pointer mode inputs are packed into the pinned buffer, moved with one copy, and the
+// kernels read the device twin; outputs come back the same way.
+struct Stager {
+    FmCtx *ctx;
+    size_t off = 0;
+    size_t in_end = 0;
+    bool host;
+    explicit Stager(FmCtx *c) : ctx(c), host(c->ptr_mode == FM_PTR_HOST) {}
+    template <typename T>
+    const T *in(const T *p, size_t count, bool *ok) {
+        if (!host || p == nullptr) return p;
+        const size_t bytes = (count * sizeof(T) + 255) & ~(size_t)255;
+        if (off + bytes > ctx->stage_bytes) { *ok = false; return nullptr; }
+        memcpy(ctx->h_stage + off, p, count * sizeof(T));
+        const T *d = reinterpret_cast<const T *>(ctx->d_stage + off);
+        off += bytes;
+        in_end = off;
+        return d;
+    }
+    cudaError_t push() {
+        if (!host || in_end == 0) return cudaSuccess;
+        return cudaMemcpyAsync(ctx->d_stage, ctx->h_stage, in_end, cudaMemcpyHostToDevice, ctx->stream);
+    }
+    template <typename T>
+    T *out(T *p, size_t count, bool *ok, size_t *where) {
+        if (!host || p == nullptr) return p;
+        const size_t bytes = (count * sizeof(T) + 255) & ~(size_t)255;
+        if (off + bytes > ctx->stage_bytes) { *ok = false; return nullptr; }
+        *where = off;
+        T *d = reinterpret_cast<T *>(ctx->d_stage + off);
+        off += bytes;
+        return d;
+    }
+    // device -> pinned -> caller; blocks until the data is in the caller's buffer
+    template <typename T>
+    cudaError_t pull(T *host_dst, size_t where, size_t count) {
+        if (!host || host_dst == nullptr) return cudaSuccess;
+        cudaError_t e = cudaMemcpyAsync(ctx->h_stage + where, ctx->d_stage + where, count * sizeof(T),
+                                        cudaMemcpyDeviceToHost, ctx->stream);
+        if (e != cudaSuccess) return e;
+        e = cudaStreamSynchronize(ctx->stream);
+        if (e != cudaSuccess) return e;
+        memcpy(host_dst, ctx->h_stage + where, count * sizeof(T));
+        return cudaSuccess;
+    }
+};
+
+// ---- token lists ------------------------------------------------------------------------------
+static fm_status check_layer_seq(FmCtx *ctx, const char *fn, int layer, int nlayers, const int *seq, int n) {
+    if (layer < 0 || layer >= nlayers) return fail(ctx, FM_ERR_INVALID, "%s: layer index %d of %d", fn, layer, nlayers);
+    if (n < 0 || n > ctx->cfg.max_batch_tokens) return fail(ctx, FM_ERR_INVALID, "%s: n=%d exceeds max_batch_tokens=%d", fn, n, ctx->cfg.max_batch_tokens);
+    for (int i = 0; i < n; i++)
+        if (seq[i] < 0 || seq[i] >= ctx->cfg.max_seqs) return fail(ctx, FM_ERR_INVALID, "%s: seq[%d]=%d of %d", fn, i, seq[i], ctx->cfg.max_seqs);
+    return FM_OK;
+}
+
+// Appends tokens [i0, i1) of an explicit list (bookkeeping already validated); k, v device pointers.
+static fm_status append_list(FmCtx *ctx, int fa_idx, const int *seq, const int *pos, const int *rows, int n,
+                             const float *k, const float *v, const uint16_t *knw) {
+    const KvView kv = kv_view(ctx, fa_idx);
+    const size_t kv_dim = (size_t)ctx->cfg.num_kv_heads * ctx->cfg.head_dim;
+    for (int i0 = 0; i0 < n; i0 += kMaxList) {
+        TokSpec t;
+        t.mode = 0;
+        t.n = std::min(kMaxList, n - i0);
+        for (int i = 0; i < t.n; i++) { t.seq[i] = seq[i0 + i]; t.pos[i] = pos[i0 + i]; t.row[i] = rows[i0 + i]; }
+        fm_status st = launched(ctx, launch_kv_append(kv, ctx->rope, t, k + i0 * kv_dim, v + i0 * kv_dim, knw, ctx->cfg.rms_norm_eps, ctx->stream), "kv_append");
+        if (st) return st;
+    }
+    return FM_OK;
+}
+
+// Reserves rows for n tokens (token i goes to sequence seq[i]); fills rows[]. All-or-nothing.
+static fm_status reserve_rows(FmCtx *ctx, int fa_idx, const int *seq, int n, std::vector<int> &rows) {
+    const FmConfig &c = ctx->cfg;
+    rows.resize(n);
+    std::vector<int> add(c.max_seqs, 0);
+    for (int i = 0; i < n; i++) {
+        rows[i] = ctx->kv_len[lidx(ctx, fa_idx, seq[i])] + add[seq[i]];
+        add[seq[i]]++;
+        if (rows[i] >= c.max_seq_len)
+            return fail(ctx, FM_ERR_CAPACITY, "KV cache overflow (pos=%d >= cap=%d)", rows[i], c.max_seq_len);
+    }
+    // page demand check before touching anything
+    size_t need = 0;
+    for (int s = 0; s < c.max_seqs; s++) {
+        if (!add[s]) continue;
+        const int new_len = ctx->kv_len[lidx(ctx, fa_idx, s)] + add[s];
+        const int gpages = (new_len + c.page_size - 1) / c.page_size;
+        const int nslots = gpages > c.seq_shard_rank ? (gpages - c.seq_shard_rank + c.seq_shard_count - 1) / c.seq_shard_count : 0;
+        const int *tab = &ctx->h_page_table[((size_t)fa_idx * c.max_seqs + s) * ctx->max_slots];
+        for (int j = 0; j < nslots; j++) need += tab[j] < 0;
+    }
+    if (need > ctx->free_pages.size())
+        return fail(ctx, FM_ERR_CAPACITY, "KV page pool exhausted (%zu more pages needed, %zu free)", need, ctx->free_pages.size());
+    for (int s = 0; s < c.max_seqs; s++) {
+        if (!add[s]) continue;
+        fm_status st = ensure_pages(ctx, fa_idx, s, ctx->kv_len[lidx(ctx, fa_idx, s)] + add[s]);
+        if (st) return st;
+    }
+    for (int s = 0; s < c.max_seqs; s++) ctx->kv_len[lidx(ctx, fa_idx, s)] += add[s];
+    return FM_OK;
+}
+
+extern "C" fm_status fm_kv_append_rope(FmCtx *ctx, int fa_idx, const int *seq, const int *pos, int n,
+                                       const float *k, const float *v, const uint16_t *k_norm_w) {
+    if (!ctx) return FM_ERR_INVALID;
+    if (!seq || !pos || !k || !v) return fail(ctx, FM_ERR_INVALID, "fm_kv_append_rope: null argument");
+    fm_status st = check_layer_seq(ctx, "fm_kv_append_rope", fa_idx, ctx->cfg.num_full_layers, seq, n);
+    if (st) return st;
+    if (n == 0) return FM_OK;
+    FM_CUDA(ctx, cudaSetDevice(ctx->cfg.device));
+    const size_t kv_dim = (size_t)ctx->cfg.num_kv_heads * ctx->cfg.head_dim;
+    Stager sg(ctx);
+    bool ok = true;
+    const float *dk = sg.in(k, n * kv_dim, &ok), *dv = sg.in(v, n * kv_dim, &ok);
+    const uint16_t *dw = sg.in(k_norm_w, (size_t)ctx->cfg.head_dim, &ok);
+    if (!ok) return fail(ctx, FM_ERR_INVALID, "fm_kv_append_rope: staging buffer too small");
+    std::vector<int> rows;
+    st = reserve_rows(ctx, fa_idx, seq, n, rows);
+    if (st) return st;
+    FM_CUDA(ctx, sg.push());
+    st = append_list(ctx, fa_idx, seq, pos, rows.data(), n, dk, dv, dw);
+    if (st) return st;
+    if (sg.host) FM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return FM_OK;
+}
+
+static int pick_splits(const FmCtx *ctx, int batch, int max_len) {
+    const FmConfig &c = ctx->cfg;
+    const int per_tok = c.num_kv_heads;
+    int want = (ctx->sm_count + per_tok * batch - 1) / (per_tok * batch);
+    const int gpages = (max_len + c.page_size - 1) / c.page_size;
+    const int slots = (gpages + c.seq_shard_count - 1) / c.seq_shard_count;
+    want = std::min(want, std::max(1, slots));
+    return std::max(1, std::min(want, ctx->max_splits));
+}
+
+// Shared body of fm_attn_decode / fm_attn_decode_partial (device pointers).
+static fm_status decode_core(FmCtx *ctx, int fa_idx, const int *seq, const int *pos, int batch,
+                             const float *q_proj_out, const float *q, const float *gate, const float *k,
+                             const float *v, const uint16_t *qnw, const uint16_t *knw, float *out,
+                             float *o_part, float *ml_part) {
+    const FmConfig &c = ctx->cfg;
+    const int H = c.num_attn_heads, D = c.head_dim;
+    std::vector<int> rows(batch);
+    if (k != nullptr) {
+        fm_status st = reserve_rows(ctx, fa_idx, seq, batch, rows);
+        if (st) return st;
+        st = append_list(ctx, fa_idx, seq, pos, rows.data(), batch, k, v, knw);
+        if (st) return st;
+    } else {
+        for (int i = 0; i < batch; i++) {
+            rows[i] = ctx->kv_len[lidx(ctx, fa_idx, seq[i])] - 1;
+            if (rows[i] < 0) return fail(ctx, FM_ERR_INVALID, "fm_attn_decode: sequence %d is empty and no k/v given", seq[i]);
+        }
+    }
+    const KvView kv = kv_view(ctx, fa_idx);
+    for (int i0 = 0; i0 < batch; i0 += kMaxList) {
+        TokSpec t;
+        t.mode = 0;
+        t.n = std::min(kMaxList, batch - i0);
+        int max_len = 1;
+        for (int i = 0; i < t.n; i++) {
+            t.seq[i] = seq[i0 + i]; t.pos[i] = pos[i0 + i]; t.row[i] = rows[i0 + i];
+            max_len = std::max(max_len, rows[i0 + i] + 1);
+        }
+        const int ns = pick_splits(ctx, t.n, max_len);
+        const float *qp = q_proj_out ? q_proj_out + (size_t)i0 * H * 2 * D : nullptr;
+        const float *qq = q ? q + (size_t)i0 * H * D : nullptr;
+        fm_status st = launched(ctx, launch_attn_decode(kv, ctx->rope, t, H, qp, qq, qnw, c.rms_norm_eps, ctx->d_part_o, ctx->d_part_ml, ns, ctx->stream), "attn_decode");
+        if (st) return st;
+        const float *gp = gate ? gate + (size_t)i0 * H * D : nullptr;
+        float *op = (out ? out : o_part) + (size_t)i0 * H * D;
+        float *mlp = ml_part ? ml_part + (size_t)i0 * H * 2 : nullptr;
+        st = launched(ctx, launch_attn_merge(ctx->d_part_o, ctx->d_part_ml, ns, D, 2, (long long)H * ns * D, (long long)H * ns * 2,
+                                             (long long)ns * D, (long long)ns * 2, t.n, H, D, qp, gp, op, mlp, ctx->stream), "attn_merge");
+        if (st) return st;
+    }
+    return FM_OK;
+}
+
+static fm_status decode_entry(FmCtx *ctx, const char *fn, int fa_idx, const int *seq, const int *pos, int batch,
+                              const float *q_proj_out, const float *q, const float *gate, const float *k,
+                              const float *v, const uint16_t *qnw, const uint16_t *knw, float *out, float *o_part,
+                              float *ml_part) {
+    if (!ctx) return FM_ERR_INVALID;
+    const bool partial = o_part != nullptr;
+    if (!seq || !pos || (!partial && !out) || (partial && !ml_part)) return fail(ctx, FM_ERR_INVALID, "%s: null argument", fn);
+    if (!q_proj_out && (!q || (!partial && !gate))) return fail(ctx, FM_ERR_INVALID, "%s: give q_proj_out, or q and gate", fn);
+    if ((k == nullptr) != (v == nullptr)) return fail(ctx, FM_ERR_INVALID, "%s: k and v go together", fn);
+    fm_status st = check_layer_seq(ctx, fn, fa_idx, ctx->cfg.num_full_layers, seq, batch);
+    if (st) return st;
+    if (batch == 0) return FM_OK;
+    for (int i = 0; i < batch; i++)
+        for (int j = 0; j < i; j++)
+            if (seq[i] == seq[j]) return fail(ctx, FM_ERR_INVALID, "%s: sequence %d appears twice in one step", fn, seq[i]);
+    FM_CUDA(ctx, cudaSetDevice(ctx->cfg.device));
+    const FmConfig &c = ctx->cfg;
+    const size_t qd = (size_t)c.num_attn_heads * c.head_dim, kvd = (size_t)c.num_kv_heads * c.head_dim;
+    Stager sg(ctx);
+    bool ok = true;
+    const float *d_qp = sg.in(q_proj_out, batch * qd * 2, &ok);
+    const float *d_q = sg.in(q_proj_out ? nullptr : q, batch * qd, &ok);
+    const float *d_g = sg.in(q_proj_out ? nullptr : gate, batch * qd, &ok);
+    const float *d_k = sg.in(k, batch * kvd, &ok), *d_v = sg.in(v, batch * kvd, &ok);
+    const uint16_t *d_qn = sg.in(qnw, (size_t)c.head_dim, &ok), *d_kn = sg.in(knw, (size_t)c.head_dim, &ok);
+    size_t w_out = 0, w_ml = 0;
+    float *d_out = sg.out(partial ? o_part : out, batch * qd, &ok, &w_out);
+    float *d_ml = sg.out(ml_part, batch * (size_t)c.num_attn_heads * 2, &ok, &w_ml);
+    if (!ok) return fail(ctx, FM_ERR_INVALID, "%s: staging buffer too small", fn);
+    FM_CUDA(ctx, sg.push());
+    st = decode_core(ctx, fa_idx, seq, pos, batch, d_qp, d_q, d_g, d_k, d_v, d_qn, d_kn, partial ? nullptr : d_out,
+                     partial ? d_out : nullptr, d_ml);
+    if (st) return st;
+    if (sg.host) {
+        if (partial) FM_CUDA(ctx, cudaMemcpyAsync(ctx->h_stage + w_ml, ctx->d_stage + w_ml, batch * (size_t)c.num_attn_heads * 2 * 4, cudaMemcpyDeviceToHost, ctx->stream));
+        FM_CUDA(ctx, sg.pull(partial ? o_part : out, w_out, batch * qd));
+        if (partial) memcpy(ml_part, ctx->h_stage + w_ml, batch * (size_t)c.num_attn_heads * 2 * 4);
+    }
+    return FM_OK;
+}
+
+extern "C" fm_status fm_attn_decode(FmCtx *ctx, int fa_idx, const int *seq, const int *pos, int batch,
+                                    const float *q_proj_out, const float *q, const float *gate, const float *k,
+                                    const float *v, const uint16_t *q_norm_w, const uint16_t *k_norm_w, float *out) {
+    return decode_entry(ctx, "fm_attn_decode", fa_idx, seq, pos, batch, q_proj_out, q, gate, k, v, q_norm_w, k_norm_w, out, nullptr, nullptr);
+}
+
+extern "C" fm_status fm_attn_decode_partial(FmCtx *ctx, int fa_idx, const int *seq, const int *pos, int batch,
+                                            const float *q_proj_out, const float *q, const float *k, const float *v,
+                                            const uint16_t *q_norm_w, const uint16_t *k_norm_w, float *o_part,
+                                            float *ml_part) {
+    if (ctx && !o_part) return fail(ctx, FM_ERR_INVALID, "fm_attn_decode_partial: null argument");
+    return decode_entry(ctx, "fm_attn_decode_partial", fa_idx, seq, pos, batch, q_proj_out, q, nullptr, k, v, q_norm_w, k_norm_w, nullptr, o_part, ml_part);
+}
+
+extern "C" fm_status fm_attn_merge_gate(FmCtx *ctx, int nparts, const float *o_parts, const float *ml_parts,
+                                        const float *q_proj_out, const float *gate, int batch, float *out) {
+    if (!ctx) return FM_ERR_INVALID;
+    if (!o_parts || !ml_parts || !out || (!q_proj_out && !gate) || nparts < 1) return fail(ctx, FM_ERR_INVALID, "fm_attn_merge_gate: bad argument");
+    if (batch < 0 || (size_t)batch * nparts > (size_t)ctx->cfg.max_batch_tokens * 64) return fail(ctx, FM_ERR_INVALID, "fm_attn_merge_gate: batch %d", batch);
+    if (batch == 0) return FM_OK;
+    FM_CUDA(ctx, cudaSetDevice(ctx->cfg.device));
+    const FmConfig &c = ctx->cfg;
+    const int H = c.num_attn_heads, D = c.head_dim;
+    const size_t qd = (size_t)H * D;
+    Stager sg(ctx);
+    bool ok = true;
+    const float *d_o = sg.in(o_parts, (size_t)nparts * batch * qd, &ok);
+    const float *d_ml = sg.in(ml_parts, (size_t)nparts * batch * H * 2, &ok);
+    const float *d_qp = sg.in(q_proj_out, batch * qd * 2, &ok);
+    const float *d_g = sg.in(q_proj_out ? nullptr : gate, batch * qd, &ok);
+    size_t w_out = 0;
+    float *d_out = sg.out(out, batch * qd, &ok, &w_out);
+    if (!ok) return fail(ctx, FM_ERR_INVALID, "fm_attn_merge_gate: staging buffer too small");
+    FM_CUDA(ctx, sg.push());
+    fm_status st = launched(ctx, launch_attn_merge(d_o, d_ml, nparts, (long long)batch * qd, (long long)batch * H * 2, (long long)qd,
+                                                   (long long)H * 2, D, 2, batch, H, D, d_qp, d_g, d_out, nullptr, ctx->stream), "attn_merge");
+    if (st) return st;
+    FM_CUDA(ctx, sg.pull(out, w_out, batch * qd));
+    return FM_OK;
+}
+
+extern "C" fm_status fm_attn_prefill(FmCtx *ctx, int fa_idx, int seq, int start_pos, int n, const float *q_proj_out,
+                                     const float *q, const float *gate, const float *k, const float *v,
+                                     const uint16_t *q_norm_w, const uint16_t *k_norm_w, float *out) {
+    if (!ctx) return FM_ERR_INVALID;
+    if (!k || !v || !out || (!q_proj_out && (!q || !gate))) return fail(ctx, FM_ERR_INVALID, "fm_attn_prefill: null argument");
+    const FmConfig &c = ctx->cfg;
+    if (fa_idx < 0 || fa_idx >= c.num_full_layers || seq < 0 || seq >= c.max_seqs) return fail(ctx, FM_ERR_INVALID, "fm_attn_prefill: layer %d / seq %d", fa_idx, seq);
+    if (n < 0 || n > c.max_batch_tokens) return fail(ctx, FM_ERR_INVALID, "fm_attn_prefill: n=%d exceeds max_batch_tokens=%d", n, c.max_batch_tokens);
+    if (c.seq_shard_count != 1) return fail(ctx, FM_ERR_UNSUPPORTED, "fm_attn_prefill: needs the whole sequence on one context (seq_shard_count=1)");
+    if (n == 0) return FM_OK;
+    FM_CUDA(ctx, cudaSetDevice(c.device));
+    const size_t qd = (size_t)c.num_attn_heads * c.head_dim, kvd = (size_t)c.num_kv_heads * c.head_dim;
+    Stager sg(ctx);
+    bool ok = true;
+    const float *d_qp = sg.in(q_proj_out, n * qd * 2, &ok);
+    const float *d_q = sg.in(q_proj_out ? nullptr : q, n * qd, &ok);
+    const float *d_g = sg.in(q_proj_out ? nullptr : gate, n * qd, &ok);
+    const float *d_k = sg.in(k, n * kvd, &ok), *d_v = sg.in(v, n * kvd, &ok);
+    const uint16_t *d_qn = sg.in(q_norm_w, (size_t)c.head_dim, &ok), *d_kn = sg.in(k_norm_w, (size_t)c.head_dim, &ok);
+    size_t w_out = 0;
+    float *d_out = sg.out(out, n * qd, &ok, &w_out);
+    if (!ok) return fail(ctx, FM_ERR_INVALID, "fm_attn_prefill: staging buffer too small");
+    const int row0 = ctx->kv_len[lidx(ctx, fa_idx, seq)];
+    if (row0 + n > c.max_seq_len) return fail(ctx, FM_ERR_CAPACITY, "KV cache overflow (pos=%d >= cap=%d)", row0 + n - 1, c.max_seq_len);
+    fm_status st = ensure_pages(ctx, fa_idx, seq, row0 + n);
+    if (st) return st;
+    ctx->kv_len[lidx(ctx, fa_idx, seq)] = row0 + n;
+    FM_CUDA(ctx, sg.push());
+    const KvView kv = kv_view(ctx, fa_idx);
+    TokSpec t;
+    t.mode = 1; t.n = n; t.seq0 = seq; t.pos0 = start_pos; t.row0 = row0;
+    st = launched(ctx, launch_kv_append(kv, ctx->rope, t, d_k, d_v, d_kn, c.rms_norm_eps, ctx->stream), "kv_append");
+    if (st) return st;
+    st = launched(ctx, launch_attn_prefill(kv, ctx->rope, seq, start_pos, row0, n, c.num_attn_heads, d_qp, d_q, d_g, d_qn,
+                                           c.rms_norm_eps, ctx->d_pf_o, ctx->d_pf_ml, d_out, ctx->stream), "attn_prefill");
+    if (st) return st;
+    FM_CUDA(ctx, sg.pull(out, w_out, n * qd));
+    return FM_OK;
+}
+
+// ---- GatedDeltaNet ----------------------------------------------------------------------------
+static GdnDims gdn_dims(const FmCtx *ctx) {
+    const FmConfig &c = ctx->cfg;
+    return GdnDims{c.linear_num_v_heads, c.linear_num_k_heads, c.linear_key_dim, c.linear_value_dim, c.conv_kernel_size, ctx->conv_dim, c.rms_norm_eps};
+}
+
+extern "C" fm_status fm_gdn_decode(FmCtx *ctx, int li, const int *seq, int batch, const float *qkv, const float *z,
+                                   const float *beta, const float *alpha, const uint16_t *conv_w, const float *A_log,
+                                   const uint16_t *dt_bias, const uint16_t *norm_w, float *out) {
+    if (!ctx) return FM_ERR_INVALID;
+    if (!seq || !qkv || !z || !beta || !alpha || !out) return fail(ctx, FM_ERR_INVALID, "fm_gdn_decode: null argument");
+    fm_status st = check_layer_seq(ctx, "fm_gdn_decode", li, ctx->cfg.num_linear_layers, seq, batch);
+    if (st) return st;
+    if (batch == 0) return FM_OK;
+    for (int i = 0; i < batch; i++)
+        for (int j = 0; j < i; j++)
+            if (seq[i] == seq[j]) return fail(ctx, FM_ERR_INVALID, "fm_gdn_decode: sequence %d appears twice in one step", seq[i]);
+    const FmConfig &c = ctx->cfg;
+    FM_CUDA(ctx, cudaSetDevice(c.device));
+    const size_t vd = (size_t)c.linear_num_v_heads * c.linear_value_dim, hv = (size_t)c.linear_num_v_heads;
+    Stager sg(ctx);
+    bool ok = true;
+    const float *d_qkv = sg.in(qkv, (size_t)batch * ctx->conv_dim, &ok), *d_z = sg.in(z, batch * vd, &ok);
+    const float *d_b = sg.in(beta, batch * hv, &ok), *d_a = sg.in(alpha, batch * hv, &ok);
+    const uint16_t *d_cw = sg.in(conv_w, (size_t)ctx->conv_dim * c.conv_kernel_size, &ok);
+    const float *d_al = sg.in(A_log, hv, &ok);
+    const uint16_t *d_db = sg.in(dt_bias, hv, &ok), *d_nw = sg.in(norm_w, (size_t)c.linear_value_dim, &ok);
+    size_t w_out = 0;
+    float *d_out = sg.out(out, batch * vd, &ok, &w_out);
+    if (!ok) return fail(ctx, FM_ERR_INVALID, "fm_gdn_decode: staging buffer too small");
+    FM_CUDA(ctx, sg.push());
+    const size_t cn = (size_t)c.conv_kernel_size * ctx->conv_dim, sn = vd * c.linear_key_dim;
+    const GdnDims g = gdn_dims(ctx);
+    for (int i0 = 0; i0 < batch; i0 += kMaxList) {
+        TokSpec t;
+        t.mode = 0;
+        t.n = std::min(kMaxList, batch - i0);
+        for (int i = 0; i < t.n; i++) {
+            t.seq[i] = seq[i0 + i];
+            t.pos[i] = ctx->gdn_steps[lidx(ctx, li, seq[i0 + i])]++;
+            t.row[i] = 0;
+        }
+        st = launched(ctx, launch_gdn_decode(g, t, ctx->d_conv_state + (size_t)li * c.max_seqs * cn, ctx->d_ssm_state + (size_t)li * c.max_seqs * sn,
+                                             (long long)cn, (long long)sn, d_qkv + (size_t)i0 * ctx->conv_dim, d_z + i0 * vd, d_b + i0 * hv,
+                                             d_a + i0 * hv, d_cw, d_al, d_db, d_nw, d_out + i0 * vd, ctx->stream), "gdn_decode");
+        if (st) return st;
+    }
+    FM_CUDA(ctx, sg.pull(out, w_out, batch * vd));
+    return FM_OK;
+}
+
+extern "C" fm_status fm_gdn_prefill(FmCtx *ctx, int li, int seq, int n, int chunk, const float *qkv, const float *z,
+                                    const float *beta, const float *alpha, const uint16_t *conv_w, const float *A_log,
+                                    const uint16_t *dt_bias, const uint16_t *norm_w, float *out) {
+    if (!ctx) return FM_ERR_INVALID;
+    if (!qkv || !z || !beta || !alpha || !out) return fail(ctx, FM_ERR_INVALID, "fm_gdn_prefill: null argument");
+    const FmConfig &c = ctx->cfg;
+    if (li < 0 || li >= c.num_linear_layers || seq < 0 || seq >= c.max_seqs) return fail(ctx, FM_ERR_INVALID, "fm_gdn_prefill: layer %d / seq %d", li, seq);
+    if (n < 0 || n > c.max_batch_tokens) return fail(ctx, FM_ERR_INVALID, "fm_gdn_prefill: n=%d exceeds max_batch_tokens=%d", n, c.max_batch_tokens);
+    if (chunk == 0) chunk = 64;
+    if (chunk != 64) return fail(ctx, FM_ERR_UNSUPPORTED, "fm_gdn_prefill: chunk %d (built for 64)", chunk);
+    if (n == 0) return FM_OK;
+    FM_CUDA(ctx, cudaSetDevice(c.device));
+    const size_t vd = (size_t)c.linear_num_v_heads * c.linear_value_dim, hv = (size_t)c.linear_num_v_heads;
+    Stager sg(ctx);
+    bool ok = true;
+    const float *d_qkv = sg.in(qkv, (size_t)n * ctx->conv_dim, &ok), *d_z = sg.in(z, n * vd, &ok);
+    const float *d_b = sg.in(beta, n * hv, &ok), *d_a = sg.in(alpha, n * hv, &ok);
+    const uint16_t *d_cw = sg.in(conv_w, (size_t)ctx->conv_dim * c.conv_kernel_size, &ok);
+    const float *d_al = sg.in(A_log, hv, &ok);
+    const uint16_t *d_db = sg.in(dt_bias, hv, &ok), *d_nw = sg.in(norm_w, (size_t)c.linear_value_dim, &ok);
+    size_t w_out = 0;
+    float *d_out = sg.out(out, n * vd, &ok, &w_out);
+    if (!ok) return fail(ctx, FM_ERR_INVALID, "fm_gdn_prefill: staging buffer too small");
+    FM_CUDA(ctx, sg.push());
+    const size_t cn = (size_t)c.conv_kernel_size * ctx->conv_dim, sn = vd * c.linear_key_dim;
+    GdnDims g = gdn_dims(ctx);
+    const int step0 = ctx->gdn_steps[lidx(ctx, li, seq)];
+    fm_status st = launched(ctx, launch_gdn_prefill(g, n, chunk, step0, ctx->d_conv_state + lidx(ctx, li, seq) * cn, ctx->d_ssm_state + lidx(ctx, li, seq) * sn,
+                                                    d_qkv, d_z, d_b, d_a, d_cw, d_al, d_db, d_nw, d_out, ctx->d_work, ctx->work_bytes, ctx->stream), "gdn_prefill");
+    if (st) return st;
+    ctx->gdn_steps[lidx(ctx, li, seq)] = step0 + n;
+    FM_CUDA(ctx, sg.pull(out, w_out, n * vd));
+    return FM_OK;
+}
+
+// ---- snapshot / restore -----------------------------------------------------------------------
+extern "C" fm_status fm_kv_export(FmCtx *ctx, int fa_idx, int seq, float *k, float *v, int max_rows, int *len_out) {
+    if (!ctx) return FM_ERR_INVALID;
+    const FmConfig &c = ctx->cfg;
+    if (fa_idx < 0 || fa_idx >= c.num_full_layers || seq < 0 || seq >= c.max_seqs || !k || !v)
+        return fail(ctx, FM_ERR_INVALID, "fm_kv_export: bad argument");
+    const int len = ctx->kv_len[lidx(ctx, fa_idx, seq)];
+    if (len_out) *len_out = len;
+    if (len > max_rows) return fail(ctx, FM_ERR_INVALID, "fm_kv_export: %d rows held, room for %d", len, max_rows);
+    if (len == 0) return FM_OK;
+    FM_CUDA(ctx, cudaSetDevice(c.device));
+    const size_t kvd = (size_t)c.num_kv_heads * c.head_dim;
+    const KvView kv = kv_view(ctx, fa_idx);
+    if (ctx->ptr_mode == FM_PTR_DEVICE)
+        return launched(ctx, launch_kv_export(kv, seq, len, k, v, ctx->stream), "kv_export");
+    // host pointers: go through a temporary device image (snapshot path, not a hot path)
+    float *tmp = nullptr;
+    FM_CUDA(ctx, cudaMalloc(&tmp, 2 * (size_t)len * kvd * sizeof(float)));
+    cudaMemsetAsync(tmp, 0, 2 * (size_t)len * kvd * sizeof(float), ctx->stream);
+    fm_status st = launched(ctx, launch_kv_export(kv, seq, len, tmp, tmp + (size_t)len * kvd, ctx->stream), "kv_export");
+    if (st == FM_OK) {
+        cudaError_t e = cudaMemcpyAsync(k, tmp, (size_t)len * kvd * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(v, tmp + (size_t)len * kvd, (size_t)len * kvd * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+        if (e != cudaSuccess) st = fail(ctx, FM_ERR_CUDA, "fm_kv_export: %s", cudaGetErrorString(e));
+    }
+    cudaFree(tmp);
+    return st;
+}
+
+extern "C" fm_status fm_kv_import(FmCtx *ctx, int fa_idx, int seq, const float *k, const float *v, int len) {
+    if (!ctx) return FM_ERR_INVALID;
+    const FmConfig &c = ctx->cfg;
+    if (fa_idx < 0 || fa_idx >= c.num_full_layers || seq < 0 || seq >= c.max_seqs || len < 0 || (len > 0 && (!k || !v)))
+        return fail(ctx, FM_ERR_INVALID, "fm_kv_import: bad argument");
+    if (len > c.max_seq_len) return fail(ctx, FM_ERR_CAPACITY, "KV cache overflow (pos=%d >= cap=%d)", len - 1, c.max_seq_len);
+    FM_CUDA(ctx, cudaSetDevice(c.device));
+    // drop pages beyond the new length, then make sure the needed ones exist
+    {
+        const int gpages = (len + c.page_size - 1) / c.page_size;
+        const int nslots = gpages > c.seq_shard_rank ? (gpages - c.seq_shard_rank + c.seq_shard_count - 1) / c.seq_shard_count : 0;
+        int *tab = &ctx->h_page_table[((size_t)fa_idx * c.max_seqs + seq) * ctx->max_slots];
+        for (int i = nslots; i < ctx->max_slots; i++)
+            if (tab[i] >= 0) { ctx->free_pages.push_back(tab[i]); tab[i] = -1; }
+    }
+    fm_status st = ensure_pages(ctx, fa_idx, seq, len);
+    if (st) return st;
+    ctx->kv_len[lidx(ctx, fa_idx, seq)] = len;
+    if (len == 0) return FM_OK;
+    const size_t kvd = (size_t)c.num_kv_heads * c.head_dim;
+    const KvView kv = kv_view(ctx, fa_idx);
+    if (ctx->ptr_mode == FM_PTR_DEVICE)
+        return launched(ctx, launch_kv_import(kv, seq, len, k, v, ctx->stream), "kv_import");
+    float *tmp = nullptr;
+    FM_CUDA(ctx, cudaMalloc(&tmp, 2 * (size_t)len * kvd * sizeof(float)));
+    cudaError_t e = cudaMemcpyAsync(tmp, k, (size_t)len * kvd * sizeof(float), cudaMemcpyHostToDevice, ctx->stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(tmp + (size_t)len * kvd, v, (size_t)len * kvd * sizeof(float), cudaMemcpyHostToDevice, ctx->stream);
+    st = e == cudaSuccess ? launched(ctx, launch_kv_import(kv, seq, len, tmp, tmp + (size_t)len * kvd, ctx->stream), "kv_import")
+                          : fail(ctx, FM_ERR_CUDA, "fm_kv_import: %s", cudaGetErrorString(e));
+    cudaStreamSynchronize(ctx->stream);
+    cudaFree(tmp);
+    return st;
+}
+
+// conv history: the reference keeps [(ks-1)][conv_dim], oldest first; the device keeps a ring of ks
+// rows indexed by token count.  Export / import translate between the two.
+extern "C" fm_status fm_state_export(FmCtx *ctx, int li, int seq, float *conv, float *ssm) {
+    if (!ctx) return FM_ERR_INVALID;
+    const FmConfig &c = ctx->cfg;
+    if (li < 0 || li >= c.num_linear_layers || seq < 0 || seq >= c.max_seqs) return fail(ctx, FM_ERR_INVALID, "fm_state_export: bad argument");
+    FM_CUDA(ctx, cudaSetDevice(c.device));
+    const cudaMemcpyKind kind = ctx->ptr_mode == FM_PTR_HOST ? cudaMemcpyDeviceToHost : cudaMemcpyDeviceToDevice;
+    const size_t cd = (size_t)ctx->conv_dim, ks = (size_t)c.conv_kernel_size;
+    const size_t sn = (size_t)c.linear_num_v_heads * c.linear_value_dim * c.linear_key_dim;
+    const int step = ctx->gdn_steps[lidx(ctx, li, seq)];
+    if (conv) {
+        const float *ring = ctx->d_conv_state + lidx(ctx, li, seq) * ks * cd;
+        for (int j = 0; j < (int)ks - 1; j++) {
+            const int tokidx = step - ((int)ks - 1) + j;
+            if (tokidx >= 0)
+                FM_CUDA(ctx, cudaMemcpyAsync(conv + j * cd, ring + (size_t)(tokidx % (int)ks) * cd, cd * sizeof(float), kind, ctx->stream));
+            else if (ctx->ptr_mode == FM_PTR_HOST)
+                memset(conv + j * cd, 0, cd * sizeof(float));
+            else
+                FM_CUDA(ctx, cudaMemsetAsync(conv + j * cd, 0, cd * sizeof(float), ctx->stream));
+        }
+    }
+    if (ssm) FM_CUDA(ctx, cudaMemcpyAsync(ssm, ctx->d_ssm_state + lidx(ctx, li, seq) * sn, sn * sizeof(float), kind, ctx->stream));
+    if (ctx->ptr_mode == FM_PTR_HOST) FM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return FM_OK;
+}
+
+extern "C" fm_status fm_state_import(FmCtx *ctx, int li, int seq, const float *conv, const float *ssm) {
+    if (!ctx) return FM_ERR_INVALID;
+    const FmConfig &c = ctx->cfg;
+    if (li < 0 || li >= c.num_linear_layers || seq < 0 || seq >= c.max_seqs) return fail(ctx, FM_ERR_INVALID, "fm_state_import: bad argument");
+    FM_CUDA(ctx, cudaSetDevice(c.device));
+    const cudaMemcpyKind kind = ctx->ptr_mode == FM_PTR_HOST ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToDevice;
+    const size_t cd = (size_t)ctx->conv_dim, ks = (size_t)c.conv_kernel_size;
+    const size_t sn = (size_t)c.linear_num_v_heads * c.linear_value_dim * c.linear_key_dim;
+    if (conv) {
+        // restart the ring: history rows become tokens 0..ks-2, the next token is number ks-1
+        float *ring = ctx->d_conv_state + lidx(ctx, li, seq) * ks * cd;
+        FM_CUDA(ctx, cudaMemcpyAsync(ring, conv, (ks - 1) * cd * sizeof(float), kind, ctx->stream));
+        ctx->gdn_steps[lidx(ctx, li, seq)] = (int)ks - 1;
+    }
+    if (ssm) FM_CUDA(ctx, cudaMemcpyAsync(ctx->d_ssm_state + lidx(ctx, li, seq) * sn, ssm, sn * sizeof(float), kind, ctx->stream));
+    if (ctx->ptr_mode == FM_PTR_HOST) FM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return FM_OK;
+}

@@ -1,0 +1,140 @@
+// Host-side context and the launcher interface between the C-ABI layer (fm_api.cu) and the kernels.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+#include <vector>
+
+#include "../../include/fm_attn.h"
+
+namespace fm {
+
+constexpr int kMaxList = 64;  // tokens a kernel takes by value in one launch
+
+// Which tokens a launch works on.  mode 0: an explicit list (decode: one token per sequence);
+// mode 1: a run of n consecutive tokens of one sequence (prefill).
+struct TokSpec {
+    int mode;
+    int n;
+    int seq0, pos0, row0;  // mode 1: token t has pos0 + t, cache row row0 + t
+    int seq[kMaxList], pos[kMaxList], row[kMaxList];
+};
+
+__host__ __device__ inline void tok_get(const TokSpec &t, int i, int &seq, int &pos, int &row) {
+    if (t.mode == 1) {
+        seq = t.seq0; pos = t.pos0 + i; row = t.row0 + i;
+    } else {
+        seq = t.seq[i]; pos = t.pos[i]; row = t.row[i];
+    }
+}
+
+// The paged bf16 KV store of one layer as a kernel sees it.
+// Page layout: [2 (K,V)][Hkv][page_size][D] bf16, so one (K or V, head) tile is contiguous.
+// Row r of a sequence lives in global page r / page_size; a context holds the pages with
+// (page % shard_count) == shard_rank, at local slot page / shard_count of its page table.
+struct KvView {
+    __nv_bfloat16 *pool;
+    const int *page_table;  // [max_seqs][max_slots] of this layer
+    int max_slots;
+    int page_size;
+    int Hkv;
+    int D;
+    int shard_rank, shard_count;
+};
+
+struct RopeParams {
+    float inv_freq[64];  // rotary_dim / 2 entries, computed on the host exactly as the reference does
+    int rotary_dim;
+    float pos_div;       // linear scaling: position is divided by this
+    float logit_scale;   // 1/sqrt(D) * YaRN temperature
+};
+
+}  // namespace fm
+
+struct FmCtx {
+    FmConfig cfg;
+    cudaStream_t stream = nullptr;
+    int ptr_mode = FM_PTR_DEVICE;
+    std::string err;
+    int64_t launches = 0;
+    int sm_count = 148;
+
+    fm::RopeParams rope;
+
+    // KV store
+    __nv_bfloat16 *pool = nullptr;
+    int64_t pool_pages = 0;
+    size_t page_elems = 0;  // bf16 elements per page
+    int max_slots = 0;      // local page slots per sequence
+    int *d_page_table = nullptr;       // [layers][seqs][max_slots]
+    std::vector<int> h_page_table;
+    std::vector<int> free_pages;
+    std::vector<int> kv_len;           // [layers][seqs] global rows
+
+    // GatedDeltaNet state
+    float *d_conv_state = nullptr;  // [layers][seqs][ks-1][conv_dim]
+    float *d_ssm_state = nullptr;   // [layers][seqs][Hv][dv][dk]
+    int conv_dim = 0;
+    std::vector<int> gdn_steps;     // [layers][seqs] tokens seen; indexes the conv ring
+
+    // decode attention scratch: split partials
+    float *d_part_o = nullptr;   // [batch][H][max_splits][D]
+    float *d_part_ml = nullptr;  // [batch][H][max_splits][2]
+    int max_splits = 0;
+
+    // prefill scratch: per-(token, head) un-normalised result and (max, sum)
+    float *d_pf_o = nullptr;   // [max_batch_tokens][H][D]
+    float *d_pf_ml = nullptr;  // [max_batch_tokens][H][2]
+    void *d_work = nullptr;             // chunked GatedDeltaNet workspace
+    size_t work_bytes = 0;
+
+    // host-pointer mode staging
+    char *h_stage = nullptr;  // pinned
+    char *d_stage = nullptr;
+    size_t stage_bytes = 0;
+};
+
+namespace fm {
+
+// ---- launchers (each returns the number of kernels it queued, or -1 with cudaGetLastError set) ----
+int launch_kv_append(const KvView &kv, const RopeParams &rope, const TokSpec &toks, const float *k,
+                     const float *v, const uint16_t *k_norm_w, float eps, cudaStream_t st);
+
+int launch_attn_decode(const KvView &kv, const RopeParams &rope, const TokSpec &toks, int H,
+                       const float *q_proj_out, const float *q, const uint16_t *q_norm_w, float eps,
+                       float *part_o, float *part_ml, int nsplits, cudaStream_t st);
+
+// merges [nparts] partials per (token, head) laid out with strides, applies the gate
+int launch_attn_merge(const float *part_o, const float *part_ml, int nparts, long long part_stride_o,
+                      long long part_stride_ml, long long tok_stride_o, long long tok_stride_ml,
+                      long long head_stride_o, long long head_stride_ml, int ntok, int H, int D,
+                      const float *q_proj_out, const float *gate, float *out, float *ml_out,
+                      cudaStream_t st);
+
+int launch_kv_export(const KvView &kv, int seq, int len, float *k, float *v, cudaStream_t st);
+int launch_kv_import(const KvView &kv, int seq, int len, const float *k, const float *v, cudaStream_t st);
+
+int launch_attn_prefill(const KvView &kv, const RopeParams &rope, int seq, int start_pos, int row0,
+                        int n, int H, const float *q_proj_out, const float *q, const float *gate,
+                        const uint16_t *q_norm_w, float eps, float *work_o, float *work_ml, float *out,
+                        cudaStream_t st);
+
+struct GdnDims {
+    int Hv, Hk, dk, dv, ks, conv_dim;
+    float eps;
+};
+int launch_gdn_decode(const GdnDims &g, const TokSpec &toks, float *conv_state, float *ssm_state,
+                      long long conv_seq_stride, long long ssm_seq_stride, const float *qkv,
+                      const float *z, const float *beta, const float *alpha, const uint16_t *conv_w,
+                      const float *A_log, const uint16_t *dt_bias, const uint16_t *norm_w, float *out,
+                      cudaStream_t st);
+int launch_gdn_prefill(const GdnDims &g, int n, int chunk, int step0, float *conv_state, float *ssm_state,
+                       const float *qkv, const float *z, const float *beta, const float *alpha,
+                       const uint16_t *conv_w, const float *A_log, const uint16_t *dt_bias,
+                       const uint16_t *norm_w, float *out, void *work, size_t work_bytes,
+                       cudaStream_t st);
+size_t gdn_prefill_work_bytes(const GdnDims &g, int max_tokens, int chunk);
+
+}  // namespace fm

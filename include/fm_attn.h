@@ -1,0 +1,197 @@
+/* fm_attn.h -- C-ABI of the Blackwell (sm_100a) attention hot path of Flash-MoE.
+ *
+ * The reference engine has no plugin/FFI layer for this path: attention and
+ * GatedDeltaNet are inline Metal encoder sequences inside
+ * fused_layer_forward() and batched_prefill().  What a caller binds there is
+ * (i) the argument lists of the Metal kernels, (ii) the KVCache /
+ * LinearAttnState structs and the MetalCtx buffers that back them.  Each entry
+ * point below replaces one such group and cites it.  All citations are paths
+ * inside the reference project.
+ *
+ * Conventions
+ *   - Every call returns fm_status; fm_last_error() gives the text (the
+ *     reference prints "ERROR: ..." to stderr and returns early; this library
+ *     prints nothing and changes no state on error).
+ *   - Tensors are fp32 unless noted, row-major, with the reference's layouts:
+ *       q_proj_out [n][H][2*D]   per head [q(D) | gate(D)]   (layer_forward.h:537-541)
+ *       q, gate, out [n][H*D];  k, v [n][Hkv*D]
+ *       qkv [n][2*Hk*dk + Hv*dv] = q | k | v                 (layer_forward.h:907-909)
+ *       z, out [n][Hv*dv];  beta, alpha [n][Hv]
+ *       norm / conv / dt_bias weights are bf16 bit patterns (uint16_t).
+ *   - Data pointers are DEVICE pointers by default; fm_set_pointer_mode(ctx,
+ *     FM_PTR_HOST) makes every data pointer a host pointer (the reference passes
+ *     host floats because Apple memory is unified); the library then stages
+ *     through its own pinned buffers.  seq[] / pos[] index arrays are always
+ *     host arrays.
+ *   - Work is queued on the context's stream (fm_set_stream; default: the
+ *     legacy default stream).  In host-pointer mode calls return after the
+ *     outputs have landed in the caller's buffers.
+ *   - A context is not re-entrant (one inference thread), like the reference.
+ */
+#ifndef FM_ATTN_H
+#define FM_ATTN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum fm_status {
+    FM_OK = 0,
+    FM_ERR_INVALID = 1,     /* bad argument, nothing done */
+    FM_ERR_CAPACITY = 2,    /* KV cache overflow: sequence full or page pool exhausted */
+    FM_ERR_NOMEM = 3,       /* device / host allocation failed */
+    FM_ERR_CUDA = 4,        /* a CUDA call failed; text in fm_last_error */
+    FM_ERR_TIMEOUT = 5,     /* a bounded device-side wait gave up */
+    FM_ERR_UNSUPPORTED = 6  /* shape outside what the kernels are built for */
+} fm_status;
+
+enum { FM_PTR_DEVICE = 0, FM_PTR_HOST = 1 };
+
+/* Plain-data configuration; replaces the ModelConfig fields this path reads
+ * (metal_infer/config.h:9-75) and the feature globals set before metal_setup()
+ * (metal_infer/timing.h:82-111).  Head counts are those HELD BY THIS CONTEXT:
+ * a head-sharded deployment creates one context per GPU with its share. */
+typedef struct FmConfig {
+    /* gated GQA full attention */
+    int num_attn_heads;      /* query heads (32) */
+    int num_kv_heads;        /* KV heads (2) */
+    int head_dim;            /* 256 (the kernels are built for 256) */
+    int rotary_dim;          /* leading dims that rotate (64); pairs (i, i+rotary_dim/2) */
+    float rope_theta;        /* 1e7 */
+    float rms_norm_eps;      /* eps of q/k norm and of the GatedDeltaNet output norm */
+    int rope_scaling_mode;   /* 0 none, 1 linear, 2 NTK, 3 YaRN (layer_forward.h:22-70) */
+    float rope_scale_factor; /* 1.0 */
+    int rope_orig_max_pos;   /* original context length used by YaRN's wavelength bounds */
+    int num_full_layers;     /* full-attention layers held (15) */
+    /* GatedDeltaNet */
+    int linear_num_v_heads;  /* 64 */
+    int linear_num_k_heads;  /* 16; v head vh reads k head vh / (Hv/Hk) */
+    int linear_key_dim;      /* 128 (kernels are built for 128) */
+    int linear_value_dim;    /* 128 */
+    int conv_kernel_size;    /* 4 */
+    int num_linear_layers;   /* GatedDeltaNet layers held (45) */
+    /* capacity */
+    int max_seqs;            /* concurrent sequences (the reference has 1) */
+    int max_seq_len;         /* positions per sequence (global, before sequence sharding) */
+    int page_size;           /* positions per KV page; 64 */
+    int64_t kv_pool_pages;   /* pages in the shared pool; 0 = enough for every sequence at max_seq_len */
+    int max_batch_tokens;    /* largest n of a prefill call / batch of a decode call */
+    /* sequence sharding of the KV store: page p of a sequence lives on the
+     * context with seq_shard_rank == p % seq_shard_count */
+    int seq_shard_rank;      /* 0 */
+    int seq_shard_count;     /* 1 */
+    int device;              /* CUDA device ordinal */
+} FmConfig;
+
+typedef struct FmCtx FmCtx;
+
+/* Fills *cfg with the Qwen3.5-397B shapes (32/2 heads x 256, rotary 64, theta 1e7; 64/16 heads x
+ * 128, conv 4; 15 + 45 layers), one sequence, 8192 positions. */
+void fm_default_config(FmConfig *cfg);
+
+/* Allocates the KV page pool, page tables, recurrent state and staging buffers.
+ * Replaces metal_setup()'s buf_kv_k/v, buf_attn_*, buf_delta_state, buf_conv_state
+ * (metal_infer/metal_ctx.h:94-130,460-526) and kv_cache_new / linear_attn_state_new
+ * (metal_infer/layer_forward.h:143-236,419-424).  State starts zeroed. */
+fm_status fm_create(const FmConfig *cfg, FmCtx **out);
+void fm_destroy(FmCtx *ctx);
+
+/* Text of the last error on this context (ctx == NULL: last fm_create failure).
+ * Mirrors flashmoe_last_error (FlashMoE-iOS/FlashMoEEngine/FlashMoEEngine.h:150-151). */
+const char *fm_last_error(const FmCtx *ctx);
+
+fm_status fm_set_stream(FmCtx *ctx, void *cuda_stream);
+fm_status fm_set_pointer_mode(FmCtx *ctx, int mode);
+fm_status fm_synchronize(FmCtx *ctx);
+
+/* Forget a sequence (seq = -1: all): KV length 0, pages back to the pool, conv and recurrent
+ * state zeroed.  Replaces reset_delta_net_state (metal_infer/metal_ctx.h:599-608) plus kv->len = 0
+ * (FlashMoE-iOS/FlashMoEEngine/FlashMoEEngine.m:1239-1258). */
+fm_status fm_reset(FmCtx *ctx, int seq);
+
+/* Rows held for (layer, sequence) -- KVCache.len (metal_infer/layer_forward.h:128). */
+int fm_kv_len(const FmCtx *ctx, int fa_idx, int seq);
+
+/* k RMS-norm (k_norm_w may be NULL) + partial RoPE at pos[i] + append of token i to sequence
+ * seq[i]; cache row = the sequence's current length, which then grows by one.  K and V are stored
+ * as bf16.  Replaces layer_forward.h:574-629 (CPU) and the Metal kernel prefill_kv_cache_bf16
+ * (metal_infer/shaders.metal:2405-2482).  FM_ERR_CAPACITY on overflow, with nothing appended. */
+fm_status fm_kv_append_rope(FmCtx *ctx, int fa_idx, const int *seq, const int *pos, int n,
+                            const float *k, const float *v, const uint16_t *k_norm_w);
+
+/* One decode step for `batch` sequences: q RMS-norm (q_norm_w may be NULL) + RoPE, append of the
+ * new k, v (skipped if k == NULL: caller already appended), softmax(q K^T / sqrt(D)) V over the
+ * whole sequence including the new row, times sigmoid(gate).
+ * Give either q_proj_out (interleaved) or q and gate.
+ * Replaces layer_forward.h:556-735 (CPU) and the Metal kernels attn_scores_batched /
+ * attn_softmax_batched / attn_values_batched / fused_attention_online / sigmoid_gate
+ * (metal_infer/shaders.metal:899-1040,1151-1313; dispatch layer_forward.h:3175-3367). */
+fm_status fm_attn_decode(FmCtx *ctx, int fa_idx, const int *seq, const int *pos, int batch,
+                         const float *q_proj_out, const float *q, const float *gate,
+                         const float *k, const float *v, const uint16_t *q_norm_w,
+                         const uint16_t *k_norm_w, float *out);
+
+/* The same step on a sequence-sharded store: attends over the rows this context holds and returns
+ * the un-normalised partial result, o_part [batch][H][D] and ml_part [batch][H][2] = (running max
+ * in log2 units, sum of weights).  The new k, v are appended only where this context owns the
+ * row's page.  No reference counterpart (the reference is single-device). */
+fm_status fm_attn_decode_partial(FmCtx *ctx, int fa_idx, const int *seq, const int *pos, int batch,
+                                 const float *q_proj_out, const float *q, const float *k,
+                                 const float *v, const uint16_t *q_norm_w,
+                                 const uint16_t *k_norm_w, float *o_part, float *ml_part);
+
+/* Log-sum-exp merge of nparts partial results ([nparts][batch][H][D] and [nparts][batch][H][2])
+ * followed by the sigmoid gate (gate [batch][H*D], or q_proj_out interleaved). */
+fm_status fm_attn_merge_gate(FmCtx *ctx, int nparts, const float *o_parts, const float *ml_parts,
+                             const float *q_proj_out, const float *gate, int batch, float *out);
+
+/* Causal prefill of n tokens of one sequence at positions start_pos..: q norm + RoPE, k norm +
+ * RoPE + append, token t attends to rows [0, len_before + t], times sigmoid(gate).
+ * Replaces batched_prefill.h:543-740 and the Metal kernels prefill_q_rope_norm_bf16 /
+ * prefill_kv_cache_bf16 / prefill_causal_attn (metal_infer/shaders.metal:2228-2482). */
+fm_status fm_attn_prefill(FmCtx *ctx, int fa_idx, int seq, int start_pos, int n,
+                          const float *q_proj_out, const float *q, const float *gate,
+                          const float *k, const float *v, const uint16_t *q_norm_w,
+                          const uint16_t *k_norm_w, float *out);
+
+/* One GatedDeltaNet step for `batch` sequences: depthwise causal conv + SiLU, conv-state shift,
+ * q/k normalise, decay and beta, delta-rule update of the [Hv][dv][dk] fp32 state, gated RMS-norm.
+ * A_log / dt_bias / norm_w may be NULL with the reference's meaning (A = 1, bias 0, no norm).
+ * Replaces layer_forward.h:886-1025 (CPU) and the Metal kernels conv1d_step / rms_norm_qk /
+ * compute_decay_beta / gated_delta_net_step(_fused) / gated_rms_norm
+ * (metal_infer/shaders.metal:1591-1850; dispatch layer_forward.h:2114-2214). */
+fm_status fm_gdn_decode(FmCtx *ctx, int li, const int *seq, int batch, const float *qkv,
+                        const float *z, const float *beta, const float *alpha,
+                        const uint16_t *conv_w, const float *A_log, const uint16_t *dt_bias,
+                        const uint16_t *norm_w, float *out);
+
+/* n tokens of one sequence through the GatedDeltaNet layer in chunked form; output and final state
+ * equal n sequential fm_gdn_decode steps.  chunk = 0 picks the default (64).
+ * Replaces batched_prefill.h:798-1037 and the Metal kernels conv1d_step_batched /
+ * rms_norm_qk_batched / compute_decay_beta_batched / gated_delta_net_step_batched /
+ * gated_rms_norm_batched (metal_infer/shaders.metal:2639-2860). */
+fm_status fm_gdn_prefill(FmCtx *ctx, int li, int seq, int n, int chunk, const float *qkv,
+                         const float *z, const float *beta, const float *alpha,
+                         const uint16_t *conv_w, const float *A_log, const uint16_t *dt_bias,
+                         const uint16_t *norm_w, float *out);
+
+/* Snapshot / restore in the reference's fp32 layouts: k, v [len][Hkv*D] (KVCache.k_cache/v_cache,
+ * layer_forward.h:121-123), conv [(ks-1)][conv_dim], ssm [Hv][dv][dk] (layer_forward.h:414-417).
+ * Replaces the system-prompt snapshot/restore of metal_infer/generate.h:710-764,897-939.
+ * On a sequence-sharded store export/import touch the rows this context owns (other rows of the
+ * caller's arrays are left alone / ignored).  Pointers follow the pointer mode. */
+fm_status fm_kv_export(FmCtx *ctx, int fa_idx, int seq, float *k, float *v, int max_rows, int *len_out);
+fm_status fm_kv_import(FmCtx *ctx, int fa_idx, int seq, const float *k, const float *v, int len);
+fm_status fm_state_export(FmCtx *ctx, int li, int seq, float *conv, float *ssm);
+fm_status fm_state_import(FmCtx *ctx, int li, int seq, const float *conv, const float *ssm);
+
+/* Number of kernels this context has launched since creation (bench bookkeeping). */
+int64_t fm_launch_count(const FmCtx *ctx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FM_ATTN_H */

@@ -26,6 +26,15 @@ static inline float bf16f(uint16_t h) {
     return f;
 }
 
+/* fp32 -> nearest-even bf16 -> fp32 */
+static inline float round_bf16f(float x) {
+    uint32_t u;
+    memcpy(&u, &x, sizeof u);
+    u = (u + 0x7FFFu + ((u >> 16) & 1u)) & 0xFFFF0000u;
+    memcpy(&x, &u, sizeof x);
+    return x;
+}
+
 /* ------------------------------------------------------------------------ */
 /* RoPE frequency with the scaling modes of metal_infer/layer_forward.h:22-63 */
 static float rope_freq(const FmoDims *d, int i) {
@@ -120,6 +129,13 @@ int fmo_attn_step(const FmoDims *d, float *k_cache, float *v_cache, int *len, in
        (metal_infer/layer_forward.h:591-646) */
     memcpy(k_cache + (size_t)*len * kv_dim, k, (size_t)kv_dim * sizeof(float));
     memcpy(v_cache + (size_t)*len * kv_dim, v_in, (size_t)kv_dim * sizeof(float));
+    if (d->store_bf16) {
+        float *kr = k_cache + (size_t)*len * kv_dim, *vr = v_cache + (size_t)*len * kv_dim;
+        for (int i = 0; i < kv_dim; i++) {
+            kr[i] = round_bf16f(kr[i]);
+            vr[i] = round_bf16f(vr[i]);
+        }
+    }
     *len += 1;
     const int L = *len;
     const int group = H / Hkv;

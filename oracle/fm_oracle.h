@@ -36,6 +36,9 @@ typedef struct {
     int linear_key_dim;      /* 128 */
     int linear_value_dim;    /* 128 */
     int conv_kernel_size;    /* 4 */
+    int store_bf16;          /* restatement only (the reference harness ignores it): round the
+                                normalised, rotated k and the v to bf16 (nearest even) before the
+                                append, i.e. reference arithmetic on top of a bf16 KV store */
 } FmoDims;
 
 #define FMO_API(prefix)                                                                         \

@@ -1,0 +1,135 @@
+"""GatedDeltaNet decode through the C-ABI against the CPU checker (needs a B200)."""
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from gpu_util import gdn_ctx
+from oracle.oracle_py import make_dims
+from parity import rel_errors
+
+pytestmark = pytest.mark.gpu
+GOLD = Path(__file__).resolve().parent / "golden"
+
+# tolerance of the task statement: 5e-3 on the recurrent state after 1000 steps
+TOL_STATE = 5e-3
+TOL_OUT = 5e-3
+
+
+def test_golden_gdn(pkg):
+    f = np.load(GOLD / "gdn_v4_k1_d128.npz")
+    c = gdn_ctx(pkg, 4, 1)
+    n = int(f["steps"])
+    outs = []
+    for t in range(n):
+        out = np.empty((1, 512), np.float32)
+        c.gdn_decode(0, [0], f["qkv"][t:t + 1].copy(), f["z"][t:t + 1].copy(), f["beta"][t:t + 1].copy(),
+                     f["alpha"][t:t + 1].copy(), out, f["conv_w"], f["A_log"], f["dt_bias"], f["norm_w"])
+        outs.append(out)
+    conv = np.empty((3, 768), np.float32); ssm = np.empty((4, 128, 128), np.float32)
+    c.state_export(0, 0, conv, ssm)
+    c.close()
+    np.testing.assert_array_equal(conv, f["conv_final"])
+    g1, _, r1 = rel_errors(np.concatenate(outs), f["out"])
+    g2, _, r2 = rel_errors(ssm, f["ssm_final"])
+    print("golden gdn out", g1, r1, "state", g2, r2)
+    assert g1 <= 1e-4 and g2 <= 1e-4
+
+
+def test_config2_1000_steps(pkg, port, synth):
+    """1000 sequential tokens at the production shape (16 q/k heads, 64 v heads, 128x128 fp32 state
+    ~ N(0, 0.02^2)); state and outputs against the CPU recurrence."""
+    n = 1000
+    dims = make_dims()
+    w = synth.gdn_weights(0)
+    qkv, z, beta, alpha = synth.gdn_step_inputs(0, n)
+    s0 = synth.gdn_state(0)
+    conv_ref = np.zeros((3, 12288), np.float32); ssm_ref = s0.copy()
+    out_ref = port.gdn_run(dims, conv_ref, ssm_ref, qkv, z, beta, alpha, w["conv_w"], w["A_log"], w["dt_bias"],
+                           w["norm_w"], threads=8)
+    c = gdn_ctx(pkg)
+    c.state_import(0, 0, None, s0)
+    outs = np.empty((n, 8192), np.float32)
+    for t in range(n):
+        c.gdn_decode(0, [0], qkv[t:t + 1].copy(), z[t:t + 1].copy(), beta[t:t + 1].copy(), alpha[t:t + 1].copy(),
+                     outs[t:t + 1], w["conv_w"], w["A_log"], w["dt_bias"], w["norm_w"])
+    conv = np.empty((3, 12288), np.float32); ssm = np.empty((64, 128, 128), np.float32)
+    c.state_export(0, 0, conv, ssm)
+    c.close()
+    np.testing.assert_array_equal(conv, conv_ref)
+    gs, _, rs = rel_errors(ssm, ssm_ref)
+    go, _, ro = rel_errors(outs, out_ref)
+    print("config2 state gated", gs, "rms-rel", rs, "| out gated", go, "rms-rel", ro)
+    assert gs <= TOL_STATE and go <= TOL_OUT
+
+
+def test_batched_sequences_and_layers(pkg, port, synth):
+    """Batch of 5 sequences (uses the whole-head-per-CTA variants) on the second of two layers; the
+    first layer's state stays zero."""
+    B, n = 5, 6
+    dims = make_dims()
+    w = synth.gdn_weights(3)
+    c = gdn_ctx(pkg, max_seqs=B, layers=2)
+    refs, states = [], []
+    ins = [synth.gdn_step_inputs(40 + s, n) for s in range(B)]
+    for s in range(B):
+        conv = np.zeros((3, 12288), np.float32); ssm = synth.gdn_state(40 + s).copy()
+        c.state_import(1, s, None, ssm)
+        refs.append(port.gdn_run(dims, conv, ssm, *ins[s], w["conv_w"], w["A_log"], w["dt_bias"], w["norm_w"], threads=8))
+        states.append(ssm)
+    for t in range(n):
+        pack = lambda j: np.ascontiguousarray(np.stack([ins[s][j][t] for s in range(B)]))
+        out = np.empty((B, 8192), np.float32)
+        c.gdn_decode(1, list(range(B)), pack(0), pack(1), pack(2), pack(3), out, w["conv_w"], w["A_log"],
+                     w["dt_bias"], w["norm_w"])
+        for s in range(B):
+            g, _, _ = rel_errors(out[s], refs[s][t])
+            assert g <= 1e-4, (t, s, g)
+    for s in range(B):
+        ssm = np.empty((64, 128, 128), np.float32)
+        c.state_export(1, s, None, ssm)
+        g, _, _ = rel_errors(ssm, states[s])
+        assert g <= 1e-4
+    z0 = np.ones((64, 128, 128), np.float32)
+    c.state_export(0, 0, None, z0)
+    assert not z0.any()
+    c.close()
+
+
+def test_large_batch_whole_head_variant(pkg, port, synth):
+    B = 9  # 64 heads x 9 >= 512 CTAs: one CTA per head
+    dims = make_dims()
+    w = synth.gdn_weights(4)
+    c = gdn_ctx(pkg, max_seqs=B)
+    qkv, z, beta, alpha = synth.gdn_step_inputs(50, B)
+    out = np.empty((B, 8192), np.float32)
+    for s in range(B):
+        c.state_import(0, s, None, synth.gdn_state(60 + s))
+    c.gdn_decode(0, list(range(B)), qkv, z, beta, alpha, out, w["conv_w"], w["A_log"], w["dt_bias"], w["norm_w"])
+    for s in range(B):
+        conv = np.zeros((3, 12288), np.float32); ssm = synth.gdn_state(60 + s).copy()
+        r = port.gdn_run(dims, conv, ssm, qkv[s:s + 1], z[s:s + 1], beta[s:s + 1], alpha[s:s + 1], w["conv_w"],
+                         w["A_log"], w["dt_bias"], w["norm_w"], threads=8)
+        g, _, _ = rel_errors(out[s], r)
+        assert g <= 1e-4
+    c.close()
+
+
+def test_reset_and_reference_defaults(pkg, port, synth):
+    """NULL A_log / dt_bias / norm weight mean A = 1, bias 0, no output norm, as in the reference;
+    fm_reset returns the layer to the zero state."""
+    dims = make_dims(linear_num_v_heads=8, linear_num_k_heads=2)
+    c = gdn_ctx(pkg, 8, 2)
+    w = synth.gdn_weights(6, 8, 2)
+    qkv, z, beta, alpha = synth.gdn_step_inputs(6, 3, 8, 2)
+    for rep in range(2):
+        conv = np.zeros((3, 1536), np.float32); ssm = np.zeros((8, 128, 128), np.float32)
+        ref = port.gdn_run(dims, conv, ssm, qkv, z, beta, alpha, w["conv_w"], None, None, None)
+        for t in range(3):
+            out = np.empty((1, 1024), np.float32)
+            c.gdn_decode(0, [0], qkv[t:t + 1].copy(), z[t:t + 1].copy(), beta[t:t + 1].copy(), alpha[t:t + 1].copy(), out,
+                         w["conv_w"], None, None, None)
+            g, _, _ = rel_errors(out, ref[t])
+            assert g <= 1e-4
+        c.reset(0)
+    c.close()

@@ -1,0 +1,63 @@
+"""Prefill entry points against sequential CPU steps (needs a B200)."""
+import numpy as np
+import pytest
+
+from gpu_util import attn_ctx, gdn_ctx, oracle_attn
+from oracle.oracle_py import make_dims
+from parity import rel_errors
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-3
+TOL_GDN = 5e-3
+
+
+@pytest.mark.parametrize("n,prefix", [(1, 0), (70, 0), (256, 0), (100, 150)])
+def test_attn_prefill_matches_sequential_steps(pkg, port, synth, n, prefix):
+    """Causal prefill of n tokens after `prefix` cached rows against n sequential CPU steps;
+    bf16-representable q, k, v as in the bf16 prefill configuration, the checker rounding the
+    rotated k rows to bf16 as the store does."""
+    k0, v0 = synth.attn_cache(70 + n, prefix)
+    q, g, k, v = synth.attn_step_inputs(70 + n, n, bf16=True)
+    c = attn_ctx(pkg, 32, 2, max_seq_len=prefix + n + 10, max_batch=max(64, n))
+    c.kv_import(0, 0, k0, v0, prefix)
+    out = np.empty((n, 8192), np.float32)
+    c.attn_prefill(0, 0, prefix, n, out, q=q, gate=g, k=k, v=v)
+    L = c.kv_len(0, 0)
+    assert L == prefix + n
+    ke = np.zeros((L, 512), np.float32); ve = np.zeros_like(ke)
+    c.kv_export(0, 0, ke, ve, L)
+    c.close()
+    ref_out, kc, vc = oracle_attn(port, 32, 2, k0, v0, q, g, k, v, start_pos=prefix)
+    np.testing.assert_allclose(ke, kc, rtol=2 ** -7, atol=1e-6)
+    gated, mom, rr = rel_errors(out, ref_out)
+    print("prefill n", n, "prefix", prefix, "gated", gated, "rms-rel", rr)
+    assert gated <= TOL
+
+
+def test_gdn_prefill_matches_sequential_steps(pkg, port, synth):
+    n = 200
+    dims = make_dims()
+    w = synth.gdn_weights(8)
+    qkv, z, beta, alpha = synth.gdn_step_inputs(8, n, bf16=True)
+    s0 = synth.gdn_state(8)
+    conv_ref = np.zeros((3, 12288), np.float32); ssm_ref = s0.copy()
+    out_ref = port.gdn_run(dims, conv_ref, ssm_ref, qkv, z, beta, alpha, w["conv_w"], w["A_log"], w["dt_bias"],
+                           w["norm_w"], threads=8)
+    c = gdn_ctx(pkg, max_batch=256)
+    c.state_import(0, 0, None, s0)
+    out = np.empty((n, 8192), np.float32)
+    c.gdn_prefill(0, 0, n, qkv, z, beta, alpha, out, w["conv_w"], w["A_log"], w["dt_bias"], w["norm_w"])
+    conv = np.empty((3, 12288), np.float32); ssm = np.empty((64, 128, 128), np.float32)
+    c.state_export(0, 0, conv, ssm)
+    # a decode step continues from the prefilled state
+    q1, z1, b1, a1 = synth.gdn_step_inputs(9, 1)
+    o1 = np.empty((1, 8192), np.float32)
+    c.gdn_decode(0, [0], q1, z1, b1, a1, o1, w["conv_w"], w["A_log"], w["dt_bias"], w["norm_w"])
+    c.close()
+    r1 = port.gdn_run(dims, conv_ref.copy(), ssm_ref.copy(), q1, z1, b1, a1, w["conv_w"], w["A_log"], w["dt_bias"], w["norm_w"])
+    np.testing.assert_array_equal(conv, conv_ref)
+    gs, _, rs = rel_errors(ssm, ssm_ref)
+    go, _, ro = rel_errors(out, out_ref)
+    g1, _, _ = rel_errors(o1, r1)
+    print("gdn prefill state", gs, rs, "out", go, ro, "next step", g1)
+    assert gs <= TOL_GDN and go <= TOL_GDN and g1 <= TOL_GDN
