@@ -21,7 +21,7 @@ EXPORTS = [
     "fm_set_pointer_mode", "fm_synchronize", "fm_reset", "fm_kv_len", "fm_kv_append_rope",
     "fm_attn_decode", "fm_attn_decode_partial", "fm_attn_merge_gate", "fm_attn_prefill",
     "fm_gdn_decode", "fm_gdn_prefill", "fm_kv_export", "fm_kv_import", "fm_state_export",
-    "fm_state_import", "fm_launch_count",
+    "fm_state_import", "fm_launch_count", "fm_profile_enable", "fm_profile_read",
 ]
 
 
@@ -140,6 +140,15 @@ class Context:
 
     def launch_count(self) -> int:
         return self.lib.fm_launch_count(self.h)
+
+    def profile_enable(self, on: bool = True):
+        self._check(self.lib.fm_profile_enable(self.h, C.c_int(1 if on else 0)))
+
+    def profile_read(self):
+        """(launches, total milliseconds) of the bracketed dominant-kernel launches since the last read."""
+        n = C.c_int(0); ms = C.c_double(0.0)
+        self._check(self.lib.fm_profile_read(self.h, C.byref(n), C.byref(ms)))
+        return n.value, ms.value
 
     def kv_append_rope(self, fa_idx, seq, pos, k, v, k_norm_w=None):
         s, sp = _ints(seq); p, pp = _ints(pos)

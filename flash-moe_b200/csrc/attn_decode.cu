@@ -24,9 +24,19 @@ constexpr int kD = 256;          // head dim the kernel is built for
 constexpr int kPage = 64;        // rows per page
 constexpr int kStages = 3;
 constexpr int kTileBytes = kPage * kD * 2;  // one K or V tile: 32 KB
-constexpr int kDecThreads = 128;
 constexpr int kQBytes = 16 * kD * 2;        // 16 heads x 256 bf16
-constexpr int kDecSmem = 2 * kQBytes + kStages * 2 * kTileBytes;
+// Warp layout: 4 row-slices of 16 rows per tile x kNS warps per slice.  The warps of a slice split
+// the head dim: each computes the partial scores over its 256/kNS dims, the partials are summed
+// through shared memory (every warp of the slice then holds the same full scores), and each
+// accumulates its own 256/kNS output dims.  More warps per scheduler hide the latency of the
+// dependent MMA chains; the accumulator shrinks to 128/kNS registers per thread.
+constexpr int kNS = 2;
+constexpr int kDecWarps = 4 * kNS;
+constexpr int kDecThreads = 32 * kDecWarps;
+constexpr int kXchgBytes = 4 * kNS * 32 * 8 * 4;  // partial scores: [slice][split][lane][8] fp32
+constexpr int kDecSmem = 2 * kQBytes + kXchgBytes + kStages * 2 * kTileBytes;
+constexpr int kKSteps = (kD / 16) / kNS;   // k-steps of 16 dims a warp takes in Q K^T
+constexpr int kNChunks = (kD / 16) / kNS;  // 16-dim output chunks a warp owns in P V
 
 __device__ __forceinline__ void load_tile_async(uint32_t dst, const __nv_bfloat16 *src, int tid) {
     // 64 rows x 32 chunks of 16 B; consecutive threads take consecutive chunks (coalesced 512 B / warp)
@@ -38,6 +48,10 @@ __device__ __forceinline__ void load_tile_async(uint32_t dst, const __nv_bfloat1
     }
 }
 
+__device__ __forceinline__ void named_barrier(int id, int nthreads) {
+    asm volatile("bar.sync %0, %1;\n" ::"r"(id), "r"(nthreads) : "memory");
+}
+
 __global__ void __launch_bounds__(kDecThreads, 1)
 attn_decode_kernel(KvView kv, RopeParams rope, TokSpec toks, int H, const float *__restrict__ q_proj_out,
                    const float *__restrict__ q_in, const uint16_t *__restrict__ qnw, float eps,
@@ -45,11 +59,14 @@ attn_decode_kernel(KvView kv, RopeParams rope, TokSpec toks, int H, const float 
     extern __shared__ __align__(128) unsigned char smem[];
     const uint32_t s_qhi = smem_u32(smem);
     const uint32_t s_qlo = s_qhi + kQBytes;
-    const uint32_t s_kv = s_qlo + kQBytes;  // stage s: K at s_kv + s*2*kTileBytes, V right after
-    unsigned char *kv_raw = smem + 2 * kQBytes;
+    float *s_x = reinterpret_cast<float *>(smem + 2 * kQBytes);
+    const uint32_t s_kv = s_qlo + kQBytes + kXchgBytes;  // stage s: K at s_kv + s*2*kTileBytes, V right after
+    unsigned char *kv_raw = smem + 2 * kQBytes + kXchgBytes;
 
     const int split = blockIdx.x, kvh = blockIdx.y, tok = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int pw = warp & 3;   // which 16 rows of the tile
+    const int hs = warp >> 2;  // which share of the head dim
     const int group = H / kv.Hkv;  // query heads per KV head (<= 16)
 
     int seq, pos, row_new;
@@ -85,7 +102,7 @@ attn_decode_kernel(KvView kv, RopeParams rope, TokSpec toks, int H, const float 
         float *scratch = reinterpret_cast<float *>(kv_raw + 2 * 2 * kTileBytes);  // [16][256]
         const float qscale = rope.logit_scale * kLog2e;
         const int half = rope.rotary_dim / 2;
-        for (int r = warp; r < 16; r += 4) {
+        for (int r = warp; r < 16; r += kDecWarps) {
             float x[8];
             if (r < group) {
                 const int head = kvh * group + r;
@@ -134,37 +151,60 @@ attn_decode_kernel(KvView kv, RopeParams rope, TokSpec toks, int H, const float 
     }
 
     // ---- main loop ----
-    float o[32][4];
+    float o[2 * kNChunks][4];
 #pragma unroll
-    for (int i = 0; i < 32; i++) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    for (int i = 0; i < 2 * kNChunks; i++) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
     float m_ref[2] = {kNegBig, kNegBig};  // rows lane/4 and lane/4 + 8
     float l_sum[2] = {0.f, 0.f};
 
     const int lm = lane >> 3, lr = lane & 7;  // ldmatrix: matrix index and row within it
+    // partial-score exchange buffer, [slice][split][2 float4 planes][lane]: lanes 16 B apart, no bank conflicts
+    float4 *xmine = reinterpret_cast<float4 *>(s_x) + (size_t)(pw * kNS + hs) * 64 + lane;
+    const float4 *xslice = reinterpret_cast<const float4 *>(s_x) + (size_t)(pw * kNS) * 64 + lane;
+    // this warp's q fragments (its share of the head dim, hi and lo terms) stay in registers
+    __syncthreads();
+    uint32_t qh[kKSteps][4], ql[kKSteps][4];
+#pragma unroll
+    for (int k8 = 0; k8 < kKSteps; k8++) {
+        const uint32_t qoff = swz_row512(lr + (lm & 1) * 8, 2 * (hs * kKSteps + k8) + (lm >> 1));
+        ldmatrix_x4(qh[k8][0], qh[k8][1], qh[k8][2], qh[k8][3], s_qhi + qoff);
+        ldmatrix_x4(ql[k8][0], ql[k8][1], ql[k8][2], ql[k8][3], s_qlo + qoff);
+    }
     for (int t = 0; t < ntiles; t++) {
         cp_async_wait<1>();
         __syncthreads();  // tile t landed for everyone; everyone is done with tile t-1 (and with q)
         issue(t + 2);
 
         const int gpage = (slot_begin + t) * kv.shard_count + kv.shard_rank;
-        const int p0 = gpage * kPage + warp * 16;  // first row of this warp's 16
-        if (p0 >= L) continue;
+        const int p0 = gpage * kPage + pw * 16;  // first row of this slice's 16
+        if (p0 >= L) continue;                   // the whole slice skips together
         const uint32_t sk = s_kv + (uint32_t)(t % kStages) * 2 * kTileBytes;
         const uint32_t sv = sk + kTileBytes;
 
-        // S = Q K^T for 16 heads x 16 rows
+        // partial S = Q K^T over this warp's dims; hi and lo terms in separate accumulators
+        float sh[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        float sl[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+        for (int k8 = 0; k8 < kKSteps; k8++) {
+            const int kk = hs * kKSteps + k8;
+            uint32_t b[4];
+            ldmatrix_x4(b[0], b[1], b[2], b[3], sk + swz_row512(pw * 16 + (lm >> 1) * 8 + lr, 2 * kk + (lm & 1)));
+            mma_bf16(sh[0], qh[k8][0], qh[k8][1], qh[k8][2], qh[k8][3], b[0], b[1]);
+            mma_bf16(sh[1], qh[k8][0], qh[k8][1], qh[k8][2], qh[k8][3], b[2], b[3]);
+            mma_bf16(sl[0], ql[k8][0], ql[k8][1], ql[k8][2], ql[k8][3], b[0], b[1]);
+            mma_bf16(sl[1], ql[k8][0], ql[k8][1], ql[k8][2], ql[k8][3], b[2], b[3]);
+        }
+        // exchange: every warp of the slice sums the kNS partials in the same order
+        xmine[0] = make_float4(sh[0][0] + sl[0][0], sh[0][1] + sl[0][1], sh[0][2] + sl[0][2], sh[0][3] + sl[0][3]);
+        xmine[32] = make_float4(sh[1][0] + sl[1][0], sh[1][1] + sl[1][1], sh[1][2] + sl[1][2], sh[1][3] + sl[1][3]);
+        named_barrier(1 + pw, 32 * kNS);
         float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
-        for (int kk = 0; kk < kD / 16; kk++) {
-            uint32_t ah[4], al[4], b[4];
-            const uint32_t qoff = swz_row512(lr + (lm & 1) * 8, 2 * kk + (lm >> 1));
-            ldmatrix_x4(ah[0], ah[1], ah[2], ah[3], s_qhi + qoff);
-            ldmatrix_x4(al[0], al[1], al[2], al[3], s_qlo + qoff);
-            ldmatrix_x4(b[0], b[1], b[2], b[3], sk + swz_row512(warp * 16 + (lm >> 1) * 8 + lr, 2 * kk + (lm & 1)));
-            mma_bf16(s[0], ah[0], ah[1], ah[2], ah[3], b[0], b[1]);
-            mma_bf16(s[1], ah[0], ah[1], ah[2], ah[3], b[2], b[3]);
-            mma_bf16(s[0], al[0], al[1], al[2], al[3], b[0], b[1]);
-            mma_bf16(s[1], al[0], al[1], al[2], al[3], b[2], b[3]);
+        for (int j = 0; j < kNS; j++) {
+            const float4 a = xslice[j * 64];
+            const float4 c = xslice[j * 64 + 32];
+            s[0][0] += a.x; s[0][1] += a.y; s[0][2] += a.z; s[0][3] += a.w;
+            s[1][0] += c.x; s[1][1] += c.y; s[1][2] += c.z; s[1][3] += c.w;
         }
         // mask rows beyond the sequence
         if (p0 + 16 > L) {
@@ -196,7 +236,7 @@ attn_decode_kernel(KvView kv, RopeParams rope, TokSpec toks, int H, const float 
                 l_sum[r] *= corr[r];
             }
 #pragma unroll
-            for (int i = 0; i < 32; i++) {
+            for (int i = 0; i < 2 * kNChunks; i++) {
                 o[i][0] *= corr[0]; o[i][1] *= corr[0];
                 o[i][2] *= corr[1]; o[i][3] *= corr[1];
             }
@@ -219,21 +259,22 @@ attn_decode_kernel(KvView kv, RopeParams rope, TokSpec toks, int H, const float 
             split_pack_bf16(p[1][0], p[1][1], ph[2], pl[2]);
             split_pack_bf16(p[1][2], p[1][3], ph[3], pl[3]);
         }
-        // O += P V
+        // O += P V on this warp's output dims
 #pragma unroll
-        for (int nn = 0; nn < kD / 16; nn++) {
+        for (int n8 = 0; n8 < kNChunks; n8++) {
+            const int nn = hs * kNChunks + n8;
             uint32_t b[4];
-            ldmatrix_x4_trans(b[0], b[1], b[2], b[3], sv + swz_row512(warp * 16 + (lm & 1) * 8 + lr, 2 * nn + (lm >> 1)));
-            mma_bf16(o[2 * nn], ph[0], ph[1], ph[2], ph[3], b[0], b[1]);
-            mma_bf16(o[2 * nn + 1], ph[0], ph[1], ph[2], ph[3], b[2], b[3]);
-            mma_bf16(o[2 * nn], pl[0], pl[1], pl[2], pl[3], b[0], b[1]);
-            mma_bf16(o[2 * nn + 1], pl[0], pl[1], pl[2], pl[3], b[2], b[3]);
+            ldmatrix_x4_trans(b[0], b[1], b[2], b[3], sv + swz_row512(pw * 16 + (lm & 1) * 8 + lr, 2 * nn + (lm >> 1)));
+            mma_bf16(o[2 * n8], ph[0], ph[1], ph[2], ph[3], b[0], b[1]);
+            mma_bf16(o[2 * n8 + 1], ph[0], ph[1], ph[2], ph[3], b[2], b[3]);
+            mma_bf16(o[2 * n8], pl[0], pl[1], pl[2], pl[3], b[0], b[1]);
+            mma_bf16(o[2 * n8 + 1], pl[0], pl[1], pl[2], pl[3], b[2], b[3]);
         }
     }
     cp_async_wait<0>();
     __syncthreads();
 
-    // ---- merge the four warps through shared memory (the ring is free now) ----
+    // ---- merge the four row-slices through shared memory (the ring is free now) ----
 #pragma unroll
     for (int r = 0; r < 2; r++) {
         l_sum[r] += __shfl_xor_sync(0xffffffffu, l_sum[r], 1);
@@ -243,21 +284,21 @@ attn_decode_kernel(KvView kv, RopeParams rope, TokSpec toks, int H, const float 
     float *s_ml = reinterpret_cast<float *>(kv_raw + 4 * 16 * kD * 4);  // [4][16][2]
     {
         const int g = lane >> 2, tq = lane & 3;
-        if (tq == 0) {
-            s_ml[(warp * 16 + g) * 2 + 0] = m_ref[0];
-            s_ml[(warp * 16 + g) * 2 + 1] = l_sum[0];
-            s_ml[(warp * 16 + g + 8) * 2 + 0] = m_ref[1];
-            s_ml[(warp * 16 + g + 8) * 2 + 1] = l_sum[1];
+        if (tq == 0 && hs == 0) {
+            s_ml[(pw * 16 + g) * 2 + 0] = m_ref[0];
+            s_ml[(pw * 16 + g) * 2 + 1] = l_sum[0];
+            s_ml[(pw * 16 + g + 8) * 2 + 0] = m_ref[1];
+            s_ml[(pw * 16 + g + 8) * 2 + 1] = l_sum[1];
         }
-        float *wo = s_o + (size_t)warp * 16 * kD;
+        float *wo = s_o + (size_t)pw * 16 * kD + hs * (kD / kNS);
 #pragma unroll
-        for (int i = 0; i < 32; i++) {
+        for (int i = 0; i < 2 * kNChunks; i++) {
             *reinterpret_cast<float2 *>(wo + g * kD + i * 8 + 2 * tq) = make_float2(o[i][0], o[i][1]);
             *reinterpret_cast<float2 *>(wo + (g + 8) * kD + i * 8 + 2 * tq) = make_float2(o[i][2], o[i][3]);
         }
     }
     __syncthreads();
-    for (int r = warp; r < group; r += 4) {
+    for (int r = warp; r < group; r += kDecWarps) {
         float mw[4], M = kNegBig;
 #pragma unroll
         for (int w = 0; w < 4; w++) {

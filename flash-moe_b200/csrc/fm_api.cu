@@ -193,6 +193,7 @@ extern "C" void fm_destroy(FmCtx *ctx) {
     cudaFree(ctx->pool); cudaFree(ctx->d_page_table); cudaFree(ctx->d_conv_state); cudaFree(ctx->d_ssm_state);
     cudaFree(ctx->d_part_o); cudaFree(ctx->d_part_ml); cudaFree(ctx->d_pf_o); cudaFree(ctx->d_pf_ml); cudaFree(ctx->d_work);
     cudaFree(ctx->d_stage);
+    for (cudaEvent_t e : ctx->prof_ev) cudaEventDestroy(e);
     if (ctx->h_stage) cudaFreeHost(ctx->h_stage);
     delete ctx;
 }
@@ -216,6 +217,49 @@ extern "C" fm_status fm_synchronize(FmCtx *ctx) {
     return FM_OK;
 }
 extern "C" int64_t fm_launch_count(const FmCtx *ctx) { return ctx ? ctx->launches : 0; }
+
+// ---- event bracketing of the dominant kernels --------------------------------------------------
+struct ProfScope {
+    FmCtx *ctx;
+    cudaEvent_t stop = nullptr;
+    explicit ProfScope(FmCtx *c) : ctx(c) {
+        if (!c->prof_on) return;
+        if (c->prof_used + 2 > c->prof_ev.size()) {
+            cudaEvent_t a, b;
+            if (c->prof_ev.size() >= 1 << 16 || cudaEventCreate(&a) != cudaSuccess) return;
+            if (cudaEventCreate(&b) != cudaSuccess) { cudaEventDestroy(a); return; }
+            c->prof_ev.push_back(a);
+            c->prof_ev.push_back(b);
+        }
+        cudaEventRecord(c->prof_ev[c->prof_used], c->stream);
+        stop = c->prof_ev[c->prof_used + 1];
+        c->prof_used += 2;
+    }
+    ~ProfScope() {
+        if (stop) cudaEventRecord(stop, ctx->stream);
+    }
+};
+
+extern "C" fm_status fm_profile_enable(FmCtx *ctx, int on) {
+    if (!ctx) return FM_ERR_INVALID;
+    ctx->prof_on = on != 0;
+    return FM_OK;
+}
+
+extern "C" fm_status fm_profile_read(FmCtx *ctx, int *launches, double *total_ms) {
+    if (!ctx || !launches || !total_ms) return FM_ERR_INVALID;
+    FM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    double tot = 0.0;
+    for (size_t i = 0; i + 1 < ctx->prof_used; i += 2) {
+        float ms = 0.f;
+        FM_CUDA(ctx, cudaEventElapsedTime(&ms, ctx->prof_ev[i], ctx->prof_ev[i + 1]));
+        tot += ms;
+    }
+    *launches = (int)(ctx->prof_used / 2);
+    *total_ms = tot;
+    ctx->prof_used = 0;
+    return FM_OK;
+}
 
 // ---- KV bookkeeping ---------------------------------------------------------------------------
 static inline size_t lidx(const FmCtx *ctx, int layer, int seq) { return (size_t)layer * ctx->cfg.max_seqs + seq; }
@@ -414,10 +458,13 @@ extern "C" fm_status fm_kv_append_rope(FmCtx *ctx, int fa_idx, const int *seq, c
     return FM_OK;
 }
 
+// Splits per (KV head, sequence): one CTA per SM is resident (shared memory), so the grid should be
+// as close to the SM count as possible without exceeding it -- a few CTAs over would run as a
+// second, nearly empty wave.
 static int pick_splits(const FmCtx *ctx, int batch, int max_len) {
     const FmConfig &c = ctx->cfg;
-    const int per_tok = c.num_kv_heads;
-    int want = (ctx->sm_count + per_tok * batch - 1) / (per_tok * batch);
+    const int units = c.num_kv_heads * batch;
+    int want = std::max(1, ctx->sm_count / units);
     const int gpages = (max_len + c.page_size - 1) / c.page_size;
     const int slots = (gpages + c.seq_shard_count - 1) / c.seq_shard_count;
     want = std::min(want, std::max(1, slots));
@@ -456,7 +503,11 @@ static fm_status decode_core(FmCtx *ctx, int fa_idx, const int *seq, const int *
         const int ns = pick_splits(ctx, t.n, max_len);
         const float *qp = q_proj_out ? q_proj_out + (size_t)i0 * H * 2 * D : nullptr;
         const float *qq = q ? q + (size_t)i0 * H * D : nullptr;
-        fm_status st = launched(ctx, launch_attn_decode(kv, ctx->rope, t, H, qp, qq, qnw, c.rms_norm_eps, ctx->d_part_o, ctx->d_part_ml, ns, ctx->stream), "attn_decode");
+        fm_status st;
+        {
+            ProfScope prof(ctx);
+            st = launched(ctx, launch_attn_decode(kv, ctx->rope, t, H, qp, qq, qnw, c.rms_norm_eps, ctx->d_part_o, ctx->d_part_ml, ns, ctx->stream), "attn_decode");
+        }
         if (st) return st;
         const float *gp = gate ? gate + (size_t)i0 * H * D : nullptr;
         float *op = (out ? out : o_part) + (size_t)i0 * H * D;
@@ -583,8 +634,11 @@ extern "C" fm_status fm_attn_prefill(FmCtx *ctx, int fa_idx, int seq, int start_
     t.mode = 1; t.n = n; t.seq0 = seq; t.pos0 = start_pos; t.row0 = row0;
     st = launched(ctx, launch_kv_append(kv, ctx->rope, t, d_k, d_v, d_kn, c.rms_norm_eps, ctx->stream), "kv_append");
     if (st) return st;
-    st = launched(ctx, launch_attn_prefill(kv, ctx->rope, seq, start_pos, row0, n, c.num_attn_heads, d_qp, d_q, d_g, d_qn,
-                                           c.rms_norm_eps, ctx->d_pf_o, ctx->d_pf_ml, d_out, ctx->stream), "attn_prefill");
+    {
+        ProfScope prof(ctx);
+        st = launched(ctx, launch_attn_prefill(kv, ctx->rope, seq, start_pos, row0, n, c.num_attn_heads, d_qp, d_q, d_g, d_qn,
+                                               c.rms_norm_eps, ctx->d_pf_o, ctx->d_pf_ml, d_out, ctx->stream), "attn_prefill");
+    }
     if (st) return st;
     FM_CUDA(ctx, sg.pull(out, w_out, n * qd));
     return FM_OK;
@@ -632,6 +686,7 @@ extern "C" fm_status fm_gdn_decode(FmCtx *ctx, int li, const int *seq, int batch
             t.pos[i] = ctx->gdn_steps[lidx(ctx, li, seq[i0 + i])]++;
             t.row[i] = 0;
         }
+        ProfScope prof(ctx);
         st = launched(ctx, launch_gdn_decode(g, t, ctx->d_conv_state + (size_t)li * c.max_seqs * cn, ctx->d_ssm_state + (size_t)li * c.max_seqs * sn,
                                              (long long)cn, (long long)sn, d_qkv + (size_t)i0 * ctx->conv_dim, d_z + i0 * vd, d_b + i0 * hv,
                                              d_a + i0 * hv, d_cw, d_al, d_db, d_nw, d_out + i0 * vd, ctx->stream), "gdn_decode");
@@ -668,8 +723,12 @@ extern "C" fm_status fm_gdn_prefill(FmCtx *ctx, int li, int seq, int n, int chun
     const size_t cn = (size_t)c.conv_kernel_size * ctx->conv_dim, sn = vd * c.linear_key_dim;
     GdnDims g = gdn_dims(ctx);
     const int step0 = ctx->gdn_steps[lidx(ctx, li, seq)];
-    fm_status st = launched(ctx, launch_gdn_prefill(g, n, chunk, step0, ctx->d_conv_state + lidx(ctx, li, seq) * cn, ctx->d_ssm_state + lidx(ctx, li, seq) * sn,
+    fm_status st;
+    {
+        ProfScope prof(ctx);
+        st = launched(ctx, launch_gdn_prefill(g, n, chunk, step0, ctx->d_conv_state + lidx(ctx, li, seq) * cn, ctx->d_ssm_state + lidx(ctx, li, seq) * sn,
                                                     d_qkv, d_z, d_b, d_a, d_cw, d_al, d_db, d_nw, d_out, ctx->d_work, ctx->work_bytes, ctx->stream), "gdn_prefill");
+    }
     if (st) return st;
     ctx->gdn_steps[lidx(ctx, li, seq)] = step0 + n;
     FM_CUDA(ctx, sg.pull(out, w_out, n * vd));

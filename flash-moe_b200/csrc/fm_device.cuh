@@ -54,13 +54,14 @@ __device__ __forceinline__ void split_bf16(float x, __nv_bfloat16 &hi, __nv_bflo
     hi = __float2bfloat16_rn(x);
     lo = __float2bfloat16_rn(x - __bfloat162float(hi));
 }
+// Packed pair version: hi = x truncated to bf16 (a byte permute, exact), lo = bf16(x - hi).
+// x - hi is exact in fp32, so hi + lo carries 16 mantissa bits whichever way hi was rounded.
 __device__ __forceinline__ void split_pack_bf16(float x0, float x1, uint32_t &hi, uint32_t &lo) {
-    __nv_bfloat16 h0, l0, h1, l1;
-    split_bf16(x0, h0, l0);
-    split_bf16(x1, h1, l1);
-    __nv_bfloat162 h = __halves2bfloat162(h0, h1), l = __halves2bfloat162(l0, l1);
-    hi = *reinterpret_cast<uint32_t *>(&h);
-    lo = *reinterpret_cast<uint32_t *>(&l);
+    const uint32_t u0 = __float_as_uint(x0), u1 = __float_as_uint(x1);
+    hi = __byte_perm(u0, u1, 0x7632);  // {x1[31:16], x0[31:16]}
+    const float r0 = x0 - __uint_as_float(u0 & 0xffff0000u);
+    const float r1 = x1 - __uint_as_float(u1 & 0xffff0000u);
+    lo = pack_bf16(r0, r1);
 }
 
 __device__ __forceinline__ float fast_exp2(float x) {

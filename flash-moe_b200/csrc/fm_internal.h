@@ -90,6 +90,11 @@ struct FmCtx {
     void *d_work = nullptr;             // chunked GatedDeltaNet workspace
     size_t work_bytes = 0;
 
+    // optional event bracketing of the dominant kernels
+    bool prof_on = false;
+    std::vector<cudaEvent_t> prof_ev;  // pairs (start, stop)
+    size_t prof_used = 0;
+
     // host-pointer mode staging
     char *h_stage = nullptr;  // pinned
     char *d_stage = nullptr;

@@ -191,6 +191,14 @@ fm_status fm_state_import(FmCtx *ctx, int li, int seq, const float *conv, const 
 /* Number of kernels this context has launched since creation (bench bookkeeping). */
 int64_t fm_launch_count(const FmCtx *ctx);
 
+/* Device timing of the dominant kernel of each entry point (the split-KV decode kernel, the prefill
+ * attention kernel, the GatedDeltaNet kernels): while enabled, every launch of those kernels is
+ * bracketed by CUDA events on the context's stream.  fm_profile_read waits for the stream, returns
+ * the number of bracketed launches and their summed duration in milliseconds, and clears the
+ * record.  Replaces the reference's --timing accumulators (metal_infer/timing.h:9-39,257-296). */
+fm_status fm_profile_enable(FmCtx *ctx, int on);
+fm_status fm_profile_read(FmCtx *ctx, int *launches, double *total_ms);
+
 #ifdef __cplusplus
 }
 #endif
