@@ -22,6 +22,7 @@ EXPORTS = [
     "fm_attn_decode", "fm_attn_decode_partial", "fm_attn_merge_gate", "fm_attn_prefill",
     "fm_gdn_decode", "fm_gdn_prefill", "fm_kv_export", "fm_kv_import", "fm_state_export",
     "fm_state_import", "fm_launch_count", "fm_profile_enable", "fm_profile_read",
+    "fm_attn_decode_static",
 ]
 
 
@@ -37,6 +38,17 @@ class FmConfig(C.Structure):
         ("max_seqs", C.c_int), ("max_seq_len", C.c_int), ("page_size", C.c_int),
         ("kv_pool_pages", C.c_int64), ("max_batch_tokens", C.c_int),
         ("seq_shard_rank", C.c_int), ("seq_shard_count", C.c_int), ("device", C.c_int),
+    ]
+
+
+class FmStaticDecodeArgs(C.Structure):
+    _fields_ = [
+        ("kv_pages", C.c_void_p), ("page_table", C.c_void_p), ("max_pages_per_seq", C.c_int),
+        ("kv_len", C.POINTER(C.c_int)), ("pos", C.POINTER(C.c_int)), ("batch", C.c_int),
+        ("num_attn_heads", C.c_int), ("num_kv_heads", C.c_int), ("rotary_dim", C.c_int),
+        ("rope_theta", C.c_float), ("rms_norm_eps", C.c_float),
+        ("q_proj_out", C.c_void_p), ("q", C.c_void_p), ("gate", C.c_void_p),
+        ("q_norm_w", C.c_void_p), ("out", C.c_void_p), ("stream", C.c_void_p),
     ]
 
 
@@ -208,3 +220,20 @@ class Context:
 
     def state_import(self, li, seq, conv, ssm):
         self._check(self.lib.fm_state_import(self.h, C.c_int(li), C.c_int(seq), _ptr(conv), _ptr(ssm)))
+
+
+def attn_decode_static(kv_pages, page_table, max_pages_per_seq, kv_len, pos, out, q_proj_out=None, q=None,
+                       gate=None, q_norm_w=None, num_attn_heads=32, num_kv_heads=2, rotary_dim=64,
+                       rope_theta=1e7, rms_norm_eps=1e-6, stream=0):
+    """fm_attn_decode_static: the decode step for callers that may not allocate device memory (no
+    context; the caller passes the KV pages and page table as device tensors).  Raises FmError."""
+    lib = load_library()
+    ln, lnp = _ints(kv_len); ps, psp = _ints(pos)
+    p = lambda t: None if t is None else t.data_ptr()
+    args = FmStaticDecodeArgs(p(kv_pages), p(page_table), max_pages_per_seq, lnp, psp, len(ln),
+                              num_attn_heads, num_kv_heads, rotary_dim, rope_theta, rms_norm_eps,
+                              p(q_proj_out), p(q), p(gate), p(q_norm_w), p(out), stream)
+    err = C.create_string_buffer(256)
+    st = lib.fm_attn_decode_static(C.byref(args), err, C.c_size_t(256))
+    if st != FM_OK:
+        raise FmError(st, err.value.decode())

@@ -199,6 +199,47 @@ int64_t fm_launch_count(const FmCtx *ctx);
 fm_status fm_profile_enable(FmCtx *ctx, int on);
 fm_status fm_profile_read(FmCtx *ctx, int *launches, double *total_ms);
 
+/* Decode attention without any allocation -- no counterpart in the reference.
+ *
+ * For callers that are not allowed to allocate device memory and therefore cannot use fm_create:
+ * a plugin living inside another engine's fixed memory plan, a serving loop that bans allocator
+ * calls once it is running, code under a tool that intercepts allocation.  The caller owns
+ * everything it passes in: the KV pages, the page table, q / gate and the output.  The scratch the
+ * split-KV kernels need (the per-split partial results) is a fixed array inside the library image,
+ * 8192 partial rows (8.45 MB), resident on every GPU that loads the library until process exit.
+ *
+ *   kv_pages    device, bf16; page p = [2 (K then V)][num_kv_heads][64 rows][256 dims]; K rows are
+ *               already normalised and rotated (what fm_kv_append_rope stores)
+ *   page_table  device, int [batch][max_pages_per_seq]; row r of sequence i lives in page
+ *               page_table[i][r / 64] at row r % 64
+ *   kv_len, pos HOST, int [batch]: rows to attend (>= 1) and the RoPE position of q
+ *   q_proj_out  device, [batch][H][512] interleaved q | gate; or q and gate, [batch][H*256]
+ *   out         device, [batch][H*256]
+ *
+ * Computes softmax(rope(norm(q)) K^T / 16) V * sigmoid(gate) like fm_attn_decode with k == NULL
+ * (nothing is appended).  Limits: batch <= 64; batch * num_attn_heads <= 8192 (FM_ERR_CAPACITY
+ * otherwise; the number of splits shrinks first so that batch * heads * splits fits).  Calls no
+ * cudaMalloc / cudaFree or other allocating routine.  The first call on each device resolves the
+ * scratch address (cudaGetSymbolAddress) with that device current: make that call before any
+ * stream capture.  Every call on a device shares the one scratch array: each call overwrites the
+ * rows it uses, nothing needs clearing, but two calls that overlap on the GPU (different streams)
+ * race on it -- serialise them.  Error text, if any, is written to err (may be NULL). */
+typedef struct FmStaticDecodeArgs {
+    const void *kv_pages;
+    const int *page_table;
+    int max_pages_per_seq;
+    const int *kv_len;
+    const int *pos;
+    int batch;
+    int num_attn_heads, num_kv_heads, rotary_dim;
+    float rope_theta, rms_norm_eps;
+    const float *q_proj_out, *q, *gate;
+    const uint16_t *q_norm_w;
+    float *out;
+    void *stream;
+} FmStaticDecodeArgs;
+fm_status fm_attn_decode_static(const FmStaticDecodeArgs *args, char *err, size_t err_cap);
+
 #ifdef __cplusplus
 }
 #endif
