@@ -1,28 +1,449 @@
-// GatedDeltaNet over a run of n tokens of one sequence.
+// GatedDeltaNet over a run of n tokens of one sequence, in chunked (WY / UT-transform) form.
+//
+// The recurrence of metal_infer/layer_forward.h:967-1009, per value head and token t,
+//     S <- g_t S ;  d_t = beta_t (v_t - S k_t) ;  S <- S + d_t k_t^T ;  o_t = S q_t ,
+// is evaluated 64 tokens at a time.  With c_t the running sum of ln g inside a chunk,
+// A[t][i] = beta_t e^{c_t-c_i} (k_t . k_i) for i < t and T = (I + A)^-1 (unit lower triangular):
+//     U = T diag(beta) V ,   W = T diag(beta e^{c}) K                       (independent of S)
+//     D = U - W S0^T ,       O = diag(e^{c}) Q S0^T + (M o Q K^T) D ,  M[t][i] = e^{c_t-c_i}, i <= t
+//     S1 = e^{c_C} S0 + D^T diag(e^{c_C-c}) K .
+// The reference has no such form (its batched kernel walks the tokens one by one,
+// metal_infer/shaders.metal:2763-2815); results are checked against sequential CPU steps.
+//
+// Launch sequence:
+//   gdn_prep_kernel    per token   : conv + SiLU, q/k normalisation, ln(decay), beta  -> workspace
+//   gdn_ring_kernel                : last three raw inputs -> conv history ring
+//   gdn_chunk_kernel   per (head, chunk), all chunks in parallel: K K^T, Q K^T, T, U, W -> workspace
+//   gdn_scan_kernel    per (head, 32-row slice of the state), chunks in sequence: D, O, S
+//   gdn_norm_kernel    per (token, head): gated RMS-norm in place
+// Contractions run on tensor cores as split tf32 (m16n8k8, two terms per operand, fp32 accumulate);
+// the triangular solve, the decay exponentials and the state stay fp32.
+#include "fm_device.cuh"
 #include "fm_internal.h"
 
 namespace fm {
 
-size_t gdn_prefill_work_bytes(const GdnDims &, int, int) { return 0; }
+constexpr int kC = 64;    // chunk length
+constexpr int kDH = 128;  // dk = dv
 
-// Token-by-token version: one fused decode launch per token (same arithmetic as n decode steps).
+__device__ __forceinline__ uint32_t to_tf32(float x) {
+    uint32_t r;
+    asm volatile("cvt.rna.tf32.f32 %0, %1;\n" : "=r"(r) : "f"(x));
+    return r;
+}
+__device__ __forceinline__ void mma_tf32(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// acc[16 x 8*NT] += A[16 x K] B[K x 8*NT] for one warp; fa(m, k) and fb(k, n) fetch operands.
+// Each operand is split into two tf32 terms (x = hi + lo) and the product taken as
+// lo*hi + hi*lo + hi*hi ("3xTF32"): plain tf32 (10 mantissa bits) left the state 5e-3 off the
+// sequential fp32 recurrence, this keeps ~21 bits.
+__device__ __forceinline__ void split_tf32(float x, uint32_t &hi, uint32_t &lo) {
+    hi = to_tf32(x);
+    lo = to_tf32(x - __uint_as_float(hi));
+}
+template <int NT, class FA, class FB>
+__device__ __forceinline__ void warp_gemm_tf32(float (&acc)[NT][4], int K, FA fa, FB fb, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    for (int k0 = 0; k0 < K; k0 += 8) {
+        uint32_t ah[4], al[4];
+        split_tf32(fa(g, k0 + t), ah[0], al[0]);
+        split_tf32(fa(g + 8, k0 + t), ah[1], al[1]);
+        split_tf32(fa(g, k0 + t + 4), ah[2], al[2]);
+        split_tf32(fa(g + 8, k0 + t + 4), ah[3], al[3]);
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+            uint32_t bh0, bl0, bh1, bl1;
+            split_tf32(fb(k0 + t, nt * 8 + g), bh0, bl0);
+            split_tf32(fb(k0 + t + 4, nt * 8 + g), bh1, bl1);
+            mma_tf32(acc[nt], al[0], al[1], al[2], al[3], bh0, bh1);
+            mma_tf32(acc[nt], ah[0], ah[1], ah[2], ah[3], bl0, bl1);
+            mma_tf32(acc[nt], ah[0], ah[1], ah[2], ah[3], bh0, bh1);
+        }
+    }
+}
+
+struct GdnWork {  // workspace carved by the host
+    float *qn, *kn, *vn;  // [n][Hk*128], [n][Hk*128], [n][Hv*128]
+    float *lg, *bt;       // [n][Hv]  ln(decay), beta
+    float *U, *W;         // [Hv][nchunks][64][128]
+    float *QK;            // [Hv][nchunks][64][64]
+    float *cv;            // [Hv][nchunks][64]  inclusive running sum of ln(decay)
+};
+
+// ---- per token: conv + SiLU, q/k normalisation, decay, beta ------------------------------------
+// grid (n), 512 threads
+__global__ void __launch_bounds__(512)
+gdn_prep_kernel(GdnDims g, int n, int step0, const float *__restrict__ ring, const float *__restrict__ qkv,
+                const float *__restrict__ beta, const float *__restrict__ alpha,
+                const uint16_t *__restrict__ conv_w, const float *__restrict__ A_log,
+                const uint16_t *__restrict__ dt_bias, GdnWork w) {
+    extern __shared__ float s_c[];  // conv output, [conv_dim]
+    const int t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int C = g.conv_dim, total_k = g.Hk * kDH;
+    for (int ch = tid; ch < C; ch += blockDim.x) {
+        float acc = 0.f;
+        if (conv_w != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 3; j++) {
+                const int tt = t - 3 + j;  // token inside this run, or history before it
+                float h;
+                if (tt >= 0)
+                    h = qkv[(size_t)tt * C + ch];
+                else {
+                    const int tokidx = step0 + tt;
+                    h = tokidx >= 0 ? ring[(size_t)(tokidx & 3) * C + ch] : 0.f;
+                }
+                acc += h * bf16_bits_to_float(conv_w[ch * 4 + j]);
+            }
+            acc += qkv[(size_t)t * C + ch] * bf16_bits_to_float(conv_w[ch * 4 + 3]);
+            acc = acc / (1.0f + expf(-acc));
+        }
+        s_c[ch] = acc;
+    }
+    __syncthreads();
+    // q and k heads: one warp per head, 4 channels per lane
+    const float inv_scale = 1.0f / sqrtf((float)kDH);
+    for (int hh = warp; hh < 2 * g.Hk; hh += blockDim.x / 32) {
+        const bool is_q = hh < g.Hk;
+        const float *src = s_c + (size_t)hh * kDH;  // q heads then k heads are contiguous in conv_out
+        const float4 x = *reinterpret_cast<const float4 *>(src + lane * 4);
+        const float ss = warp_sum(x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w);
+        const float inv = 1.0f / sqrtf(ss / kDH + 1e-6f);
+        const float mul = is_q ? inv_scale * inv_scale : inv_scale;
+        float4 y = make_float4(x.x * inv * mul, x.y * inv * mul, x.z * inv * mul, x.w * inv * mul);
+        float *dst = (is_q ? w.qn : w.kn) + (size_t)t * total_k + (size_t)(is_q ? hh : hh - g.Hk) * kDH;
+        *reinterpret_cast<float4 *>(dst + lane * 4) = y;
+    }
+    const int total_v = g.Hv * kDH;
+    for (int i = tid * 4; i < total_v; i += blockDim.x * 4)
+        *reinterpret_cast<float4 *>(w.vn + (size_t)t * total_v + i) = *reinterpret_cast<const float4 *>(s_c + 2 * total_k + i);
+    for (int vh = tid; vh < g.Hv; vh += blockDim.x) {
+        const float bias = dt_bias ? bf16_bits_to_float(dt_bias[vh]) : 0.f;
+        const float A = A_log ? expf(A_log[vh]) : 1.0f;
+        const float sp = logf(1.0f + expf(alpha[(size_t)t * g.Hv + vh] + bias));
+        w.lg[(size_t)t * g.Hv + vh] = -A * sp;  // ln of the decay
+        w.bt[(size_t)t * g.Hv + vh] = 1.0f / (1.0f + expf(-beta[(size_t)t * g.Hv + vh]));
+    }
+}
+
+// raw inputs of the last min(n, 3) tokens -> ring slots (token count & 3)
+__global__ void gdn_ring_kernel(int C, int n, int step0, float *__restrict__ ring, const float *__restrict__ qkv) {
+    const int first = n > 3 ? n - 3 : 0;
+    for (int t = first + blockIdx.y; t < n; t += gridDim.y)
+        for (int ch = blockIdx.x * blockDim.x + threadIdx.x; ch < C; ch += gridDim.x * blockDim.x)
+            ring[(size_t)((step0 + t) & 3) * C + ch] = qkv[(size_t)t * C + ch];
+}
+
+// ---- per (head, chunk): everything that does not depend on the state ---------------------------
+constexpr int kLdK = kDH + 4;   // [row][k] operands read as (row g, k t): stride = 4 mod 32
+constexpr int kLdT = kC + 4;
+constexpr int kChunkSmem = (3 * kC * kLdK + 2 * kC * kLdT + 2 * kC) * 4;
+
+// grid (nchunks, Hv), 256 threads
+__global__ void __launch_bounds__(256, 1)
+gdn_chunk_kernel(GdnDims g, int n, GdnWork w, int nchunks) {
+    extern __shared__ __align__(16) float sm[];
+    float *sK = sm, *sQ = sK + kC * kLdK, *sV = sQ + kC * kLdK;
+    float *sA = sV + kC * kLdK, *sT = sA + kC * kLdT;
+    float *sc = sT + kC * kLdT, *sb = sc + kC;
+    const int chunk = blockIdx.x, vh = blockIdx.y, kh = vh / (g.Hv / g.Hk);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int t0 = chunk * kC;
+    const int total_k = g.Hk * kDH, total_v = g.Hv * kDH;
+
+    // rows past the end of the run are zero (beta 0, decay 1: they leave the state alone)
+    for (int i = tid; i < kC * (kDH / 4); i += 256) {
+        const int r = i >> 5, c4 = (i & 31) * 4;
+        float4 k4 = make_float4(0.f, 0.f, 0.f, 0.f), q4 = k4, v4 = k4;
+        if (t0 + r < n) {
+            k4 = *reinterpret_cast<const float4 *>(w.kn + (size_t)(t0 + r) * total_k + (size_t)kh * kDH + c4);
+            q4 = *reinterpret_cast<const float4 *>(w.qn + (size_t)(t0 + r) * total_k + (size_t)kh * kDH + c4);
+            v4 = *reinterpret_cast<const float4 *>(w.vn + (size_t)(t0 + r) * total_v + (size_t)vh * kDH + c4);
+        }
+        *reinterpret_cast<float4 *>(sK + r * kLdK + c4) = k4;
+        *reinterpret_cast<float4 *>(sQ + r * kLdK + c4) = q4;
+        *reinterpret_cast<float4 *>(sV + r * kLdK + c4) = v4;
+    }
+    if (warp == 0) {  // inclusive scan of ln(decay) over the 64 rows, two per lane
+        float a = (t0 + lane < n) ? w.lg[(size_t)(t0 + lane) * g.Hv + vh] : 0.f;
+        float b = (t0 + 32 + lane < n) ? w.lg[(size_t)(t0 + 32 + lane) * g.Hv + vh] : 0.f;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const float ua = __shfl_up_sync(0xffffffffu, a, o), ub = __shfl_up_sync(0xffffffffu, b, o);
+            if (lane >= o) { a += ua; b += ub; }
+        }
+        b += __shfl_sync(0xffffffffu, a, 31);
+        sc[lane] = a; sc[32 + lane] = b;
+        sb[lane] = (t0 + lane < n) ? w.bt[(size_t)(t0 + lane) * g.Hv + vh] : 0.f;
+        sb[32 + lane] = (t0 + 32 + lane < n) ? w.bt[(size_t)(t0 + 32 + lane) * g.Hv + vh] : 0.f;
+        float *cv = w.cv + ((size_t)vh * nchunks + chunk) * kC;
+        cv[lane] = a; cv[32 + lane] = b;
+    }
+    __syncthreads();
+
+    // K K^T and Q K^T (64 x 64 x 128): warp = (16-row tile, 32-column half)
+    {
+        const int mt = warp & 3, nh = warp >> 2;
+        float akk[4][4] = {}, aqk[4][4] = {};
+        const float *Ka = sK + (mt * 16) * kLdK, *Qa = sQ + (mt * 16) * kLdK, *Kb = sK + (nh * 32) * kLdK;
+        auto fb = [&](int k, int nn) { return Kb[nn * kLdK + k]; };
+        warp_gemm_tf32<4>(akk, kDH, [&](int m, int k) { return Ka[m * kLdK + k]; }, fb, lane);
+        warp_gemm_tf32<4>(aqk, kDH, [&](int m, int k) { return Qa[m * kLdK + k]; }, fb, lane);
+        float *qk_out = w.QK + ((size_t)vh * nchunks + chunk) * kC * kC;
+        const int gq = lane >> 2, tq = lane & 3;
+#pragma unroll
+        for (int nt = 0; nt < 4; nt++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int r = mt * 16 + gq + (e >> 1) * 8, c = nh * 32 + nt * 8 + 2 * tq + (e & 1);
+                const float dec = c <= r ? expf(sc[r] - sc[c]) : 0.f;
+                sA[r * kLdT + c] = c < r ? sb[r] * dec * akk[nt][e] : 0.f;
+                qk_out[r * kC + c] = dec * aqk[nt][e];
+            }
+    }
+    __syncthreads();
+    // T = (I + A)^-1 by forward substitution; thread j owns column j
+    if (tid < kC) {
+        const int j = tid;
+        for (int r = 0; r < kC; r++) {
+            float acc = r == j ? 1.f : 0.f;
+            for (int i = j; i < r; i++) acc -= sA[r * kLdT + i] * sT[i * kLdT + j];
+            sT[r * kLdT + j] = r >= j ? acc : 0.f;
+        }
+    }
+    // scale rows: V <- beta V, K <- beta e^{c} K
+    for (int i = tid; i < kC * kDH; i += 256) {
+        const int r = i >> 7, c = i & 127;
+        sV[r * kLdK + c] *= sb[r];
+        sK[r * kLdK + c] *= sb[r] * expf(sc[r]);
+    }
+    __syncthreads();
+    // U = T (beta V), W = T (beta e^c K): 64 x 128 x 64, warp = (16-row tile, 64-column half)
+    {
+        const int mt = warp & 3, nh = warp >> 2;
+        float au[8][4] = {}, aw[8][4] = {};
+        const float *Ta = sT + (mt * 16) * kLdT;
+        auto fa = [&](int m, int k) { return Ta[m * kLdT + k]; };
+        // T is lower triangular: rows of this tile only reach columns < 16 (mt + 1)
+        const int kmax = 16 * (mt + 1);
+        warp_gemm_tf32<8>(au, kmax, fa, [&](int k, int nn) { return sV[k * kLdK + nh * 64 + nn]; }, lane);
+        warp_gemm_tf32<8>(aw, kmax, fa, [&](int k, int nn) { return sK[k * kLdK + nh * 64 + nn]; }, lane);
+        float *Uo = w.U + ((size_t)vh * nchunks + chunk) * kC * kDH, *Wo = w.W + ((size_t)vh * nchunks + chunk) * kC * kDH;
+        const int gq = lane >> 2, tq = lane & 3;
+#pragma unroll
+        for (int nt = 0; nt < 8; nt++) {
+            const int c = nh * 64 + nt * 8 + 2 * tq;
+            const int r = mt * 16 + gq;
+            *reinterpret_cast<float2 *>(Uo + r * kDH + c) = make_float2(au[nt][0], au[nt][1]);
+            *reinterpret_cast<float2 *>(Uo + (r + 8) * kDH + c) = make_float2(au[nt][2], au[nt][3]);
+            *reinterpret_cast<float2 *>(Wo + r * kDH + c) = make_float2(aw[nt][0], aw[nt][1]);
+            *reinterpret_cast<float2 *>(Wo + (r + 8) * kDH + c) = make_float2(aw[nt][2], aw[nt][3]);
+        }
+    }
+}
+
+// ---- per (head, 32-row slice of the state): walk the chunks ------------------------------------
+constexpr int kSl = 32;           // state rows (value dims) per CTA
+constexpr int kLdS = kDH + 4;     // S[vi][ki] read as B[n = vi][k = ki]
+constexpr int kLdKs = kDH + 8;    // scaled K read as B[k = i][n = ki]
+constexpr int kLdD = kSl + 8;     // D[i][vi] read as B[k = i][n = vi] and as A[m = vi][k = i]
+constexpr int kScanSmem = (kSl * kLdS + 2 * kC * kLdK + kC * kLdKs + kC * kLdT + kC * kLdD + 2 * kC) * 4;
+
+// grid (128 / kSl, Hv), 128 threads
+__global__ void __launch_bounds__(128, 1)
+gdn_scan_kernel(GdnDims g, int n, GdnWork w, int nchunks, float *__restrict__ ssm, float *__restrict__ out) {
+    extern __shared__ __align__(16) float sm[];
+    float *sS = sm, *sW = sS + kSl * kLdS, *sQ = sW + kC * kLdK, *sKs = sQ + kC * kLdK;
+    float *sQK = sKs + kC * kLdKs, *sD = sQK + kC * kLdT, *sc = sD + kC * kLdD, *se = sc + kC;
+    const int slice = blockIdx.x, vh = blockIdx.y, kh = vh / (g.Hv / g.Hk);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int gq = lane >> 2, tq = lane & 3;
+    const int total_k = g.Hk * kDH, total_v = g.Hv * kDH;
+    float *Sg = ssm + ((size_t)vh * kDH + slice * kSl) * kDH;
+    for (int i = tid; i < kSl * (kDH / 4); i += 128) {
+        const int r = i >> 5, c4 = (i & 31) * 4;
+        *reinterpret_cast<float4 *>(sS + r * kLdS + c4) = *reinterpret_cast<const float4 *>(Sg + (size_t)r * kDH + c4);
+    }
+    for (int chunk = 0; chunk < nchunks; chunk++) {
+        const int t0 = chunk * kC;
+        const size_t hc = (size_t)vh * nchunks + chunk;
+        __syncthreads();  // previous chunk's readers are done with every buffer
+        if (tid < kC) {
+            const float c = w.cv[hc * kC + tid];
+            sc[tid] = c;
+        }
+        {
+            const float *Wg = w.W + hc * kC * kDH, *QKg = w.QK + hc * kC * kC;
+            for (int i = tid; i < kC * (kDH / 4); i += 128) {
+                const int r = i >> 5, c4 = (i & 31) * 4;
+                cp_async16(smem_u32(sW + r * kLdK + c4), Wg + (size_t)r * kDH + c4);
+                if (t0 + r < n) {
+                    cp_async16(smem_u32(sQ + r * kLdK + c4), w.qn + (size_t)(t0 + r) * total_k + (size_t)kh * kDH + c4);
+                    cp_async16(smem_u32(sKs + r * kLdKs + c4), w.kn + (size_t)(t0 + r) * total_k + (size_t)kh * kDH + c4);
+                } else {
+                    *reinterpret_cast<float4 *>(sQ + r * kLdK + c4) = make_float4(0.f, 0.f, 0.f, 0.f);
+                    *reinterpret_cast<float4 *>(sKs + r * kLdKs + c4) = make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+            }
+            for (int i = tid; i < kC * (kC / 4); i += 128) {
+                const int r = i >> 4, c4 = (i & 15) * 4;
+                cp_async16(smem_u32(sQK + r * kLdT + c4), QKg + (size_t)r * kC + c4);
+            }
+            cp_async_commit();
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const float cC = sc[kC - 1];
+        if (tid < kC) se[tid] = expf(cC - sc[tid]);
+        __syncthreads();
+        for (int i = tid; i < kC * kDH; i += 128) {  // K rows scaled for the state update
+            const int r = i >> 7, c = i & 127;
+            sKs[r * kLdKs + c] *= se[r];
+        }
+        // D = U - W S^T and Q S^T: warp = 16 token rows, all 32 state rows of the slice
+        float ad[4][4] = {}, aq[4][4] = {};
+        {
+            const float *Wa = sW + (warp * 16) * kLdK, *Qa = sQ + (warp * 16) * kLdK;
+            auto fb = [&](int k, int nn) { return sS[nn * kLdS + k]; };
+            warp_gemm_tf32<4>(ad, kDH, [&](int m, int k) { return Wa[m * kLdK + k]; }, fb, lane);
+            warp_gemm_tf32<4>(aq, kDH, [&](int m, int k) { return Qa[m * kLdK + k]; }, fb, lane);
+            const float *Ug = w.U + hc * kC * kDH + slice * kSl;
+#pragma unroll
+            for (int nt = 0; nt < 4; nt++) {
+                const int r = warp * 16 + gq, c = nt * 8 + 2 * tq;
+                const float2 u0 = *reinterpret_cast<const float2 *>(Ug + (size_t)r * kDH + c);
+                const float2 u1 = *reinterpret_cast<const float2 *>(Ug + (size_t)(r + 8) * kDH + c);
+                sD[r * kLdD + c] = u0.x - ad[nt][0];
+                sD[r * kLdD + c + 1] = u0.y - ad[nt][1];
+                sD[(r + 8) * kLdD + c] = u1.x - ad[nt][2];
+                sD[(r + 8) * kLdD + c + 1] = u1.y - ad[nt][3];
+                const float e0 = expf(sc[r]), e1 = expf(sc[r + 8]);
+                aq[nt][0] *= e0; aq[nt][1] *= e0; aq[nt][2] *= e1; aq[nt][3] *= e1;
+            }
+        }
+        __syncthreads();  // D complete; S fully read
+        // O = e^{c} Q S^T + (M o Q K^T) D
+        {
+            const float *QKa = sQK + (warp * 16) * kLdT;
+            warp_gemm_tf32<4>(aq, kC, [&](int m, int k) { return QKa[m * kLdT + k]; },
+                              [&](int k, int nn) { return sD[k * kLdD + nn]; }, lane);
+#pragma unroll
+            for (int nt = 0; nt < 4; nt++) {
+                const int r = warp * 16 + gq, c = slice * kSl + nt * 8 + 2 * tq;
+                if (t0 + r < n)
+                    *reinterpret_cast<float2 *>(out + (size_t)(t0 + r) * total_v + (size_t)vh * kDH + c) = make_float2(aq[nt][0], aq[nt][1]);
+                if (t0 + r + 8 < n)
+                    *reinterpret_cast<float2 *>(out + (size_t)(t0 + r + 8) * total_v + (size_t)vh * kDH + c) = make_float2(aq[nt][2], aq[nt][3]);
+            }
+        }
+        // S <- e^{c_C} S + D^T (e^{c_C - c} K): warp = (16 state rows, 64 key columns)
+        {
+            const int mt = warp & 1, nh = warp >> 1;
+            const float eC = expf(cC);
+            float as[8][4];
+#pragma unroll
+            for (int nt = 0; nt < 8; nt++) {
+                const int r = mt * 16 + gq, c = nh * 64 + nt * 8 + 2 * tq;
+                as[nt][0] = eC * sS[r * kLdS + c]; as[nt][1] = eC * sS[r * kLdS + c + 1];
+                as[nt][2] = eC * sS[(r + 8) * kLdS + c]; as[nt][3] = eC * sS[(r + 8) * kLdS + c + 1];
+            }
+            warp_gemm_tf32<8>(as, kC, [&](int m, int k) { return sD[k * kLdD + mt * 16 + m]; },
+                              [&](int k, int nn) { return sKs[k * kLdKs + nh * 64 + nn]; }, lane);
+#pragma unroll
+            for (int nt = 0; nt < 8; nt++) {
+                const int r = mt * 16 + gq, c = nh * 64 + nt * 8 + 2 * tq;
+                sS[r * kLdS + c] = as[nt][0]; sS[r * kLdS + c + 1] = as[nt][1];
+                sS[(r + 8) * kLdS + c] = as[nt][2]; sS[(r + 8) * kLdS + c + 1] = as[nt][3];
+            }
+        }
+    }
+    __syncthreads();
+    for (int i = tid; i < kSl * (kDH / 4); i += 128) {
+        const int r = i >> 5, c4 = (i & 31) * 4;
+        *reinterpret_cast<float4 *>(Sg + (size_t)r * kDH + c4) = *reinterpret_cast<const float4 *>(sS + r * kLdS + c4);
+    }
+}
+
+// ---- gated RMS-norm in place: o * rsqrt(mean o^2 + eps) * w * silu(z) --------------------------
+// grid (Hv, n), 32 threads (4 dims per lane)
+__global__ void gdn_norm_kernel(GdnDims g, const float *__restrict__ z, const uint16_t *__restrict__ norm_w,
+                                float *__restrict__ out) {
+    const int vh = blockIdx.x, t = blockIdx.y, lane = threadIdx.x;
+    const size_t o = (size_t)t * g.Hv * kDH + (size_t)vh * kDH + lane * 4;
+    float4 x = *reinterpret_cast<const float4 *>(out + o);
+    const float ss = warp_sum(x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w);
+    const float inv = 1.0f / sqrtf(ss / kDH + g.eps);
+    const float4 zz = *reinterpret_cast<const float4 *>(z + o);
+    auto f = [&](float v, float zv, int d) {
+        return v * inv * bf16_bits_to_float(norm_w[d]) * (zv / (1.0f + expf(-zv)));
+    };
+    x.x = f(x.x, zz.x, lane * 4); x.y = f(x.y, zz.y, lane * 4 + 1);
+    x.z = f(x.z, zz.z, lane * 4 + 2); x.w = f(x.w, zz.w, lane * 4 + 3);
+    *reinterpret_cast<float4 *>(out + o) = x;
+}
+
+// ---- host side ---------------------------------------------------------------------------------
+static size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
+
+static size_t carve(const GdnDims &g, int n, void *base, GdnWork *w) {
+    const int nchunks = (n + kC - 1) / kC;
+    size_t off = 0;
+    auto take = [&](size_t floats) {
+        float *p = base ? reinterpret_cast<float *>(static_cast<char *>(base) + off) : nullptr;
+        off += align256(floats * sizeof(float));
+        return p;
+    };
+    GdnWork t;
+    t.qn = take((size_t)n * g.Hk * kDH);
+    t.kn = take((size_t)n * g.Hk * kDH);
+    t.vn = take((size_t)n * g.Hv * kDH);
+    t.lg = take((size_t)n * g.Hv);
+    t.bt = take((size_t)n * g.Hv);
+    t.U = take((size_t)g.Hv * nchunks * kC * kDH);
+    t.W = take((size_t)g.Hv * nchunks * kC * kDH);
+    t.QK = take((size_t)g.Hv * nchunks * kC * kC);
+    t.cv = take((size_t)g.Hv * nchunks * kC);
+    if (w) *w = t;
+    return off;
+}
+
+size_t gdn_prefill_work_bytes(const GdnDims &g, int max_tokens, int chunk) {
+    (void)chunk;
+    return carve(g, max_tokens, nullptr, nullptr);
+}
+
 int launch_gdn_prefill(const GdnDims &g, int n, int chunk, int step0, float *conv_state, float *ssm_state,
                        const float *qkv, const float *z, const float *beta, const float *alpha,
                        const uint16_t *conv_w, const float *A_log, const uint16_t *dt_bias,
                        const uint16_t *norm_w, float *out, void *work, size_t work_bytes, cudaStream_t st) {
-    (void)chunk; (void)work; (void)work_bytes;
-    const size_t vd = (size_t)g.Hv * g.dv;
-    int launches = 0;
-    for (int t = 0; t < n; t++) {
-        TokSpec ts;
-        ts.mode = 0; ts.n = 1; ts.seq[0] = 0; ts.pos[0] = step0 + t; ts.row[0] = 0;
-        const int r = launch_gdn_decode(g, ts, conv_state, ssm_state, 0, 0, qkv + (size_t)t * g.conv_dim, z + t * vd,
-                                        beta + (size_t)t * g.Hv, alpha + (size_t)t * g.Hv, conv_w, A_log, dt_bias,
-                                        norm_w, out + t * vd, st);
-        if (r < 0) return -1;
-        launches += r;
+    (void)chunk;
+    GdnWork w;
+    if (carve(g, n, work, &w) > work_bytes) return -1;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(gdn_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, g.conv_dim * 4) != cudaSuccess ||
+            cudaFuncSetAttribute(gdn_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kChunkSmem) != cudaSuccess ||
+            cudaFuncSetAttribute(gdn_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kScanSmem) != cudaSuccess)
+            return -1;
+        configured = true;
     }
-    return launches;
+    const int nchunks = (n + kC - 1) / kC;
+    gdn_prep_kernel<<<n, 512, g.conv_dim * 4, st>>>(g, n, step0, conv_state, qkv, beta, alpha, conv_w, A_log, dt_bias, w);
+    gdn_ring_kernel<<<dim3(12, 3), 256, 0, st>>>(g.conv_dim, n, step0, conv_state, qkv);
+    gdn_chunk_kernel<<<dim3(nchunks, g.Hv), 256, kChunkSmem, st>>>(g, n, w, nchunks);
+    gdn_scan_kernel<<<dim3(kDH / kSl, g.Hv), 128, kScanSmem, st>>>(g, n, w, nchunks, ssm_state, out);
+    int launches = 4;
+    if (norm_w != nullptr) {
+        gdn_norm_kernel<<<dim3(g.Hv, n), 32, 0, st>>>(g, z, norm_w, out);
+        launches++;
+    }
+    return cudaGetLastError() == cudaSuccess ? launches : -1;
 }
 
 }  // namespace fm

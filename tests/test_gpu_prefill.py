@@ -34,22 +34,30 @@ def test_attn_prefill_matches_sequential_steps(pkg, port, synth, n, prefix):
     assert gated <= TOL
 
 
-def test_gdn_prefill_matches_sequential_steps(pkg, port, synth):
-    n = 200
+@pytest.mark.parametrize("sizes", [(1,), (63,), (64,), (65,), (200,), (100, 70, 3), (4096,)])
+def test_gdn_prefill_matches_sequential_steps(pkg, port, synth, sizes):
+    """Chunked GatedDeltaNet prefill against sequential CPU steps: output, final recurrent state and
+    conv history; bf16-representable inputs, fp32 state ~ N(0, 0.02^2).  (4096,) is the full chunked
+    prefill configuration (sequence 4096, chunk 64, 16 qk / 64 v heads x 128); several sizes in a
+    row exercise continuation across calls, and a decode step continues from the prefilled state."""
+    n = sum(sizes)
     dims = make_dims()
     w = synth.gdn_weights(8)
     qkv, z, beta, alpha = synth.gdn_step_inputs(8, n, bf16=True)
     s0 = synth.gdn_state(8)
     conv_ref = np.zeros((3, 12288), np.float32); ssm_ref = s0.copy()
     out_ref = port.gdn_run(dims, conv_ref, ssm_ref, qkv, z, beta, alpha, w["conv_w"], w["A_log"], w["dt_bias"],
-                           w["norm_w"], threads=8)
-    c = gdn_ctx(pkg, max_batch=256)
+                           w["norm_w"], threads=16)
+    c = gdn_ctx(pkg, max_batch=max(sizes))
     c.state_import(0, 0, None, s0)
     out = np.empty((n, 8192), np.float32)
-    c.gdn_prefill(0, 0, n, qkv, z, beta, alpha, out, w["conv_w"], w["A_log"], w["dt_bias"], w["norm_w"])
+    t = 0
+    for m in sizes:
+        c.gdn_prefill(0, 0, m, qkv[t:t + m].copy(), z[t:t + m].copy(), beta[t:t + m].copy(), alpha[t:t + m].copy(),
+                      out[t:t + m], w["conv_w"], w["A_log"], w["dt_bias"], w["norm_w"])
+        t += m
     conv = np.empty((3, 12288), np.float32); ssm = np.empty((64, 128, 128), np.float32)
     c.state_export(0, 0, conv, ssm)
-    # a decode step continues from the prefilled state
     q1, z1, b1, a1 = synth.gdn_step_inputs(9, 1)
     o1 = np.empty((1, 8192), np.float32)
     c.gdn_decode(0, [0], q1, z1, b1, a1, o1, w["conv_w"], w["A_log"], w["dt_bias"], w["norm_w"])
@@ -59,5 +67,5 @@ def test_gdn_prefill_matches_sequential_steps(pkg, port, synth):
     gs, _, rs = rel_errors(ssm, ssm_ref)
     go, _, ro = rel_errors(out, out_ref)
     g1, _, _ = rel_errors(o1, r1)
-    print("gdn prefill state", gs, rs, "out", go, ro, "next step", g1)
+    print("gdn prefill", sizes, "state", gs, rs, "out", go, ro, "next step", g1)
     assert gs <= TOL_GDN and go <= TOL_GDN and g1 <= TOL_GDN
