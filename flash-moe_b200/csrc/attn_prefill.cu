@@ -1,26 +1,495 @@
-// Causal prefill attention over the paged KV store (rows already appended by the caller):
-// token t of the run attends to rows [0, row0 + t] and is multiplied by sigmoid(gate).
-// Math of the Metal kernel prefill_causal_attn (metal_infer/shaders.metal:2228-2315).
+// Causal prefill attention on the 5th-generation tensor cores (tcgen05 + TMEM), fed by TMA.
 //
-// This version runs every token of the run as an independent decode problem on the split-KV
-// kernel of attn_decode.cu (one CTA per (KV head, token), the 16 grouped query heads as the MMA M
-// dimension), followed by the normalise + gate kernel.  K/V tiles are re-read from L2 per token.
+// Math of the Metal kernels prefill_q_rope_norm_bf16 / prefill_causal_attn
+// (metal_infer/shaders.metal:2228-2397; dispatch metal_infer/batched_prefill.h:574-668): q is
+// normalised and rotated, token t of the run attends to cache rows [0, row0 + t] (the run's own rows
+// were appended before this kernel runs), the result is multiplied by sigmoid(gate).
+//
+// Organisation
+//   attn_q_prep_kernel    q -> RMS-norm, partial RoPE, * (1/sqrt(D)) * log2(e) -> fp16 hi | lo workspace
+//   attn_kv_f16_kernel    K, V rows of the sequence: bf16 pages -> contiguous fp16 workspace
+//   attn_prefill_kernel   one CTA per (128 query tokens, query head):
+//       warp 4 (one lane)  TMA producer: Q tile once, then K / V tiles of 32 rows into 2-stage rings
+//       warp 5 (one lane)  issues tcgen05.mma: S = [Q_hi | Q_lo] [K | K]^T (M128 N32 K512) into one of
+//                          two TMEM score buffers, O += [P_hi | P_lo] [V ; V] (M128 N256 K64) into the
+//                          TMEM accumulator
+//       warps 0-3          one query row per thread: tcgen05.ld of the scores, causal mask, online
+//                          softmax in the exp2 domain (row-local, no shuffles), P as fp16 into a
+//                          swizzled shared-memory tile that the next MMA reads; the accumulator is
+//                          rescaled in TMEM only when some row's maximum grew by more than 2^8;
+//                          epilogue: O / l * sigmoid(gate) -> fp32 output
+//   Precision: q after RoPE and the softmax weights are not representable in 16 bits; a single fp16
+//   rounding of either (2^-12) measured 4e-3 against the fp32 reference on short contexts, over the
+//   2e-3 bound.  Both therefore enter the MMAs as two fp16 terms (hi + lo) laid side by side along
+//   the contraction dimension, the K / V tile being read twice; that doubles the tensor work and is
+//   the price of the bound.  K and V are exact (bf16 -> fp16 is lossless inside fp16's range; values
+//   beyond +-65504 are clamped).
+//   TMEM: 2 x 32 columns of scores + 256 columns of output.
+//   Every mbarrier wait is bounded; on expiry the CTA records an error code and winds down.
+#include <cuda.h>
+#include <cuda_fp16.h>
+
+#include "fm_device.cuh"
 #include "fm_internal.h"
 
 namespace fm {
 
-int launch_attn_prefill(const KvView &kv, const RopeParams &rope, int seq, int start_pos, int row0, int n,
-                        int H, const float *q_proj_out, const float *q, const float *gate,
-                        const uint16_t *q_norm_w, float eps, float *work_o, float *work_ml, float *out,
-                        cudaStream_t st) {
-    TokSpec t;
-    t.mode = 1; t.n = n; t.seq0 = seq; t.pos0 = start_pos; t.row0 = row0;
-    const int D = kv.D;
-    if (launch_attn_decode(kv, rope, t, H, q_proj_out, q, q_norm_w, eps, work_o, work_ml, 1, st) < 0) return -1;
-    if (launch_attn_merge(work_o, work_ml, 1, D, 2, (long long)H * D, (long long)H * 2, D, 2, n, H, D,
-                          q_proj_out, gate, out, nullptr, st) < 0)
+constexpr int kBM = 128;  // query rows per CTA
+constexpr int kBN = 32;   // kv rows per tile
+constexpr int kHD = 256;  // head dim
+constexpr int kSlabQ = kBM * 128;  // bytes of one 64-column slab of the Q tile
+constexpr int kSlabKV = kBN * 128;
+constexpr int kQBytesPf = 8 * kSlabQ;    // 128 KB: four slabs of q_hi then four of q_lo
+constexpr int kKVBytesPf = 4 * kSlabKV;  // 16 KB per K or V tile
+constexpr int kPBytes = kBM * 128;       // 16 KB: P tile, per row 32 fp16 of p_hi then 32 of p_lo
+constexpr int kPfSmem = kQBytesPf + 4 * kKVBytesPf + 2 * kPBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int kPfThreads = 192;
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kColS = 0, kColO = 128;
+
+enum PfBar { BAR_Q = 0, BAR_KFULL = 1, BAR_KEMPTY = 3, BAR_VFULL = 5, BAR_VEMPTY = 7, BAR_SFULL = 9, BAR_SEMPTY = 11,
+             BAR_PFULL = 13, BAR_PVDONE = 15, BAR_COUNT = 17 };
+
+// ---- PTX wrappers ------------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: gives up after ~1e9 clock ticks (about half a second), or at once when another
+// thread of the CTA already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+    if (mbar_try(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (true) {
+        if (mbar_try(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > 1000000000LL) {
+            *abort_flag = 1;
+            return false;
+        }
+    }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// 32 lanes x 32 consecutive 32-bit columns: thread i of the warp gets its lane's 32 columns
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,"
+        "%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,"
+        "%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
+        "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]),
+        "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]),
+        "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
+
+// Shared-memory matrix descriptor, 128-byte swizzle, version 1 (sm_100).
+//   K-major operand  (rows x 64 fp16, row = 128 B): SBO = 1024 (next group of 8 rows); LBO unused.
+//   MN-major operand (8 k-rows x 64 fp16 atoms):    LBO = bytes to the next 64-element block along
+//                    M/N, SBO = 1024 (next group of 8 k-rows).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+    d |= (uint64_t)1 << 46;  // descriptor version
+    d |= (uint64_t)2 << 61;  // SWIZZLE_128B
+    return d;
+}
+// Instruction descriptor for kind::f16: fp16 A and B, fp32 accumulate.
+__host__ __device__ constexpr uint32_t idesc_f16(int M, int N, bool b_mn_major) {
+    return (1u << 4)                            // D format fp32
+           | (0u << 7) | (0u << 10)             // A, B format fp16
+           | (0u << 15)                         // A K-major
+           | ((b_mn_major ? 1u : 0u) << 16)     // B major
+           | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+// ---- q preparation: norm, RoPE, scale -> fp16 [n][H][hi(256) | lo(256)] ------------------------
+// grid (H, n), 256 threads
+__global__ void attn_q_prep_kernel(RopeParams rope, int H, int start_pos, const float *__restrict__ q_proj_out,
+                                   const float *__restrict__ q_in, const uint16_t *__restrict__ qnw, float eps,
+                                   __half *__restrict__ q16) {
+    __shared__ float sx[kHD];
+    __shared__ float sred[8];
+    const int h = blockIdx.x, t = blockIdx.y, d = threadIdx.x;
+    const float *src = q_proj_out ? q_proj_out + ((size_t)t * H + h) * 2 * kHD : q_in + ((size_t)t * H + h) * kHD;
+    float x = src[d];
+    if (qnw != nullptr) {
+        const float ss = warp_sum(x * x);
+        if ((d & 31) == 0) sred[d >> 5] = ss;
+        __syncthreads();
+        float tot = 0.f;
+        for (int w = 0; w < 8; w++) tot += sred[w];
+        x = x * (1.0f / sqrtf(tot / kHD + eps)) * bf16_bits_to_float(qnw[d]);
+    }
+    sx[d] = x;
+    __syncthreads();
+    const int half = rope.rotary_dim / 2;
+    if (d < rope.rotary_dim) {
+        const int i = d < half ? d : d - half;
+        const float ang = ((float)(start_pos + t) / rope.pos_div) * rope.inv_freq[i];
+        const float c = cosf(ang), s = sinf(ang);
+        x = d < half ? x * c - sx[d + half] * s : sx[d - half] * s + x * c;
+    }
+    const float y = x * rope.logit_scale * kLog2e;
+    const __half hi = __float2half_rn(y);
+    q16[((size_t)t * H + h) * 2 * kHD + d] = hi;                                         // q_hi
+    q16[((size_t)t * H + h) * 2 * kHD + kHD + d] = __float2half_rn(y - __half2float(hi));  // q_lo
+}
+
+// ---- K, V rows [0, L) of one sequence: bf16 pages -> fp16 [L][Hkv*256] --------------------------
+// grid (L), 256 threads
+__global__ void attn_kv_f16_kernel(KvView kv, int seq, int L, __half *__restrict__ k16, __half *__restrict__ v16) {
+    const int row = blockIdx.x;
+    const int page = kv.page_table[(size_t)seq * kv.max_slots + row / kv.page_size];
+    const int r = row % kv.page_size;
+    const size_t page_elems = (size_t)2 * kv.Hkv * kv.page_size * kHD;
+    for (int e = threadIdx.x; e < kv.Hkv * kHD; e += blockDim.x) {
+        const int kvh = e / kHD, d = e - kvh * kHD;
+        const __nv_bfloat16 *kp = kv.pool + (size_t)page * page_elems + ((size_t)kvh * kv.page_size + r) * kHD + d;
+        const __nv_bfloat16 *vp = kp + (size_t)kv.Hkv * kv.page_size * kHD;
+        const float kf = fminf(fmaxf(__bfloat162float(*kp), -65504.f), 65504.f);
+        const float vf = fminf(fmaxf(__bfloat162float(*vp), -65504.f), 65504.f);
+        k16[(size_t)row * kv.Hkv * kHD + e] = __float2half_rn(kf);
+        v16[(size_t)row * kv.Hkv * kHD + e] = __float2half_rn(vf);
+    }
+}
+
+// ---- the attention kernel ----------------------------------------------------------------------
+struct PfParams {
+    int n;         // tokens in the run
+    int row0;      // cache rows before the run
+    int H, Hkv;
+    const float *q_proj_out;  // gate source: interleaved ...
+    const float *gate;        // ... or separate
+    float *out;
+    int *err;      // device word: 0 ok, else (code << 16 | blockIdx info)
+};
+
+__global__ void __launch_bounds__(kPfThreads, 1)
+attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                    const __grid_constant__ CUtensorMap map_v, PfParams p) {
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ uint32_t s_tmem_base;
+    __shared__ int s_abort;
+    // 1024-byte aligned tiles (128-byte swizzle atoms are 1024 bytes)
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    const uint32_t sQ = base;
+    const uint32_t sK = sQ + kQBytesPf;        // 2 stages
+    const uint32_t sV = sK + 2 * kKVBytesPf;   // 2 stages
+    const uint32_t sP = sV + 2 * kKVBytesPf;   // 2 buffers
+    const uint32_t sBar = sP + 2 * kPBytes;    // BAR_COUNT mbarriers, 8 bytes each
+    unsigned char *sP_gen = smem_raw + (sP - raw);
+    auto bar = [&](int i) { return sBar + 8u * (uint32_t)i; };
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // heavy tiles first: blockIdx.x = 0 is the last (longest) query tile
+    const int nqt = gridDim.x;
+    const int qt = nqt - 1 - blockIdx.x;
+    const int head = blockIdx.y;
+    const int kvh = head / (p.H / p.Hkv);
+    const int t0 = qt * kBM;
+    const int L = p.row0 + p.n;
+    const int last_row = min(p.row0 + t0 + kBM - 1, L - 1);  // last cache row any query of this tile sees
+    const int ntiles = last_row / kBN + 1;
+
+    if (tid == 0) {
+        s_abort = 0;
+        mbar_init(bar(BAR_Q), 1);
+        for (int s = 0; s < 2; s++) {
+            mbar_init(bar(BAR_KFULL + s), 1);
+            mbar_init(bar(BAR_KEMPTY + s), 1);
+            mbar_init(bar(BAR_VFULL + s), 1);
+            mbar_init(bar(BAR_VEMPTY + s), 1);
+            mbar_init(bar(BAR_SFULL + s), 1);
+            mbar_init(bar(BAR_SEMPTY + s), 128);
+            mbar_init(bar(BAR_PFULL + s), 128);
+            mbar_init(bar(BAR_PVDONE + s), 1);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 5) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&s_tmem_base)), "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = s_tmem_base;
+    volatile int *abortp = &s_abort;
+
+    if (warp == 4) {
+        // ================= TMA producer =================
+        if (lane == 0) {
+            mbar_expect_tx(bar(BAR_Q), kQBytesPf);
+            for (int s = 0; s < 8; s++) tma_load_2d(sQ + s * kSlabQ, &map_q, head * 2 * kHD + s * 64, t0, bar(BAR_Q));
+            for (int j = 0; j < ntiles; j++) {
+                const int b = j & 1, u = j >> 1;
+                if (u > 0 && !mbar_wait(bar(BAR_KEMPTY + b), (u - 1) & 1, abortp)) break;
+                mbar_expect_tx(bar(BAR_KFULL + b), kKVBytesPf);
+                for (int s = 0; s < 4; s++)
+                    tma_load_2d(sK + b * kKVBytesPf + s * kSlabKV, &map_k, kvh * kHD + s * 64, j * kBN, bar(BAR_KFULL + b));
+                if (u > 0 && !mbar_wait(bar(BAR_VEMPTY + b), (u - 1) & 1, abortp)) break;
+                mbar_expect_tx(bar(BAR_VFULL + b), kKVBytesPf);
+                for (int s = 0; s < 4; s++)
+                    tma_load_2d(sV + b * kKVBytesPf + s * kSlabKV, &map_v, kvh * kHD + s * 64, j * kBN, bar(BAR_VFULL + b));
+            }
+        }
+    } else if (warp == 5) {
+        // ================= MMA issuer =================
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = idesc_f16(kBM, kBN, false);   // S = Q K^T, both K-major
+            constexpr uint32_t idesc_o = idesc_f16(kBM, kHD, true);    // O = P V, V is MN-major
+            auto issue_s = [&](int j) {
+                const int b = j & 1;
+                const uint32_t d = tmem + kColS + b * kBN;
+#pragma unroll
+                for (int ks = 0; ks < 2 * kHD / 16; ks++) {  // q_hi slabs 0-3, then q_lo slabs 4-7, against the same K tile
+                    const uint32_t off_a = (ks >> 2) * kSlabQ + (ks & 3) * 32, off_b = ((ks >> 2) & 3) * kSlabKV + (ks & 3) * 32;
+                    tc_mma_f16(d, smem_desc(sQ + off_a, 16, 1024), smem_desc(sK + b * kKVBytesPf + off_b, 16, 1024), idesc_s, ks > 0);
+                }
+                tc_commit(bar(BAR_SFULL + b));
+                tc_commit(bar(BAR_KEMPTY + b));
+            };
+            bool ok = mbar_wait(bar(BAR_Q), 0, abortp) && mbar_wait(bar(BAR_KFULL + 0), 0, abortp);
+            if (ok) {
+                tc_fence_after();
+                issue_s(0);
+            }
+            for (int j = 0; ok && j < ntiles; j++) {
+                const int b = j & 1, u = j >> 1;
+                if (j + 1 < ntiles) {
+                    const int b1 = (j + 1) & 1, u1 = (j + 1) >> 1;
+                    ok = mbar_wait(bar(BAR_KFULL + b1), u1 & 1, abortp);
+                    if (ok && u1 > 0) ok = mbar_wait(bar(BAR_SEMPTY + b1), (u1 - 1) & 1, abortp);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_s(j + 1);
+                }
+                ok = mbar_wait(bar(BAR_PFULL + b), u & 1, abortp) && mbar_wait(bar(BAR_VFULL + b), u & 1, abortp);
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < 2 * kBN / 16; ks++)  // p_hi columns 0-31, then p_lo columns 32-63, against the same V tile
+                    tc_mma_f16(tmem + kColO, smem_desc(sP + b * kPBytes + ks * 32, 16, 1024),
+                               smem_desc(sV + b * kKVBytesPf + (ks & 1) * 2048, kSlabKV, 1024), idesc_o, (j > 0 || ks > 0));
+                tc_commit(bar(BAR_PVDONE + b));
+                tc_commit(bar(BAR_VEMPTY + b));
+            }
+        }
+    } else {
+        // ================= softmax / correction / epilogue: one query row per thread =================
+        const int r = tid;                        // row of the tile = TMEM lane
+        const int my_last = p.row0 + t0 + r;      // last cache row this query may see
+        const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+        float m_ref = kNegBig, l_sum = 0.f;
+        bool ok = true;
+        for (int j = 0; j < ntiles; j++) {
+            const int b = j & 1, u = j >> 1;
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_SFULL + b), u & 1, abortp));
+            if (!ok) break;  // warp-uniform: the tcgen05.ld / st below are warp-collective
+            tc_fence_after();
+            uint32_t sr[32];
+            tc_ld32(tmem + lane_base + kColS + b * kBN, sr);
+            tc_wait_ld();
+            tc_fence_before();
+            mbar_arrive(bar(BAR_SEMPTY + b));
+            // causal mask (only tiles that reach past the first query's limit need it)
+            float mx = kNegBig;
+            const int col0 = j * kBN;
+#pragma unroll
+            for (int i = 0; i < kBN; i++) {
+                float s = __uint_as_float(sr[i]);
+                if (col0 + i > my_last) s = kNegBig;
+                sr[i] = __float_as_uint(s);
+                mx = fmaxf(mx, s);
+            }
+            // lazy rescale of the accumulator: warp-uniform because tcgen05.ld/st are warp-collective
+            const bool grow = mx > m_ref + 8.f;
+            if (__any_sync(0xffffffffu, grow)) {
+                const float m_new = grow ? mx : m_ref;
+                const float corr = fast_exp2(m_ref - m_new);
+                m_ref = m_new;
+                l_sum *= corr;
+                if (j > 0) {
+                    // the previous P V must have landed in the accumulator
+                    const int bp = (j - 1) & 1, up = (j - 1) >> 1;
+                    ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_PVDONE + bp), up & 1, abortp));
+                    if (!ok) break;
+                    tc_fence_after();
+#pragma unroll 1
+                    for (int c = 0; c < kHD; c += 32) {
+                        uint32_t o[32];
+                        tc_ld32(tmem + lane_base + kColO + c, o);
+                        tc_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
+                        tc_st32(tmem + lane_base + kColO + c, o);
+                    }
+                    tc_wait_st();
+                }
+            }
+            // the P buffer must be free: P V of tile j-2 done
+            if (u > 0) {
+                ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_PVDONE + b), (u - 1) & 1, abortp));
+                if (!ok) break;
+            }
+            unsigned char *prow = sP_gen + b * kPBytes + r * 128;
+#pragma unroll
+            for (int c = 0; c < 4; c++) {  // 16-byte chunk c holds p_hi of 8 columns, chunk 4 + c their p_lo
+                uint32_t wh[4], wl[4];
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const float p0 = fast_exp2(__uint_as_float(sr[c * 8 + 2 * e]) - m_ref);
+                    const float p1 = fast_exp2(__uint_as_float(sr[c * 8 + 2 * e + 1]) - m_ref);
+                    l_sum += p0 + p1;
+                    const __half2 hh = __floats2half2_rn(p0, p1);
+                    const float2 hf = __half22float2(hh);
+                    const __half2 ll = __floats2half2_rn(p0 - hf.x, p1 - hf.y);
+                    wh[e] = *reinterpret_cast<const uint32_t *>(&hh);
+                    wl[e] = *reinterpret_cast<const uint32_t *>(&ll);
+                }
+                *reinterpret_cast<uint4 *>(prow + ((c ^ (r & 7)) << 4)) = make_uint4(wh[0], wh[1], wh[2], wh[3]);
+                *reinterpret_cast<uint4 *>(prow + (((4 + c) ^ (r & 7)) << 4)) = make_uint4(wl[0], wl[1], wl[2], wl[3]);
+            }
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            tc_fence_before();
+            mbar_arrive(bar(BAR_PFULL + b));
+        }
+        // epilogue
+        if (ok && ntiles > 0) {
+            const int bl = (ntiles - 1) & 1, ul = (ntiles - 1) >> 1;
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_PVDONE + bl), ul & 1, abortp));
+        }
+        if (ok) {
+            tc_fence_after();
+            const int t = t0 + r;
+            const float inv = l_sum > 0.f ? 1.0f / l_sum : 0.f;
+            const size_t orow = ((size_t)t * p.H + head) * kHD;
+            const float *grow_ptr = p.q_proj_out ? p.q_proj_out + ((size_t)t * p.H + head) * 2 * kHD + kHD : p.gate + orow;
+#pragma unroll 1
+            for (int c = 0; c < kHD; c += 32) {
+                uint32_t o[32];
+                tc_ld32(tmem + lane_base + kColO + c, o);
+                tc_wait_ld();
+                if (t < p.n) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4) {
+                        const float4 g = *reinterpret_cast<const float4 *>(grow_ptr + c + i);
+                        float4 y;
+                        y.x = __uint_as_float(o[i]) * inv / (1.0f + __expf(-g.x));
+                        y.y = __uint_as_float(o[i + 1]) * inv / (1.0f + __expf(-g.y));
+                        y.z = __uint_as_float(o[i + 2]) * inv / (1.0f + __expf(-g.z));
+                        y.w = __uint_as_float(o[i + 3]) * inv / (1.0f + __expf(-g.w));
+                        *reinterpret_cast<float4 *>(p.out + orow + c + i) = y;
+                    }
+                }
+            }
+        }
+    }
+    // ---- wind down: everyone meets, TMEM goes back ----
+    tc_fence_before();
+    __syncthreads();
+    if (s_abort && tid == 0) atomicCAS(p.err, 0, (1 << 16) | (blockIdx.y << 8) | (blockIdx.x & 0xff));
+    if (warp == 5) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(kTmemCols) : "memory");
+    }
+}
+
+// ---- host --------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn) return fn;
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) != cudaSuccess || qres != cudaDriverEntryPointSuccess)
+        return nullptr;
+    fn = reinterpret_cast<EncodeTiledFn>(p);
+    return fn;
+}
+
+// 2-D fp16 tensor [rows][cols], box [box_rows][64 cols], 128-byte swizzle, zero fill outside
+static bool make_map(CUtensorMap *m, const void *base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+    EncodeTiledFn enc = get_encode();
+    if (!enc) return false;
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {cols * 2};
+    const cuuint32_t box[2] = {64, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    return enc(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int launch_attn_prefill(const KvView &kv, const RopeParams &rope, int seq, int start_pos, int row0, int n, int H,
+                        const float *q_proj_out, const float *q, const float *gate, const uint16_t *q_norm_w, float eps,
+                        const PrefillWork &wk, float *out, cudaStream_t st) {
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmem) != cudaSuccess) return -1;
+        configured = true;
+    }
+    const int L = row0 + n;
+    CUtensorMap mq, mk, mv;
+    if (!make_map(&mq, wk.q16, (uint64_t)n, (uint64_t)H * 2 * kHD, kBM) || !make_map(&mk, wk.k16, (uint64_t)L, (uint64_t)kv.Hkv * kHD, kBN) ||
+        !make_map(&mv, wk.v16, (uint64_t)L, (uint64_t)kv.Hkv * kHD, kBN))
         return -1;
-    return 2;
+    attn_q_prep_kernel<<<dim3(H, n), kHD, 0, st>>>(rope, H, start_pos, q_proj_out, q, q_norm_w, eps, reinterpret_cast<__half *>(wk.q16));
+    attn_kv_f16_kernel<<<L, 256, 0, st>>>(kv, seq, L, reinterpret_cast<__half *>(wk.k16), reinterpret_cast<__half *>(wk.v16));
+    PfParams p;
+    p.n = n; p.row0 = row0; p.H = H; p.Hkv = kv.Hkv;
+    p.q_proj_out = q_proj_out; p.gate = gate; p.out = out; p.err = wk.err;
+    attn_prefill_kernel<<<dim3((n + kBM - 1) / kBM, H), kPfThreads, kPfSmem, st>>>(mq, mk, mv, p);
+    return cudaGetLastError() == cudaSuccess ? 3 : -1;
 }
 
 }  // namespace fm

@@ -160,8 +160,11 @@ extern "C" fm_status fm_create(const FmConfig *cfg, FmCtx **out) {
         const size_t rows = ((size_t)2 * ctx->sm_count + (size_t)c.num_kv_heads * c.max_batch_tokens) * 16 + 64;
         CREATE_CUDA(cudaMalloc(&ctx->d_part_o, rows * c.head_dim * sizeof(float)));
         CREATE_CUDA(cudaMalloc(&ctx->d_part_ml, rows * 2 * sizeof(float)));
-        CREATE_CUDA(cudaMalloc(&ctx->d_pf_o, (size_t)c.max_batch_tokens * c.num_attn_heads * c.head_dim * sizeof(float)));
-        CREATE_CUDA(cudaMalloc(&ctx->d_pf_ml, (size_t)c.max_batch_tokens * c.num_attn_heads * 2 * sizeof(float)));
+        if (c.seq_shard_count == 1) {  // prefill needs the whole sequence on one context
+            CREATE_CUDA(cudaMalloc(&ctx->d_pf_q16, (size_t)c.max_batch_tokens * c.num_attn_heads * c.head_dim * 2 * 2));  // hi | lo
+            CREATE_CUDA(cudaMalloc(&ctx->d_pf_k16, (size_t)c.max_seq_len * c.num_kv_heads * c.head_dim * 2));
+            CREATE_CUDA(cudaMalloc(&ctx->d_pf_v16, (size_t)c.max_seq_len * c.num_kv_heads * c.head_dim * 2));
+        }
     }
     if (has_gdn) {
         ctx->conv_dim = 2 * c.linear_num_k_heads * c.linear_key_dim + c.linear_num_v_heads * c.linear_value_dim;
@@ -177,6 +180,10 @@ extern "C" fm_status fm_create(const FmConfig *cfg, FmCtx **out) {
         ctx->work_bytes = gdn_prefill_work_bytes(g, c.max_batch_tokens, 64);
         if (ctx->work_bytes) CREATE_CUDA(cudaMalloc(&ctx->d_work, ctx->work_bytes));
     }
+    CREATE_CUDA(cudaMalloc(&ctx->d_err, sizeof(int)));
+    CREATE_CUDA(cudaMemset(ctx->d_err, 0, sizeof(int)));
+    CREATE_CUDA(cudaMallocHost(&ctx->h_err, sizeof(int)));
+    *ctx->h_err = 0;
     ctx->stage_bytes = stage_need(c);
     CREATE_CUDA(cudaMallocHost(&ctx->h_stage, ctx->stage_bytes));
     CREATE_CUDA(cudaMalloc(&ctx->d_stage, ctx->stage_bytes));
@@ -191,7 +198,8 @@ extern "C" void fm_destroy(FmCtx *ctx) {
     cudaSetDevice(ctx->cfg.device);
     cudaDeviceSynchronize();
     cudaFree(ctx->pool); cudaFree(ctx->d_page_table); cudaFree(ctx->d_conv_state); cudaFree(ctx->d_ssm_state);
-    cudaFree(ctx->d_part_o); cudaFree(ctx->d_part_ml); cudaFree(ctx->d_pf_o); cudaFree(ctx->d_pf_ml); cudaFree(ctx->d_work);
+    cudaFree(ctx->d_part_o); cudaFree(ctx->d_part_ml); cudaFree(ctx->d_pf_q16); cudaFree(ctx->d_pf_k16); cudaFree(ctx->d_pf_v16); cudaFree(ctx->d_err);
+    if (ctx->h_err) cudaFreeHost(ctx->h_err); cudaFree(ctx->d_work);
     cudaFree(ctx->d_stage);
     for (cudaEvent_t e : ctx->prof_ev) cudaEventDestroy(e);
     if (ctx->h_stage) cudaFreeHost(ctx->h_stage);
@@ -211,10 +219,19 @@ extern "C" fm_status fm_set_pointer_mode(FmCtx *ctx, int mode) {
     ctx->ptr_mode = mode;
     return FM_OK;
 }
+// A kernel whose bounded device-side wait expired leaves a code in the error word.
+static fm_status check_device_error(FmCtx *ctx) {
+    if (*ctx->h_err == 0) return FM_OK;
+    const int code = *ctx->h_err;
+    *ctx->h_err = 0;
+    cudaMemsetAsync(ctx->d_err, 0, sizeof(int), ctx->stream);
+    return fail(ctx, FM_ERR_TIMEOUT, "a device-side wait expired (code 0x%x); the results of that call are invalid", code);
+}
+
 extern "C" fm_status fm_synchronize(FmCtx *ctx) {
     if (!ctx) return FM_ERR_INVALID;
     FM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-    return FM_OK;
+    return check_device_error(ctx);
 }
 extern "C" int64_t fm_launch_count(const FmCtx *ctx) { return ctx ? ctx->launches : 0; }
 
@@ -636,11 +653,14 @@ extern "C" fm_status fm_attn_prefill(FmCtx *ctx, int fa_idx, int seq, int start_
     if (st) return st;
     {
         ProfScope prof(ctx);
+        const PrefillWork wk{ctx->d_pf_q16, ctx->d_pf_k16, ctx->d_pf_v16, ctx->d_err};
         st = launched(ctx, launch_attn_prefill(kv, ctx->rope, seq, start_pos, row0, n, c.num_attn_heads, d_qp, d_q, d_g, d_qn,
-                                               c.rms_norm_eps, ctx->d_pf_o, ctx->d_pf_ml, d_out, ctx->stream), "attn_prefill");
+                                               c.rms_norm_eps, wk, d_out, ctx->stream), "attn_prefill");
     }
     if (st) return st;
+    FM_CUDA(ctx, cudaMemcpyAsync(ctx->h_err, ctx->d_err, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
     FM_CUDA(ctx, sg.pull(out, w_out, n * qd));
+    if (sg.host) return check_device_error(ctx);
     return FM_OK;
 }
 

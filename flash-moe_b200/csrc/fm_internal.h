@@ -84,9 +84,12 @@ struct FmCtx {
     float *d_part_ml = nullptr;  // [batch][H][max_splits][2]
     int max_splits = 0;
 
-    // prefill scratch: per-(token, head) un-normalised result and (max, sum)
-    float *d_pf_o = nullptr;   // [max_batch_tokens][H][D]
-    float *d_pf_ml = nullptr;  // [max_batch_tokens][H][2]
+    // prefill scratch: fp16 copies of q (normalised, rotated, scaled) and of the sequence's K, V rows
+    void *d_pf_q16 = nullptr;  // [max_batch_tokens][H*D]
+    void *d_pf_k16 = nullptr;  // [max_seq_len][Hkv*D]
+    void *d_pf_v16 = nullptr;
+    int *d_err = nullptr;      // device-side error word written by kernels whose bounded waits expired
+    int *h_err = nullptr;      // pinned copy
     void *d_work = nullptr;             // chunked GatedDeltaNet workspace
     size_t work_bytes = 0;
 
@@ -121,9 +124,13 @@ int launch_attn_merge(const float *part_o, const float *part_ml, int nparts, lon
 int launch_kv_export(const KvView &kv, int seq, int len, float *k, float *v, cudaStream_t st);
 int launch_kv_import(const KvView &kv, int seq, int len, const float *k, const float *v, cudaStream_t st);
 
+struct PrefillWork {
+    void *q16, *k16, *v16;
+    int *err;
+};
 int launch_attn_prefill(const KvView &kv, const RopeParams &rope, int seq, int start_pos, int row0,
                         int n, int H, const float *q_proj_out, const float *q, const float *gate,
-                        const uint16_t *q_norm_w, float eps, float *work_o, float *work_ml, float *out,
+                        const uint16_t *q_norm_w, float eps, const PrefillWork &wk, float *out,
                         cudaStream_t st);
 
 struct GdnDims {

@@ -11,7 +11,7 @@ TOL = 2e-3
 TOL_GDN = 5e-3
 
 
-@pytest.mark.parametrize("n,prefix", [(1, 0), (70, 0), (256, 0), (100, 150)])
+@pytest.mark.parametrize("n,prefix", [(1, 0), (70, 0), (128, 0), (129, 0), (256, 0), (100, 150), (300, 1000), (2048, 0)])
 def test_attn_prefill_matches_sequential_steps(pkg, port, synth, n, prefix):
     """Causal prefill of n tokens after `prefix` cached rows against n sequential CPU steps;
     bf16-representable q, k, v as in the bf16 prefill configuration, the checker rounding the
