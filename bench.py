@@ -358,10 +358,25 @@ def run_ours(args):
 TRAFFIC_NCU = None
 
 
-def extra_measurements(pkg, torch, dev, peak):
-    """Batch-1 context sweep (us per layer and KV GB/s), prefill attention TFLOP/s, GatedDeltaNet decode."""
+def extra_measurements(pkg, torch, dev, peak, only=None):
+    """Batch-1 context sweep (us per layer and KV GB/s), prefill attention TFLOP/s, GatedDeltaNet decode
+    and chunked prefill.  `only` runs a single one of them (used when profiling one kernel)."""
     res = {}
     gen = torch.Generator(device=dev); gen.manual_seed(7)
+    want = lambda name: only is None or only == name
+    if want("sweep"):
+        res.update(_probe_sweep(pkg, torch, dev, peak, gen))
+    if want("prefill"):
+        res.update(_probe_prefill(pkg, torch, dev, gen))
+    if want("gdn_decode"):
+        res.update(_probe_gdn_decode(pkg, torch, dev, peak, gen))
+    if want("gdn_prefill"):
+        res.update(_probe_gdn_prefill(pkg, torch, dev, gen))
+    return res
+
+
+def _probe_sweep(pkg, torch, dev, peak, gen):
+    res = {}
     # ---- batch-1 decode sweep; 32 layers so that even the 4K case streams more than L2 per pass ----
     NL = 32
     sweep = {}
@@ -401,7 +416,11 @@ def extra_measurements(pkg, torch, dev, peak):
     ctx.close()
     del K, V
     torch.cuda.empty_cache()
+    return res
 
+
+def _probe_prefill(pkg, torch, dev, gen):
+    res = {}
     # ---- causal prefill attention, T = 2048, empty cache ----
     T = 2048
     cfg = pkg.default_config(num_full_layers=1, num_linear_layers=0, max_seqs=1, max_seq_len=T + 64, max_batch_tokens=T)
@@ -423,15 +442,28 @@ def extra_measurements(pkg, torch, dev, peak):
         times.append(e0.elapsed_time(e1))
     ms = min(times[1:])
     flops = 4 * H * D * T * (T + 1) / 2
-    res["prefill_attn_T2048"] = {"ms": ms, "tflops": flops / ms / 1e9, "algorithmic_gflop": flops / 1e9}
+    ctx.profile_read(); ctx.profile_enable(True)
+    ctx.reset(0)
+    ctx.attn_prefill(0, 0, 0, T, o, q=q, gate=g, k=k, v=v)
+    n_k, k_ms = ctx.profile_read(); ctx.profile_enable(False)
+    res["prefill_attn_T2048"] = {"ms": ms, "tflops": flops / ms / 1e9, "algorithmic_gflop": flops / 1e9,
+                                 "ms_kernels_after_append": k_ms, "tflops_kernels_after_append": flops / k_ms / 1e9}
     ctx.close()
+    return res
 
+
+def _gdn_weights(pkg, torch, dev):
+    w = pkg.synth.gdn_weights(0)
+    return {k_: torch.from_numpy(v_.view(np.int16) if v_.dtype == np.uint16 else v_).to(dev) for k_, v_ in w.items()}
+
+
+def _probe_gdn_decode(pkg, torch, dev, peak, gen):
+    res = {}
     # ---- GatedDeltaNet decode, batch 1, cycling the 45 layers (180 MiB of state > L2) ----
     cfg = pkg.default_config(num_full_layers=0, num_linear_layers=45, max_seqs=1)
     ctx = pkg.Context(cfg)
     ctx.set_stream(torch.cuda.current_stream().cuda_stream)
-    w = pkg.synth.gdn_weights(0)
-    tw = {k_: torch.from_numpy(v_.view(np.int16) if v_.dtype == np.uint16 else v_).to(dev) for k_, v_ in w.items()}
+    tw = _gdn_weights(pkg, torch, dev)
     qkv = torch.randn((1, 12288), device=dev, generator=gen)
     z = torch.randn((1, 8192), device=dev, generator=gen)
     be = torch.randn((1, 64), device=dev, generator=gen)
@@ -460,6 +492,36 @@ def extra_measurements(pkg, torch, dev, peak):
     return res
 
 
+def _probe_gdn_prefill(pkg, torch, dev, gen):
+    res = {}
+    tw = _gdn_weights(pkg, torch, dev)
+    # ---- chunked GatedDeltaNet prefill, T = 4096, chunk 64 ----
+    T = 4096
+    cfg = pkg.default_config(num_full_layers=0, num_linear_layers=1, max_seqs=1, max_batch_tokens=T)
+    ctx = pkg.Context(cfg)
+    ctx.set_stream(torch.cuda.current_stream().cuda_stream)
+    qkv = torch.randn((T, 12288), device=dev, generator=gen).bfloat16().float()
+    z = torch.randn((T, 8192), device=dev, generator=gen).bfloat16().float()
+    be = torch.randn((T, 64), device=dev, generator=gen)
+    al = torch.randn((T, 64), device=dev, generator=gen)
+    go = torch.empty((T, 8192), device=dev)
+    times = []
+    for it in range(4):
+        ctx.reset(0)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        ctx.gdn_prefill(0, 0, T, qkv, z, be, al, go, tw["conv_w"], tw["A_log"], tw["dt_bias"], tw["norm_w"])
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    ms = min(times[1:])
+    gflop = 64 * 64 * (4 * 64 * 64 * 128 + 2 * 64 * 64 * 128 + 64 * 64 * 128 + 6 * 64 * 128 * 128) / 1e9
+    res["gdn_prefill_T4096"] = {"ms": ms, "tflops": gflop / ms, "algorithmic_gflop": gflop,
+                                "sequential_form_gflop": 7 * 2 ** 20 * T / 1e9}
+    ctx.close()
+    return res
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -472,7 +534,16 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=10)
     ap.add_argument("--no-extra", action="store_true", help="skip the context sweep / prefill / GatedDeltaNet figures")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--probe", default=None, choices=["sweep", "prefill", "gdn_decode", "gdn_prefill"],
+                    help="run only one of the extra measurements and print it (for profiling one kernel)")
     args = ap.parse_args()
+    if args.probe:
+        import torch
+        from __graft_entry__ import load_package
+        torch.cuda.set_device(0)
+        peak, _ = load_peaks()
+        print(json.dumps({"probe": args.probe, **extra_measurements(load_package(), torch, torch.device("cuda", 0), peak, args.probe)}))
+        return
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -9,14 +9,14 @@
 //   attn_q_prep_kernel    q -> RMS-norm, partial RoPE, * (1/sqrt(D)) * log2(e) -> fp16 hi | lo workspace
 //   attn_kv_f16_kernel    K, V rows of the sequence: bf16 pages -> contiguous fp16 workspace
 //   attn_prefill_kernel   one CTA per (128 query tokens, query head):
-//       warp 4 (one lane)  TMA producer: Q tile once, then K / V tiles of 32 rows into 2-stage rings
-//       warp 5 (one lane)  issues tcgen05.mma: S = [Q_hi | Q_lo] [K | K]^T (M128 N32 K512) into one of
-//                          two TMEM score buffers, O += [P_hi | P_lo] [V ; V] (M128 N256 K64) into the
-//                          TMEM accumulator
-//       warps 0-3          one query row per thread: tcgen05.ld of the scores, causal mask, online
-//                          softmax in the exp2 domain (row-local, no shuffles), P as fp16 into a
-//                          swizzled shared-memory tile that the next MMA reads; the accumulator is
-//                          rescaled in TMEM only when some row's maximum grew by more than 2^8;
+//       warp 4 (one lane)  TMA producer: q_hi tile once, then K / V tiles of 64 rows into 2-stage rings
+//       warp 5 (one lane)  issues tcgen05.mma: S = q_hi K^T + q_lo K^T (M128 N64 K256 each; q_hi from
+//                          shared memory, q_lo from tensor memory) into the TMEM score buffer,
+//                          O += p_hi V + p_lo V (M128 N256 K64 each, P from tensor memory)
+//       warps 0-3          one query row per thread: q_lo row -> TMEM once; per tile tcgen05.ld of the
+//                          scores, causal mask, online softmax in the exp2 domain (row-local, no
+//                          shuffles), P as fp16 pairs back into TMEM for the next MMA; the accumulator
+//                          is rescaled in TMEM only when some row's maximum grew by more than 2^8;
 //                          epilogue: O / l * sigmoid(gate) -> fp32 output
 //   Precision: q after RoPE and the softmax weights are not representable in 16 bits; a single fp16
 //   rounding of either (2^-12) measured 4e-3 against the fp32 reference on short contexts, over the
@@ -24,7 +24,7 @@
 //   the contraction dimension, the K / V tile being read twice; that doubles the tensor work and is
 //   the price of the bound.  K and V are exact (bf16 -> fp16 is lossless inside fp16's range; values
 //   beyond +-65504 are clamped).
-//   TMEM: 2 x 32 columns of scores + 256 columns of output.
+//   TMEM: 64 columns of scores + 64 of P + 256 of output + 128 of q_lo = 512.
 //   Every mbarrier wait is bounded; on expiry the CTA records an error code and winds down.
 #include <cuda.h>
 #include <cuda_fp16.h>
@@ -35,20 +35,23 @@
 namespace fm {
 
 constexpr int kBM = 128;  // query rows per CTA
-constexpr int kBN = 32;   // kv rows per tile
+constexpr int kBN = 64;   // kv rows per tile
 constexpr int kHD = 256;  // head dim
-constexpr int kSlabQ = kBM * 128;  // bytes of one 64-column slab of the Q tile
+constexpr int kSlabQ = kBM * 128;  // bytes of one 64-column slab of the q_hi tile
 constexpr int kSlabKV = kBN * 128;
-constexpr int kQBytesPf = 8 * kSlabQ;    // 128 KB: four slabs of q_hi then four of q_lo
-constexpr int kKVBytesPf = 4 * kSlabKV;  // 16 KB per K or V tile
-constexpr int kPBytes = kBM * 128;       // 16 KB: P tile, per row 32 fp16 of p_hi then 32 of p_lo
-constexpr int kPfSmem = kQBytesPf + 4 * kKVBytesPf + 2 * kPBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int kQBytesPf = 4 * kSlabQ;    // 64 KB: q_hi
+constexpr int kKVBytesPf = 4 * kSlabKV;  // 32 KB per K or V tile
+constexpr int kPfSmem = kQBytesPf + 4 * kKVBytesPf + 1024 /*alignment slack*/ + 256 /*barriers*/;
 constexpr int kPfThreads = 192;
+// TMEM columns (32-bit each, 128 lanes = the 128 query rows)
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kColS = 0, kColO = 128;
+constexpr uint32_t kColS = 0;      // 64: scores of the current tile
+constexpr uint32_t kColP = 64;     // 64: softmax weights as fp16 pairs, p_hi (32 columns) then p_lo (32)
+constexpr uint32_t kColO = 128;    // 256: output accumulator
+constexpr uint32_t kColQlo = 384;  // 128: q_lo as fp16 pairs
 
-enum PfBar { BAR_Q = 0, BAR_KFULL = 1, BAR_KEMPTY = 3, BAR_VFULL = 5, BAR_VEMPTY = 7, BAR_SFULL = 9, BAR_SEMPTY = 11,
-             BAR_PFULL = 13, BAR_PVDONE = 15, BAR_COUNT = 17 };
+enum PfBar { BAR_Q = 0, BAR_QLO = 1, BAR_KFULL = 2, BAR_KEMPTY = 4, BAR_VFULL = 6, BAR_VEMPTY = 8, BAR_SFULL = 10,
+             BAR_SFREE = 11, BAR_PFULL = 12, BAR_PVDONE = 13, BAR_COUNT = 14 };
 
 // ---- PTX wrappers ------------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -98,6 +101,14 @@ __device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uin
     asm volatile(
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(d_tmem),
         "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// A operand in tensor memory: row m of A is TMEM lane m, each 32-bit column holds two K-adjacent
+// 16-bit elements (K = 16 per instruction = 8 columns).
+__device__ __forceinline__ void tc_mma_f16_ta(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 // 32 lanes x 32 consecutive 32-bit columns: thread i of the warp gets its lane's 32 columns
@@ -203,6 +214,7 @@ struct PfParams {
     int n;         // tokens in the run
     int row0;      // cache rows before the run
     int H, Hkv;
+    const __half *q16;        // [n][H][hi(256) | lo(256)]
     const float *q_proj_out;  // gate source: interleaved ...
     const float *gate;        // ... or separate
     float *out;
@@ -218,12 +230,10 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     // 1024-byte aligned tiles (128-byte swizzle atoms are 1024 bytes)
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
-    const uint32_t sQ = base;
+    const uint32_t sQ = base;                  // q_hi, 4 slabs
     const uint32_t sK = sQ + kQBytesPf;        // 2 stages
     const uint32_t sV = sK + 2 * kKVBytesPf;   // 2 stages
-    const uint32_t sP = sV + 2 * kKVBytesPf;   // 2 buffers
-    const uint32_t sBar = sP + 2 * kPBytes;    // BAR_COUNT mbarriers, 8 bytes each
-    unsigned char *sP_gen = smem_raw + (sP - raw);
+    const uint32_t sBar = sV + 2 * kKVBytesPf; // BAR_COUNT mbarriers, 8 bytes each
     auto bar = [&](int i) { return sBar + 8u * (uint32_t)i; };
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -240,16 +250,17 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     if (tid == 0) {
         s_abort = 0;
         mbar_init(bar(BAR_Q), 1);
+        mbar_init(bar(BAR_QLO), 128);
         for (int s = 0; s < 2; s++) {
             mbar_init(bar(BAR_KFULL + s), 1);
             mbar_init(bar(BAR_KEMPTY + s), 1);
             mbar_init(bar(BAR_VFULL + s), 1);
             mbar_init(bar(BAR_VEMPTY + s), 1);
-            mbar_init(bar(BAR_SFULL + s), 1);
-            mbar_init(bar(BAR_SEMPTY + s), 128);
-            mbar_init(bar(BAR_PFULL + s), 128);
-            mbar_init(bar(BAR_PVDONE + s), 1);
         }
+        mbar_init(bar(BAR_SFULL), 1);
+        mbar_init(bar(BAR_SFREE), 128);
+        mbar_init(bar(BAR_PFULL), 128);
+        mbar_init(bar(BAR_PVDONE), 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     if (warp == 5) {
@@ -267,7 +278,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         // ================= TMA producer =================
         if (lane == 0) {
             mbar_expect_tx(bar(BAR_Q), kQBytesPf);
-            for (int s = 0; s < 8; s++) tma_load_2d(sQ + s * kSlabQ, &map_q, head * 2 * kHD + s * 64, t0, bar(BAR_Q));
+            for (int s = 0; s < 4; s++) tma_load_2d(sQ + s * kSlabQ, &map_q, head * 2 * kHD + s * 64, t0, bar(BAR_Q));
             for (int j = 0; j < ntiles; j++) {
                 const int b = j & 1, u = j >> 1;
                 if (u > 0 && !mbar_wait(bar(BAR_KEMPTY + b), (u - 1) & 1, abortp)) break;
@@ -285,18 +296,26 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         if (lane == 0) {
             constexpr uint32_t idesc_s = idesc_f16(kBM, kBN, false);   // S = Q K^T, both K-major
             constexpr uint32_t idesc_o = idesc_f16(kBM, kHD, true);    // O = P V, V is MN-major
+            // descriptors differ only in their start-address field (16-byte units): build once, add offsets
+            const uint64_t dq0 = smem_desc(sQ, 16, 1024);
+            const uint64_t dk0 = smem_desc(sK, 16, 1024);
+            const uint64_t dv0 = smem_desc(sV, kSlabKV, 1024);
             auto issue_s = [&](int j) {
-                const int b = j & 1;
-                const uint32_t d = tmem + kColS + b * kBN;
+                const uint64_t dk = dk0 + (uint64_t)(((j & 1) * kKVBytesPf) >> 4);
 #pragma unroll
-                for (int ks = 0; ks < 2 * kHD / 16; ks++) {  // q_hi slabs 0-3, then q_lo slabs 4-7, against the same K tile
-                    const uint32_t off_a = (ks >> 2) * kSlabQ + (ks & 3) * 32, off_b = ((ks >> 2) & 3) * kSlabKV + (ks & 3) * 32;
-                    tc_mma_f16(d, smem_desc(sQ + off_a, 16, 1024), smem_desc(sK + b * kKVBytesPf + off_b, 16, 1024), idesc_s, ks > 0);
+                for (int ks = 0; ks < kHD / 16; ks++) {  // q_hi from shared memory
+                    const uint32_t off_a = (ks >> 2) * kSlabQ + (ks & 3) * 32, off_b = (ks >> 2) * kSlabKV + (ks & 3) * 32;
+                    tc_mma_f16(tmem + kColS, dq0 + (off_a >> 4), dk + (off_b >> 4), idesc_s, ks > 0);
                 }
-                tc_commit(bar(BAR_SFULL + b));
-                tc_commit(bar(BAR_KEMPTY + b));
+#pragma unroll
+                for (int ks = 0; ks < kHD / 16; ks++) {  // q_lo from tensor memory, same K tile
+                    const uint32_t off_b = (ks >> 2) * kSlabKV + (ks & 3) * 32;
+                    tc_mma_f16_ta(tmem + kColS, tmem + kColQlo + ks * 8, dk + (off_b >> 4), idesc_s, 1);
+                }
+                tc_commit(bar(BAR_SFULL));
+                tc_commit(bar(BAR_KEMPTY + (j & 1)));
             };
-            bool ok = mbar_wait(bar(BAR_Q), 0, abortp) && mbar_wait(bar(BAR_KFULL + 0), 0, abortp);
+            bool ok = mbar_wait(bar(BAR_Q), 0, abortp) && mbar_wait(bar(BAR_QLO), 0, abortp) && mbar_wait(bar(BAR_KFULL + 0), 0, abortp);
             if (ok) {
                 tc_fence_after();
                 issue_s(0);
@@ -304,21 +323,20 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             for (int j = 0; ok && j < ntiles; j++) {
                 const int b = j & 1, u = j >> 1;
                 if (j + 1 < ntiles) {
-                    const int b1 = (j + 1) & 1, u1 = (j + 1) >> 1;
-                    ok = mbar_wait(bar(BAR_KFULL + b1), u1 & 1, abortp);
-                    if (ok && u1 > 0) ok = mbar_wait(bar(BAR_SEMPTY + b1), (u1 - 1) & 1, abortp);
+                    // next scores: their K tile has landed and the softmax threads have read S_j out
+                    ok = mbar_wait(bar(BAR_KFULL + ((j + 1) & 1)), ((j + 1) >> 1) & 1, abortp) && mbar_wait(bar(BAR_SFREE), j & 1, abortp);
                     if (!ok) break;
                     tc_fence_after();
                     issue_s(j + 1);
                 }
-                ok = mbar_wait(bar(BAR_PFULL + b), u & 1, abortp) && mbar_wait(bar(BAR_VFULL + b), u & 1, abortp);
+                ok = mbar_wait(bar(BAR_PFULL), j & 1, abortp) && mbar_wait(bar(BAR_VFULL + b), u & 1, abortp);
                 if (!ok) break;
                 tc_fence_after();
+                const uint64_t dv = dv0 + (uint64_t)((b * kKVBytesPf) >> 4);
 #pragma unroll
-                for (int ks = 0; ks < 2 * kBN / 16; ks++)  // p_hi columns 0-31, then p_lo columns 32-63, against the same V tile
-                    tc_mma_f16(tmem + kColO, smem_desc(sP + b * kPBytes + ks * 32, 16, 1024),
-                               smem_desc(sV + b * kKVBytesPf + (ks & 1) * 2048, kSlabKV, 1024), idesc_o, (j > 0 || ks > 0));
-                tc_commit(bar(BAR_PVDONE + b));
+                for (int ks = 0; ks < 2 * kBN / 16; ks++)  // p_hi (4 k-steps) then p_lo (4) against the same V tile
+                    tc_mma_f16_ta(tmem + kColO, tmem + kColP + ks * 8, dv + (uint64_t)(((ks & 3) * 2048) >> 4), idesc_o, (j > 0 || ks > 0));
+                tc_commit(bar(BAR_PVDONE));
                 tc_commit(bar(BAR_VEMPTY + b));
             }
         }
@@ -327,41 +345,66 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         const int r = tid;                        // row of the tile = TMEM lane
         const int my_last = p.row0 + t0 + r;      // last cache row this query may see
         const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+        // q_lo of this row -> tensor memory (two fp16 per column)
+        {
+            const int t = t0 + r;
+            const uint4 *src = reinterpret_cast<const uint4 *>(p.q16 + ((size_t)t * p.H + head) * 2 * kHD + kHD);
+#pragma unroll 1
+            for (int c = 0; c < 128; c += 32) {
+                uint32_t w[32];
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const uint4 v = t < p.n ? src[(c >> 2) + i] : make_uint4(0u, 0u, 0u, 0u);
+                    w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
+                }
+                tc_st32(tmem + lane_base + kColQlo + c, w);
+            }
+            tc_wait_st();
+            tc_fence_before();
+            mbar_arrive(bar(BAR_QLO));
+        }
         float m_ref = kNegBig, l_sum = 0.f;
         bool ok = true;
         for (int j = 0; j < ntiles; j++) {
-            const int b = j & 1, u = j >> 1;
-            ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_SFULL + b), u & 1, abortp));
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_SFULL), j & 1, abortp));
             if (!ok) break;  // warp-uniform: the tcgen05.ld / st below are warp-collective
             tc_fence_after();
-            uint32_t sr[32];
-            tc_ld32(tmem + lane_base + kColS + b * kBN, sr);
-            tc_wait_ld();
+            uint32_t sr[64];
+            {
+                uint32_t lo[32], hi[32];
+                tc_ld32(tmem + lane_base + kColS, lo);
+                tc_ld32(tmem + lane_base + kColS + 32, hi);
+                tc_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 32; i++) { sr[i] = lo[i]; sr[32 + i] = hi[i]; }
+            }
             tc_fence_before();
-            mbar_arrive(bar(BAR_SEMPTY + b));
-            // causal mask (only tiles that reach past the first query's limit need it)
+            mbar_arrive(bar(BAR_SFREE));
+            // causal mask and row maximum
             float mx = kNegBig;
             const int col0 = j * kBN;
+            if (col0 + kBN - 1 > p.row0 + t0) {  // the tile reaches past the first query's limit
 #pragma unroll
-            for (int i = 0; i < kBN; i++) {
-                float s = __uint_as_float(sr[i]);
-                if (col0 + i > my_last) s = kNegBig;
-                sr[i] = __float_as_uint(s);
-                mx = fmaxf(mx, s);
+                for (int i = 0; i < kBN; i++)
+                    if (col0 + i > my_last) sr[i] = __float_as_uint(kNegBig);
             }
-            // lazy rescale of the accumulator: warp-uniform because tcgen05.ld/st are warp-collective
+#pragma unroll
+            for (int i = 0; i < kBN; i++) mx = fmaxf(mx, __uint_as_float(sr[i]));
             const bool grow = mx > m_ref + 8.f;
-            if (__any_sync(0xffffffffu, grow)) {
+            const bool any_grow = __any_sync(0xffffffffu, grow);
+            // P V of the previous tile must be complete before its P is overwritten (and before the
+            // accumulator is rescaled)
+            if (j > 0) {
+                ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_PVDONE), (j - 1) & 1, abortp));
+                if (!ok) break;
+                tc_fence_after();
+            }
+            if (any_grow) {  // lazy rescale, warp-uniform because tcgen05.ld/st are warp-collective
                 const float m_new = grow ? mx : m_ref;
                 const float corr = fast_exp2(m_ref - m_new);
                 m_ref = m_new;
                 l_sum *= corr;
                 if (j > 0) {
-                    // the previous P V must have landed in the accumulator
-                    const int bp = (j - 1) & 1, up = (j - 1) >> 1;
-                    ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_PVDONE + bp), up & 1, abortp));
-                    if (!ok) break;
-                    tc_fence_after();
 #pragma unroll 1
                     for (int c = 0; c < kHD; c += 32) {
                         uint32_t o[32];
@@ -371,41 +414,29 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                         for (int i = 0; i < 32; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
                         tc_st32(tmem + lane_base + kColO + c, o);
                     }
-                    tc_wait_st();
                 }
             }
-            // the P buffer must be free: P V of tile j-2 done
-            if (u > 0) {
-                ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_PVDONE + b), (u - 1) & 1, abortp));
-                if (!ok) break;
-            }
-            unsigned char *prow = sP_gen + b * kPBytes + r * 128;
+            // weights as two fp16 terms, packed two per column: p_hi -> columns 0..31, p_lo -> 32..63
+            uint32_t ph[32], pl[32];
 #pragma unroll
-            for (int c = 0; c < 4; c++) {  // 16-byte chunk c holds p_hi of 8 columns, chunk 4 + c their p_lo
-                uint32_t wh[4], wl[4];
-#pragma unroll
-                for (int e = 0; e < 4; e++) {
-                    const float p0 = fast_exp2(__uint_as_float(sr[c * 8 + 2 * e]) - m_ref);
-                    const float p1 = fast_exp2(__uint_as_float(sr[c * 8 + 2 * e + 1]) - m_ref);
-                    l_sum += p0 + p1;
-                    const __half2 hh = __floats2half2_rn(p0, p1);
-                    const float2 hf = __half22float2(hh);
-                    const __half2 ll = __floats2half2_rn(p0 - hf.x, p1 - hf.y);
-                    wh[e] = *reinterpret_cast<const uint32_t *>(&hh);
-                    wl[e] = *reinterpret_cast<const uint32_t *>(&ll);
-                }
-                *reinterpret_cast<uint4 *>(prow + ((c ^ (r & 7)) << 4)) = make_uint4(wh[0], wh[1], wh[2], wh[3]);
-                *reinterpret_cast<uint4 *>(prow + (((4 + c) ^ (r & 7)) << 4)) = make_uint4(wl[0], wl[1], wl[2], wl[3]);
+            for (int i = 0; i < 32; i++) {
+                const float p0 = fast_exp2(__uint_as_float(sr[2 * i]) - m_ref);
+                const float p1 = fast_exp2(__uint_as_float(sr[2 * i + 1]) - m_ref);
+                l_sum += p0 + p1;
+                const __half2 hh = __floats2half2_rn(p0, p1);
+                const float2 hf = __half22float2(hh);
+                const __half2 ll = __floats2half2_rn(p0 - hf.x, p1 - hf.y);
+                ph[i] = *reinterpret_cast<const uint32_t *>(&hh);
+                pl[i] = *reinterpret_cast<const uint32_t *>(&ll);
             }
-            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            tc_st32(tmem + lane_base + kColP, ph);
+            tc_st32(tmem + lane_base + kColP + 32, pl);
+            tc_wait_st();
             tc_fence_before();
-            mbar_arrive(bar(BAR_PFULL + b));
+            mbar_arrive(bar(BAR_PFULL));
         }
         // epilogue
-        if (ok && ntiles > 0) {
-            const int bl = (ntiles - 1) & 1, ul = (ntiles - 1) >> 1;
-            ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_PVDONE + bl), ul & 1, abortp));
-        }
+        if (ok && ntiles > 0) ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_PVDONE), (ntiles - 1) & 1, abortp));
         if (ok) {
             tc_fence_after();
             const int t = t0 + r;
@@ -487,6 +518,7 @@ int launch_attn_prefill(const KvView &kv, const RopeParams &rope, int seq, int s
     attn_kv_f16_kernel<<<L, 256, 0, st>>>(kv, seq, L, reinterpret_cast<__half *>(wk.k16), reinterpret_cast<__half *>(wk.v16));
     PfParams p;
     p.n = n; p.row0 = row0; p.H = H; p.Hkv = kv.Hkv;
+    p.q16 = reinterpret_cast<const __half *>(wk.q16);
     p.q_proj_out = q_proj_out; p.gate = gate; p.out = out; p.err = wk.err;
     attn_prefill_kernel<<<dim3((n + kBM - 1) / kBM, H), kPfThreads, kPfSmem, st>>>(mq, mk, mv, p);
     return cudaGetLastError() == cudaSuccess ? 3 : -1;
