@@ -275,7 +275,9 @@ def run_ours(args):
                 "peak_source": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs)" if peak_kind == "measured" else "fallback 6650 GB/s",
                 "unit": "GB/s", "frac": achieved / peak if achieved else None,
                 "us_per_launch": kern_s * 1e6, "launches_timed": n_kern,
-                "algorithmic_bytes_per_launch": alg_bytes_launch, "traffic": TRAFFIC_NCU}
+                "algorithmic_bytes_per_launch": alg_bytes_launch,
+                "traffic": TRAFFIC_NCU_1SEQ_128K * (B / world) * (L_mean / 131073.0),
+                "traffic_source": "ncu capture at batch 1, scaled by sequences x rows per launch"}
 
     # ---- end to end through the C-ABI with host buffers (rank-local copies inside the timed region) ----
     e2e = None
@@ -353,9 +355,10 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-# DRAM bytes (read + write) of one attn_decode_kernel launch from the committed ncu capture,
-# scaled to the bench launch; None until a capture exists (see profiles/).
-TRAFFIC_NCU = None
+# DRAM bytes (read + write) of one attn_decode_kernel launch for ONE sequence at 131073 rows, from
+# the committed ncu capture (profiles/attn_decode_kernel_b1_ctx128k_ncu.md): 268.96 MB + 5.49 MB.
+# Traffic grows in proportion to rows x sequences, so the bench launch is scaled from it.
+TRAFFIC_NCU_1SEQ_128K = 274.45e6
 
 
 def extra_measurements(pkg, torch, dev, peak, only=None):

@@ -14,8 +14,11 @@ CSRC = HERE / "csrc"
 OBJ = HERE / "build"
 LIB = HERE / "libfm_b200.so"
 
+import os
+
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-              "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-Xptxas", "-v"]
+              "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-Xptxas", "-v",
+              *os.environ.get("FM_EXTRA_NVCC_FLAGS", "").split()]
 
 
 def sources():

@@ -210,7 +210,21 @@ __global__ void attn_kv_f16_kernel(KvView kv, int seq, int L, __half *__restrict
 }
 
 // ---- the attention kernel ----------------------------------------------------------------------
+// Optional per-tile clock trace of one CTA (development builds only: -DFM_PF_TRACE).
+#ifdef FM_PF_TRACE
+extern "C" {
+long long *fm_pf_trace = nullptr;  // device buffer, [64 tiles][8 events]
+}
+#define PF_TR(slot)                                                                           \
+    do {                                                                                      \
+        if (p.trace && blockIdx.x == 0 && blockIdx.y == 0 && j < 64) p.trace[j * 8 + (slot)] = clock64(); \
+    } while (0)
+#else
+#define PF_TR(slot) do { } while (0)
+#endif
+
 struct PfParams {
+    long long *trace;
     int n;         // tokens in the run
     int row0;      // cache rows before the run
     int H, Hkv;
@@ -327,17 +341,21 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     ok = mbar_wait(bar(BAR_KFULL + ((j + 1) & 1)), ((j + 1) >> 1) & 1, abortp) && mbar_wait(bar(BAR_SFREE), j & 1, abortp);
                     if (!ok) break;
                     tc_fence_after();
+                    PF_TR(4);
                     issue_s(j + 1);
+                    PF_TR(5);
                 }
                 ok = mbar_wait(bar(BAR_PFULL), j & 1, abortp) && mbar_wait(bar(BAR_VFULL + b), u & 1, abortp);
                 if (!ok) break;
                 tc_fence_after();
+                PF_TR(6);
                 const uint64_t dv = dv0 + (uint64_t)((b * kKVBytesPf) >> 4);
 #pragma unroll
                 for (int ks = 0; ks < 2 * kBN / 16; ks++)  // p_hi (4 k-steps) then p_lo (4) against the same V tile
                     tc_mma_f16_ta(tmem + kColO, tmem + kColP + ks * 8, dv + (uint64_t)(((ks & 3) * 2048) >> 4), idesc_o, (j > 0 || ks > 0));
                 tc_commit(bar(BAR_PVDONE));
                 tc_commit(bar(BAR_VEMPTY + b));
+                PF_TR(7);
             }
         }
     } else {
@@ -369,6 +387,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_SFULL), j & 1, abortp));
             if (!ok) break;  // warp-uniform: the tcgen05.ld / st below are warp-collective
             tc_fence_after();
+            if (tid == 0) PF_TR(0);
             uint32_t sr[64];
             {
                 uint32_t lo[32], hi[32];
@@ -380,6 +399,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             }
             tc_fence_before();
             mbar_arrive(bar(BAR_SFREE));
+            if (tid == 0) PF_TR(1);
             // causal mask and row maximum
             float mx = kNegBig;
             const int col0 = j * kBN;
@@ -399,6 +419,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 if (!ok) break;
                 tc_fence_after();
             }
+            if (tid == 0) PF_TR(2);
             if (any_grow) {  // lazy rescale, warp-uniform because tcgen05.ld/st are warp-collective
                 const float m_new = grow ? mx : m_ref;
                 const float corr = fast_exp2(m_ref - m_new);
@@ -434,6 +455,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             tc_wait_st();
             tc_fence_before();
             mbar_arrive(bar(BAR_PFULL));
+            if (tid == 0) PF_TR(3);
         }
         // epilogue
         if (ok && ntiles > 0) ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_PVDONE), (ntiles - 1) & 1, abortp));
@@ -518,6 +540,11 @@ int launch_attn_prefill(const KvView &kv, const RopeParams &rope, int seq, int s
     attn_kv_f16_kernel<<<L, 256, 0, st>>>(kv, seq, L, reinterpret_cast<__half *>(wk.k16), reinterpret_cast<__half *>(wk.v16));
     PfParams p;
     p.n = n; p.row0 = row0; p.H = H; p.Hkv = kv.Hkv;
+#ifdef FM_PF_TRACE
+    p.trace = fm_pf_trace;
+#else
+    p.trace = nullptr;
+#endif
     p.q16 = reinterpret_cast<const __half *>(wk.q16);
     p.q_proj_out = q_proj_out; p.gate = gate; p.out = out; p.err = wk.err;
     attn_prefill_kernel<<<dim3((n + kBM - 1) / kBM, H), kPfThreads, kPfSmem, st>>>(mq, mk, mv, p);
