@@ -183,13 +183,13 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     # mesh: KV-head groups x sequence shards
-    hg = min(HKV, world)
-    ss = world // hg
-    my_hg, my_ss = rank % hg, rank // hg
+    mesh = pkg.sharding.mesh_for(world, HKV)
+    hg, ss = mesh.head_groups, mesh.seq_shards
+    my_hg, my_ss = mesh.coords(rank)
     seq_group = None
     if ss > 1:
         for g_ in range(hg):
-            grp = dist.new_group([r for r in range(world) if r % hg == g_])
+            grp = dist.new_group(mesh.seq_group_ranks(g_))
             if g_ == my_hg:
                 seq_group = grp
     Hl, Hkvl = H // hg, HKV // hg

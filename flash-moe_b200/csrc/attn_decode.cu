@@ -383,10 +383,10 @@ __global__ void attn_merge_kernel(const float *__restrict__ part_o, const float 
                                    : gate + ((size_t)tok * H + head) * D + d;
     const float4 g = *reinterpret_cast<const float4 *>(gsrc);
     float4 r;
-    r.x = acc.x * inv * (1.0f / (1.0f + __expf(-g.x)));
-    r.y = acc.y * inv * (1.0f / (1.0f + __expf(-g.y)));
-    r.z = acc.z * inv * (1.0f / (1.0f + __expf(-g.z)));
-    r.w = acc.w * inv * (1.0f / (1.0f + __expf(-g.w)));
+    r.x = acc.x * inv * fast_sigmoid(g.x);
+    r.y = acc.y * inv * fast_sigmoid(g.y);
+    r.z = acc.z * inv * fast_sigmoid(g.z);
+    r.w = acc.w * inv * fast_sigmoid(g.w);
     *reinterpret_cast<float4 *>(dst) = r;
 }
 

@@ -159,36 +159,67 @@ __host__ __device__ constexpr uint32_t idesc_f16(int M, int N, bool b_mn_major) 
 }
 
 // ---- q preparation: norm, RoPE, scale -> fp16 [n][H][hi(256) | lo(256)] ------------------------
-// grid (H, n), 256 threads
-__global__ void attn_q_prep_kernel(RopeParams rope, int H, int start_pos, const float *__restrict__ q_proj_out,
-                                   const float *__restrict__ q_in, const uint16_t *__restrict__ qnw, float eps,
-                                   __half *__restrict__ q16) {
-    __shared__ float sx[kHD];
-    __shared__ float sred[8];
-    const int h = blockIdx.x, t = blockIdx.y, d = threadIdx.x;
-    const float *src = q_proj_out ? q_proj_out + ((size_t)t * H + h) * 2 * kHD : q_in + ((size_t)t * H + h) * kHD;
-    float x = src[d];
-    if (qnw != nullptr) {
-        const float ss = warp_sum(x * x);
-        if ((d & 31) == 0) sred[d >> 5] = ss;
-        __syncthreads();
-        float tot = 0.f;
-        for (int w = 0; w < 8; w++) tot += sred[w];
-        x = x * (1.0f / sqrtf(tot / kHD + eps)) * bf16_bits_to_float(qnw[d]);
-    }
-    sx[d] = x;
-    __syncthreads();
+// grid (n), 256 threads: the rotation table of the token is built once, then each warp walks heads
+// (a lane holds 8 consecutive dims of the head).
+__global__ void __launch_bounds__(256)
+attn_q_prep_kernel(RopeParams rope, int H, int start_pos, const float *__restrict__ q_proj_out,
+                   const float *__restrict__ q_in, const uint16_t *__restrict__ qnw, float eps,
+                   __half *__restrict__ q16) {
+    __shared__ float s_cos[64], s_sin[64];
+    __shared__ float s_x[8][kHD];
+    const int t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int half = rope.rotary_dim / 2;
-    if (d < rope.rotary_dim) {
-        const int i = d < half ? d : d - half;
-        const float ang = ((float)(start_pos + t) / rope.pos_div) * rope.inv_freq[i];
-        const float c = cosf(ang), s = sinf(ang);
-        x = d < half ? x * c - sx[d + half] * s : sx[d - half] * s + x * c;
+    if (tid < half) {
+        const float ang = ((float)(start_pos + t) / rope.pos_div) * rope.inv_freq[tid];
+        s_cos[tid] = cosf(ang);
+        s_sin[tid] = sinf(ang);
     }
-    const float y = x * rope.logit_scale * kLog2e;
-    const __half hi = __float2half_rn(y);
-    q16[((size_t)t * H + h) * 2 * kHD + d] = hi;                                         // q_hi
-    q16[((size_t)t * H + h) * 2 * kHD + kHD + d] = __float2half_rn(y - __half2float(hi));  // q_lo
+    __syncthreads();
+    const float qscale = rope.logit_scale * kLog2e;
+    float w8[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) w8[j] = qnw ? bf16_bits_to_float(qnw[lane * 8 + j]) : 1.0f;
+    for (int h = warp; h < H; h += 8) {
+        const float *src = q_proj_out ? q_proj_out + ((size_t)t * H + h) * 2 * kHD : q_in + ((size_t)t * H + h) * kHD;
+        const float4 a = __ldg(reinterpret_cast<const float4 *>(src + lane * 8));
+        const float4 b = __ldg(reinterpret_cast<const float4 *>(src + lane * 8 + 4));
+        float x[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+        if (qnw != nullptr) {
+            float ss = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; j++) ss += x[j] * x[j];
+            ss = warp_sum(ss);
+            const float inv = 1.0f / sqrtf(ss / kHD + eps);
+#pragma unroll
+            for (int j = 0; j < 8; j++) x[j] = x[j] * inv * w8[j];
+        }
+        float *sx = s_x[warp];
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 8; j++) sx[lane * 8 + j] = x[j];
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const int d = lane * 8 + j;
+            if (d < rope.rotary_dim) {
+                const int i = d < half ? d : d - half;
+                x[j] = d < half ? x[j] * s_cos[i] - sx[d + half] * s_sin[i] : sx[d - half] * s_sin[i] + x[j] * s_cos[i];
+            }
+        }
+        uint32_t hi[4], lo[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const float y0 = x[2 * j] * qscale, y1 = x[2 * j + 1] * qscale;
+            const __half2 hh = __floats2half2_rn(y0, y1);
+            const float2 hf = __half22float2(hh);
+            const __half2 ll = __floats2half2_rn(y0 - hf.x, y1 - hf.y);
+            hi[j] = *reinterpret_cast<const uint32_t *>(&hh);
+            lo[j] = *reinterpret_cast<const uint32_t *>(&ll);
+        }
+        __half *dst = q16 + ((size_t)t * H + h) * 2 * kHD + lane * 8;
+        *reinterpret_cast<uint4 *>(dst) = make_uint4(hi[0], hi[1], hi[2], hi[3]);        // q_hi
+        *reinterpret_cast<uint4 *>(dst + kHD) = make_uint4(lo[0], lo[1], lo[2], lo[3]);  // q_lo
+    }
 }
 
 // ---- K, V rows [0, L) of one sequence: bf16 pages -> fp16 [L][Hkv*256] --------------------------
@@ -219,8 +250,18 @@ long long *fm_pf_trace = nullptr;  // device buffer, [64 tiles][8 events]
     do {                                                                                      \
         if (p.trace && blockIdx.x == 0 && blockIdx.y == 0 && j < 64) p.trace[j * 8 + (slot)] = clock64(); \
     } while (0)
+__device__ __forceinline__ long long pf_gtime() {
+    long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define PF_CTA(k)                                                                                  \
+    do {                                                                                           \
+        if (p.trace && threadIdx.x == 0) p.trace[512 + (blockIdx.x * gridDim.y + blockIdx.y) * 8 + (k)] = pf_gtime(); \
+    } while (0)
 #else
 #define PF_TR(slot) do { } while (0)
+#define PF_CTA(k) do { } while (0)
 #endif
 
 struct PfParams {
@@ -251,10 +292,12 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     auto bar = [&](int i) { return sBar + 8u * (uint32_t)i; };
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    // heavy tiles first: blockIdx.x = 0 is the last (longest) query tile
-    const int nqt = gridDim.x;
-    const int qt = nqt - 1 - blockIdx.x;
-    const int head = blockIdx.y;
+    PF_CTA(0);
+    // heavy tiles first: CTAs are handed out in linear order (x fastest), so x walks the heads and
+    // y = 0 is the last (longest) query tile of every head
+    const int nqt = gridDim.y;
+    const int qt = nqt - 1 - blockIdx.y;
+    const int head = blockIdx.x;
     const int kvh = head / (p.H / p.Hkv);
     const int t0 = qt * kBM;
     const int L = p.row0 + p.n;
@@ -368,14 +411,17 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             const int t = t0 + r;
             const uint4 *src = reinterpret_cast<const uint4 *>(p.q16 + ((size_t)t * p.H + head) * 2 * kHD + kHD);
 #pragma unroll 1
-            for (int c = 0; c < 128; c += 32) {
-                uint32_t w[32];
+            for (int c = 0; c < 128; c += 64) {  // 16 loads of 16 bytes in flight per pass
+                uint32_t w0[32], w1[32];
 #pragma unroll
                 for (int i = 0; i < 8; i++) {
-                    const uint4 v = t < p.n ? src[(c >> 2) + i] : make_uint4(0u, 0u, 0u, 0u);
-                    w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
+                    const uint4 v = t < p.n ? __ldg(src + (c >> 2) + i) : make_uint4(0u, 0u, 0u, 0u);
+                    const uint4 u = t < p.n ? __ldg(src + (c >> 2) + 8 + i) : make_uint4(0u, 0u, 0u, 0u);
+                    w0[4 * i] = v.x; w0[4 * i + 1] = v.y; w0[4 * i + 2] = v.z; w0[4 * i + 3] = v.w;
+                    w1[4 * i] = u.x; w1[4 * i + 1] = u.y; w1[4 * i + 2] = u.z; w1[4 * i + 3] = u.w;
                 }
-                tc_st32(tmem + lane_base + kColQlo + c, w);
+                tc_st32(tmem + lane_base + kColQlo + c, w0);
+                tc_st32(tmem + lane_base + kColQlo + c + 32, w1);
             }
             tc_wait_st();
             tc_fence_before();
@@ -383,6 +429,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         }
         float m_ref = kNegBig, l_sum = 0.f;
         bool ok = true;
+        PF_CTA(1);
         for (int j = 0; j < ntiles; j++) {
             ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_SFULL), j & 1, abortp));
             if (!ok) break;  // warp-uniform: the tcgen05.ld / st below are warp-collective
@@ -459,36 +506,65 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         }
         // epilogue
         if (ok && ntiles > 0) ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_PVDONE), (ntiles - 1) & 1, abortp));
+        PF_CTA(2);
         if (ok) {
+            // All MMAs have completed, so every K / V / q tile in shared memory is dead.  Each thread
+            // gates its own row in registers -- the gate row comes straight from global memory through
+            // read-only 16-byte loads, one chunk ahead -- and parks the result in shared memory at a
+            // pitch of 1040 bytes (conflict-free 128-bit stores, rows still contiguous); every row then
+            // leaves through one 1 KB bulk asynchronous copy.
             tc_fence_after();
-            const int t = t0 + r;
+            constexpr uint32_t kPitch = 1040;
             const float inv = l_sum > 0.f ? 1.0f / l_sum : 0.f;
-            const size_t orow = ((size_t)t * p.H + head) * kHD;
-            const float *grow_ptr = p.q_proj_out ? p.q_proj_out + ((size_t)t * p.H + head) * 2 * kHD + kHD : p.gate + orow;
+            const int t = t0 + r;
+            const bool live = t < p.n;
+            const float4 *gp = reinterpret_cast<const float4 *>(
+                p.q_proj_out ? p.q_proj_out + ((size_t)(live ? t : 0) * p.H + head) * 2 * kHD + kHD
+                             : p.gate + ((size_t)(live ? t : 0) * p.H + head) * kHD);
+            float4 gn[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) gn[i] = __ldg(gp + i);
+            PF_CTA(4);
 #pragma unroll 1
             for (int c = 0; c < kHD; c += 32) {
                 uint32_t o[32];
                 tc_ld32(tmem + lane_base + kColO + c, o);
-                tc_wait_ld();
-                if (t < p.n) {
+                float4 g[8];
 #pragma unroll
-                    for (int i = 0; i < 32; i += 4) {
-                        const float4 g = *reinterpret_cast<const float4 *>(grow_ptr + c + i);
-                        float4 y;
-                        y.x = __uint_as_float(o[i]) * inv / (1.0f + __expf(-g.x));
-                        y.y = __uint_as_float(o[i + 1]) * inv / (1.0f + __expf(-g.y));
-                        y.z = __uint_as_float(o[i + 2]) * inv / (1.0f + __expf(-g.z));
-                        y.w = __uint_as_float(o[i + 3]) * inv / (1.0f + __expf(-g.w));
-                        *reinterpret_cast<float4 *>(p.out + orow + c + i) = y;
-                    }
+                for (int i = 0; i < 8; i++) g[i] = gn[i];
+                if (c + 32 < kHD) {
+#pragma unroll
+                    for (int i = 0; i < 8; i++) gn[i] = __ldg(gp + ((c + 32) >> 2) + i);
+                }
+                tc_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const float y0 = __uint_as_float(o[4 * i]) * inv * fast_sigmoid(g[i].x);
+                    const float y1 = __uint_as_float(o[4 * i + 1]) * inv * fast_sigmoid(g[i].y);
+                    const float y2 = __uint_as_float(o[4 * i + 2]) * inv * fast_sigmoid(g[i].z);
+                    const float y3 = __uint_as_float(o[4 * i + 3]) * inv * fast_sigmoid(g[i].w);
+                    asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};\n" ::"r"(sQ + r * kPitch + (c + 4 * i) * 4), "f"(y0), "f"(y1),
+                                 "f"(y2), "f"(y3)
+                                 : "memory");
                 }
             }
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            PF_CTA(5);
+            if (live) {
+                float *orow = p.out + ((size_t)t * p.H + head) * kHD;
+                asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], 1024;\n" ::"l"(orow), "r"(sQ + r * kPitch) : "memory");
+            }
+            asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
+            // shared memory must stay valid until the bulk copies have read it
+            asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");
         }
     }
     // ---- wind down: everyone meets, TMEM goes back ----
+    PF_CTA(6);
     tc_fence_before();
     __syncthreads();
-    if (s_abort && tid == 0) atomicCAS(p.err, 0, (1 << 16) | (blockIdx.y << 8) | (blockIdx.x & 0xff));
+    PF_CTA(3);
+    if (s_abort && tid == 0) atomicCAS(p.err, 0, (1 << 16) | ((blockIdx.y & 0xff) << 8) | (blockIdx.x & 0xff));
     if (warp == 5) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(kTmemCols) : "memory");
@@ -536,7 +612,7 @@ int launch_attn_prefill(const KvView &kv, const RopeParams &rope, int seq, int s
     if (!make_map(&mq, wk.q16, (uint64_t)n, (uint64_t)H * 2 * kHD, kBM) || !make_map(&mk, wk.k16, (uint64_t)L, (uint64_t)kv.Hkv * kHD, kBN) ||
         !make_map(&mv, wk.v16, (uint64_t)L, (uint64_t)kv.Hkv * kHD, kBN))
         return -1;
-    attn_q_prep_kernel<<<dim3(H, n), kHD, 0, st>>>(rope, H, start_pos, q_proj_out, q, q_norm_w, eps, reinterpret_cast<__half *>(wk.q16));
+    attn_q_prep_kernel<<<n, 256, 0, st>>>(rope, H, start_pos, q_proj_out, q, q_norm_w, eps, reinterpret_cast<__half *>(wk.q16));
     attn_kv_f16_kernel<<<L, 256, 0, st>>>(kv, seq, L, reinterpret_cast<__half *>(wk.k16), reinterpret_cast<__half *>(wk.v16));
     PfParams p;
     p.n = n; p.row0 = row0; p.H = H; p.Hkv = kv.Hkv;
@@ -547,7 +623,7 @@ int launch_attn_prefill(const KvView &kv, const RopeParams &rope, int seq, int s
 #endif
     p.q16 = reinterpret_cast<const __half *>(wk.q16);
     p.q_proj_out = q_proj_out; p.gate = gate; p.out = out; p.err = wk.err;
-    attn_prefill_kernel<<<dim3((n + kBM - 1) / kBM, H), kPfThreads, kPfSmem, st>>>(mq, mk, mv, p);
+    attn_prefill_kernel<<<dim3(H, (n + kBM - 1) / kBM), kPfThreads, kPfSmem, st>>>(mq, mk, mv, p);
     return cudaGetLastError() == cudaSuccess ? 3 : -1;
 }
 

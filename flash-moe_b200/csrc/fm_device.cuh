@@ -70,6 +70,14 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
+__device__ __forceinline__ float fast_rcp(float x) {
+    float y;
+    asm volatile("rcp.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+// 1 / (1 + e^-x) from the two special-function approximations (ex2: 2 ulp, rcp: 1 ulp)
+__device__ __forceinline__ float fast_sigmoid(float x) { return fast_rcp(1.0f + fast_exp2(-1.4426950408889634f * x)); }
+
 __device__ __forceinline__ float bf16_bits_to_float(uint16_t b) {
     return __uint_as_float(static_cast<uint32_t>(b) << 16);
 }
