@@ -216,12 +216,24 @@ def run_ours(args):
     o_part = torch.empty((B, Hl, D), device=dev); ml_part = torch.empty((B, Hl, 2), device=dev)
     o_all = torch.empty((ss, B, Hl, D), device=dev); ml_all = torch.empty((ss, B, Hl, 2), device=dev)
     cur = [L]
+    p2p = ss > 1 and args.exchange == "p2p"
+    if p2p:
+        # exchange buffers the ranks of a sequence group map for each other (symmetric memory);
+        # the library then moves the partial results itself with peer stores, no collective call
+        import torch.distributed._symmetric_memory as symm
+        xbuf = symm.empty(ctx.exchange_bytes(ss) // 4, dtype=torch.float32, device=dev)
+        hdl = symm.rendezvous(xbuf, group=seq_group)
+        ctx.exchange_attach(hdl.rank, list(hdl.buffer_ptrs))
+        torch.cuda.synchronize()
+        dist.barrier()
 
     def step():
         pos = [cur[0]] * B
         for layer in range(NL):
             if ss == 1:
                 ctx.attn_decode(layer, seqs, pos, out[layer], q_proj_out=qp[layer], k=kn[layer], v=vn[layer])
+            elif p2p:
+                ctx.attn_decode_exchange(layer, seqs, pos, out[layer], q_proj_out=qp[layer], k=kn[layer], v=vn[layer])
             else:
                 ctx.attn_decode_partial(layer, seqs, pos, o_part, ml_part, q_proj_out=qp[layer], k=kn[layer], v=vn[layer])
                 dist.all_gather_into_tensor(o_all, o_part, group=seq_group)
@@ -292,6 +304,8 @@ def run_ours(args):
             for layer in range(NL):
                 if ss == 1:
                     ctx.attn_decode(layer, seqs, pos, h_out[layer], q_proj_out=h_qp[layer], k=h_k[layer], v=h_v[layer])
+                elif p2p:
+                    ctx.attn_decode_exchange(layer, seqs, pos, h_out[layer], q_proj_out=h_qp[layer], k=h_k[layer], v=h_v[layer])
                 else:
                     ctx.attn_decode_partial(layer, seqs, pos, h_o, h_ml, q_proj_out=h_qp[layer], k=h_k[layer], v=h_v[layer])
                     o_part.copy_(torch.from_numpy(h_o)); ml_part.copy_(torch.from_numpy(h_ml))
@@ -343,6 +357,8 @@ def run_ours(args):
             "data": "synthetic",
             "config": {"workload": workload_name(args), "batch": B, "ctx": L, "layers": NL,
                        "parallelism": f"kv-head groups {hg} x sequence shards {ss}",
+                       "exchange": ("none" if ss == 1 else "peer stores + flags (fm_attn_decode_exchange)" if p2p
+                                    else "NCCL all-gather + fm_attn_merge_gate"),
                        "l2": "inputs larger than L2 (KV streamed per step: %.1f GB)" % (kv_bytes_step / 1e9)},
             "us_per_layer": ms_step * 1e3 / NL,
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches),
@@ -537,6 +553,8 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=10)
     ap.add_argument("--no-extra", action="store_true", help="skip the context sweep / prefill / GatedDeltaNet figures")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"],
+                    help="how sequence shards exchange partial results: the library's peer-memory kernels, or NCCL all-gathers")
     ap.add_argument("--probe", default=None, choices=["sweep", "prefill", "gdn_decode", "gdn_prefill"],
                     help="run only one of the extra measurements and print it (for profiling one kernel)")
     args = ap.parse_args()

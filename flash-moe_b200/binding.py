@@ -22,7 +22,8 @@ EXPORTS = [
     "fm_attn_decode", "fm_attn_decode_partial", "fm_attn_merge_gate", "fm_attn_prefill",
     "fm_gdn_decode", "fm_gdn_prefill", "fm_kv_export", "fm_kv_import", "fm_state_export",
     "fm_state_import", "fm_launch_count", "fm_profile_enable", "fm_profile_read",
-    "fm_attn_decode_static",
+    "fm_attn_decode_static", "fm_exchange_bytes", "fm_exchange_attach", "fm_attn_decode_exchange_push",
+    "fm_attn_decode_exchange_merge", "fm_attn_decode_exchange",
 ]
 
 
@@ -71,6 +72,8 @@ def load_library() -> C.CDLL:
     lib.fm_destroy.restype = None
     lib.fm_destroy.argtypes = [C.c_void_p]
     lib.fm_default_config.restype = None
+    lib.fm_exchange_bytes.restype = C.c_size_t
+    lib.fm_exchange_bytes.argtypes = [C.c_void_p, C.c_int]
     return lib
 
 
@@ -185,6 +188,30 @@ class Context:
     def attn_merge_gate(self, nparts, o_parts, ml_parts, batch, out, q_proj_out=None, gate=None):
         self._check(self.lib.fm_attn_merge_gate(self.h, C.c_int(nparts), _ptr(o_parts), _ptr(ml_parts),
                                                 _ptr(q_proj_out), _ptr(gate), C.c_int(batch), _ptr(out)))
+
+    def exchange_bytes(self, nranks: int) -> int:
+        return self.lib.fm_exchange_bytes(self.h, C.c_int(nranks))
+
+    def exchange_attach(self, my_index: int, peer_ptrs):
+        """peer_ptrs: device addresses (ints) of every rank's exchange buffer as mapped in this process."""
+        arr = (C.c_void_p * len(peer_ptrs))(*[C.c_void_p(int(p)) for p in peer_ptrs])
+        self._check(self.lib.fm_exchange_attach(self.h, C.c_int(len(peer_ptrs)), C.c_int(my_index), arr))
+
+    def attn_decode_exchange_push(self, fa_idx, seq, pos, q_proj_out=None, q=None, k=None, v=None, q_norm_w=None,
+                                  k_norm_w=None):
+        s, sp = _ints(seq); p, pp = _ints(pos)
+        self._check(self.lib.fm_attn_decode_exchange_push(self.h, C.c_int(fa_idx), sp, pp, C.c_int(len(s)), _ptr(q_proj_out),
+                                                          _ptr(q), _ptr(k), _ptr(v), _ptr(q_norm_w), _ptr(k_norm_w)))
+
+    def attn_decode_exchange_merge(self, batch, out, q_proj_out=None, gate=None):
+        self._check(self.lib.fm_attn_decode_exchange_merge(self.h, C.c_int(batch), _ptr(q_proj_out), _ptr(gate), _ptr(out)))
+
+    def attn_decode_exchange(self, fa_idx, seq, pos, out, q_proj_out=None, q=None, gate=None, k=None, v=None,
+                             q_norm_w=None, k_norm_w=None):
+        s, sp = _ints(seq); p, pp = _ints(pos)
+        self._check(self.lib.fm_attn_decode_exchange(self.h, C.c_int(fa_idx), sp, pp, C.c_int(len(s)), _ptr(q_proj_out),
+                                                     _ptr(q), _ptr(gate), _ptr(k), _ptr(v), _ptr(q_norm_w),
+                                                     _ptr(k_norm_w), _ptr(out)))
 
     def attn_prefill(self, fa_idx, seq, start_pos, n, out, q_proj_out=None, q=None, gate=None, k=None,
                      v=None, q_norm_w=None, k_norm_w=None):

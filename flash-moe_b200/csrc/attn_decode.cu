@@ -402,3 +402,128 @@ int launch_attn_merge(const float *part_o, const float *part_ml, int nparts, lon
 }
 
 }  // namespace fm
+
+// ---- cross-GPU exchange of partial results over peer memory -----------------------------------
+// Each rank of a sequence group owns an exchange buffer that its peers can address (plain peer
+// stores over NVLink; no multicast, no collective library call):
+//     slots [2 (step parity)][nranks (source)][cap tokens][H][D + 2] floats, then flags [2][nranks].
+// attn_merge_push_kernel merges the local split partials of one (token, head) and stores the result
+// (un-normalised O, running max, sum) into slot [parity][me] of EVERY rank's buffer; the last CTA
+// to finish publishes the step number in every rank's flag [parity][me].  attn_wait_merge_kernel
+// waits -- for a bounded time -- until the flags of all sources show the step, then merges the
+// nranks partials by log-sum-exp and applies the gate.  The two are separate launches: no CTA waits
+// for another CTA of its own GPU, so nothing depends on co-residency.
+
+namespace fm {
+
+__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// grid (H, tokens), D/4 threads
+__global__ void attn_merge_push_kernel(const float *__restrict__ part_o, const float *__restrict__ part_ml, int nsplits, int H,
+                                       XchgView x, uint32_t step, unsigned int *__restrict__ done_counter) {
+    constexpr int D = kD;
+    const int head = blockIdx.x, tok = blockIdx.y, d = threadIdx.x * 4;
+    const float *o0 = part_o + ((size_t)tok * H + head) * nsplits * D;
+    const float *ml0 = part_ml + ((size_t)tok * H + head) * nsplits * 2;
+    float M = kNegBig;
+    for (int j = 0; j < nsplits; j++) M = fmaxf(M, ml0[j * 2]);
+    float lt = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int j = 0; j < nsplits; j++) {
+        const float w = fast_exp2(ml0[j * 2] - M);
+        lt += w * ml0[j * 2 + 1];
+        const float4 v = *reinterpret_cast<const float4 *>(o0 + (size_t)j * D + d);
+        acc.x += w * v.x; acc.y += w * v.y; acc.z += w * v.z; acc.w += w * v.w;
+    }
+    const int par = step & 1;
+    const size_t row = (((size_t)par * x.nranks + x.me) * x.cap + tok) * H + head;
+    for (int r = 0; r < x.nranks; r++) {
+        float *dst = x.peer[r] + row * (D + 2);
+        *reinterpret_cast<float2 *>(dst + d) = make_float2(acc.x, acc.y);  // rows are 8-byte aligned (D + 2 floats)
+        *reinterpret_cast<float2 *>(dst + d + 2) = make_float2(acc.z, acc.w);
+        if (threadIdx.x == 0) *reinterpret_cast<float2 *>(dst + D) = make_float2(M, lt);
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned int total = gridDim.x * gridDim.y;
+        if (atomicAdd(done_counter, 1u) == total - 1) {
+            *done_counter = 0;
+            __threadfence_system();
+            for (int r = 0; r < x.nranks; r++) {
+                uint32_t *flags = reinterpret_cast<uint32_t *>(x.peer[r] + x.flag_offset_floats);
+                st_release_sys(flags + par * x.nranks + x.me, step);
+            }
+        }
+    }
+}
+
+// grid (H, tokens), D/4 threads
+__global__ void attn_wait_merge_kernel(XchgView x, uint32_t step, int H, const float *__restrict__ q_proj_out,
+                                       const float *__restrict__ gate, float *__restrict__ out, int *__restrict__ err) {
+    constexpr int D = kD;
+    __shared__ int s_ok;
+    const int head = blockIdx.x, tok = blockIdx.y, d = threadIdx.x * 4;
+    const int par = step & 1;
+    const float *mine = x.peer[x.me];
+    if (threadIdx.x == 0) {
+        const uint32_t *flags = reinterpret_cast<const uint32_t *>(mine + x.flag_offset_floats) + par * x.nranks;
+        int ok = 1;
+        const long long t0 = clock64();
+        for (int r = 0; r < x.nranks && ok; r++) {
+            while ((int32_t)(ld_acquire_sys(flags + r) - step) < 0) {
+                if (clock64() - t0 > x.wait_limit_cycles) {  // a peer never published this step
+                    ok = 0;
+                    atomicCAS(err, 0, (2 << 16) | r);
+                    break;
+                }
+            }
+        }
+        s_ok = ok;
+    }
+    __syncthreads();
+    float *dst = out + ((size_t)tok * H + head) * D + d;
+    if (!s_ok) {
+        *reinterpret_cast<float4 *>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
+        return;
+    }
+    float M = kNegBig;
+    for (int r = 0; r < x.nranks; r++) {
+        const float *row = mine + ((((size_t)par * x.nranks + r) * x.cap + tok) * H + head) * (D + 2);
+        M = fmaxf(M, __ldcg(row + D));
+    }
+    float lt = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int r = 0; r < x.nranks; r++) {
+        const float *row = mine + ((((size_t)par * x.nranks + r) * x.cap + tok) * H + head) * (D + 2);
+        const float w = fast_exp2(__ldcg(row + D) - M);
+        lt += w * __ldcg(row + D + 1);
+        const float2 a = __ldcg(reinterpret_cast<const float2 *>(row + d)), b = __ldcg(reinterpret_cast<const float2 *>(row + d + 2));
+        acc.x += w * a.x; acc.y += w * a.y; acc.z += w * b.x; acc.w += w * b.y;
+    }
+    const float inv = lt > 0.f ? 1.0f / lt : 0.f;
+    const float *gsrc = q_proj_out ? q_proj_out + ((size_t)tok * H + head) * 2 * D + D + d : gate + ((size_t)tok * H + head) * D + d;
+    const float4 g = *reinterpret_cast<const float4 *>(gsrc);
+    *reinterpret_cast<float4 *>(dst) = make_float4(acc.x * inv * fast_sigmoid(g.x), acc.y * inv * fast_sigmoid(g.y),
+                                                   acc.z * inv * fast_sigmoid(g.z), acc.w * inv * fast_sigmoid(g.w));
+}
+
+int launch_attn_merge_push(const float *part_o, const float *part_ml, int nsplits, int ntok, int H, const XchgView &x,
+                           uint32_t step, unsigned int *done_counter, cudaStream_t st) {
+    attn_merge_push_kernel<<<dim3(H, ntok), kD / 4, 0, st>>>(part_o, part_ml, nsplits, H, x, step, done_counter);
+    return cudaGetLastError() == cudaSuccess ? 1 : -1;
+}
+int launch_attn_wait_merge(const XchgView &x, uint32_t step, int ntok, int H, const float *q_proj_out, const float *gate,
+                           float *out, int *err, cudaStream_t st) {
+    attn_wait_merge_kernel<<<dim3(H, ntok), kD / 4, 0, st>>>(x, step, H, q_proj_out, gate, out, err);
+    return cudaGetLastError() == cudaSuccess ? 1 : -1;
+}
+
+}  // namespace fm

@@ -198,7 +198,7 @@ extern "C" void fm_destroy(FmCtx *ctx) {
     cudaSetDevice(ctx->cfg.device);
     cudaDeviceSynchronize();
     cudaFree(ctx->pool); cudaFree(ctx->d_page_table); cudaFree(ctx->d_conv_state); cudaFree(ctx->d_ssm_state);
-    cudaFree(ctx->d_part_o); cudaFree(ctx->d_part_ml); cudaFree(ctx->d_pf_q16); cudaFree(ctx->d_pf_k16); cudaFree(ctx->d_pf_v16); cudaFree(ctx->d_err);
+    cudaFree(ctx->d_part_o); cudaFree(ctx->d_part_ml); cudaFree(ctx->d_xchg_counter); cudaFree(ctx->d_pf_q16); cudaFree(ctx->d_pf_k16); cudaFree(ctx->d_pf_v16); cudaFree(ctx->d_err);
     if (ctx->h_err) cudaFreeHost(ctx->h_err); cudaFree(ctx->d_work);
     cudaFree(ctx->d_stage);
     for (cudaEvent_t e : ctx->prof_ev) cudaEventDestroy(e);
@@ -864,4 +864,141 @@ extern "C" fm_status fm_state_import(FmCtx *ctx, int li, int seq, const float *c
     if (ssm) FM_CUDA(ctx, cudaMemcpyAsync(ctx->d_ssm_state + lidx(ctx, li, seq) * sn, ssm, sn * sizeof(float), kind, ctx->stream));
     if (ctx->ptr_mode == FM_PTR_HOST) FM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     return FM_OK;
+}
+
+// ---- cross-GPU exchange of decode partials over peer memory ------------------------------------
+static int xchg_cap(const FmCtx *ctx) { return std::min(ctx->cfg.max_batch_tokens, kMaxList); }
+static size_t xchg_slot_floats(const FmCtx *ctx, int nranks) {
+    return (size_t)2 * nranks * xchg_cap(ctx) * ctx->cfg.num_attn_heads * (ctx->cfg.head_dim + 2);
+}
+
+extern "C" size_t fm_exchange_bytes(const FmCtx *ctx, int nranks) {
+    if (!ctx || nranks < 1 || nranks > kMaxXchgRanks) return 0;
+    const size_t slots = (xchg_slot_floats(ctx, nranks) * sizeof(float) + 255) & ~(size_t)255;
+    return slots + 256;  // flags [2][nranks] of 32 bits after the slots
+}
+
+extern "C" fm_status fm_exchange_attach(FmCtx *ctx, int nranks, int my_index, void *const *peer_bufs) {
+    if (!ctx) return FM_ERR_INVALID;
+    if (nranks < 1 || nranks > kMaxXchgRanks || my_index < 0 || my_index >= nranks || !peer_bufs)
+        return fail(ctx, FM_ERR_INVALID, "fm_exchange_attach: %d ranks (1..%d), index %d", nranks, kMaxXchgRanks, my_index);
+    if (ctx->cfg.num_full_layers <= 0) return fail(ctx, FM_ERR_INVALID, "fm_exchange_attach: context holds no full-attention layers");
+    for (int r = 0; r < nranks; r++)
+        if (!peer_bufs[r]) return fail(ctx, FM_ERR_INVALID, "fm_exchange_attach: peer buffer %d is null", r);
+    FM_CUDA(ctx, cudaSetDevice(ctx->cfg.device));
+    if (!ctx->d_xchg_counter) {
+        FM_CUDA(ctx, cudaMalloc(&ctx->d_xchg_counter, sizeof(unsigned int)));
+        FM_CUDA(ctx, cudaMemset(ctx->d_xchg_counter, 0, sizeof(unsigned int)));
+    }
+    XchgView &x = ctx->xchg;
+    for (int r = 0; r < nranks; r++) x.peer[r] = static_cast<float *>(peer_bufs[r]);
+    x.nranks = nranks;
+    x.me = my_index;
+    x.cap = xchg_cap(ctx);
+    x.flag_offset_floats = (long long)(((xchg_slot_floats(ctx, nranks) * sizeof(float) + 255) & ~(size_t)255) / sizeof(float));
+    int khz = 0;
+    cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, ctx->cfg.device);
+    x.wait_limit_cycles = (long long)(khz > 0 ? khz : 1900000) * 500;  // about half a second of SM clock
+    ctx->xchg_step = 0;
+    // the local buffer starts zeroed: flags hold step 0, the first exchange is step 1
+    FM_CUDA(ctx, cudaMemsetAsync(x.peer[my_index], 0, fm_exchange_bytes(ctx, nranks), ctx->stream));
+    FM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return FM_OK;
+}
+
+extern "C" fm_status fm_attn_decode_exchange_push(FmCtx *ctx, int fa_idx, const int *seq, const int *pos, int batch,
+                                                  const float *q_proj_out, const float *q, const float *k, const float *v,
+                                                  const uint16_t *q_norm_w, const uint16_t *k_norm_w) {
+    if (!ctx) return FM_ERR_INVALID;
+    const char *fn = "fm_attn_decode_exchange_push";
+    if (ctx->xchg.nranks < 1) return fail(ctx, FM_ERR_INVALID, "%s: call fm_exchange_attach first", fn);
+    if (!seq || !pos || (!q_proj_out && !q)) return fail(ctx, FM_ERR_INVALID, "%s: null argument", fn);
+    if ((k == nullptr) != (v == nullptr)) return fail(ctx, FM_ERR_INVALID, "%s: k and v go together", fn);
+    fm_status st = check_layer_seq(ctx, fn, fa_idx, ctx->cfg.num_full_layers, seq, batch);
+    if (st) return st;
+    if (batch < 1 || batch > ctx->xchg.cap) return fail(ctx, FM_ERR_INVALID, "%s: batch %d (1..%d)", fn, batch, ctx->xchg.cap);
+    for (int i = 0; i < batch; i++)
+        for (int j = 0; j < i; j++)
+            if (seq[i] == seq[j]) return fail(ctx, FM_ERR_INVALID, "%s: sequence %d appears twice in one step", fn, seq[i]);
+    const FmConfig &c = ctx->cfg;
+    FM_CUDA(ctx, cudaSetDevice(c.device));
+    const int H = c.num_attn_heads, D = c.head_dim;
+    const size_t qd = (size_t)H * D, kvd = (size_t)c.num_kv_heads * D;
+    Stager sg(ctx);
+    bool ok = true;
+    const float *d_qp = sg.in(q_proj_out, batch * qd * 2, &ok);
+    const float *d_q = sg.in(q_proj_out ? nullptr : q, batch * qd, &ok);
+    const float *d_k = sg.in(k, batch * kvd, &ok), *d_v = sg.in(v, batch * kvd, &ok);
+    const uint16_t *d_qn = sg.in(q_norm_w, (size_t)D, &ok), *d_kn = sg.in(k_norm_w, (size_t)D, &ok);
+    if (!ok) return fail(ctx, FM_ERR_INVALID, "%s: staging buffer too small", fn);
+    std::vector<int> rows(batch);
+    if (k != nullptr) {
+        st = reserve_rows(ctx, fa_idx, seq, batch, rows);
+        if (st) return st;
+    } else {
+        for (int i = 0; i < batch; i++) {
+            rows[i] = ctx->kv_len[lidx(ctx, fa_idx, seq[i])] - 1;
+            if (rows[i] < 0) return fail(ctx, FM_ERR_INVALID, "%s: sequence %d is empty and no k/v given", fn, seq[i]);
+        }
+    }
+    FM_CUDA(ctx, sg.push());
+    if (k != nullptr) {
+        st = append_list(ctx, fa_idx, seq, pos, rows.data(), batch, d_k, d_v, d_kn);
+        if (st) return st;
+    }
+    TokSpec t;
+    t.mode = 0;
+    t.n = batch;
+    int max_len = 1;
+    for (int i = 0; i < batch; i++) {
+        t.seq[i] = seq[i]; t.pos[i] = pos[i]; t.row[i] = rows[i];
+        max_len = std::max(max_len, rows[i] + 1);
+    }
+    const int ns = pick_splits(ctx, batch, max_len);
+    {
+        ProfScope prof(ctx);
+        st = launched(ctx, launch_attn_decode(kv_view(ctx, fa_idx), ctx->rope, t, H, d_qp, d_q, d_qn, c.rms_norm_eps, ctx->d_part_o,
+                                              ctx->d_part_ml, ns, ctx->stream), "attn_decode");
+    }
+    if (st) return st;
+    ctx->xchg_step++;
+    st = launched(ctx, launch_attn_merge_push(ctx->d_part_o, ctx->d_part_ml, ns, batch, H, ctx->xchg, ctx->xchg_step, ctx->d_xchg_counter,
+                                              ctx->stream), "attn_merge_push");
+    if (st) return st;
+    if (sg.host) FM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));  // the staged inputs may be reused by the next call
+    return FM_OK;
+}
+
+extern "C" fm_status fm_attn_decode_exchange_merge(FmCtx *ctx, int batch, const float *q_proj_out, const float *gate, float *out) {
+    if (!ctx) return FM_ERR_INVALID;
+    const char *fn = "fm_attn_decode_exchange_merge";
+    if (ctx->xchg.nranks < 1 || ctx->xchg_step == 0) return fail(ctx, FM_ERR_INVALID, "%s: nothing was pushed", fn);
+    if (!out || (!q_proj_out && !gate)) return fail(ctx, FM_ERR_INVALID, "%s: null argument", fn);
+    if (batch < 1 || batch > ctx->xchg.cap) return fail(ctx, FM_ERR_INVALID, "%s: batch %d (1..%d)", fn, batch, ctx->xchg.cap);
+    const FmConfig &c = ctx->cfg;
+    FM_CUDA(ctx, cudaSetDevice(c.device));
+    const size_t qd = (size_t)c.num_attn_heads * c.head_dim;
+    Stager sg(ctx);
+    bool ok = true;
+    const float *d_qp = sg.in(q_proj_out, batch * qd * 2, &ok);
+    const float *d_g = sg.in(q_proj_out ? nullptr : gate, batch * qd, &ok);
+    size_t w_out = 0;
+    float *d_out = sg.out(out, batch * qd, &ok, &w_out);
+    if (!ok) return fail(ctx, FM_ERR_INVALID, "%s: staging buffer too small", fn);
+    FM_CUDA(ctx, sg.push());
+    fm_status st = launched(ctx, launch_attn_wait_merge(ctx->xchg, ctx->xchg_step, batch, c.num_attn_heads, d_qp, d_g, d_out, ctx->d_err,
+                                                        ctx->stream), "attn_wait_merge");
+    if (st) return st;
+    FM_CUDA(ctx, cudaMemcpyAsync(ctx->h_err, ctx->d_err, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+    FM_CUDA(ctx, sg.pull(out, w_out, batch * qd));
+    if (sg.host) return check_device_error(ctx);
+    return FM_OK;
+}
+
+extern "C" fm_status fm_attn_decode_exchange(FmCtx *ctx, int fa_idx, const int *seq, const int *pos, int batch,
+                                             const float *q_proj_out, const float *q, const float *gate, const float *k,
+                                             const float *v, const uint16_t *q_norm_w, const uint16_t *k_norm_w, float *out) {
+    fm_status st = fm_attn_decode_exchange_push(ctx, fa_idx, seq, pos, batch, q_proj_out, q, k, v, q_norm_w, k_norm_w);
+    if (st) return st;
+    return fm_attn_decode_exchange_merge(ctx, batch, q_proj_out, gate, out);
 }

@@ -44,6 +44,16 @@ struct KvView {
     int shard_rank, shard_count;
 };
 
+// Exchange buffers of a sequence group as a kernel sees them (see attn_decode.cu).
+constexpr int kMaxXchgRanks = 8;
+struct XchgView {
+    float *peer[kMaxXchgRanks];  // every rank's buffer, addressable from this GPU; peer[me] is the local one
+    int nranks, me;
+    int cap;                     // token capacity of a slot
+    long long flag_offset_floats;
+    long long wait_limit_cycles;
+};
+
 struct RopeParams {
     float inv_freq[64];  // rotary_dim / 2 entries, computed on the host exactly as the reference does
     int rotary_dim;
@@ -93,6 +103,11 @@ struct FmCtx {
     void *d_work = nullptr;             // chunked GatedDeltaNet workspace
     size_t work_bytes = 0;
 
+    // cross-GPU exchange of partial results (fm_exchange_attach)
+    fm::XchgView xchg = {};
+    uint32_t xchg_step = 0;
+    unsigned int *d_xchg_counter = nullptr;
+
     // optional event bracketing of the dominant kernels
     bool prof_on = false;
     std::vector<cudaEvent_t> prof_ev;  // pairs (start, stop)
@@ -120,6 +135,11 @@ int launch_attn_merge(const float *part_o, const float *part_ml, int nparts, lon
                       long long head_stride_o, long long head_stride_ml, int ntok, int H, int D,
                       const float *q_proj_out, const float *gate, float *out, float *ml_out,
                       cudaStream_t st);
+
+int launch_attn_merge_push(const float *part_o, const float *part_ml, int nsplits, int ntok, int H, const XchgView &x,
+                           uint32_t step, unsigned int *done_counter, cudaStream_t st);
+int launch_attn_wait_merge(const XchgView &x, uint32_t step, int ntok, int H, const float *q_proj_out, const float *gate,
+                           float *out, int *err, cudaStream_t st);
 
 int launch_kv_export(const KvView &kv, int seq, int len, float *k, float *v, cudaStream_t st);
 int launch_kv_import(const KvView &kv, int seq, int len, const float *k, const float *v, cudaStream_t st);

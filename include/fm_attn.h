@@ -148,6 +148,33 @@ fm_status fm_attn_decode_partial(FmCtx *ctx, int fa_idx, const int *seq, const i
 fm_status fm_attn_merge_gate(FmCtx *ctx, int nparts, const float *o_parts, const float *ml_parts,
                              const float *q_proj_out, const float *gate, int batch, float *out);
 
+/* The sequence-sharded decode step with the exchange done by this library over peer memory (plain
+ * stores over NVLink into buffers that the ranks of a sequence group have mapped for each other --
+ * e.g. CUDA IPC or symmetric memory -- no collective call on the path).  No reference counterpart.
+ *   fm_exchange_bytes   size of the buffer every rank must provide (nranks <= 8)
+ *   fm_exchange_attach  peer_bufs[r] = rank r's buffer as addressable from this GPU; peer_bufs[my_index]
+ *                       is the local one and is zeroed here.  All ranks attach before the first step.
+ *   ..._exchange_push   the partial step (as fm_attn_decode_partial), then each (token, head) partial is
+ *                       stored into every rank's buffer and the step number published to every rank
+ *   ..._exchange_merge  waits until every rank has published the step -- for about half a second at
+ *                       most: FM_ERR_TIMEOUT, reported at the next synchronising call, with zeros in
+ *                       `out`, and the context stays usable -- then merges by log-sum-exp and applies
+ *                       the gate (gate, or q_proj_out interleaved)
+ *   fm_attn_decode_exchange  push + merge.
+ * All ranks of the group call these in lockstep (same number of steps); batch <= 64. */
+size_t fm_exchange_bytes(const FmCtx *ctx, int nranks);
+fm_status fm_exchange_attach(FmCtx *ctx, int nranks, int my_index, void *const *peer_bufs);
+fm_status fm_attn_decode_exchange_push(FmCtx *ctx, int fa_idx, const int *seq, const int *pos, int batch,
+                                       const float *q_proj_out, const float *q, const float *k,
+                                       const float *v, const uint16_t *q_norm_w,
+                                       const uint16_t *k_norm_w);
+fm_status fm_attn_decode_exchange_merge(FmCtx *ctx, int batch, const float *q_proj_out,
+                                        const float *gate, float *out);
+fm_status fm_attn_decode_exchange(FmCtx *ctx, int fa_idx, const int *seq, const int *pos, int batch,
+                                  const float *q_proj_out, const float *q, const float *gate,
+                                  const float *k, const float *v, const uint16_t *q_norm_w,
+                                  const uint16_t *k_norm_w, float *out);
+
 /* Causal prefill of n tokens of one sequence at positions start_pos..: q norm + RoPE, k norm +
  * RoPE + append, token t attends to rows [0, len_before + t], times sigmoid(gate).
  * Replaces batched_prefill.h:543-740 and the Metal kernels prefill_q_rope_norm_bf16 /

@@ -97,6 +97,22 @@ def test_ragged_contexts(pkg, port, synth, ctx):
     np.testing.assert_allclose(ke[ctx:], kc[ctx:], rtol=2 ** -7, atol=1e-6)
 
 
+@pytest.mark.parametrize("mode,factor", [(1, 4.0), (2, 4.0), (3, 4.0), (3, 1.0)])
+def test_rope_scaling_modes(pkg, port, synth, mode, factor):
+    """Linear / NTK / YaRN position scaling (and YaRN's logit temperature) follow the CPU code; a
+    factor of 1 leaves every mode equal to no scaling."""
+    ctx = 500
+    k0, v0 = synth.attn_cache(77, ctx)
+    q, g, k, v = synth.attn_step_inputs(77, 2)
+    kw = dict(rope_scaling_mode=mode, rope_scale_factor=factor)
+    ref_out, kc, vc = oracle_attn(port, 32, 2, k0, v0, q, g, k, v, start_pos=30000, max_seq_len=4096, **kw)
+    out, ke, ve, _ = run_decode(pkg, 32, 2, k0, v0, q, g, k, v, start_pos=30000, rope_orig_max_pos=4096, **kw)
+    gated, _, rr = rel_errors(out, ref_out)
+    print("rope mode", mode, factor, "gated", gated, "rms-rel", rr)
+    assert gated <= TOL
+    np.testing.assert_allclose(ke[ctx:], kc[ctx:], rtol=2 ** -7, atol=1e-6)
+
+
 def test_batched_ragged_sequences(pkg, port, synth):
     """Eight sequences of different lengths in one call; one of them empty."""
     lens = [0, 5, 64, 65, 300, 1000, 129, 2047]
