@@ -13,8 +13,9 @@
 // Launch sequence:
 //   gdn_prep_kernel    per token   : conv + SiLU, q/k normalisation, ln(decay), beta  -> workspace
 //   gdn_ring_kernel                : last three raw inputs -> conv history ring
-//   gdn_chunk_kernel   per (head, chunk), all chunks in parallel: K K^T, Q K^T, T, U, W -> workspace
-//   gdn_scan_kernel    per (head, 32-row slice of the state), chunks in sequence: D, O, S
+//   gdn_chunk_kernel   per (head, chunk), all chunks in parallel: K K^T, Q K^T, A, then U and W by
+//                      forward substitution -> workspace
+//   gdn_scan_kernel    per (head, 64-row slice of the state), chunks in sequence: D, O, S
 //   gdn_norm_kernel    per (token, head): gated RMS-norm in place
 // Contractions run on tensor cores as split tf32 (m16n8k8, two terms per operand, fp32 accumulate);
 // the triangular solve, the decay exponentials and the state stay fp32.
@@ -208,55 +209,48 @@ gdn_chunk_kernel(GdnDims g, int n, GdnWork w, int nchunks) {
             }
     }
     __syncthreads();
-    // T = (I + A)^-1 by forward substitution; thread j owns column j
-    if (tid < kC) {
-        const int j = tid;
-        for (int r = 0; r < kC; r++) {
-            float acc = r == j ? 1.f : 0.f;
-            for (int i = j; i < r; i++) acc -= sA[r * kLdT + i] * sT[i * kLdT + j];
-            sT[r * kLdT + j] = r >= j ? acc : 0.f;
-        }
-    }
-    // scale rows: V <- beta V, K <- beta e^{c} K
-    for (int i = tid; i < kC * kDH; i += 256) {
-        const int r = i >> 7, c = i & 127;
-        sV[r * kLdK + c] *= sb[r];
-        sK[r * kLdK + c] *= sb[r] * expf(sc[r]);
-    }
+    // (I + A) X = [beta V | beta e^c K] by forward substitution: thread c owns column c of X (a column
+    // of U for c < 128, of W otherwise) and keeps its 64 entries in registers; A is read as broadcast
+    // 128-bit loads and four partial sums shorten the dependent chain.  This replaces forming
+    // T = (I + A)^-1 and multiplying by it.
+    if (tid < kC) sT[tid] = sb[tid] * expf(sc[tid]);  // row scale of the K block
     __syncthreads();
-    // U = T (beta V), W = T (beta e^c K): 64 x 128 x 64, warp = (16-row tile, 64-column half)
     {
-        const int mt = warp & 3, nh = warp >> 2;
-        float au[8][4] = {}, aw[8][4] = {};
-        const float *Ta = sT + (mt * 16) * kLdT;
-        auto fa = [&](int m, int k) { return Ta[m * kLdT + k]; };
-        // T is lower triangular: rows of this tile only reach columns < 16 (mt + 1)
-        const int kmax = 16 * (mt + 1);
-        warp_gemm_tf32<8>(au, kmax, fa, [&](int k, int nn) { return sV[k * kLdK + nh * 64 + nn]; }, lane);
-        warp_gemm_tf32<8>(aw, kmax, fa, [&](int k, int nn) { return sK[k * kLdK + nh * 64 + nn]; }, lane);
-        float *Uo = w.U + ((size_t)vh * nchunks + chunk) * kC * kDH, *Wo = w.W + ((size_t)vh * nchunks + chunk) * kC * kDH;
-        const int gq = lane >> 2, tq = lane & 3;
+        const int c = tid;
+        const bool is_u = c < kDH;
+        const float *src = is_u ? sV + c : sK + (c - kDH);
+        const float *scale = is_u ? sb : sT;
+        float x[kC];
 #pragma unroll
-        for (int nt = 0; nt < 8; nt++) {
-            const int c = nh * 64 + nt * 8 + 2 * tq;
-            const int r = mt * 16 + gq;
-            *reinterpret_cast<float2 *>(Uo + r * kDH + c) = make_float2(au[nt][0], au[nt][1]);
-            *reinterpret_cast<float2 *>(Uo + (r + 8) * kDH + c) = make_float2(au[nt][2], au[nt][3]);
-            *reinterpret_cast<float2 *>(Wo + r * kDH + c) = make_float2(aw[nt][0], aw[nt][1]);
-            *reinterpret_cast<float2 *>(Wo + (r + 8) * kDH + c) = make_float2(aw[nt][2], aw[nt][3]);
+        for (int r = 0; r < kC; r++) x[r] = src[r * kLdK] * scale[r];
+#pragma unroll
+        for (int r = 1; r < kC; r++) {
+            const float *Ar = sA + r * kLdT;
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+            for (int i = 0; i + 3 < r; i += 4) {
+                const float4 a = *reinterpret_cast<const float4 *>(Ar + i);
+                a0 += a.x * x[i]; a1 += a.y * x[i + 1]; a2 += a.z * x[i + 2]; a3 += a.w * x[i + 3];
+            }
+#pragma unroll
+            for (int i = r & ~3; i < r; i++) a0 += Ar[i] * x[i];
+            x[r] -= (a0 + a1) + (a2 + a3);
         }
+        float *dst = (is_u ? w.U : w.W) + ((size_t)vh * nchunks + chunk) * kC * kDH + (is_u ? c : c - kDH);
+#pragma unroll
+        for (int r = 0; r < kC; r++) dst[r * kDH] = x[r];
     }
 }
 
-// ---- per (head, 32-row slice of the state): walk the chunks ------------------------------------
-constexpr int kSl = 32;           // state rows (value dims) per CTA
+// ---- per (head, 64-row slice of the state): walk the chunks ------------------------------------
+constexpr int kSl = 64;           // state rows (value dims) per CTA: 64 heads x 2 slices = 128 CTAs, one wave
 constexpr int kLdS = kDH + 4;     // S[vi][ki] read as B[n = vi][k = ki]
 constexpr int kLdKs = kDH + 8;    // scaled K read as B[k = i][n = ki]
 constexpr int kLdD = kSl + 8;     // D[i][vi] read as B[k = i][n = vi] and as A[m = vi][k = i]
 constexpr int kScanSmem = (kSl * kLdS + 2 * kC * kLdK + kC * kLdKs + kC * kLdT + kC * kLdD + 2 * kC) * 4;
 
-// grid (128 / kSl, Hv), 128 threads
-__global__ void __launch_bounds__(128, 1)
+// grid (128 / kSl, Hv), 256 threads
+__global__ void __launch_bounds__(256, 1)
 gdn_scan_kernel(GdnDims g, int n, GdnWork w, int nchunks, float *__restrict__ ssm, float *__restrict__ out) {
     extern __shared__ __align__(16) float sm[];
     float *sS = sm, *sW = sS + kSl * kLdS, *sQ = sW + kC * kLdK, *sKs = sQ + kC * kLdK;
@@ -266,7 +260,7 @@ gdn_scan_kernel(GdnDims g, int n, GdnWork w, int nchunks, float *__restrict__ ss
     const int gq = lane >> 2, tq = lane & 3;
     const int total_k = g.Hk * kDH, total_v = g.Hv * kDH;
     float *Sg = ssm + ((size_t)vh * kDH + slice * kSl) * kDH;
-    for (int i = tid; i < kSl * (kDH / 4); i += 128) {
+    for (int i = tid; i < kSl * (kDH / 4); i += 256) {
         const int r = i >> 5, c4 = (i & 31) * 4;
         *reinterpret_cast<float4 *>(sS + r * kLdS + c4) = *reinterpret_cast<const float4 *>(Sg + (size_t)r * kDH + c4);
     }
@@ -280,7 +274,7 @@ gdn_scan_kernel(GdnDims g, int n, GdnWork w, int nchunks, float *__restrict__ ss
         }
         {
             const float *Wg = w.W + hc * kC * kDH, *QKg = w.QK + hc * kC * kC;
-            for (int i = tid; i < kC * (kDH / 4); i += 128) {
+            for (int i = tid; i < kC * (kDH / 4); i += 256) {
                 const int r = i >> 5, c4 = (i & 31) * 4;
                 cp_async16(smem_u32(sW + r * kLdK + c4), Wg + (size_t)r * kDH + c4);
                 if (t0 + r < n) {
@@ -291,7 +285,7 @@ gdn_scan_kernel(GdnDims g, int n, GdnWork w, int nchunks, float *__restrict__ ss
                     *reinterpret_cast<float4 *>(sKs + r * kLdKs + c4) = make_float4(0.f, 0.f, 0.f, 0.f);
                 }
             }
-            for (int i = tid; i < kC * (kC / 4); i += 128) {
+            for (int i = tid; i < kC * (kC / 4); i += 256) {
                 const int r = i >> 4, c4 = (i & 15) * 4;
                 cp_async16(smem_u32(sQK + r * kLdT + c4), QKg + (size_t)r * kC + c4);
             }
@@ -302,21 +296,22 @@ gdn_scan_kernel(GdnDims g, int n, GdnWork w, int nchunks, float *__restrict__ ss
         const float cC = sc[kC - 1];
         if (tid < kC) se[tid] = expf(cC - sc[tid]);
         __syncthreads();
-        for (int i = tid; i < kC * kDH; i += 128) {  // K rows scaled for the state update
+        for (int i = tid; i < kC * kDH; i += 256) {  // K rows scaled for the state update
             const int r = i >> 7, c = i & 127;
             sKs[r * kLdKs + c] *= se[r];
         }
-        // D = U - W S^T and Q S^T: warp = 16 token rows, all 32 state rows of the slice
+        // D = U - W S^T and Q S^T: warp = (16 token rows, 32 of the slice's 64 state rows)
+        const int mtok = warp & 3, nhs = warp >> 2;
         float ad[4][4] = {}, aq[4][4] = {};
         {
-            const float *Wa = sW + (warp * 16) * kLdK, *Qa = sQ + (warp * 16) * kLdK;
-            auto fb = [&](int k, int nn) { return sS[nn * kLdS + k]; };
+            const float *Wa = sW + (mtok * 16) * kLdK, *Qa = sQ + (mtok * 16) * kLdK;
+            auto fb = [&](int k, int nn) { return sS[(nhs * 32 + nn) * kLdS + k]; };
             warp_gemm_tf32<4>(ad, kDH, [&](int m, int k) { return Wa[m * kLdK + k]; }, fb, lane);
             warp_gemm_tf32<4>(aq, kDH, [&](int m, int k) { return Qa[m * kLdK + k]; }, fb, lane);
             const float *Ug = w.U + hc * kC * kDH + slice * kSl;
 #pragma unroll
             for (int nt = 0; nt < 4; nt++) {
-                const int r = warp * 16 + gq, c = nt * 8 + 2 * tq;
+                const int r = mtok * 16 + gq, c = nhs * 32 + nt * 8 + 2 * tq;
                 const float2 u0 = *reinterpret_cast<const float2 *>(Ug + (size_t)r * kDH + c);
                 const float2 u1 = *reinterpret_cast<const float2 *>(Ug + (size_t)(r + 8) * kDH + c);
                 sD[r * kLdD + c] = u0.x - ad[nt][0];
@@ -330,12 +325,12 @@ gdn_scan_kernel(GdnDims g, int n, GdnWork w, int nchunks, float *__restrict__ ss
         __syncthreads();  // D complete; S fully read
         // O = e^{c} Q S^T + (M o Q K^T) D
         {
-            const float *QKa = sQK + (warp * 16) * kLdT;
+            const float *QKa = sQK + (mtok * 16) * kLdT;
             warp_gemm_tf32<4>(aq, kC, [&](int m, int k) { return QKa[m * kLdT + k]; },
-                              [&](int k, int nn) { return sD[k * kLdD + nn]; }, lane);
+                              [&](int k, int nn) { return sD[k * kLdD + nhs * 32 + nn]; }, lane);
 #pragma unroll
             for (int nt = 0; nt < 4; nt++) {
-                const int r = warp * 16 + gq, c = slice * kSl + nt * 8 + 2 * tq;
+                const int r = mtok * 16 + gq, c = slice * kSl + nhs * 32 + nt * 8 + 2 * tq;
                 if (t0 + r < n)
                     *reinterpret_cast<float2 *>(out + (size_t)(t0 + r) * total_v + (size_t)vh * kDH + c) = make_float2(aq[nt][0], aq[nt][1]);
                 if (t0 + r + 8 < n)
@@ -344,7 +339,7 @@ gdn_scan_kernel(GdnDims g, int n, GdnWork w, int nchunks, float *__restrict__ ss
         }
         // S <- e^{c_C} S + D^T (e^{c_C - c} K): warp = (16 state rows, 64 key columns)
         {
-            const int mt = warp & 1, nh = warp >> 1;
+            const int mt = warp & 3, nh = warp >> 2;
             const float eC = expf(cC);
             float as[8][4];
 #pragma unroll
@@ -364,7 +359,7 @@ gdn_scan_kernel(GdnDims g, int n, GdnWork w, int nchunks, float *__restrict__ ss
         }
     }
     __syncthreads();
-    for (int i = tid; i < kSl * (kDH / 4); i += 128) {
+    for (int i = tid; i < kSl * (kDH / 4); i += 256) {
         const int r = i >> 5, c4 = (i & 31) * 4;
         *reinterpret_cast<float4 *>(Sg + (size_t)r * kDH + c4) = *reinterpret_cast<const float4 *>(sS + r * kLdS + c4);
     }
@@ -437,7 +432,7 @@ int launch_gdn_prefill(const GdnDims &g, int n, int chunk, int step0, float *con
     gdn_prep_kernel<<<n, 512, g.conv_dim * 4, st>>>(g, n, step0, conv_state, qkv, beta, alpha, conv_w, A_log, dt_bias, w);
     gdn_ring_kernel<<<dim3(12, 3), 256, 0, st>>>(g.conv_dim, n, step0, conv_state, qkv);
     gdn_chunk_kernel<<<dim3(nchunks, g.Hv), 256, kChunkSmem, st>>>(g, n, w, nchunks);
-    gdn_scan_kernel<<<dim3(kDH / kSl, g.Hv), 128, kScanSmem, st>>>(g, n, w, nchunks, ssm_state, out);
+    gdn_scan_kernel<<<dim3(kDH / kSl, g.Hv), 256, kScanSmem, st>>>(g, n, w, nchunks, ssm_state, out);
     int launches = 4;
     if (norm_w != nullptr) {
         gdn_norm_kernel<<<dim3(g.Hv, n), 32, 0, st>>>(g, z, norm_w, out);
