@@ -15,10 +15,23 @@
 //     mantissa bits: K and V are exact in bf16, so the result tracks the fp32 reference to ~1e-4;
 //   * each CTA writes an un-normalised partial (O, max, sum); a second kernel merges the partials
 //     and applies the gate.
+#include <cooperative_groups.h>
+
 #include "fm_device.cuh"
 #include "fm_internal.h"
 
+namespace cg = cooperative_groups;
+
 namespace fm {
+
+__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
 
 constexpr int kD = 256;          // head dim the kernel is built for
 constexpr int kPage = 64;        // rows per page
@@ -52,10 +65,30 @@ __device__ __forceinline__ void named_barrier(int id, int nthreads) {
     asm volatile("bar.sync %0, %1;\n" ::"r"(id), "r"(nthreads) : "memory");
 }
 
+// What the fused form of the kernel does besides the split partials:
+//   * append: the CTA whose last tile holds the step's new row forms that row itself (k: RMS-norm +
+//     RoPE), stores it to the page and patches its shared-memory tile -- no separate append launch;
+//   * tail: with one split per (KV head, sequence) the CTA finishes its rows itself; with several, the
+//     grid (launched cooperatively, at most one CTA per SM) meets at a grid barrier and the (token,
+//     head) rows are merged by all CTAs -- no separate merge launch.  tail = 1: normalise, gate,
+//     write the output; 2: un-normalised row and (max, sum) for the caller to exchange; 3: store the
+//     row into every peer's exchange buffer and publish the step.
+struct DecodeFused {
+    const float *k_new, *v_new;  // [tokens][Hkv*D] or null
+    const uint16_t *knw;
+    int tail;
+    const float *gate;  // [tokens][H*D] when q_proj_out is not given
+    float *out;
+    float *ml_out;
+    XchgView x;
+    uint32_t step;
+};
+
+template <bool kFused>
 __global__ void __launch_bounds__(kDecThreads, 1)
 attn_decode_kernel(KvView kv, RopeParams rope, TokSpec toks, int H, const float *__restrict__ q_proj_out,
                    const float *__restrict__ q_in, const uint16_t *__restrict__ qnw, float eps,
-                   float *__restrict__ part_o, float *__restrict__ part_ml, int nsplits) {
+                   float *__restrict__ part_o, float *__restrict__ part_ml, int nsplits, DecodeFused f) {
     extern __shared__ __align__(128) unsigned char smem[];
     const uint32_t s_qhi = smem_u32(smem);
     const uint32_t s_qlo = s_qhi + kQBytes;
@@ -176,6 +209,40 @@ attn_decode_kernel(KvView kv, RopeParams rope, TokSpec toks, int H, const float 
         issue(t + 2);
 
         const int gpage = (slot_begin + t) * kv.shard_count + kv.shard_rank;
+        if (kFused && f.k_new != nullptr && gpage == row_new / kPage) {
+            // this tile holds the step's new row: form it, store it to the page, patch the tile
+            const int rn = row_new - gpage * kPage, d = tid;  // 256 threads = 256 dims
+            float *red = s_x, *xs = s_x + 8;               // the score-exchange buffer is idle here
+            float x = f.k_new[((size_t)tok * kv.Hkv + kvh) * kD + d];
+            if (f.knw != nullptr) {
+                const float ss = warp_sum(x * x);
+                if (lane == 0) red[warp] = ss;
+                __syncthreads();
+                float tot = 0.f;
+#pragma unroll
+                for (int w = 0; w < kDecWarps; w++) tot += red[w];
+                x = x * (1.0f / sqrtf(tot / kD + eps)) * bf16_bits_to_float(f.knw[d]);
+            }
+            xs[d] = x;
+            __syncthreads();
+            const int half = rope.rotary_dim / 2;
+            if (d < rope.rotary_dim) {
+                const int i = d < half ? d : d - half;
+                const float ang = ((float)pos / rope.pos_div) * rope.inv_freq[i];
+                const float c = cosf(ang), sn = sinf(ang);
+                x = d < half ? x * c - xs[d + half] * sn : xs[d - half] * sn + x * c;
+            }
+            const __nv_bfloat16 kb = __float2bfloat16_rn(x);
+            const __nv_bfloat16 vb = __float2bfloat16_rn(f.v_new[((size_t)tok * kv.Hkv + kvh) * kD + d]);
+            __nv_bfloat16 *pg = kv.pool + (size_t)ptab[slot_begin + t] * page_elems;
+            pg[((size_t)kvh * kPage + rn) * kD + d] = kb;
+            pg[((size_t)(kv.Hkv + kvh) * kPage + rn) * kD + d] = vb;
+            const uint32_t tile = s_kv + (uint32_t)(t % kStages) * 2 * kTileBytes;
+            const uint32_t off = swz_row512(rn, d >> 3) + (d & 7) * 2;
+            asm volatile("st.shared.b16 [%0], %1;\n" ::"r"(tile + off), "h"(*reinterpret_cast<const unsigned short *>(&kb)) : "memory");
+            asm volatile("st.shared.b16 [%0], %1;\n" ::"r"(tile + kTileBytes + off), "h"(*reinterpret_cast<const unsigned short *>(&vb)) : "memory");
+            __syncthreads();
+        }
         const int p0 = gpage * kPage + pw * 16;  // first row of this slice's 16
         if (p0 >= L) continue;                   // the whole slice skips together
         const uint32_t sk = s_kv + (uint32_t)(t % kStages) * 2 * kTileBytes;
@@ -298,6 +365,32 @@ attn_decode_kernel(KvView kv, RopeParams rope, TokSpec toks, int H, const float 
         }
     }
     __syncthreads();
+    // finishes one (token, head) row chunk of 4 dims according to the tail mode
+    auto emit = [&](int tk, int head, int d, float4 acc, float M, float lt) {
+        if (f.tail == 1) {
+            const float inv = lt > 0.f ? 1.0f / lt : 0.f;
+            const float *gsrc = q_proj_out ? q_proj_out + ((size_t)tk * H + head) * 2 * kD + kD + d : f.gate + ((size_t)tk * H + head) * kD + d;
+            const float4 g = *reinterpret_cast<const float4 *>(gsrc);
+            *reinterpret_cast<float4 *>(f.out + ((size_t)tk * H + head) * kD + d) =
+                make_float4(acc.x * inv * fast_sigmoid(g.x), acc.y * inv * fast_sigmoid(g.y), acc.z * inv * fast_sigmoid(g.z),
+                            acc.w * inv * fast_sigmoid(g.w));
+        } else if (f.tail == 2) {
+            *reinterpret_cast<float4 *>(f.out + ((size_t)tk * H + head) * kD + d) = acc;
+            if (d == 0) {
+                f.ml_out[((size_t)tk * H + head) * 2 + 0] = M;
+                f.ml_out[((size_t)tk * H + head) * 2 + 1] = lt;
+            }
+        } else {
+            const size_t row = ((((size_t)(f.step & 1) * f.x.nranks + f.x.me) * f.x.cap + tk) * H + head) * (kD + 2);
+            for (int r = 0; r < f.x.nranks; r++) {
+                float *dst = f.x.peer[r] + row;
+                *reinterpret_cast<float2 *>(dst + d) = make_float2(acc.x, acc.y);
+                *reinterpret_cast<float2 *>(dst + d + 2) = make_float2(acc.z, acc.w);
+                if (d == 0) *reinterpret_cast<float2 *>(dst + kD) = make_float2(M, lt);
+            }
+        }
+    };
+    const bool direct = kFused && nsplits == 1;  // this CTA is the only split: finish the rows here
     for (int r = warp; r < group; r += kDecWarps) {
         float mw[4], M = kNegBig;
 #pragma unroll
@@ -305,11 +398,11 @@ attn_decode_kernel(KvView kv, RopeParams rope, TokSpec toks, int H, const float 
             mw[w] = s_ml[(w * 16 + r) * 2];
             M = fmaxf(M, mw[w]);
         }
-        float f[4], lt = 0.f;
+        float fw[4], lt = 0.f;
 #pragma unroll
         for (int w = 0; w < 4; w++) {
-            f[w] = fast_exp2(mw[w] - M);
-            lt += f[w] * s_ml[(w * 16 + r) * 2 + 1];
+            fw[w] = fast_exp2(mw[w] - M);
+            lt += fw[w] * s_ml[(w * 16 + r) * 2 + 1];
         }
         const int head = kvh * group + r;
         const size_t prow = ((size_t)tok * H + head) * nsplits + split;
@@ -321,13 +414,74 @@ attn_decode_kernel(KvView kv, RopeParams rope, TokSpec toks, int H, const float 
 #pragma unroll
             for (int w = 0; w < 4; w++) {
                 const float4 v = *reinterpret_cast<const float4 *>(s_o + ((size_t)w * 16 + r) * kD + d);
-                acc.x += f[w] * v.x; acc.y += f[w] * v.y; acc.z += f[w] * v.z; acc.w += f[w] * v.w;
+                acc.x += fw[w] * v.x; acc.y += fw[w] * v.y; acc.z += fw[w] * v.z; acc.w += fw[w] * v.w;
             }
-            *reinterpret_cast<float4 *>(dst + d) = acc;
+            if (direct)
+                emit(tok, head, d, acc, M, lt);
+            else
+                *reinterpret_cast<float4 *>(dst + d) = acc;
         }
-        if (lane == 0) {
+        if (!direct && lane == 0) {
             part_ml[prow * 2 + 0] = M;
             part_ml[prow * 2 + 1] = lt;
+        }
+    }
+    if (!kFused) return;
+    if (!direct) {
+        // ---- every CTA's partials are written: meet, then merge the (token, head) rows grid-wide ----
+        cg::grid_group grid = cg::this_grid();
+        __threadfence();
+        grid.sync();
+        const int ncta = gridDim.x * gridDim.y * gridDim.z;
+        const int cta = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+        // work unit = (token, head, quarter of the head dim): 16 lanes of 4 dims x 16 groups of splits,
+        // so that a batch-1 step (32 rows) still spreads over 128 CTAs and no thread walks more than a
+        // few splits
+        const int units = gridDim.z * H * 4;
+        const int sg = tid >> 4, dl = tid & 15;
+        float2 *s_mlb = reinterpret_cast<float2 *>(kv_raw);                       // [nsplits] (max, sum)
+        float4 *s_acc = reinterpret_cast<float4 *>(kv_raw + 2048);                // [16][16]
+        float *s_lt = reinterpret_cast<float *>(kv_raw + 2048 + 16 * 16 * 16);    // [16]
+        for (int u = cta; u < units; u += ncta) {
+            const int item = u >> 2, qd = u & 3;
+            const int tk = item / H, head = item - tk * H;
+            const size_t prow0 = ((size_t)tk * H + head) * nsplits;
+            __syncthreads();
+            for (int j = tid; j < nsplits; j += kDecThreads) s_mlb[j] = __ldcg(reinterpret_cast<const float2 *>(part_ml) + prow0 + j);
+            __syncthreads();
+            float M = kNegBig;
+            for (int j = 0; j < nsplits; j++) M = fmaxf(M, s_mlb[j].x);
+            float lt = 0.f;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int j = sg; j < nsplits; j += 16) {
+                const float w = fast_exp2(s_mlb[j].x - M);
+                lt += w * s_mlb[j].y;
+                const float4 v = __ldcg(reinterpret_cast<const float4 *>(part_o + (prow0 + j) * kD + qd * 64) + dl);
+                acc.x += w * v.x; acc.y += w * v.y; acc.z += w * v.z; acc.w += w * v.w;
+            }
+            s_acc[sg * 16 + dl] = acc;
+            if (dl == 0) s_lt[sg] = lt;
+            __syncthreads();
+            if (sg == 0) {
+                float ltot = s_lt[0];
+#pragma unroll
+                for (int g2 = 1; g2 < 16; g2++) {
+                    const float4 v = s_acc[g2 * 16 + dl];
+                    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+                    ltot += s_lt[g2];
+                }
+                emit(tk, head, qd * 64 + dl * 4, acc, M, ltot);
+            }
+        }
+    }
+    if (f.tail == 3) {
+        // every row is in every peer's buffer before the step is published
+        cg::grid_group grid = cg::this_grid();
+        __threadfence_system();
+        grid.sync();
+        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && tid < f.x.nranks) {
+            uint32_t *flags = reinterpret_cast<uint32_t *>(f.x.peer[tid] + f.x.flag_offset_floats);
+            st_release_sys(flags + (f.step & 1) * f.x.nranks + f.x.me, f.step);
         }
     }
 }
@@ -337,14 +491,46 @@ int launch_attn_decode(const KvView &kv, const RopeParams &rope, const TokSpec &
                        float *part_o, float *part_ml, int nsplits, cudaStream_t st) {
     static bool configured = false;
     if (!configured) {
-        if (cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmem) != cudaSuccess)
+        if (cudaFuncSetAttribute(attn_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmem) != cudaSuccess)
             return -1;
         configured = true;
     }
     dim3 grid(nsplits, kv.Hkv, toks.n);
-    attn_decode_kernel<<<grid, kDecThreads, kDecSmem, st>>>(kv, rope, toks, H, q_proj_out, q, q_norm_w, eps,
-                                                            part_o, part_ml, nsplits);
+    DecodeFused f = {};
+    attn_decode_kernel<false><<<grid, kDecThreads, kDecSmem, st>>>(kv, rope, toks, H, q_proj_out, q, q_norm_w, eps,
+                                                                   part_o, part_ml, nsplits, f);
     return cudaGetLastError() == cudaSuccess ? 1 : -1;
+}
+
+// The whole decode step in one launch (see DecodeFused).  With several splits the launch is
+// cooperative: the grid never exceeds one CTA per SM, so all CTAs are resident for the grid barrier.
+int launch_attn_decode_fused(const KvView &kv, const RopeParams &rope, const TokSpec &toks, int H,
+                             const float *q_proj_out, const float *q, const uint16_t *q_norm_w, float eps,
+                             float *part_o, float *part_ml, int nsplits, const float *k_new, const float *v_new,
+                             const uint16_t *k_norm_w, int tail, const float *gate, float *out, float *ml_out,
+                             const XchgView *x, uint32_t step, cudaStream_t st) {
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(attn_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmem) != cudaSuccess)
+            return -1;
+        configured = true;
+    }
+    dim3 grid(nsplits, kv.Hkv, toks.n);
+    DecodeFused f = {};
+    f.k_new = k_new; f.v_new = v_new; f.knw = k_norm_w;
+    f.tail = tail; f.gate = gate; f.out = out; f.ml_out = ml_out;
+    if (x) f.x = *x;
+    f.step = step;
+    KvView kv_ = kv; RopeParams rope_ = rope; TokSpec toks_ = toks;
+    if (nsplits == 1 && tail != 3) {
+        attn_decode_kernel<true><<<grid, kDecThreads, kDecSmem, st>>>(kv_, rope_, toks_, H, q_proj_out, q, q_norm_w, eps, part_o,
+                                                                      part_ml, nsplits, f);
+        return cudaGetLastError() == cudaSuccess ? 1 : -1;
+    }
+    void *args[] = {&kv_, &rope_, &toks_, &H, &q_proj_out, &q, &q_norm_w, &eps, &part_o, &part_ml, &nsplits, &f};
+    const cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<void *>(attn_decode_kernel<true>), grid, dim3(kDecThreads), args,
+                                                      kDecSmem, st);
+    return e == cudaSuccess ? 1 : -1;
 }
 
 // ---- merge of partial results + sigmoid gate -------------------------------------------------
@@ -415,15 +601,6 @@ int launch_attn_merge(const float *part_o, const float *part_ml, int nparts, lon
 // for another CTA of its own GPU, so nothing depends on co-residency.
 
 namespace fm {
-
-__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
 
 // grid (H, tokens), D/4 threads
 __global__ void attn_merge_push_kernel(const float *__restrict__ part_o, const float *__restrict__ part_ml, int nsplits, int H,

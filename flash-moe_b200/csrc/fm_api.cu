@@ -497,9 +497,7 @@ static fm_status decode_core(FmCtx *ctx, int fa_idx, const int *seq, const int *
     const int H = c.num_attn_heads, D = c.head_dim;
     std::vector<int> rows(batch);
     if (k != nullptr) {
-        fm_status st = reserve_rows(ctx, fa_idx, seq, batch, rows);
-        if (st) return st;
-        st = append_list(ctx, fa_idx, seq, pos, rows.data(), batch, k, v, knw);
+        fm_status st = reserve_rows(ctx, fa_idx, seq, batch, rows);  // pages and lengths; the kernel writes the rows
         if (st) return st;
     } else {
         for (int i = 0; i < batch; i++) {
@@ -508,6 +506,7 @@ static fm_status decode_core(FmCtx *ctx, int fa_idx, const int *seq, const int *
         }
     }
     const KvView kv = kv_view(ctx, fa_idx);
+    const size_t kvd = (size_t)c.num_kv_heads * D;
     for (int i0 = 0; i0 < batch; i0 += kMaxList) {
         TokSpec t;
         t.mode = 0;
@@ -520,17 +519,14 @@ static fm_status decode_core(FmCtx *ctx, int fa_idx, const int *seq, const int *
         const int ns = pick_splits(ctx, t.n, max_len);
         const float *qp = q_proj_out ? q_proj_out + (size_t)i0 * H * 2 * D : nullptr;
         const float *qq = q ? q + (size_t)i0 * H * D : nullptr;
-        fm_status st;
-        {
-            ProfScope prof(ctx);
-            st = launched(ctx, launch_attn_decode(kv, ctx->rope, t, H, qp, qq, qnw, c.rms_norm_eps, ctx->d_part_o, ctx->d_part_ml, ns, ctx->stream), "attn_decode");
-        }
-        if (st) return st;
         const float *gp = gate ? gate + (size_t)i0 * H * D : nullptr;
         float *op = (out ? out : o_part) + (size_t)i0 * H * D;
         float *mlp = ml_part ? ml_part + (size_t)i0 * H * 2 : nullptr;
-        st = launched(ctx, launch_attn_merge(ctx->d_part_o, ctx->d_part_ml, ns, D, 2, (long long)H * ns * D, (long long)H * ns * 2,
-                                             (long long)ns * D, (long long)ns * 2, t.n, H, D, qp, gp, op, mlp, ctx->stream), "attn_merge");
+        // one launch: append of the new rows, split-KV attention, merge of the splits, gate
+        ProfScope prof(ctx);
+        fm_status st = launched(ctx, launch_attn_decode_fused(kv, ctx->rope, t, H, qp, qq, qnw, c.rms_norm_eps, ctx->d_part_o, ctx->d_part_ml, ns,
+                                                              k ? k + i0 * kvd : nullptr, v ? v + i0 * kvd : nullptr, knw, out ? 1 : 2, gp, op, mlp,
+                                                              nullptr, 0, ctx->stream), "attn_decode");
         if (st) return st;
     }
     return FM_OK;
@@ -942,10 +938,6 @@ extern "C" fm_status fm_attn_decode_exchange_push(FmCtx *ctx, int fa_idx, const 
         }
     }
     FM_CUDA(ctx, sg.push());
-    if (k != nullptr) {
-        st = append_list(ctx, fa_idx, seq, pos, rows.data(), batch, d_k, d_v, d_kn);
-        if (st) return st;
-    }
     TokSpec t;
     t.mode = 0;
     t.n = batch;
@@ -955,15 +947,14 @@ extern "C" fm_status fm_attn_decode_exchange_push(FmCtx *ctx, int fa_idx, const 
         max_len = std::max(max_len, rows[i] + 1);
     }
     const int ns = pick_splits(ctx, batch, max_len);
-    {
-        ProfScope prof(ctx);
-        st = launched(ctx, launch_attn_decode(kv_view(ctx, fa_idx), ctx->rope, t, H, d_qp, d_q, d_qn, c.rms_norm_eps, ctx->d_part_o,
-                                              ctx->d_part_ml, ns, ctx->stream), "attn_decode");
-    }
-    if (st) return st;
     ctx->xchg_step++;
-    st = launched(ctx, launch_attn_merge_push(ctx->d_part_o, ctx->d_part_ml, ns, batch, H, ctx->xchg, ctx->xchg_step, ctx->d_xchg_counter,
-                                              ctx->stream), "attn_merge_push");
+    {
+        // one launch: append, split-KV attention, merge of the splits, rows into every peer's buffer, step published
+        ProfScope prof(ctx);
+        st = launched(ctx, launch_attn_decode_fused(kv_view(ctx, fa_idx), ctx->rope, t, H, d_qp, d_q, d_qn, c.rms_norm_eps, ctx->d_part_o,
+                                                    ctx->d_part_ml, ns, d_k, d_v, d_kn, 3, nullptr, nullptr, nullptr, &ctx->xchg,
+                                                    ctx->xchg_step, ctx->stream), "attn_decode");
+    }
     if (st) return st;
     if (sg.host) FM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));  // the staged inputs may be reused by the next call
     return FM_OK;

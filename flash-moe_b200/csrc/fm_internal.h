@@ -129,6 +129,12 @@ int launch_attn_decode(const KvView &kv, const RopeParams &rope, const TokSpec &
                        const float *q_proj_out, const float *q, const uint16_t *q_norm_w, float eps,
                        float *part_o, float *part_ml, int nsplits, cudaStream_t st);
 
+int launch_attn_decode_fused(const KvView &kv, const RopeParams &rope, const TokSpec &toks, int H,
+                             const float *q_proj_out, const float *q, const uint16_t *q_norm_w, float eps,
+                             float *part_o, float *part_ml, int nsplits, const float *k_new, const float *v_new,
+                             const uint16_t *k_norm_w, int tail, const float *gate, float *out, float *ml_out,
+                             const XchgView *x, uint32_t step, cudaStream_t st);
+
 // merges [nparts] partials per (token, head) laid out with strides, applies the gate
 int launch_attn_merge(const float *part_o, const float *part_ml, int nparts, long long part_stride_o,
                       long long part_stride_ml, long long tok_stride_o, long long tok_stride_ml,
