@@ -82,7 +82,27 @@ struct DecodeFused {
     float *ml_out;
     XchgView x;
     uint32_t step;
+    long long *trace;  // development builds only (-DFM_DEC_TRACE)
 };
+
+#ifdef FM_DEC_TRACE
+extern "C" {
+long long *fm_dec_trace = nullptr;  // device buffer [CTAs][8]
+}
+__device__ long long *g_dec_trace = nullptr;
+__device__ __forceinline__ long long dec_gtime() {
+    long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define DEC_TR(k)                                                                                          \
+    do {                                                                                                   \
+        if (f.trace && threadIdx.x == 0)                                                                   \
+            f.trace[((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 8 + (k)] = dec_gtime(); \
+    } while (0)
+#else
+#define DEC_TR(k) do { } while (0)
+#endif
 
 template <bool kFused>
 __global__ void __launch_bounds__(kDecThreads, 1)
@@ -98,6 +118,7 @@ attn_decode_kernel(KvView kv, RopeParams rope, TokSpec toks, int H, const float 
 
     const int split = blockIdx.x, kvh = blockIdx.y, tok = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    DEC_TR(0);
     const int pw = warp & 3;   // which 16 rows of the tile
     const int hs = warp >> 2;  // which share of the head dim
     const int group = H / kv.Hkv;  // query heads per KV head (<= 16)
@@ -131,6 +152,16 @@ attn_decode_kernel(KvView kv, RopeParams rope, TokSpec toks, int H, const float 
 
     // ---- q: RMS-norm, partial RoPE, scale, split into two bf16 terms -> shared memory ----
     // stage 2 of the ring is free until the first loop iteration: use it as fp32 scratch
+    // rotation table of this token: one sincos per lane instead of eight per row on a few lanes (the
+    // accurate sincosf is some hundred instructions, more beyond |x| ~ 1e5)
+    __shared__ float s_rc[64], s_rs[64];
+    if (tid < rope.rotary_dim / 2) {
+        float sn, cs;
+        sincos_reduced(((float)pos / rope.pos_div) * rope.inv_freq[tid], sn, cs);
+        s_rc[tid] = cs;
+        s_rs[tid] = sn;
+    }
+    __syncthreads();
     {
         float *scratch = reinterpret_cast<float *>(kv_raw + 2 * 2 * kTileBytes);  // [16][256]
         const float qscale = rope.logit_scale * kLog2e;
@@ -168,8 +199,7 @@ attn_decode_kernel(KvView kv, RopeParams rope, TokSpec toks, int H, const float 
                     const int d = lane * 8 + j;
                     if (d < rope.rotary_dim) {
                         const int i = d < half ? d : d - half;
-                        const float ang = ((float)pos / rope.pos_div) * rope.inv_freq[i];
-                        const float c = cosf(ang), s = sinf(ang);
+                        const float c = s_rc[i], s = s_rs[i];
                         x[j] = d < half ? x[j] * c - srow[d + half] * s : srow[d - half] * s + x[j] * c;
                     }
                 }
@@ -196,6 +226,7 @@ attn_decode_kernel(KvView kv, RopeParams rope, TokSpec toks, int H, const float 
     const float4 *xslice = reinterpret_cast<const float4 *>(s_x) + (size_t)(pw * kNS) * 64 + lane;
     // this warp's q fragments (its share of the head dim, hi and lo terms) stay in registers
     __syncthreads();
+    DEC_TR(1);
     uint32_t qh[kKSteps][4], ql[kKSteps][4];
 #pragma unroll
     for (int k8 = 0; k8 < kKSteps; k8++) {
@@ -228,8 +259,7 @@ attn_decode_kernel(KvView kv, RopeParams rope, TokSpec toks, int H, const float 
             const int half = rope.rotary_dim / 2;
             if (d < rope.rotary_dim) {
                 const int i = d < half ? d : d - half;
-                const float ang = ((float)pos / rope.pos_div) * rope.inv_freq[i];
-                const float c = cosf(ang), sn = sinf(ang);
+                const float c = s_rc[i], sn = s_rs[i];
                 x = d < half ? x * c - xs[d + half] * sn : xs[d - half] * sn + x * c;
             }
             const __nv_bfloat16 kb = __float2bfloat16_rn(x);
@@ -340,6 +370,7 @@ attn_decode_kernel(KvView kv, RopeParams rope, TokSpec toks, int H, const float 
     }
     cp_async_wait<0>();
     __syncthreads();
+    DEC_TR(2);
 
     // ---- merge the four row-slices through shared memory (the ring is free now) ----
 #pragma unroll
@@ -431,7 +462,9 @@ attn_decode_kernel(KvView kv, RopeParams rope, TokSpec toks, int H, const float 
         // ---- every CTA's partials are written: meet, then merge the (token, head) rows grid-wide ----
         cg::grid_group grid = cg::this_grid();
         __threadfence();
+        DEC_TR(3);
         grid.sync();
+        DEC_TR(4);
         const int ncta = gridDim.x * gridDim.y * gridDim.z;
         const int cta = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
         // work unit = (token, head, quarter of the head dim): 16 lanes of 4 dims x 16 groups of splits,
@@ -453,10 +486,11 @@ attn_decode_kernel(KvView kv, RopeParams rope, TokSpec toks, int H, const float 
             for (int j = 0; j < nsplits; j++) M = fmaxf(M, s_mlb[j].x);
             float lt = 0.f;
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 5
             for (int j = sg; j < nsplits; j += 16) {
+                const float4 v = __ldcg(reinterpret_cast<const float4 *>(part_o + (prow0 + j) * kD + qd * 64) + dl);
                 const float w = fast_exp2(s_mlb[j].x - M);
                 lt += w * s_mlb[j].y;
-                const float4 v = __ldcg(reinterpret_cast<const float4 *>(part_o + (prow0 + j) * kD + qd * 64) + dl);
                 acc.x += w * v.x; acc.y += w * v.y; acc.z += w * v.z; acc.w += w * v.w;
             }
             s_acc[sg * 16 + dl] = acc;
@@ -474,6 +508,7 @@ attn_decode_kernel(KvView kv, RopeParams rope, TokSpec toks, int H, const float 
             }
         }
     }
+    DEC_TR(5);
     if (f.tail == 3) {
         // every row is in every peer's buffer before the step is published
         cg::grid_group grid = cg::this_grid();
@@ -521,6 +556,9 @@ int launch_attn_decode_fused(const KvView &kv, const RopeParams &rope, const Tok
     f.tail = tail; f.gate = gate; f.out = out; f.ml_out = ml_out;
     if (x) f.x = *x;
     f.step = step;
+#ifdef FM_DEC_TRACE
+    f.trace = fm_dec_trace;
+#endif
     KvView kv_ = kv; RopeParams rope_ = rope; TokSpec toks_ = toks;
     if (nsplits == 1 && tail != 3) {
         attn_decode_kernel<true><<<grid, kDecThreads, kDecSmem, st>>>(kv_, rope_, toks_, H, q_proj_out, q, q_norm_w, eps, part_o,

@@ -170,9 +170,7 @@ attn_q_prep_kernel(RopeParams rope, int H, int start_pos, const float *__restric
     const int t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int half = rope.rotary_dim / 2;
     if (tid < half) {
-        const float ang = ((float)(start_pos + t) / rope.pos_div) * rope.inv_freq[tid];
-        s_cos[tid] = cosf(ang);
-        s_sin[tid] = sinf(ang);
+        sincos_reduced(((float)(start_pos + t) / rope.pos_div) * rope.inv_freq[tid], s_sin[tid], s_cos[tid]);
     }
     __syncthreads();
     const float qscale = rope.logit_scale * kLog2e;

@@ -53,8 +53,8 @@ __global__ void kv_append_kernel(KvView kv, RopeParams rope, TokSpec toks, const
     const int half = rope.rotary_dim / 2;
     if (d < rope.rotary_dim) {
         const int i = d < half ? d : d - half;
-        const float ang = ((float)pos / rope.pos_div) * rope.inv_freq[i];
-        const float c = cosf(ang), s = sinf(ang);
+        float c, s;
+        sincos_reduced(((float)pos / rope.pos_div) * rope.inv_freq[i], s, c);
         if (d < half)
             x = x * c - sx[d + half] * s;
         else
