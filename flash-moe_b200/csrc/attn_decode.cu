@@ -82,6 +82,9 @@ struct DecodeFused {
     float *ml_out;
     XchgView x;
     uint32_t step;
+    unsigned int *counters;  // [tokens*Hkv] arrivals per (token, KV head) + [1] finished groups; self-resetting
+    int coop;                // 1: cooperative launch, the splits are merged grid-wide after a grid barrier;
+                             // 0: ordinary launch, the last CTA to arrive for a (token, KV head) merges its splits
     long long *trace;  // development builds only (-DFM_DEC_TRACE)
 };
 
@@ -458,7 +461,10 @@ attn_decode_kernel(KvView kv, RopeParams rope, TokSpec toks, int H, const float 
         }
     }
     if (!kFused) return;
-    if (!direct) {
+    // work unit of the split merge = (token, head, eighth of the head dim), one warp each: 8 lanes of 4
+    // dims x 4 groups of splits, warp shuffles only
+    const int sg = lane >> 3, dl = lane & 7;
+    if (!direct && f.coop) {
         // ---- every CTA's partials are written: meet, then merge the (token, head) rows grid-wide ----
         cg::grid_group grid = cg::this_grid();
         __threadfence();
@@ -467,48 +473,90 @@ attn_decode_kernel(KvView kv, RopeParams rope, TokSpec toks, int H, const float 
         DEC_TR(4);
         const int ncta = gridDim.x * gridDim.y * gridDim.z;
         const int cta = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
-        // work unit = (token, head, quarter of the head dim): 16 lanes of 4 dims x 16 groups of splits,
-        // so that a batch-1 step (32 rows) still spreads over 128 CTAs and no thread walks more than a
-        // few splits
-        const int units = gridDim.z * H * 4;
-        const int sg = tid >> 4, dl = tid & 15;
-        float2 *s_mlb = reinterpret_cast<float2 *>(kv_raw);                       // [nsplits] (max, sum)
-        float4 *s_acc = reinterpret_cast<float4 *>(kv_raw + 2048);                // [16][16]
-        float *s_lt = reinterpret_cast<float *>(kv_raw + 2048 + 16 * 16 * 16);    // [16]
-        for (int u = cta; u < units; u += ncta) {
-            const int item = u >> 2, qd = u & 3;
+        const int units = gridDim.z * H * 8;
+        for (int u = cta * kDecWarps + warp; u < units; u += ncta * kDecWarps) {
+            const int item = u >> 3, e8 = u & 7;
             const int tk = item / H, head = item - tk * H;
             const size_t prow0 = ((size_t)tk * H + head) * nsplits;
-            __syncthreads();
-            for (int j = tid; j < nsplits; j += kDecThreads) s_mlb[j] = __ldcg(reinterpret_cast<const float2 *>(part_ml) + prow0 + j);
-            __syncthreads();
+            const float2 *mlp = reinterpret_cast<const float2 *>(part_ml) + prow0;
             float M = kNegBig;
-            for (int j = 0; j < nsplits; j++) M = fmaxf(M, s_mlb[j].x);
+            for (int j = lane; j < nsplits; j += 32) M = fmaxf(M, __ldcg(mlp + j).x);
+            M = warp_max(M);
             float lt = 0.f;
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 5
-            for (int j = sg; j < nsplits; j += 16) {
-                const float4 v = __ldcg(reinterpret_cast<const float4 *>(part_o + (prow0 + j) * kD + qd * 64) + dl);
-                const float w = fast_exp2(s_mlb[j].x - M);
-                lt += w * s_mlb[j].y;
+#pragma unroll 4
+            for (int j = sg; j < nsplits; j += 4) {
+                const float4 v = __ldcg(reinterpret_cast<const float4 *>(part_o + (prow0 + j) * kD + e8 * 32) + dl);
+                const float2 ml2 = __ldcg(mlp + j);
+                const float w = fast_exp2(ml2.x - M);
+                lt += w * ml2.y;
                 acc.x += w * v.x; acc.y += w * v.y; acc.z += w * v.z; acc.w += w * v.w;
             }
-            s_acc[sg * 16 + dl] = acc;
-            if (dl == 0) s_lt[sg] = lt;
-            __syncthreads();
-            if (sg == 0) {
-                float ltot = s_lt[0];
 #pragma unroll
-                for (int g2 = 1; g2 < 16; g2++) {
-                    const float4 v = s_acc[g2 * 16 + dl];
-                    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-                    ltot += s_lt[g2];
-                }
-                emit(tk, head, qd * 64 + dl * 4, acc, M, ltot);
+            for (int o = 8; o <= 16; o <<= 1) {
+                acc.x += __shfl_xor_sync(0xffffffffu, acc.x, o);
+                acc.y += __shfl_xor_sync(0xffffffffu, acc.y, o);
+                acc.z += __shfl_xor_sync(0xffffffffu, acc.z, o);
+                acc.w += __shfl_xor_sync(0xffffffffu, acc.w, o);
+                lt += __shfl_xor_sync(0xffffffffu, lt, o);
             }
+            if (sg == 0) emit(tk, head, e8 * 32 + dl * 4, acc, M, lt);
+        }
+    } else if (!direct) {
+        // ---- the last CTA to arrive for this (token, KV head) merges its splits ----
+        __shared__ int s_last;
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) {
+            unsigned int *cnt = f.counters + tok * kv.Hkv + kvh;
+            const unsigned int old = atomicAdd(cnt, 1u);
+            s_last = old == (unsigned int)nsplits - 1;
+            if (s_last) *cnt = 0;
+        }
+        __syncthreads();
+        if (!s_last) return;
+        __threadfence();
+        // a warp takes whole heads: lane j holds the (max, sum) of split j (at most 24 splits on this
+        // path), the weights travel by shuffle, and all row loads of a head are in flight together
+        for (int r = warp; r < group; r += kDecWarps) {
+            const int head = kvh * group + r;
+            const size_t prow0 = ((size_t)tok * H + head) * nsplits;
+            const float2 mlj = lane < nsplits ? __ldcg(reinterpret_cast<const float2 *>(part_ml) + prow0 + lane) : make_float2(kNegBig, 0.f);
+            const float M = warp_max(mlj.x);
+            const float wj = fast_exp2(mlj.x - M);
+            const float lt = warp_sum(wj * mlj.y);
+            float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0;
+            const float4 *src = reinterpret_cast<const float4 *>(part_o + prow0 * kD) + lane * 2;
+#pragma unroll 8
+            for (int j = 0; j < nsplits; j++) {
+                const float w = __shfl_sync(0xffffffffu, wj, j);
+                const float4 v0 = __ldcg(src + (size_t)j * (kD / 4)), v1 = __ldcg(src + (size_t)j * (kD / 4) + 1);
+                a0.x += w * v0.x; a0.y += w * v0.y; a0.z += w * v0.z; a0.w += w * v0.w;
+                a1.x += w * v1.x; a1.y += w * v1.y; a1.z += w * v1.z; a1.w += w * v1.w;
+            }
+            emit(tok, head, lane * 8, a0, M, lt);
+            emit(tok, head, lane * 8 + 4, a1, M, lt);
         }
     }
     DEC_TR(5);
+    if (f.tail == 3 && !f.coop) {
+        // this (token, KV head) is in every peer's buffer; the last group to get here publishes the step
+        __threadfence_system();
+        __syncthreads();
+        if (tid == 0) {
+            unsigned int *done = f.counters + gridDim.z * kv.Hkv;
+            const unsigned int groups = gridDim.y * gridDim.z;
+            if (atomicAdd(done, 1u) == groups - 1) {
+                *done = 0;
+                __threadfence_system();
+                for (int r = 0; r < f.x.nranks; r++) {
+                    uint32_t *flags = reinterpret_cast<uint32_t *>(f.x.peer[r] + f.x.flag_offset_floats);
+                    st_release_sys(flags + (f.step & 1) * f.x.nranks + f.x.me, f.step);
+                }
+            }
+        }
+        return;
+    }
     if (f.tail == 3) {
         // every row is in every peer's buffer before the step is published
         cg::grid_group grid = cg::this_grid();
@@ -543,7 +591,7 @@ int launch_attn_decode_fused(const KvView &kv, const RopeParams &rope, const Tok
                              const float *q_proj_out, const float *q, const uint16_t *q_norm_w, float eps,
                              float *part_o, float *part_ml, int nsplits, const float *k_new, const float *v_new,
                              const uint16_t *k_norm_w, int tail, const float *gate, float *out, float *ml_out,
-                             const XchgView *x, uint32_t step, cudaStream_t st) {
+                             const XchgView *x, uint32_t step, unsigned int *counters, cudaStream_t st) {
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(attn_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmem) != cudaSuccess)
@@ -559,8 +607,13 @@ int launch_attn_decode_fused(const KvView &kv, const RopeParams &rope, const Tok
 #ifdef FM_DEC_TRACE
     f.trace = fm_dec_trace;
 #endif
+    f.counters = counters;
+    // Few splits per (KV head, sequence): an ordinary launch, the last CTA of each group merges (a
+    // cooperative launch costs ~10 us more to start).  Many splits (small batch): one CTA could not
+    // merge them quickly, so the grid meets at a barrier and every warp takes a share.
+    f.coop = nsplits > 24;
     KvView kv_ = kv; RopeParams rope_ = rope; TokSpec toks_ = toks;
-    if (nsplits == 1 && tail != 3) {
+    if (!f.coop) {
         attn_decode_kernel<true><<<grid, kDecThreads, kDecSmem, st>>>(kv_, rope_, toks_, H, q_proj_out, q, q_norm_w, eps, part_o,
                                                                       part_ml, nsplits, f);
         return cudaGetLastError() == cudaSuccess ? 1 : -1;

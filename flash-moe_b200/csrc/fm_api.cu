@@ -160,6 +160,8 @@ extern "C" fm_status fm_create(const FmConfig *cfg, FmCtx **out) {
         const size_t rows = ((size_t)2 * ctx->sm_count + (size_t)c.num_kv_heads * c.max_batch_tokens) * 16 + 64;
         CREATE_CUDA(cudaMalloc(&ctx->d_part_o, rows * c.head_dim * sizeof(float)));
         CREATE_CUDA(cudaMalloc(&ctx->d_part_ml, rows * 2 * sizeof(float)));
+        CREATE_CUDA(cudaMalloc(&ctx->d_dec_counters, ((size_t)kMaxList * c.num_kv_heads + 1) * sizeof(unsigned int)));
+        CREATE_CUDA(cudaMemset(ctx->d_dec_counters, 0, ((size_t)kMaxList * c.num_kv_heads + 1) * sizeof(unsigned int)));
         if (c.seq_shard_count == 1) {  // prefill needs the whole sequence on one context
             CREATE_CUDA(cudaMalloc(&ctx->d_pf_q16, (size_t)c.max_batch_tokens * c.num_attn_heads * c.head_dim * 2 * 2));  // hi | lo
             CREATE_CUDA(cudaMalloc(&ctx->d_pf_k16, (size_t)c.max_seq_len * c.num_kv_heads * c.head_dim * 2));
@@ -198,7 +200,7 @@ extern "C" void fm_destroy(FmCtx *ctx) {
     cudaSetDevice(ctx->cfg.device);
     cudaDeviceSynchronize();
     cudaFree(ctx->pool); cudaFree(ctx->d_page_table); cudaFree(ctx->d_conv_state); cudaFree(ctx->d_ssm_state);
-    cudaFree(ctx->d_part_o); cudaFree(ctx->d_part_ml); cudaFree(ctx->d_xchg_counter); cudaFree(ctx->d_pf_q16); cudaFree(ctx->d_pf_k16); cudaFree(ctx->d_pf_v16); cudaFree(ctx->d_err);
+    cudaFree(ctx->d_part_o); cudaFree(ctx->d_part_ml); cudaFree(ctx->d_dec_counters); cudaFree(ctx->d_xchg_counter); cudaFree(ctx->d_pf_q16); cudaFree(ctx->d_pf_k16); cudaFree(ctx->d_pf_v16); cudaFree(ctx->d_err);
     if (ctx->h_err) cudaFreeHost(ctx->h_err); cudaFree(ctx->d_work);
     cudaFree(ctx->d_stage);
     for (cudaEvent_t e : ctx->prof_ev) cudaEventDestroy(e);
@@ -526,7 +528,7 @@ static fm_status decode_core(FmCtx *ctx, int fa_idx, const int *seq, const int *
         ProfScope prof(ctx);
         fm_status st = launched(ctx, launch_attn_decode_fused(kv, ctx->rope, t, H, qp, qq, qnw, c.rms_norm_eps, ctx->d_part_o, ctx->d_part_ml, ns,
                                                               k ? k + i0 * kvd : nullptr, v ? v + i0 * kvd : nullptr, knw, out ? 1 : 2, gp, op, mlp,
-                                                              nullptr, 0, ctx->stream), "attn_decode");
+                                                              nullptr, 0, ctx->d_dec_counters, ctx->stream), "attn_decode");
         if (st) return st;
     }
     return FM_OK;
@@ -953,7 +955,7 @@ extern "C" fm_status fm_attn_decode_exchange_push(FmCtx *ctx, int fa_idx, const 
         ProfScope prof(ctx);
         st = launched(ctx, launch_attn_decode_fused(kv_view(ctx, fa_idx), ctx->rope, t, H, d_qp, d_q, d_qn, c.rms_norm_eps, ctx->d_part_o,
                                                     ctx->d_part_ml, ns, d_k, d_v, d_kn, 3, nullptr, nullptr, nullptr, &ctx->xchg,
-                                                    ctx->xchg_step, ctx->stream), "attn_decode");
+                                                    ctx->xchg_step, ctx->d_dec_counters, ctx->stream), "attn_decode");
     }
     if (st) return st;
     if (sg.host) FM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));  // the staged inputs may be reused by the next call

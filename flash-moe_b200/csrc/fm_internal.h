@@ -93,6 +93,7 @@ struct FmCtx {
     float *d_part_o = nullptr;   // [batch][H][max_splits][D]
     float *d_part_ml = nullptr;  // [batch][H][max_splits][2]
     int max_splits = 0;
+    unsigned int *d_dec_counters = nullptr;  // arrival counters of the fused decode kernel
 
     // prefill scratch: fp16 copies of q (normalised, rotated, scaled) and of the sequence's K, V rows
     void *d_pf_q16 = nullptr;  // [max_batch_tokens][H*D]
@@ -133,7 +134,7 @@ int launch_attn_decode_fused(const KvView &kv, const RopeParams &rope, const Tok
                              const float *q_proj_out, const float *q, const uint16_t *q_norm_w, float eps,
                              float *part_o, float *part_ml, int nsplits, const float *k_new, const float *v_new,
                              const uint16_t *k_norm_w, int tail, const float *gate, float *out, float *ml_out,
-                             const XchgView *x, uint32_t step, cudaStream_t st);
+                             const XchgView *x, uint32_t step, unsigned int *counters, cudaStream_t st);
 
 // merges [nparts] partials per (token, head) laid out with strides, applies the gate
 int launch_attn_merge(const float *part_o, const float *part_ml, int nparts, long long part_stride_o,
