@@ -227,13 +227,18 @@ def run_ours(args):
         torch.cuda.synchronize()
         dist.barrier()
 
+    sq, skv, so = B * Hl * 2 * D, B * Hkvl * D, B * Hl * D  # floats between consecutive layers
+
     def step():
         pos = [cur[0]] * B
+        if ss == 1 or p2p:
+            # the layer loop runs inside the library, as in a C host (one call per token)
+            ctx.attn_decode_layers(0, NL, seqs, pos, out, qp, kn, vn, sq, skv, so, exchange=p2p)
+            cur[0] += 1
+            return
         for layer in range(NL):
-            if ss == 1:
-                ctx.attn_decode(layer, seqs, pos, out[layer], q_proj_out=qp[layer], k=kn[layer], v=vn[layer])
-            elif p2p:
-                ctx.attn_decode_exchange(layer, seqs, pos, out[layer], q_proj_out=qp[layer], k=kn[layer], v=vn[layer])
+            if False:
+                pass
             else:
                 ctx.attn_decode_partial(layer, seqs, pos, o_part, ml_part, q_proj_out=qp[layer], k=kn[layer], v=vn[layer])
                 dist.all_gather_into_tensor(o_all, o_part, group=seq_group)
@@ -301,11 +306,13 @@ def run_ours(args):
 
         def step_host():
             pos = [cur[0]] * B
+            if ss == 1 or p2p:
+                ctx.attn_decode_layers(0, NL, seqs, pos, h_out, h_qp, h_k, h_v, sq, skv, so, exchange=p2p)
+                cur[0] += 1
+                return
             for layer in range(NL):
-                if ss == 1:
-                    ctx.attn_decode(layer, seqs, pos, h_out[layer], q_proj_out=h_qp[layer], k=h_k[layer], v=h_v[layer])
-                elif p2p:
-                    ctx.attn_decode_exchange(layer, seqs, pos, h_out[layer], q_proj_out=h_qp[layer], k=h_k[layer], v=h_v[layer])
+                if False:
+                    pass
                 else:
                     ctx.attn_decode_partial(layer, seqs, pos, h_o, h_ml, q_proj_out=h_qp[layer], k=h_k[layer], v=h_v[layer])
                     o_part.copy_(torch.from_numpy(h_o)); ml_part.copy_(torch.from_numpy(h_ml))

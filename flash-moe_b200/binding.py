@@ -23,7 +23,7 @@ EXPORTS = [
     "fm_gdn_decode", "fm_gdn_prefill", "fm_kv_export", "fm_kv_import", "fm_state_export",
     "fm_state_import", "fm_launch_count", "fm_profile_enable", "fm_profile_read",
     "fm_attn_decode_static", "fm_exchange_bytes", "fm_exchange_attach", "fm_attn_decode_exchange_push",
-    "fm_attn_decode_exchange_merge", "fm_attn_decode_exchange",
+    "fm_attn_decode_exchange_merge", "fm_attn_decode_exchange", "fm_attn_decode_layers",
 ]
 
 
@@ -212,6 +212,15 @@ class Context:
         self._check(self.lib.fm_attn_decode_exchange(self.h, C.c_int(fa_idx), sp, pp, C.c_int(len(s)), _ptr(q_proj_out),
                                                      _ptr(q), _ptr(gate), _ptr(k), _ptr(v), _ptr(q_norm_w),
                                                      _ptr(k_norm_w), _ptr(out)))
+
+    def attn_decode_layers(self, first_layer, n_layers, seq, pos, out, q_proj_out, k, v, stride_q, stride_kv, stride_out,
+                           q_norm_w=None, k_norm_w=None, exchange=False):
+        """All layers of one token in one call; strides in floats between consecutive layers."""
+        s, sp = _ints(seq); p, pp = _ints(pos)
+        self._check(self.lib.fm_attn_decode_layers(self.h, C.c_int(first_layer), C.c_int(n_layers), sp, pp, C.c_int(len(s)),
+                                                   _ptr(q_proj_out), C.c_size_t(stride_q), _ptr(k), _ptr(v), C.c_size_t(stride_kv),
+                                                   _ptr(q_norm_w), _ptr(k_norm_w), _ptr(out), C.c_size_t(stride_out),
+                                                   C.c_int(1 if exchange else 0)))
 
     def attn_prefill(self, fa_idx, seq, start_pos, n, out, q_proj_out=None, q=None, gate=None, k=None,
                      v=None, q_norm_w=None, k_norm_w=None):

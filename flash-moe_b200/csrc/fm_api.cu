@@ -995,3 +995,21 @@ extern "C" fm_status fm_attn_decode_exchange(FmCtx *ctx, int fa_idx, const int *
     if (st) return st;
     return fm_attn_decode_exchange_merge(ctx, batch, q_proj_out, gate, out);
 }
+
+// ---- one token through several full-attention layers -------------------------------------------
+extern "C" fm_status fm_attn_decode_layers(FmCtx *ctx, int first_layer, int n_layers, const int *seq, const int *pos, int batch,
+                                           const float *q_proj_out, size_t layer_stride_q, const float *k, const float *v,
+                                           size_t layer_stride_kv, const uint16_t *q_norm_w, const uint16_t *k_norm_w, float *out,
+                                           size_t layer_stride_out, int exchange) {
+    if (!ctx) return FM_ERR_INVALID;
+    if (!q_proj_out || !out || n_layers < 0) return fail(ctx, FM_ERR_INVALID, "fm_attn_decode_layers: bad argument");
+    for (int l = 0; l < n_layers; l++) {
+        const float *qp = q_proj_out + (size_t)l * layer_stride_q;
+        const float *kk = k ? k + (size_t)l * layer_stride_kv : nullptr, *vv = v ? v + (size_t)l * layer_stride_kv : nullptr;
+        float *oo = out + (size_t)l * layer_stride_out;
+        const fm_status st = exchange ? fm_attn_decode_exchange(ctx, first_layer + l, seq, pos, batch, qp, nullptr, nullptr, kk, vv, q_norm_w, k_norm_w, oo)
+                                      : fm_attn_decode(ctx, first_layer + l, seq, pos, batch, qp, nullptr, nullptr, kk, vv, q_norm_w, k_norm_w, oo);
+        if (st) return st;
+    }
+    return FM_OK;
+}

@@ -175,6 +175,18 @@ fm_status fm_attn_decode_exchange(FmCtx *ctx, int fa_idx, const int *seq, const 
                                   const float *k, const float *v, const uint16_t *q_norm_w,
                                   const uint16_t *k_norm_w, float *out);
 
+/* One token of `batch` sequences through n_layers consecutive full-attention layers: the layer loop
+ * of the reference's generation loop (metal_infer/generate.h:2187-2250, one fused_layer_forward per
+ * layer) for hosts that have every layer's projections at hand.  Layer first_layer + l reads
+ * q_proj_out + l * layer_stride_q (interleaved q | gate), k and v + l * layer_stride_kv, and writes
+ * out + l * layer_stride_out (strides in floats).  exchange != 0 runs each layer through
+ * fm_attn_decode_exchange (sequence-sharded store), else through fm_attn_decode. */
+fm_status fm_attn_decode_layers(FmCtx *ctx, int first_layer, int n_layers, const int *seq, const int *pos,
+                                int batch, const float *q_proj_out, size_t layer_stride_q, const float *k,
+                                const float *v, size_t layer_stride_kv, const uint16_t *q_norm_w,
+                                const uint16_t *k_norm_w, float *out, size_t layer_stride_out,
+                                int exchange);
+
 /* Causal prefill of n tokens of one sequence at positions start_pos..: q norm + RoPE, k norm +
  * RoPE + append, token t attends to rows [0, len_before + t], times sigmoid(gate).
  * Replaces batched_prefill.h:543-740 and the Metal kernels prefill_q_rope_norm_bf16 /
