@@ -61,6 +61,11 @@ __device__ __forceinline__ void load_tile_async(uint32_t dst, const __nv_bfloat1
     }
 }
 
+// Programmatic dependent launch (griddepcontrol): both are no-ops unless the launch carries the
+// programmatic-stream-serialization attribute.
+__device__ __forceinline__ void dep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+__device__ __forceinline__ void dep_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+
 __device__ __forceinline__ void named_barrier(int id, int nthreads) {
     asm volatile("bar.sync %0, %1;\n" ::"r"(id), "r"(nthreads) : "memory");
 }
@@ -122,6 +127,9 @@ attn_decode_kernel(KvView kv, RopeParams rope, TokSpec toks, int H, const float 
     const int split = blockIdx.x, kvh = blockIdx.y, tok = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     DEC_TR(0);
+    // A following launch marked as programmatically dependent may start filling free SMs now; it
+    // holds back its own writes to the shared scratch until this grid has completed (dep_wait below).
+    if (kFused) dep_launch_dependents();
     const int pw = warp & 3;   // which 16 rows of the tile
     const int hs = warp >> 2;  // which share of the head dim
     const int group = H / kv.Hkv;  // query heads per KV head (<= 16)
@@ -425,6 +433,9 @@ attn_decode_kernel(KvView kv, RopeParams rope, TokSpec toks, int H, const float 
         }
     };
     const bool direct = kFused && nsplits == 1;  // this CTA is the only split: finish the rows here
+    // From here on the kernel writes what the previous launch may still be reading (partials,
+    // arrival counters, exchange slots): wait for it to complete.  No effect for an ordinary launch.
+    if (kFused) dep_wait();
     for (int r = warp; r < group; r += kDecWarps) {
         float mw[4], M = kNegBig;
 #pragma unroll
@@ -591,7 +602,8 @@ int launch_attn_decode_fused(const KvView &kv, const RopeParams &rope, const Tok
                              const float *q_proj_out, const float *q, const uint16_t *q_norm_w, float eps,
                              float *part_o, float *part_ml, int nsplits, const float *k_new, const float *v_new,
                              const uint16_t *k_norm_w, int tail, const float *gate, float *out, float *ml_out,
-                             const XchgView *x, uint32_t step, unsigned int *counters, cudaStream_t st) {
+                             const XchgView *x, uint32_t step, unsigned int *counters, bool overlap_prev,
+                             cudaStream_t st) {
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(attn_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmem) != cudaSuccess)
@@ -614,9 +626,18 @@ int launch_attn_decode_fused(const KvView &kv, const RopeParams &rope, const Tok
     f.coop = nsplits > 24;
     KvView kv_ = kv; RopeParams rope_ = rope; TokSpec toks_ = toks;
     if (!f.coop) {
-        attn_decode_kernel<true><<<grid, kDecThreads, kDecSmem, st>>>(kv_, rope_, toks_, H, q_proj_out, q, q_norm_w, eps, part_o,
-                                                                      part_ml, nsplits, f);
-        return cudaGetLastError() == cudaSuccess ? 1 : -1;
+        // overlap_prev: the caller vouches that this launch reads nothing the previous kernel in the
+        // stream writes except through the scratch the kernel guards itself (another layer's step).
+        // Its CTAs then take SMs as the previous grid's CTAs retire instead of after the grid drains.
+        cudaLaunchConfig_t lc = {};
+        lc.gridDim = grid; lc.blockDim = dim3(kDecThreads); lc.dynamicSmemBytes = kDecSmem; lc.stream = st;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[0].val.programmaticStreamSerializationAllowed = 1;
+        lc.attrs = at; lc.numAttrs = overlap_prev ? 1 : 0;
+        const cudaError_t e = cudaLaunchKernelEx(&lc, attn_decode_kernel<true>, kv_, rope_, toks_, H, q_proj_out, q, q_norm_w, eps,
+                                                 part_o, part_ml, nsplits, f);
+        return e == cudaSuccess ? 1 : -1;
     }
     void *args[] = {&kv_, &rope_, &toks_, &H, &q_proj_out, &q, &q_norm_w, &eps, &part_o, &part_ml, &nsplits, &f};
     const cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<void *>(attn_decode_kernel<true>), grid, dim3(kDecThreads), args,
@@ -741,6 +762,7 @@ __global__ void attn_wait_merge_kernel(XchgView x, uint32_t step, int H, const f
     const int head = blockIdx.x, tok = blockIdx.y, d = threadIdx.x * 4;
     const int par = step & 1;
     const float *mine = x.peer[x.me];
+    dep_launch_dependents();
     if (threadIdx.x == 0) {
         const uint32_t *flags = reinterpret_cast<const uint32_t *>(mine + x.flag_offset_floats) + par * x.nranks;
         int ok = 1;
@@ -757,6 +779,7 @@ __global__ void attn_wait_merge_kernel(XchgView x, uint32_t step, int H, const f
         s_ok = ok;
     }
     __syncthreads();
+    dep_wait();  // launched ahead of the previous kernel's end: its writes are complete from here on
     float *dst = out + ((size_t)tok * H + head) * D + d;
     if (!s_ok) {
         *reinterpret_cast<float4 *>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -789,9 +812,17 @@ int launch_attn_merge_push(const float *part_o, const float *part_ml, int nsplit
     return cudaGetLastError() == cudaSuccess ? 1 : -1;
 }
 int launch_attn_wait_merge(const XchgView &x, uint32_t step, int ntok, int H, const float *q_proj_out, const float *gate,
-                           float *out, int *err, cudaStream_t st) {
-    attn_wait_merge_kernel<<<dim3(H, ntok), kD / 4, 0, st>>>(x, step, H, q_proj_out, gate, out, err);
-    return cudaGetLastError() == cudaSuccess ? 1 : -1;
+                           float *out, int *err, bool overlap_prev, cudaStream_t st) {
+    // overlap_prev: the CTAs may start (and poll the flags) while the kernel that pushes this rank's
+    // own rows is still running; they read only what the flags cover
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3(H, ntok); lc.blockDim = dim3(kD / 4); lc.dynamicSmemBytes = 0; lc.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = at; lc.numAttrs = overlap_prev ? 1 : 0;
+    const cudaError_t e = cudaLaunchKernelEx(&lc, attn_wait_merge_kernel, x, step, H, q_proj_out, gate, out, err);
+    return e == cudaSuccess ? 1 : -1;
 }
 
 }  // namespace fm

@@ -203,6 +203,8 @@ extern "C" void fm_destroy(FmCtx *ctx) {
     cudaFree(ctx->d_part_o); cudaFree(ctx->d_part_ml); cudaFree(ctx->d_dec_counters); cudaFree(ctx->d_xchg_counter); cudaFree(ctx->d_pf_q16); cudaFree(ctx->d_pf_k16); cudaFree(ctx->d_pf_v16); cudaFree(ctx->d_err);
     if (ctx->h_err) cudaFreeHost(ctx->h_err); cudaFree(ctx->d_work);
     cudaFree(ctx->d_stage);
+    cudaFree(ctx->d_lstage);
+    if (ctx->h_lstage) cudaFreeHost(ctx->h_lstage);
     for (cudaEvent_t e : ctx->prof_ev) cudaEventDestroy(e);
     if (ctx->h_stage) cudaFreeHost(ctx->h_stage);
     delete ctx;
@@ -230,8 +232,11 @@ static fm_status check_device_error(FmCtx *ctx) {
     return fail(ctx, FM_ERR_TIMEOUT, "a device-side wait expired (code 0x%x); the results of that call are invalid", code);
 }
 
+// The error word comes to the host only where the host waits anyway (a copy per call would sit
+// between consecutive launches of a device-pointer caller).
 extern "C" fm_status fm_synchronize(FmCtx *ctx) {
     if (!ctx) return FM_ERR_INVALID;
+    FM_CUDA(ctx, cudaMemcpyAsync(ctx->h_err, ctx->d_err, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
     FM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     return check_device_error(ctx);
 }
@@ -490,6 +495,8 @@ static int pick_splits(const FmCtx *ctx, int batch, int max_len) {
     return std::max(1, std::min(want, ctx->max_splits));
 }
 
+static inline bool sg_host(const FmCtx *ctx) { return ctx->ptr_mode == FM_PTR_HOST; }
+
 // Shared body of fm_attn_decode / fm_attn_decode_partial (device pointers).
 static fm_status decode_core(FmCtx *ctx, int fa_idx, const int *seq, const int *pos, int batch,
                              const float *q_proj_out, const float *q, const float *gate, const float *k,
@@ -528,7 +535,8 @@ static fm_status decode_core(FmCtx *ctx, int fa_idx, const int *seq, const int *
         ProfScope prof(ctx);
         fm_status st = launched(ctx, launch_attn_decode_fused(kv, ctx->rope, t, H, qp, qq, qnw, c.rms_norm_eps, ctx->d_part_o, ctx->d_part_ml, ns,
                                                               k ? k + i0 * kvd : nullptr, v ? v + i0 * kvd : nullptr, knw, out ? 1 : 2, gp, op, mlp,
-                                                              nullptr, 0, ctx->d_dec_counters, ctx->stream), "attn_decode");
+                                                              nullptr, 0, ctx->d_dec_counters, ctx->overlap_prev && i0 == 0 && !sg_host(ctx),
+                                                              ctx->stream), "attn_decode");
         if (st) return st;
     }
     return FM_OK;
@@ -656,7 +664,7 @@ extern "C" fm_status fm_attn_prefill(FmCtx *ctx, int fa_idx, int seq, int start_
                                                c.rms_norm_eps, wk, d_out, ctx->stream), "attn_prefill");
     }
     if (st) return st;
-    FM_CUDA(ctx, cudaMemcpyAsync(ctx->h_err, ctx->d_err, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+    if (sg.host) FM_CUDA(ctx, cudaMemcpyAsync(ctx->h_err, ctx->d_err, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
     FM_CUDA(ctx, sg.pull(out, w_out, n * qd));
     if (sg.host) return check_device_error(ctx);
     return FM_OK;
@@ -955,7 +963,8 @@ extern "C" fm_status fm_attn_decode_exchange_push(FmCtx *ctx, int fa_idx, const 
         ProfScope prof(ctx);
         st = launched(ctx, launch_attn_decode_fused(kv_view(ctx, fa_idx), ctx->rope, t, H, d_qp, d_q, d_qn, c.rms_norm_eps, ctx->d_part_o,
                                                     ctx->d_part_ml, ns, d_k, d_v, d_kn, 3, nullptr, nullptr, nullptr, &ctx->xchg,
-                                                    ctx->xchg_step, ctx->d_dec_counters, ctx->stream), "attn_decode");
+                                                    ctx->xchg_step, ctx->d_dec_counters, ctx->overlap_prev && !sg.host, ctx->stream),
+                      "attn_decode");
     }
     if (st) return st;
     if (sg.host) FM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));  // the staged inputs may be reused by the next call
@@ -980,9 +989,9 @@ extern "C" fm_status fm_attn_decode_exchange_merge(FmCtx *ctx, int batch, const 
     if (!ok) return fail(ctx, FM_ERR_INVALID, "%s: staging buffer too small", fn);
     FM_CUDA(ctx, sg.push());
     fm_status st = launched(ctx, launch_attn_wait_merge(ctx->xchg, ctx->xchg_step, batch, c.num_attn_heads, d_qp, d_g, d_out, ctx->d_err,
-                                                        ctx->stream), "attn_wait_merge");
+                                                        ctx->overlap_merge && !sg.host, ctx->stream), "attn_wait_merge");
     if (st) return st;
-    FM_CUDA(ctx, cudaMemcpyAsync(ctx->h_err, ctx->d_err, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+    if (sg.host) FM_CUDA(ctx, cudaMemcpyAsync(ctx->h_err, ctx->d_err, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
     FM_CUDA(ctx, sg.pull(out, w_out, batch * qd));
     if (sg.host) return check_device_error(ctx);
     return FM_OK;
@@ -997,13 +1006,92 @@ extern "C" fm_status fm_attn_decode_exchange(FmCtx *ctx, int fa_idx, const int *
 }
 
 // ---- one token through several full-attention layers -------------------------------------------
+static bool is_pinned(const void *p) {
+    cudaPointerAttributes a;
+    if (cudaPointerGetAttributes(&a, p) != cudaSuccess) { cudaGetLastError(); return false; }
+    return a.type == cudaMemoryTypeHost;
+}
+
+// Host-pointer form: every layer's inputs go to the device in one batch of copies, the layers run
+// back to back on device pointers, the outputs come back in one copy.  Page-locked caller buffers are
+// copied directly; pageable ones pass through the context's own page-locked staging area.
+static fm_status decode_layers_host(FmCtx *ctx, int first_layer, int n_layers, const int *seq, const int *pos, int batch,
+                                    const float *q_proj_out, size_t sq, const float *k, const float *v, size_t skv,
+                                    const uint16_t *qnw, const uint16_t *knw, float *out, size_t so, int exchange) {
+    const FmConfig &c = ctx->cfg;
+    if (batch < 0 || batch > c.max_batch_tokens) return fail(ctx, FM_ERR_INVALID, "fm_attn_decode_layers: batch %d", batch);
+    FM_CUDA(ctx, cudaSetDevice(c.device));
+    const size_t qf = (size_t)batch * c.num_attn_heads * 2 * c.head_dim, kvf = (size_t)batch * c.num_kv_heads * c.head_dim;
+    const size_t of = (size_t)batch * c.num_attn_heads * c.head_dim, nl = (size_t)n_layers;
+    auto up = [](size_t b) { return (b + 255) & ~(size_t)255; };
+    const size_t o_w = 0, o_q = 1024, o_k = o_q + up(nl * qf * 4), o_v = o_k + up(nl * kvf * 4), o_out = o_v + up(nl * kvf * 4);
+    const size_t need = o_out + up(nl * of * 4);
+    if (need > ctx->lstage_bytes) {
+        FM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        cudaFree(ctx->d_lstage);
+        if (ctx->h_lstage) cudaFreeHost(ctx->h_lstage);
+        ctx->d_lstage = ctx->h_lstage = nullptr;
+        ctx->lstage_bytes = 0;
+        FM_CUDA(ctx, cudaMallocHost(&ctx->h_lstage, need));
+        FM_CUDA(ctx, cudaMalloc(&ctx->d_lstage, need));
+        ctx->lstage_bytes = need;
+    }
+    char *hs = ctx->h_lstage, *ds = ctx->d_lstage;
+    // host -> device of n_layers blocks of `block` floats, `stride` floats apart at the source
+    auto send = [&](const float *src, size_t stride, size_t block, size_t off) -> cudaError_t {
+        if (src == nullptr || block == 0) return cudaSuccess;
+        if (is_pinned(src))
+            return cudaMemcpy2DAsync(ds + off, block * 4, src, stride * 4, block * 4, nl, cudaMemcpyHostToDevice, ctx->stream);
+        for (size_t l = 0; l < nl; l++) memcpy(hs + off + l * block * 4, src + l * stride, block * 4);
+        return cudaMemcpyAsync(ds + off, hs + off, nl * block * 4, cudaMemcpyHostToDevice, ctx->stream);
+    };
+    if (qnw) memcpy(hs + o_w, qnw, (size_t)c.head_dim * 2);
+    if (knw) memcpy(hs + o_w + 512, knw, (size_t)c.head_dim * 2);
+    if (qnw || knw) FM_CUDA(ctx, cudaMemcpyAsync(ds + o_w, hs + o_w, 1024, cudaMemcpyHostToDevice, ctx->stream));
+    FM_CUDA(ctx, send(q_proj_out, sq, qf, o_q));
+    FM_CUDA(ctx, send(k, skv, kvf, o_k));
+    FM_CUDA(ctx, send(v, skv, kvf, o_v));
+    ctx->ptr_mode = FM_PTR_DEVICE;
+    const fm_status st = fm_attn_decode_layers(ctx, first_layer, n_layers, seq, pos, batch, reinterpret_cast<const float *>(ds + o_q), qf,
+                                               k ? reinterpret_cast<const float *>(ds + o_k) : nullptr,
+                                               v ? reinterpret_cast<const float *>(ds + o_v) : nullptr, kvf,
+                                               qnw ? reinterpret_cast<const uint16_t *>(ds + o_w) : nullptr,
+                                               knw ? reinterpret_cast<const uint16_t *>(ds + o_w + 512) : nullptr,
+                                               reinterpret_cast<float *>(ds + o_out), of, exchange);
+    ctx->ptr_mode = FM_PTR_HOST;
+    if (st) return st;
+    FM_CUDA(ctx, cudaMemcpyAsync(ctx->h_err, ctx->d_err, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+    const bool direct = is_pinned(out);
+    if (direct)
+        FM_CUDA(ctx, cudaMemcpy2DAsync(out, so * 4, ds + o_out, of * 4, of * 4, nl, cudaMemcpyDeviceToHost, ctx->stream));
+    else
+        FM_CUDA(ctx, cudaMemcpyAsync(hs + o_out, ds + o_out, nl * of * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    FM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (!direct)
+        for (size_t l = 0; l < nl; l++) memcpy(out + l * so, hs + o_out + l * of * 4, of * 4);
+    return check_device_error(ctx);
+}
+
 extern "C" fm_status fm_attn_decode_layers(FmCtx *ctx, int first_layer, int n_layers, const int *seq, const int *pos, int batch,
                                            const float *q_proj_out, size_t layer_stride_q, const float *k, const float *v,
                                            size_t layer_stride_kv, const uint16_t *q_norm_w, const uint16_t *k_norm_w, float *out,
                                            size_t layer_stride_out, int exchange) {
     if (!ctx) return FM_ERR_INVALID;
     if (!q_proj_out || !out || n_layers < 0) return fail(ctx, FM_ERR_INVALID, "fm_attn_decode_layers: bad argument");
+    if ((k == nullptr) != (v == nullptr)) return fail(ctx, FM_ERR_INVALID, "fm_attn_decode_layers: k and v go together");
+    if (ctx->ptr_mode == FM_PTR_HOST && n_layers > 0 && batch > 0)
+        return decode_layers_host(ctx, first_layer, n_layers, seq, pos, batch, q_proj_out, layer_stride_q, k, v, layer_stride_kv, q_norm_w,
+                                  k_norm_w, out, layer_stride_out, exchange);
+    // Between layers nothing is shared but the library's own scratch, which the kernels guard: a
+    // layer's launch may overlap the end of the previous one.  Not while launches are bracketed by
+    // timing events, and not in host-pointer mode (copies sit between the launches anyway).
+    struct Overlap {
+        FmCtx *c;
+        ~Overlap() { c->overlap_prev = c->overlap_merge = false; }
+    } guard{ctx};
     for (int l = 0; l < n_layers; l++) {
+        ctx->overlap_prev = l > 0 && !ctx->prof_on;
+        ctx->overlap_merge = !ctx->prof_on;
         const float *qp = q_proj_out + (size_t)l * layer_stride_q;
         const float *kk = k ? k + (size_t)l * layer_stride_kv : nullptr, *vv = v ? v + (size_t)l * layer_stride_kv : nullptr;
         float *oo = out + (size_t)l * layer_stride_out;

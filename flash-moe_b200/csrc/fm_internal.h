@@ -111,6 +111,9 @@ struct FmCtx {
 
     // optional event bracketing of the dominant kernels
     bool prof_on = false;
+    // set by fm_attn_decode_layers between layers: the next decode launch may start while the previous
+    // layer's kernel drains (different layers touch different pages, inputs and outputs)
+    bool overlap_prev = false, overlap_merge = false;
     std::vector<cudaEvent_t> prof_ev;  // pairs (start, stop)
     size_t prof_used = 0;
 
@@ -118,6 +121,9 @@ struct FmCtx {
     char *h_stage = nullptr;  // pinned
     char *d_stage = nullptr;
     size_t stage_bytes = 0;
+    // staging of all layers of one fm_attn_decode_layers call in host-pointer mode (grown on demand)
+    char *h_lstage = nullptr, *d_lstage = nullptr;
+    size_t lstage_bytes = 0;
 };
 
 namespace fm {
@@ -134,7 +140,8 @@ int launch_attn_decode_fused(const KvView &kv, const RopeParams &rope, const Tok
                              const float *q_proj_out, const float *q, const uint16_t *q_norm_w, float eps,
                              float *part_o, float *part_ml, int nsplits, const float *k_new, const float *v_new,
                              const uint16_t *k_norm_w, int tail, const float *gate, float *out, float *ml_out,
-                             const XchgView *x, uint32_t step, unsigned int *counters, cudaStream_t st);
+                             const XchgView *x, uint32_t step, unsigned int *counters, bool overlap_prev,
+                             cudaStream_t st);
 
 // merges [nparts] partials per (token, head) laid out with strides, applies the gate
 int launch_attn_merge(const float *part_o, const float *part_ml, int nparts, long long part_stride_o,
@@ -146,7 +153,7 @@ int launch_attn_merge(const float *part_o, const float *part_ml, int nparts, lon
 int launch_attn_merge_push(const float *part_o, const float *part_ml, int nsplits, int ntok, int H, const XchgView &x,
                            uint32_t step, unsigned int *done_counter, cudaStream_t st);
 int launch_attn_wait_merge(const XchgView &x, uint32_t step, int ntok, int H, const float *q_proj_out, const float *gate,
-                           float *out, int *err, cudaStream_t st);
+                           float *out, int *err, bool overlap_prev, cudaStream_t st);
 
 int launch_kv_export(const KvView &kv, int seq, int len, float *k, float *v, cudaStream_t st);
 int launch_kv_import(const KvView &kv, int seq, int len, const float *k, const float *v, cudaStream_t st);

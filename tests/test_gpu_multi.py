@@ -1,0 +1,36 @@
+"""Decode over several GPUs: sequence shards exchanging partial results over peer memory inside
+fm_attn_decode_layers (needs 2 or more B200s on one node; skipped otherwise)."""
+import json
+import os
+import socket
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parents[1]
+TOL = 2e-3
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_layers_call_with_peer_exchange_matches_checker(world):
+    import torch
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+                        "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
+                        str(ROOT / "tests" / "multi_gpu_worker.py")], capture_output=True, text=True, timeout=600, env=env)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    line = [l for l in r.stdout.splitlines() if l.startswith("{")][-1]
+    worst = json.loads(line)["worst_gated"]
+    print("peer exchange over", world, "GPUs: worst gated", worst)
+    assert worst <= TOL
