@@ -77,7 +77,10 @@ __device__ __forceinline__ void named_barrier(int id, int nthreads) {
 //     grid (launched cooperatively, at most one CTA per SM) meets at a grid barrier and the (token,
 //     head) rows are merged by all CTAs -- no separate merge launch.  tail = 1: normalise, gate,
 //     write the output; 2: un-normalised row and (max, sum) for the caller to exchange; 3: store the
-//     row into every peer's exchange buffer and publish the step.
+//     row into every peer's exchange buffer and publish the step; 4 (ordinary launch only): store the
+//     rows of this (token, KV head) into every peer's buffer, publish that unit, wait -- bounded --
+//     for every peer's rows of the same unit, merge them by log-sum-exp, gate, write the output: the
+//     whole sequence-sharded step in this one kernel.
 struct DecodeFused {
     const float *k_new, *v_new;  // [tokens][Hkv*D] or null
     const uint16_t *knw;
@@ -90,6 +93,7 @@ struct DecodeFused {
     unsigned int *counters;  // [tokens*Hkv] arrivals per (token, KV head) + [1] finished groups; self-resetting
     int coop;                // 1: cooperative launch, the splits are merged grid-wide after a grid barrier;
                              // 0: ordinary launch, the last CTA to arrive for a (token, KV head) merges its splits
+    int *err;                // tail 4: device error word (a peer never published)
     long long *trace;  // development builds only (-DFM_DEC_TRACE)
 };
 
@@ -550,6 +554,64 @@ attn_decode_kernel(KvView kv, RopeParams rope, TokSpec toks, int H, const float 
         }
     }
     DEC_TR(5);
+    if (f.tail == 4) {
+        // ---- this CTA has stored the unit's rows into every rank's buffer: publish, wait, merge ----
+        __shared__ int s_ok;
+        const int nr = f.x.nranks, par = f.step & 1;
+        const int nunits = f.x.cap * kv.Hkv, unit = tok * kv.Hkv + kvh;
+        if (tid == 0) s_ok = 1;
+        __threadfence_system();
+        __syncthreads();
+        if (tid < nr) {
+            uint32_t *theirs = reinterpret_cast<uint32_t *>(f.x.peer[tid] + f.x.unit_flag_offset_floats) + ((size_t)par * nr + f.x.me) * nunits + unit;
+            st_release_sys(theirs, f.step);
+            const uint32_t *mine_f = reinterpret_cast<const uint32_t *>(f.x.peer[f.x.me] + f.x.unit_flag_offset_floats) + ((size_t)par * nr + tid) * nunits + unit;
+            const long long t0 = clock64();
+            while ((int32_t)(ld_acquire_sys(mine_f) - f.step) < 0) {
+                if (clock64() - t0 > f.x.wait_limit_cycles) {  // rank `tid` never published this unit
+                    s_ok = 0;
+                    atomicCAS(f.err, 0, (2 << 16) | tid);
+                    break;
+                }
+            }
+        }
+        __syncthreads();
+        const float *mine = f.x.peer[f.x.me];
+        for (int r = warp; r < group; r += kDecWarps) {
+            const int head = kvh * group + r;
+            float *dst = f.out + ((size_t)tok * H + head) * kD + lane * 8;
+            if (!s_ok) {
+                *reinterpret_cast<float4 *>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
+                *reinterpret_cast<float4 *>(dst + 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+                continue;
+            }
+            const size_t row0 = (((size_t)par * nr * f.x.cap + tok) * H + head) * (kD + 2);  // rank 0's row
+            const size_t rstride = (size_t)f.x.cap * H * (kD + 2);
+            const float2 mlj = lane < nr ? __ldcg(reinterpret_cast<const float2 *>(mine + row0 + lane * rstride + kD)) : make_float2(kNegBig, 0.f);
+            const float M = warp_max(mlj.x);
+            const float wj = fast_exp2(mlj.x - M);
+            const float lt = warp_sum(wj * mlj.y);
+            float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (int j = 0; j < nr; j++) {
+                const float w = __shfl_sync(0xffffffffu, wj, j);
+                const float2 *src = reinterpret_cast<const float2 *>(mine + row0 + j * rstride + lane * 8);
+#pragma unroll
+                for (int q2 = 0; q2 < 4; q2++) {
+                    const float2 v = __ldcg(src + q2);
+                    a[2 * q2] += w * v.x;
+                    a[2 * q2 + 1] += w * v.y;
+                }
+            }
+            const float inv = lt > 0.f ? 1.0f / lt : 0.f;
+            const float *gsrc = q_proj_out ? q_proj_out + ((size_t)tok * H + head) * 2 * kD + kD + lane * 8 : f.gate + ((size_t)tok * H + head) * kD + lane * 8;
+            const float4 g0 = *reinterpret_cast<const float4 *>(gsrc), g1 = *reinterpret_cast<const float4 *>(gsrc + 4);
+            *reinterpret_cast<float4 *>(dst) = make_float4(a[0] * inv * fast_sigmoid(g0.x), a[1] * inv * fast_sigmoid(g0.y),
+                                                           a[2] * inv * fast_sigmoid(g0.z), a[3] * inv * fast_sigmoid(g0.w));
+            *reinterpret_cast<float4 *>(dst + 4) = make_float4(a[4] * inv * fast_sigmoid(g1.x), a[5] * inv * fast_sigmoid(g1.y),
+                                                               a[6] * inv * fast_sigmoid(g1.z), a[7] * inv * fast_sigmoid(g1.w));
+        }
+        return;
+    }
     if (f.tail == 3 && !f.coop) {
         // this (token, KV head) is in every peer's buffer; the last group to get here publishes the step
         __threadfence_system();
@@ -602,7 +664,7 @@ int launch_attn_decode_fused(const KvView &kv, const RopeParams &rope, const Tok
                              const float *q_proj_out, const float *q, const uint16_t *q_norm_w, float eps,
                              float *part_o, float *part_ml, int nsplits, const float *k_new, const float *v_new,
                              const uint16_t *k_norm_w, int tail, const float *gate, float *out, float *ml_out,
-                             const XchgView *x, uint32_t step, unsigned int *counters, bool overlap_prev,
+                             const XchgView *x, uint32_t step, unsigned int *counters, int *err, bool overlap_prev,
                              cudaStream_t st) {
     static bool configured = false;
     if (!configured) {
@@ -620,10 +682,12 @@ int launch_attn_decode_fused(const KvView &kv, const RopeParams &rope, const Tok
     f.trace = fm_dec_trace;
 #endif
     f.counters = counters;
+    f.err = err;
     // Few splits per (KV head, sequence): an ordinary launch, the last CTA of each group merges (a
     // cooperative launch costs ~10 us more to start).  Many splits (small batch): one CTA could not
     // merge them quickly, so the grid meets at a barrier and every warp takes a share.
-    f.coop = nsplits > 24;
+    f.coop = nsplits > kDecMaxLastCtaSplits;
+    if (tail == 4 && f.coop) return -1;  // the caller picks tail 3 + the separate merge for many splits
     KvView kv_ = kv; RopeParams rope_ = rope; TokSpec toks_ = toks;
     if (!f.coop) {
         // overlap_prev: the caller vouches that this launch reads nothing the previous kernel in the

@@ -535,7 +535,7 @@ static fm_status decode_core(FmCtx *ctx, int fa_idx, const int *seq, const int *
         ProfScope prof(ctx);
         fm_status st = launched(ctx, launch_attn_decode_fused(kv, ctx->rope, t, H, qp, qq, qnw, c.rms_norm_eps, ctx->d_part_o, ctx->d_part_ml, ns,
                                                               k ? k + i0 * kvd : nullptr, v ? v + i0 * kvd : nullptr, knw, out ? 1 : 2, gp, op, mlp,
-                                                              nullptr, 0, ctx->d_dec_counters, ctx->overlap_prev && i0 == 0 && !sg_host(ctx),
+                                                              nullptr, 0, ctx->d_dec_counters, ctx->d_err, ctx->overlap_prev && i0 == 0 && !sg_host(ctx),
                                                               ctx->stream), "attn_decode");
         if (st) return st;
     }
@@ -881,7 +881,9 @@ static size_t xchg_slot_floats(const FmCtx *ctx, int nranks) {
 extern "C" size_t fm_exchange_bytes(const FmCtx *ctx, int nranks) {
     if (!ctx || nranks < 1 || nranks > kMaxXchgRanks) return 0;
     const size_t slots = (xchg_slot_floats(ctx, nranks) * sizeof(float) + 255) & ~(size_t)255;
-    return slots + 256;  // flags [2][nranks] of 32 bits after the slots
+    // after the slots: step flags [2][nranks], then flags per (token, KV head) [2][nranks][cap * Hkv], 32 bits each
+    const size_t unit_flags = ((size_t)2 * nranks * xchg_cap(ctx) * ctx->cfg.num_kv_heads * 4 + 255) & ~(size_t)255;
+    return slots + 256 + unit_flags;
 }
 
 extern "C" fm_status fm_exchange_attach(FmCtx *ctx, int nranks, int my_index, void *const *peer_bufs) {
@@ -902,6 +904,7 @@ extern "C" fm_status fm_exchange_attach(FmCtx *ctx, int nranks, int my_index, vo
     x.me = my_index;
     x.cap = xchg_cap(ctx);
     x.flag_offset_floats = (long long)(((xchg_slot_floats(ctx, nranks) * sizeof(float) + 255) & ~(size_t)255) / sizeof(float));
+    x.unit_flag_offset_floats = x.flag_offset_floats + 64;
     int khz = 0;
     cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, ctx->cfg.device);
     x.wait_limit_cycles = (long long)(khz > 0 ? khz : 1900000) * 500;  // about half a second of SM clock
@@ -912,11 +915,14 @@ extern "C" fm_status fm_exchange_attach(FmCtx *ctx, int nranks, int my_index, vo
     return FM_OK;
 }
 
-extern "C" fm_status fm_attn_decode_exchange_push(FmCtx *ctx, int fa_idx, const int *seq, const int *pos, int batch,
-                                                  const float *q_proj_out, const float *q, const float *k, const float *v,
-                                                  const uint16_t *q_norm_w, const uint16_t *k_norm_w) {
+// Shared body of the exchange step.  out == nullptr: push only (the rows go to the peers, the step is
+// published; fm_attn_decode_exchange_merge finishes).  out != nullptr: the whole step in the decode
+// launch where the split count allows (*finished = true), else push only.
+static fm_status xchg_push(FmCtx *ctx, const char *fn, int fa_idx, const int *seq, const int *pos, int batch,
+                           const float *q_proj_out, const float *q, const float *k, const float *v,
+                           const uint16_t *q_norm_w, const uint16_t *k_norm_w, const float *gate, float *out, bool *finished) {
     if (!ctx) return FM_ERR_INVALID;
-    const char *fn = "fm_attn_decode_exchange_push";
+    *finished = false;
     if (ctx->xchg.nranks < 1) return fail(ctx, FM_ERR_INVALID, "%s: call fm_exchange_attach first", fn);
     if (!seq || !pos || (!q_proj_out && !q)) return fail(ctx, FM_ERR_INVALID, "%s: null argument", fn);
     if ((k == nullptr) != (v == nullptr)) return fail(ctx, FM_ERR_INVALID, "%s: k and v go together", fn);
@@ -936,8 +942,15 @@ extern "C" fm_status fm_attn_decode_exchange_push(FmCtx *ctx, int fa_idx, const 
     const float *d_q = sg.in(q_proj_out ? nullptr : q, batch * qd, &ok);
     const float *d_k = sg.in(k, batch * kvd, &ok), *d_v = sg.in(v, batch * kvd, &ok);
     const uint16_t *d_qn = sg.in(q_norm_w, (size_t)D, &ok), *d_kn = sg.in(k_norm_w, (size_t)D, &ok);
-    if (!ok) return fail(ctx, FM_ERR_INVALID, "%s: staging buffer too small", fn);
     std::vector<int> rows(batch);
+    int max_len = 1;
+    for (int i = 0; i < batch; i++) max_len = std::max(max_len, ctx->kv_len[lidx(ctx, fa_idx, seq[i])] + (k ? 1 : 0));
+    const int ns = pick_splits(ctx, batch, max_len);
+    const bool whole = out != nullptr && ns <= kDecMaxLastCtaSplits;
+    const float *d_g = whole ? sg.in(q_proj_out ? nullptr : gate, batch * qd, &ok) : nullptr;
+    size_t w_out = 0;
+    float *d_out = whole ? sg.out(out, batch * qd, &ok, &w_out) : nullptr;
+    if (!ok) return fail(ctx, FM_ERR_INVALID, "%s: staging buffer too small", fn);
     if (k != nullptr) {
         st = reserve_rows(ctx, fa_idx, seq, batch, rows);
         if (st) return st;
@@ -951,24 +964,36 @@ extern "C" fm_status fm_attn_decode_exchange_push(FmCtx *ctx, int fa_idx, const 
     TokSpec t;
     t.mode = 0;
     t.n = batch;
-    int max_len = 1;
-    for (int i = 0; i < batch; i++) {
-        t.seq[i] = seq[i]; t.pos[i] = pos[i]; t.row[i] = rows[i];
-        max_len = std::max(max_len, rows[i] + 1);
-    }
-    const int ns = pick_splits(ctx, batch, max_len);
+    for (int i = 0; i < batch; i++) { t.seq[i] = seq[i]; t.pos[i] = pos[i]; t.row[i] = rows[i]; }
     ctx->xchg_step++;
     {
-        // one launch: append, split-KV attention, merge of the splits, rows into every peer's buffer, step published
+        // one launch: append, split-KV attention, merge of the splits, rows into every peer's buffer; then either the
+        // step is published for the separate merge, or the peers' rows are awaited, merged and gated right there
         ProfScope prof(ctx);
         st = launched(ctx, launch_attn_decode_fused(kv_view(ctx, fa_idx), ctx->rope, t, H, d_qp, d_q, d_qn, c.rms_norm_eps, ctx->d_part_o,
-                                                    ctx->d_part_ml, ns, d_k, d_v, d_kn, 3, nullptr, nullptr, nullptr, &ctx->xchg,
-                                                    ctx->xchg_step, ctx->d_dec_counters, ctx->overlap_prev && !sg.host, ctx->stream),
+                                                    ctx->d_part_ml, ns, d_k, d_v, d_kn, whole ? 4 : 3, d_g, d_out, nullptr, &ctx->xchg,
+                                                    ctx->xchg_step, ctx->d_dec_counters, ctx->d_err, ctx->overlap_prev && !sg.host,
+                                                    ctx->stream),
                       "attn_decode");
     }
     if (st) return st;
+    *finished = whole;
+    if (whole) {
+        if (sg.host) FM_CUDA(ctx, cudaMemcpyAsync(ctx->h_err, ctx->d_err, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+        FM_CUDA(ctx, sg.pull(out, w_out, batch * qd));
+        if (sg.host) return check_device_error(ctx);
+        return FM_OK;
+    }
     if (sg.host) FM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));  // the staged inputs may be reused by the next call
     return FM_OK;
+}
+
+extern "C" fm_status fm_attn_decode_exchange_push(FmCtx *ctx, int fa_idx, const int *seq, const int *pos, int batch,
+                                                  const float *q_proj_out, const float *q, const float *k, const float *v,
+                                                  const uint16_t *q_norm_w, const uint16_t *k_norm_w) {
+    bool finished;
+    return xchg_push(ctx, "fm_attn_decode_exchange_push", fa_idx, seq, pos, batch, q_proj_out, q, k, v, q_norm_w, k_norm_w, nullptr, nullptr,
+                     &finished);
 }
 
 extern "C" fm_status fm_attn_decode_exchange_merge(FmCtx *ctx, int batch, const float *q_proj_out, const float *gate, float *out) {
@@ -1000,8 +1025,11 @@ extern "C" fm_status fm_attn_decode_exchange_merge(FmCtx *ctx, int batch, const 
 extern "C" fm_status fm_attn_decode_exchange(FmCtx *ctx, int fa_idx, const int *seq, const int *pos, int batch,
                                              const float *q_proj_out, const float *q, const float *gate, const float *k,
                                              const float *v, const uint16_t *q_norm_w, const uint16_t *k_norm_w, float *out) {
-    fm_status st = fm_attn_decode_exchange_push(ctx, fa_idx, seq, pos, batch, q_proj_out, q, k, v, q_norm_w, k_norm_w);
-    if (st) return st;
+    if (ctx && (!out || (!q_proj_out && !gate))) return fail(ctx, FM_ERR_INVALID, "fm_attn_decode_exchange: null argument");
+    bool finished = false;
+    fm_status st = xchg_push(ctx, "fm_attn_decode_exchange", fa_idx, seq, pos, batch, q_proj_out, q, k, v, q_norm_w, k_norm_w, gate, out,
+                             &finished);
+    if (st || finished) return st;
     return fm_attn_decode_exchange_merge(ctx, batch, q_proj_out, gate, out);
 }
 

@@ -50,7 +50,8 @@ struct XchgView {
     float *peer[kMaxXchgRanks];  // every rank's buffer, addressable from this GPU; peer[me] is the local one
     int nranks, me;
     int cap;                     // token capacity of a slot
-    long long flag_offset_floats;
+    long long flag_offset_floats;       // step flags [2][nranks]
+    long long unit_flag_offset_floats;  // flags per (token, KV head) [2][nranks][cap * Hkv]
     long long wait_limit_cycles;
 };
 
@@ -140,8 +141,9 @@ int launch_attn_decode_fused(const KvView &kv, const RopeParams &rope, const Tok
                              const float *q_proj_out, const float *q, const uint16_t *q_norm_w, float eps,
                              float *part_o, float *part_ml, int nsplits, const float *k_new, const float *v_new,
                              const uint16_t *k_norm_w, int tail, const float *gate, float *out, float *ml_out,
-                             const XchgView *x, uint32_t step, unsigned int *counters, bool overlap_prev,
+                             const XchgView *x, uint32_t step, unsigned int *counters, int *err, bool overlap_prev,
                              cudaStream_t st);
+constexpr int kDecMaxLastCtaSplits = 24;  // more splits per (KV head, sequence): cooperative launch, grid-wide merge
 
 // merges [nparts] partials per (token, head) laid out with strides, applies the gate
 int launch_attn_merge(const float *part_o, const float *part_ml, int nparts, long long part_stride_o,

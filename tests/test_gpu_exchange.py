@@ -90,3 +90,64 @@ def test_missing_peer_times_out_and_context_survives(pkg, synth):
     assert np.isfinite(oa.cpu().numpy()).all() and oa.abs().max().item() > 0
     for c in ctxs:
         c.close()
+
+
+@pytest.mark.parametrize("lens", [(1400, 900), (60, 40)])
+def test_whole_step_in_one_launch_single_rank_group(pkg, port, synth, lens):
+    """fm_attn_decode_exchange with a group of one rank: the decode launch pushes its rows to its own
+    buffer, sees its own unit flags and merges -- the one-launch path of the sharded step, which must
+    reproduce the plain step."""
+    import torch
+    dev = torch.device("cuda:0")
+    steps = 3
+    cfg = pkg.default_config(num_full_layers=1, num_linear_layers=0, max_seqs=2, max_seq_len=max(lens) + 64)
+    c = pkg.Context(cfg)
+    c.set_stream(torch.cuda.current_stream().cuda_stream)
+    buf = torch.empty(c.exchange_bytes(1) // 4, dtype=torch.float32, device=dev)
+    c.exchange_attach(0, [buf.data_ptr()])
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+    refs = []
+    for s in range(2):
+        k0, v0 = synth.attn_cache(63, lens[s], tag=f"s{s}")
+        q, g, k, v = synth.attn_step_inputs(63, steps, tag=f"s{s}")
+        k, v = synth.round_bf16(k), synth.round_bf16(v)
+        c.kv_import(0, s, t(k0), t(v0), lens[s])
+        refs.append((q, g, k, v, oracle_attn(port, 32, 2, k0, v0, q, g, k, v)[0]))
+    launches0 = c.launch_count()
+    for st in range(steps):
+        out = torch.empty((2, 8192), device=dev)
+        stack = lambda i: t(np.stack([refs[s][i][st] for s in range(2)]))
+        c.attn_decode_exchange(0, [0, 1], [lens[0] + st, lens[1] + st], out, q=stack(0), gate=stack(1), k=stack(2), v=stack(3))
+        c.synchronize()
+        for s in range(2):
+            gated, _, _ = rel_errors(out[s].cpu().numpy(), refs[s][4][st])
+            assert gated <= TOL, (st, s, gated)
+    assert c.launch_count() - launches0 == steps  # one launch per step
+    c.close()
+
+
+def test_whole_step_times_out_without_the_peer(pkg, synth):
+    """Group of two, the second rank never runs: the one-launch step waits about half a second for the
+    peer's unit flags, reports FM_ERR_TIMEOUT with zeros in the output, and the context stays usable."""
+    import torch
+    dev = torch.device("cuda:0")
+    L = 300
+    cfg = pkg.default_config(num_full_layers=1, num_linear_layers=0, max_seqs=1, max_seq_len=L + 64,
+                             seq_shard_rank=0, seq_shard_count=2)
+    c = pkg.Context(cfg)
+    c.set_stream(torch.cuda.current_stream().cuda_stream)
+    bufs = [torch.zeros(c.exchange_bytes(2) // 4, dtype=torch.float32, device=dev) for _ in range(2)]
+    c.exchange_attach(0, [b.data_ptr() for b in bufs])
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+    k0, v0 = synth.attn_cache(64, L)
+    q, g, k, v = synth.attn_step_inputs(64, 1)
+    c.kv_import(0, 0, t(k0), t(v0), L)
+    out = torch.full((1, 8192), 7.0, device=dev)
+    c.attn_decode_exchange(0, [0], [L], out, q=t(q), gate=t(g), k=t(k), v=t(v))
+    with pytest.raises(pkg.FmError) as e:
+        c.synchronize()
+    assert e.value.status == pkg.binding.FM_ERR_TIMEOUT
+    assert not out.cpu().numpy().any()
+    c.synchronize()  # the error is reported once; the context answers again
+    assert c.kv_len(0, 0) == L + 1
+    c.close()
