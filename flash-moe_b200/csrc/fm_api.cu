@@ -753,7 +753,7 @@ extern "C" fm_status fm_gdn_prefill(FmCtx *ctx, int li, int seq, int n, int chun
     {
         ProfScope prof(ctx);
         st = launched(ctx, launch_gdn_prefill(g, n, chunk, step0, ctx->d_conv_state + lidx(ctx, li, seq) * cn, ctx->d_ssm_state + lidx(ctx, li, seq) * sn,
-                                                    d_qkv, d_z, d_b, d_a, d_cw, d_al, d_db, d_nw, d_out, ctx->d_work, ctx->work_bytes, ctx->stream), "gdn_prefill");
+                                                    d_qkv, d_z, d_b, d_a, d_cw, d_al, d_db, d_nw, d_out, ctx->d_work, ctx->work_bytes, ctx->d_err, ctx->stream), "gdn_prefill");
     }
     if (st) return st;
     ctx->gdn_steps[lidx(ctx, li, seq)] = step0 + n;

@@ -181,7 +181,7 @@ int launch_gdn_decode(const GdnDims &g, const TokSpec &toks, float *conv_state, 
 int launch_gdn_prefill(const GdnDims &g, int n, int chunk, int step0, float *conv_state, float *ssm_state,
                        const float *qkv, const float *z, const float *beta, const float *alpha,
                        const uint16_t *conv_w, const float *A_log, const uint16_t *dt_bias,
-                       const uint16_t *norm_w, float *out, void *work, size_t work_bytes,
+                       const uint16_t *norm_w, float *out, void *work, size_t work_bytes, int *err,
                        cudaStream_t st);
 size_t gdn_prefill_work_bytes(const GdnDims &g, int max_tokens, int chunk);
 

@@ -21,6 +21,8 @@
 // the triangular solve, the decay exponentials and the state stay fp32.
 #include "fm_device.cuh"
 #include "fm_internal.h"
+#include "fm_tc.cuh"
+#include <cstdlib>
 
 namespace fm {
 
@@ -75,6 +77,7 @@ struct GdnWork {  // workspace carved by the host
     float *U, *W;         // [Hv][nchunks][64][128]
     float *QK;            // [Hv][nchunks][64][64]
     float *cv;            // [Hv][nchunks][64]  inclusive running sum of ln(decay)
+    float *KT;            // [Hk][nchunks][128][64]  normalised k of each chunk, transposed (key dim major)
 };
 
 // ---- per token: conv + SiLU, q/k normalisation, decay, beta ------------------------------------
@@ -187,6 +190,10 @@ gdn_chunk_kernel(GdnDims g, int n, GdnWork w, int nchunks) {
         cv[lane] = a; cv[32 + lane] = b;
     }
     __syncthreads();
+    if (vh % (g.Hv / g.Hk) == 0) {  // one CTA per key head leaves the chunk's k transposed for the scan
+        float *kt = w.KT + ((size_t)kh * nchunks + chunk) * kDH * kC;
+        for (int i = tid; i < kDH * kC; i += 256) kt[i] = sK[(i & (kC - 1)) * kLdK + (i >> 6)];
+    }
 
     // K K^T and Q K^T (64 x 64 x 128): warp = (16-row tile, 32-column half)
     {
@@ -365,6 +372,345 @@ gdn_scan_kernel(GdnDims g, int n, GdnWork w, int nchunks, float *__restrict__ ss
     }
 }
 
+// ---- the scan on the 5th-generation tensor cores ------------------------------------------------
+// One CTA per value head walks the chunks with the state in tensor memory, transposed so that the
+// state row (value dim v) is the TMEM lane and every product has its A operand in TMEM and a K-major
+// B tile brought by TMA:
+//     Dt[v][t]  = U[t][v] - sum_k S[v][k] W[t][k]                     (M128 N64  K128)
+//     O1[v][t]  = sum_k S[v][k] Q[t][k]                                (M128 N64  K128)
+//     O2[v][t]  = sum_i Dt[v][i] QKm[t][i]                             (M128 N64  K64)
+//     S[v][k]   = e^{cC} S[v][k] + sum_i Dt[v][i] e^{cC-c_i} K[i][k]   (M128 N128 K64, B = scaled K^T)
+//     out[t][v] = e^{c_t} O1[v][t] + O2[v][t]
+// kind::tf32 reads 19 bits of each operand, so the recurrent operands enter as two terms: the TMEM
+// operands S and Dt keep a second copy of their truncated remainder (x - tf32(x)), and W and the
+// B tiles (W, Q, QKm, scaled K) get a remainder tile in shared memory; the cross terms hi*lo and lo*hi
+// are extra MMAs into the same accumulator ("3xTF32").
+//   warps 0-3   one state row per thread: initial S -> TMEM, per chunk U - acc -> Dt (+ remainder),
+//               S *= e^{cC}, remainder of the new S, output rows
+//   warp 4      TMA producer (single-buffered tiles: W, Q are free again after the first product
+//               group, QKm, K^T after the second)
+//   warp 5      MMA issuer
+//   warps 6-9   operand preparation in shared memory: decay tables, remainder tiles, scaled K^T
+// TMEM: S 128 + S remainder 128 + Dt 64 + Dt remainder 64 + O1 64 + O2 64 = 512 columns.
+// Every mbarrier wait is bounded; on expiry the CTA records an error code and winds down.
+constexpr int kScThreads = 320;
+constexpr uint32_t kTcS = 0, kTcSl = 128, kTcD = 256, kTcDl = 320, kTcO1 = 384, kTcO2 = 448;
+constexpr int kSlab64 = 64 * 128;    // bytes of one 32-float-wide slab of a 64-row tile
+constexpr int kSlab128 = 128 * 128;  // ... of a 128-row tile
+constexpr int kOffW = 0, kOffWl = 32768, kOffQ = 65536, kOffQl = 98304, kOffQK = 131072, kOffQKl = 147456, kOffKT = 163840,
+              kOffKTl = 196608;
+constexpr int kOffTab = 229376;      // 2 x [64 K-row scales | 64 output scales | e^{cC} ...] floats
+constexpr int kTabFloats = 144;
+constexpr int kOffBar = kOffTab + 2 * kTabFloats * 4;
+enum ScBar { SB_SREADY = 0, SB_WQFULL, SB_WLFULL, SB_KQKFULL, SB_KSFULL, SB_CVFULL, SB_DACC, SB_QDONE, SB_WEMPTY, SB_DFULL,
+             SB_SSCALED, SB_CDONE, SB_KEMPTY, SB_OFREE, SB_COUNT };
+constexpr int kScSmem = kOffBar + SB_COUNT * 8 + 1024 /*alignment slack*/;
+
+__device__ __forceinline__ float tf32_rest(float x) { return x - __uint_as_float(__float_as_uint(x) & 0xFFFFE000u); }
+
+struct ScanParams {
+    int n, nchunks, Hv, Hk;
+    const float *U, *cv;
+    float *ssm, *out;
+    int *err;
+};
+
+__global__ void __launch_bounds__(kScThreads, 1)
+gdn_scan_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_q,
+                   const __grid_constant__ CUtensorMap map_qk, const __grid_constant__ CUtensorMap map_kt, ScanParams p) {
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ uint32_t s_tmem_base;
+    __shared__ int s_abort;
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    unsigned char *gbase = smem_raw + (base - smem_u32(smem_raw));
+    auto bar = [&](int i) { return base + kOffBar + 8u * (uint32_t)i; };
+    float *tabs = reinterpret_cast<float *>(gbase + kOffTab);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int vh = blockIdx.x, kh = vh / (p.Hv / p.Hk);
+    const int nchunks = p.nchunks;
+
+    if (tid == 0) {
+        s_abort = 0;
+        mbar_init(bar(SB_SREADY), 128);
+        mbar_init(bar(SB_WQFULL), 1);
+        mbar_init(bar(SB_WLFULL), 128);
+        mbar_init(bar(SB_KQKFULL), 1);
+        mbar_init(bar(SB_KSFULL), 128);
+        mbar_init(bar(SB_CVFULL), 128);
+        mbar_init(bar(SB_DACC), 1);
+        mbar_init(bar(SB_QDONE), 1);
+        mbar_init(bar(SB_WEMPTY), 1);
+        mbar_init(bar(SB_DFULL), 128);
+        mbar_init(bar(SB_SSCALED), 128);
+        mbar_init(bar(SB_CDONE), 1);
+        mbar_init(bar(SB_KEMPTY), 1);
+        mbar_init(bar(SB_OFREE), 128);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 5) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&s_tmem_base)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = s_tmem_base;
+    volatile int *abortp = &s_abort;
+
+    if (warp == 4) {
+        // ================= TMA producer =================
+        if (lane == 0) {
+            for (int j = 0; j < nchunks; j++) {
+                const int hc = vh * nchunks + j;
+                if (j > 0 && !mbar_wait(bar(SB_WEMPTY), (j - 1) & 1, abortp)) break;
+                mbar_expect_tx(bar(SB_WQFULL), 65536);
+                for (int s = 0; s < 4; s++) tma_load_2d(base + kOffW + s * kSlab64, &map_w, s * 32, hc * kC, bar(SB_WQFULL));
+                for (int s = 0; s < 4; s++) tma_load_2d(base + kOffQ + s * kSlab64, &map_q, kh * kDH + s * 32, j * kC, bar(SB_WQFULL));
+                if (j > 0 && !mbar_wait(bar(SB_KEMPTY), (j - 1) & 1, abortp)) break;
+                mbar_expect_tx(bar(SB_KQKFULL), 16384 + 32768);
+                for (int s = 0; s < 2; s++) tma_load_2d(base + kOffQK + s * kSlab64, &map_qk, s * 32, hc * kC, bar(SB_KQKFULL));
+                for (int s = 0; s < 2; s++)
+                    tma_load_2d(base + kOffKT + s * kSlab128, &map_kt, s * 32, (kh * nchunks + j) * kDH, bar(SB_KQKFULL));
+            }
+        }
+    } else if (warp == 5) {
+        // ================= MMA issuer =================
+        if (lane == 0) {
+            constexpr uint32_t id64 = idesc_dense(128, 64, false, 2), id128 = idesc_dense(128, 128, false, 2);
+            const uint64_t dW = smem_desc(base + kOffW, 16, 1024), dWl = smem_desc(base + kOffWl, 16, 1024);
+            const uint64_t dQ = smem_desc(base + kOffQ, 16, 1024), dQK = smem_desc(base + kOffQK, 16, 1024);
+            const uint64_t dQl = smem_desc(base + kOffQl, 16, 1024), dQKl = smem_desc(base + kOffQKl, 16, 1024);
+            const uint64_t dKT = smem_desc(base + kOffKT, 16, 1024), dKTl = smem_desc(base + kOffKTl, 16, 1024);
+            auto k64 = [](int ks) { return (uint64_t)((((ks >> 2) * kSlab64) + (ks & 3) * 32) >> 4); };
+            auto k128 = [](int ks) { return (uint64_t)((((ks >> 2) * kSlab128) + (ks & 3) * 32) >> 4); };
+            for (int j = 0; j < nchunks; j++) {
+                const uint32_t ph = j & 1;
+                bool ok = mbar_wait(bar(SB_SREADY), ph, abortp) && mbar_wait(bar(SB_WQFULL), ph, abortp) && mbar_wait(bar(SB_WLFULL), ph, abortp);
+                if (!ok) break;
+                tc_fence_after();
+                // Dt = S W^T, three terms
+#pragma unroll
+                for (int ks = 0; ks < 16; ks++) tc_mma_tf32_ta(tmem + kTcD, tmem + kTcS + ks * 8, dW + k64(ks), id64, ks > 0);
+#pragma unroll
+                for (int ks = 0; ks < 16; ks++) tc_mma_tf32_ta(tmem + kTcD, tmem + kTcSl + ks * 8, dW + k64(ks), id64, 1);
+#pragma unroll
+                for (int ks = 0; ks < 16; ks++) tc_mma_tf32_ta(tmem + kTcD, tmem + kTcS + ks * 8, dWl + k64(ks), id64, 1);
+                tc_commit(bar(SB_DACC));
+                // O1 = S Q^T: the output accumulators of the previous chunk must have been read out
+                if (j > 0 && !mbar_wait(bar(SB_OFREE), (j - 1) & 1, abortp)) break;
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < 16; ks++) tc_mma_tf32_ta(tmem + kTcO1, tmem + kTcS + ks * 8, dQ + k64(ks), id64, ks > 0);
+#pragma unroll
+                for (int ks = 0; ks < 16; ks++) tc_mma_tf32_ta(tmem + kTcO1, tmem + kTcSl + ks * 8, dQ + k64(ks), id64, 1);
+#pragma unroll
+                for (int ks = 0; ks < 16; ks++) tc_mma_tf32_ta(tmem + kTcO1, tmem + kTcS + ks * 8, dQl + k64(ks), id64, 1);
+                tc_commit(bar(SB_QDONE));
+                tc_commit(bar(SB_WEMPTY));
+                // O2 = Dt QKm^T
+                ok = mbar_wait(bar(SB_DFULL), ph, abortp) && mbar_wait(bar(SB_KQKFULL), ph, abortp) && mbar_wait(bar(SB_KSFULL), ph, abortp);
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < 8; ks++) tc_mma_tf32_ta(tmem + kTcO2, tmem + kTcD + ks * 8, dQK + k64(ks), id64, ks > 0);
+#pragma unroll
+                for (int ks = 0; ks < 8; ks++) tc_mma_tf32_ta(tmem + kTcO2, tmem + kTcDl + ks * 8, dQK + k64(ks), id64, 1);
+#pragma unroll
+                for (int ks = 0; ks < 8; ks++) tc_mma_tf32_ta(tmem + kTcO2, tmem + kTcD + ks * 8, dQKl + k64(ks), id64, 1);
+                // S = e^{cC} S + Dt (scaled K^T)^T, three terms
+                ok = mbar_wait(bar(SB_SSCALED), ph, abortp);
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < 8; ks++) tc_mma_tf32_ta(tmem + kTcS, tmem + kTcD + ks * 8, dKT + k128(ks), id128, 1);
+#pragma unroll
+                for (int ks = 0; ks < 8; ks++) tc_mma_tf32_ta(tmem + kTcS, tmem + kTcDl + ks * 8, dKT + k128(ks), id128, 1);
+#pragma unroll
+                for (int ks = 0; ks < 8; ks++) tc_mma_tf32_ta(tmem + kTcS, tmem + kTcD + ks * 8, dKTl + k128(ks), id128, 1);
+                tc_commit(bar(SB_CDONE));
+                tc_commit(bar(SB_KEMPTY));
+            }
+        }
+    } else if (warp >= 6) {
+        // ================= operand preparation in shared memory =================
+        const int q = tid - 192;  // 0..127
+        for (int j = 0; j < nchunks; j++) {
+            const uint32_t ph = j & 1;
+            const float *cvp = p.cv + ((size_t)vh * nchunks + j) * kC;
+            float *tab = tabs + (j & 1) * kTabFloats;
+            const float cC = __ldg(cvp + kC - 1);
+            if (q < kC) {
+                const float c = __ldg(cvp + q);
+                tab[q] = expf(cC - c);   // scale of K row q in the state update
+                tab[kC + q] = expf(c);   // scale of the S q term of output row q
+            }
+            if (q == 0) tab[2 * kC] = expf(cC);
+            // the table is complete for the preparation threads once all of them have arrived; the state
+            // threads read it only after the chunk's first products (which wait for SB_WLFULL below) are done
+            mbar_arrive(bar(SB_CVFULL));
+            if (!mbar_wait(bar(SB_CVFULL), ph, abortp)) break;
+            // remainder tile of W
+            if (!mbar_wait(bar(SB_WQFULL), ph, abortp)) break;
+            for (int i = q; i < 4096; i += 128) {  // W | Wl | Q | Ql are consecutive 32 KB tiles
+                const int o = (i & 2047) * 16 + (i >> 11) * 65536;
+                const float4 v = *reinterpret_cast<const float4 *>(gbase + kOffW + o);
+                *reinterpret_cast<float4 *>(gbase + kOffWl + o) = make_float4(tf32_rest(v.x), tf32_rest(v.y), tf32_rest(v.z), tf32_rest(v.w));
+            }
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            mbar_arrive(bar(SB_WLFULL));
+            // K^T tile: column i scaled by e^{cC - c_i}, and its remainder tile
+            if (!mbar_wait(bar(SB_KQKFULL), ph, abortp)) break;
+            for (int i = q; i < 2048; i += 128) {
+                const int o = i * 16, slab = o >> 14, row = (o & 16383) >> 7, lc = ((o >> 4) & 7) ^ (row & 7);
+                const float *sc4 = tab + slab * 32 + lc * 4;
+                float4 v = *reinterpret_cast<const float4 *>(gbase + kOffKT + o);
+                v.x *= sc4[0]; v.y *= sc4[1]; v.z *= sc4[2]; v.w *= sc4[3];
+                *reinterpret_cast<float4 *>(gbase + kOffKT + o) = v;
+                *reinterpret_cast<float4 *>(gbase + kOffKTl + o) = make_float4(tf32_rest(v.x), tf32_rest(v.y), tf32_rest(v.z), tf32_rest(v.w));
+            }
+            for (int i = q; i < 1024; i += 128) {  // remainder tile of QKm
+                const float4 v = *reinterpret_cast<const float4 *>(gbase + kOffQK + i * 16);
+                *reinterpret_cast<float4 *>(gbase + kOffQKl + i * 16) = make_float4(tf32_rest(v.x), tf32_rest(v.y), tf32_rest(v.z), tf32_rest(v.w));
+            }
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            // the table of chunk j - 1 is rewritten at the top of chunk j + 1: its last readers (the output
+            // rows of chunk j - 1) must be done before this chunk can complete
+            if (j > 0 && !mbar_wait(bar(SB_OFREE), (j - 1) & 1, abortp)) break;
+            mbar_arrive(bar(SB_KSFULL));
+        }
+    } else {
+        // ================= state rows: one value dim per thread =================
+        const int r = tid;  // state row = TMEM lane
+        const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+        float *Srow = p.ssm + ((size_t)vh * kDH + r) * kDH;
+        const int total_v = p.Hv * kDH;
+#pragma unroll 1
+        for (int c = 0; c < kDH; c += 32) {
+            uint32_t hi[32], lo[32];
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const float4 v = *reinterpret_cast<const float4 *>(Srow + c + 4 * i);
+                hi[4 * i] = __float_as_uint(v.x); hi[4 * i + 1] = __float_as_uint(v.y);
+                hi[4 * i + 2] = __float_as_uint(v.z); hi[4 * i + 3] = __float_as_uint(v.w);
+            }
+#pragma unroll
+            for (int i = 0; i < 32; i++) lo[i] = __float_as_uint(tf32_rest(__uint_as_float(hi[i])));
+            tc_st32(tmem + lane_base + kTcS + c, hi);
+            tc_st32(tmem + lane_base + kTcSl + c, lo);
+        }
+        tc_wait_st();
+        tc_fence_before();
+        mbar_arrive(bar(SB_SREADY));
+        bool ok = true;
+        for (int j = 0; j < nchunks; j++) {
+            const uint32_t ph = j & 1;
+            const int t0 = j * kC;
+            const float *Ug = p.U + ((size_t)vh * nchunks + j) * kC * kDH + r;
+            const float *tab = tabs + (j & 1) * kTabFloats;
+            // Dt = U - acc, and its remainder
+            {
+                uint32_t a0[32], a1[32];
+                float u[kC];
+#pragma unroll
+                for (int t = 0; t < kC; t++) u[t] = __ldg(Ug + (size_t)t * kDH);
+                ok = __all_sync(0xffffffffu, mbar_wait(bar(SB_DACC), ph, abortp));
+                if (!ok) break;
+                tc_fence_after();
+                tc_ld32(tmem + lane_base + kTcD, a0);
+                tc_ld32(tmem + lane_base + kTcD + 32, a1);
+                tc_wait_ld();
+                uint32_t l0[32], l1[32];
+#pragma unroll
+                for (int i = 0; i < 32; i++) {
+                    const float d0 = u[i] - __uint_as_float(a0[i]), d1 = u[32 + i] - __uint_as_float(a1[i]);
+                    a0[i] = __float_as_uint(d0); a1[i] = __float_as_uint(d1);
+                    l0[i] = __float_as_uint(tf32_rest(d0)); l1[i] = __float_as_uint(tf32_rest(d1));
+                }
+                tc_st32(tmem + lane_base + kTcD, a0);
+                tc_st32(tmem + lane_base + kTcD + 32, a1);
+                tc_st32(tmem + lane_base + kTcDl, l0);
+                tc_st32(tmem + lane_base + kTcDl + 32, l1);
+                tc_wait_st();
+                tc_fence_before();
+                mbar_arrive(bar(SB_DFULL));
+            }
+            // S *= e^{cC}, once every product that reads the old S has completed
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(SB_QDONE), ph, abortp));
+            if (!ok) break;
+            tc_fence_after();
+            {
+                const float eC = tab[2 * kC];
+#pragma unroll 1
+                for (int c = 0; c < kDH; c += 32) {
+                    uint32_t x[32];
+                    tc_ld32(tmem + lane_base + kTcS + c, x);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; i++) x[i] = __float_as_uint(__uint_as_float(x[i]) * eC);
+                    tc_st32(tmem + lane_base + kTcS + c, x);
+                }
+                tc_wait_st();
+                tc_fence_before();
+                mbar_arrive(bar(SB_SSCALED));
+            }
+            // the new state: remainder copy for the next chunk's products
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(SB_CDONE), ph, abortp));
+            if (!ok) break;
+            tc_fence_after();
+#pragma unroll 1
+            for (int c = 0; c < kDH; c += 32) {
+                uint32_t x[32];
+                tc_ld32(tmem + lane_base + kTcS + c, x);
+                tc_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 32; i++) x[i] = __float_as_uint(tf32_rest(__uint_as_float(x[i])));
+                tc_st32(tmem + lane_base + kTcSl + c, x);
+            }
+            tc_wait_st();
+            tc_fence_before();
+            mbar_arrive(bar(SB_SREADY));
+            // output rows of this chunk (off the critical path: the next chunk's first products run meanwhile)
+            {
+                uint32_t o1[32], o2[32];
+#pragma unroll 1
+                for (int c = 0; c < kC; c += 32) {
+                    tc_ld32(tmem + lane_base + kTcO1 + c, o1);
+                    tc_ld32(tmem + lane_base + kTcO2 + c, o2);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; i++) {
+                        const int t = t0 + c + i;
+                        if (t < p.n) p.out[(size_t)t * total_v + (size_t)vh * kDH + r] = tab[kC + c + i] * __uint_as_float(o1[i]) + __uint_as_float(o2[i]);
+                    }
+                }
+                tc_fence_before();
+                mbar_arrive(bar(SB_OFREE));
+            }
+        }
+        if (ok) {  // final state back to memory
+#pragma unroll 1
+            for (int c = 0; c < kDH; c += 32) {
+                uint32_t x[32];
+                tc_ld32(tmem + lane_base + kTcS + c, x);
+                tc_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 8; i++)
+                    *reinterpret_cast<float4 *>(Srow + c + 4 * i) = make_float4(__uint_as_float(x[4 * i]), __uint_as_float(x[4 * i + 1]),
+                                                                                __uint_as_float(x[4 * i + 2]), __uint_as_float(x[4 * i + 3]));
+            }
+        }
+    }
+    // ---- wind down: everyone meets, TMEM goes back ----
+    tc_fence_before();
+    __syncthreads();
+    if (s_abort && tid == 0) atomicCAS(p.err, 0, (3 << 16) | (blockIdx.x & 0xffff));
+    if (warp == 5) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(512u) : "memory");
+    }
+}
+
 // ---- gated RMS-norm in place: o * rsqrt(mean o^2 + eps) * w * silu(z) --------------------------
 // grid (Hv, n), 32 threads (4 dims per lane)
 __global__ void gdn_norm_kernel(GdnDims g, const float *__restrict__ z, const uint16_t *__restrict__ norm_w,
@@ -404,6 +750,7 @@ static size_t carve(const GdnDims &g, int n, void *base, GdnWork *w) {
     t.W = take((size_t)g.Hv * nchunks * kC * kDH);
     t.QK = take((size_t)g.Hv * nchunks * kC * kC);
     t.cv = take((size_t)g.Hv * nchunks * kC);
+    t.KT = take((size_t)g.Hk * nchunks * kDH * kC);
     if (w) *w = t;
     return off;
 }
@@ -416,7 +763,7 @@ size_t gdn_prefill_work_bytes(const GdnDims &g, int max_tokens, int chunk) {
 int launch_gdn_prefill(const GdnDims &g, int n, int chunk, int step0, float *conv_state, float *ssm_state,
                        const float *qkv, const float *z, const float *beta, const float *alpha,
                        const uint16_t *conv_w, const float *A_log, const uint16_t *dt_bias,
-                       const uint16_t *norm_w, float *out, void *work, size_t work_bytes, cudaStream_t st) {
+                       const uint16_t *norm_w, float *out, void *work, size_t work_bytes, int *err, cudaStream_t st) {
     (void)chunk;
     GdnWork w;
     if (carve(g, n, work, &w) > work_bytes) return -1;
@@ -424,7 +771,8 @@ int launch_gdn_prefill(const GdnDims &g, int n, int chunk, int step0, float *con
     if (!configured) {
         if (cudaFuncSetAttribute(gdn_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, g.conv_dim * 4) != cudaSuccess ||
             cudaFuncSetAttribute(gdn_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kChunkSmem) != cudaSuccess ||
-            cudaFuncSetAttribute(gdn_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kScanSmem) != cudaSuccess)
+            cudaFuncSetAttribute(gdn_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kScanSmem) != cudaSuccess ||
+            cudaFuncSetAttribute(gdn_scan_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kScSmem) != cudaSuccess)
             return -1;
         configured = true;
     }
@@ -432,7 +780,21 @@ int launch_gdn_prefill(const GdnDims &g, int n, int chunk, int step0, float *con
     gdn_prep_kernel<<<n, 512, g.conv_dim * 4, st>>>(g, n, step0, conv_state, qkv, beta, alpha, conv_w, A_log, dt_bias, w);
     gdn_ring_kernel<<<dim3(12, 3), 256, 0, st>>>(g.conv_dim, n, step0, conv_state, qkv);
     gdn_chunk_kernel<<<dim3(nchunks, g.Hv), 256, kChunkSmem, st>>>(g, n, w, nchunks);
-    gdn_scan_kernel<<<dim3(kDH / kSl, g.Hv), 256, kScanSmem, st>>>(g, n, w, nchunks, ssm_state, out);
+    static const bool legacy_scan = getenv("FM_GDN_SCAN_MMA_SYNC") != nullptr;  // development switch
+    if (legacy_scan) {
+        gdn_scan_kernel<<<dim3(kDH / kSl, g.Hv), 256, kScanSmem, st>>>(g, n, w, nchunks, ssm_state, out);
+    } else {
+        CUtensorMap mw, mq, mqk, mkt;
+        if (!make_map_2d(&mw, w.W, (uint64_t)g.Hv * nchunks * kC, kDH, kC, true) ||
+            !make_map_2d(&mq, w.qn, (uint64_t)n, (uint64_t)g.Hk * kDH, kC, true) ||
+            !make_map_2d(&mqk, w.QK, (uint64_t)g.Hv * nchunks * kC, kC, kC, true) ||
+            !make_map_2d(&mkt, w.KT, (uint64_t)g.Hk * nchunks * kDH, kC, kDH, true))
+            return -1;
+        ScanParams sp;
+        sp.n = n; sp.nchunks = nchunks; sp.Hv = g.Hv; sp.Hk = g.Hk;
+        sp.U = w.U; sp.cv = w.cv; sp.ssm = ssm_state; sp.out = out; sp.err = err;
+        gdn_scan_tc_kernel<<<g.Hv, kScThreads, kScSmem, st>>>(mw, mq, mqk, mkt, sp);
+    }
     int launches = 4;
     if (norm_w != nullptr) {
         gdn_norm_kernel<<<dim3(g.Hv, n), 32, 0, st>>>(g, z, norm_w, out);
