@@ -64,14 +64,6 @@ __device__ __forceinline__ void tc_mma_f16_ta(uint32_t d_tmem, uint32_t a_tmem, 
         "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
-// kind::tf32 with A in tensor memory: row m of A is TMEM lane m, one 32-bit element per column (the low
-// 13 mantissa bits are ignored), K = 8 per instruction = 8 columns; B is a K-major shared-memory tile.
-__device__ __forceinline__ void tc_mma_tf32_ta(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}\n" ::"r"(d_tmem),
-        "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
 // 32 lanes x 32 consecutive 32-bit columns: thread i of the warp gets its lane's 32 columns
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile(
@@ -94,6 +86,14 @@ __device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32])
         "r"(r[31])
         : "memory");
 }
+// 32 lanes x 16 consecutive 32-bit columns
+__device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};\n" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
+        "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
 
@@ -111,7 +111,7 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes,
     return d;
 }
 // Instruction descriptor fields common to the dense kinds: fp32 accumulate, K-major A, M, N, B major.
-// `fmt` is the A and B element format: 0 fp16, 1 bf16 (kind::f16); 2 tf32 (kind::tf32).
+// `fmt` is the A and B element format of kind::f16: 0 fp16, 1 bf16.
 __host__ __device__ constexpr uint32_t idesc_dense(int M, int N, bool b_mn_major, uint32_t fmt) {
     return (1u << 4)                            // D format fp32
            | (fmt << 7) | (fmt << 10)           // A, B format
