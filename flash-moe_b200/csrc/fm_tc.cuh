@@ -136,8 +136,9 @@ static inline EncodeTiledFn get_encode() {
     return fn;
 }
 
-// 2-D tensor [rows][cols] of 2- or 4-byte elements, box [box_rows][128 bytes], 128-byte swizzle, zero fill outside
-static inline bool make_map_2d(CUtensorMap *m, const void *base, uint64_t rows, uint64_t cols, uint32_t box_rows, bool fp32) {
+// 2-D tensor [rows][cols] of 2- or 4-byte elements, box [box_rows][128 bytes], 128-byte swizzle (or none), zero fill outside
+static inline bool make_map_2d(CUtensorMap *m, const void *base, uint64_t rows, uint64_t cols, uint32_t box_rows, bool fp32,
+                               bool swizzle = true) {
     EncodeTiledFn enc = get_encode();
     if (!enc) return false;
     const uint32_t esz = fp32 ? 4 : 2;
@@ -146,7 +147,7 @@ static inline bool make_map_2d(CUtensorMap *m, const void *base, uint64_t rows, 
     const cuuint32_t box[2] = {128 / esz, box_rows};
     const cuuint32_t estr[2] = {1, 1};
     return enc(m, fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(base), dims, strides, box,
-               estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 

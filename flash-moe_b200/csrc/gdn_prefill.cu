@@ -314,20 +314,21 @@ gdn_chunk_kernel(GdnDims g, int n, GdnWork w, int nchunks) {
 // and Dt are split by the state threads.  The fp32 state itself only ever lives in its accumulator
 // columns; after each update one pass writes its two-term copy for the next chunk's products and
 // scales the accumulator by the next chunk's total decay, so the next update accumulates on top.
-//   warps 0-3   one state row per thread: S -> TMEM, per chunk Dt = U - acc (split), the pass over
-//               the new S, the output rows
-//   warp 4      TMA producer (single-buffered tiles: W | Q are free again after the first two product
-//               groups, QKm | Ks after the last two)
-//   warp 5      MMA issuer
+//   warps 0-7   state threads, two per state row (each takes half of the columns of every pass):
+//               S -> TMEM, per chunk Dt = U - acc (split), the pass over the new S, the output rows
+//   warp 8      TMA producer (single-buffered tiles: W | Q are free again after the first two product
+//               groups, U after Dt is formed, QKm | Ks after the last two)
+//   warp 9      MMA issuer
 // TMEM: S 128 + S hi 64 + S lo 64 + acc 64 + Dt hi 32 + Dt lo 32 + O1 64 + O2 64 = 512 columns.
 // Every mbarrier wait is bounded; on expiry the CTA records an error code and winds down.
-constexpr int kScThreads = 192;
+constexpr int kScThreads = 320;
 constexpr uint32_t kTcS = 0, kTcSh = 128, kTcSl = 192, kTcAcc = 256, kTcDh = 320, kTcDl = 352, kTcO1 = 384, kTcO2 = 448;
 constexpr int kSlab64 = 64 * 128;    // bytes of one 64-element-wide slab of a 64-row fp16 tile
 constexpr int kSlab128 = 128 * 128;  // ... of a 128-row tile
 // shared-memory tiles (fp16, 128-byte swizzle): [hi | lo] pairs
-constexpr int kOffW = 0, kOffQ = 32768, kOffQK = 65536, kOffKT = 81920, kOffBar = 114688;
-enum ScBar { SB_SREADY = 0, SB_WQFULL, SB_KQKFULL, SB_DACC, SB_WEMPTY, SB_DFULL, SB_CDONE, SB_KEMPTY, SB_OFREE, SB_COUNT };
+constexpr int kOffW = 0, kOffQ = 32768, kOffQK = 65536, kOffKT = 81920, kOffU = 114688 /*fp32 [64][128], unswizzled slabs*/,
+              kOffBar = 147456;
+enum ScBar { SB_SREADY = 0, SB_WQFULL, SB_UFULL, SB_KQKFULL, SB_DACC, SB_WEMPTY, SB_DFULL, SB_CDONE, SB_KEMPTY, SB_OFREE, SB_COUNT };
 constexpr int kScSmem = kOffBar + SB_COUNT * 8 + 1024 /*alignment slack*/;
 
 // x -> (hi, lo) fp16 with hi + lo = x to 22 bits; two values per 32-bit word (first value in the low half)
@@ -362,11 +363,13 @@ struct ScanParams {
 
 __global__ void __launch_bounds__(kScThreads, 1)
 gdn_scan_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_q,
-                const __grid_constant__ CUtensorMap map_qk, const __grid_constant__ CUtensorMap map_kt, ScanParams p) {
+                const __grid_constant__ CUtensorMap map_qk, const __grid_constant__ CUtensorMap map_kt,
+                const __grid_constant__ CUtensorMap map_u, ScanParams p) {
     extern __shared__ unsigned char smem_raw[];
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const float *sU = reinterpret_cast<const float *>(smem_raw + (base - smem_u32(smem_raw)) + kOffU);
     auto bar = [&](int i) { return base + kOffBar + 8u * (uint32_t)i; };
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -375,18 +378,19 @@ gdn_scan_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
 
     if (tid == 0) {
         s_abort = 0;
-        mbar_init(bar(SB_SREADY), 128);
+        mbar_init(bar(SB_SREADY), 256);
         mbar_init(bar(SB_WQFULL), 1);
+        mbar_init(bar(SB_UFULL), 1);
         mbar_init(bar(SB_KQKFULL), 1);
         mbar_init(bar(SB_DACC), 1);
         mbar_init(bar(SB_WEMPTY), 1);
-        mbar_init(bar(SB_DFULL), 128);
+        mbar_init(bar(SB_DFULL), 256);
         mbar_init(bar(SB_CDONE), 1);
         mbar_init(bar(SB_KEMPTY), 1);
-        mbar_init(bar(SB_OFREE), 128);
+        mbar_init(bar(SB_OFREE), 256);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
-    if (warp == 5) {
+    if (warp == 9) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&s_tmem_base)), "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
     }
@@ -396,7 +400,7 @@ gdn_scan_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     const uint32_t tmem = s_tmem_base;
     volatile int *abortp = &s_abort;
 
-    if (warp == 4) {
+    if (warp == 8) {
         // ================= TMA producer =================
         if (lane == 0) {
             for (int j = 0; j < nchunks; j++) {
@@ -405,13 +409,16 @@ gdn_scan_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                 mbar_expect_tx(bar(SB_WQFULL), 65536);
                 for (int s = 0; s < 4; s++) tma_load_2d(base + kOffW + s * kSlab64, &map_w, s * 64, hc * kC, bar(SB_WQFULL));
                 for (int s = 0; s < 4; s++) tma_load_2d(base + kOffQ + s * kSlab64, &map_q, kh * 2 * kDH + s * 64, j * kC, bar(SB_WQFULL));
+                if (j > 0 && !mbar_wait(bar(SB_DFULL), (j - 1) & 1, abortp)) break;  // U of the previous chunk has been read
+                mbar_expect_tx(bar(SB_UFULL), 32768);
+                for (int s = 0; s < 4; s++) tma_load_2d(base + kOffU + s * kSlab64, &map_u, s * 32, hc * kC, bar(SB_UFULL));
                 if (j > 0 && !mbar_wait(bar(SB_KEMPTY), (j - 1) & 1, abortp)) break;
                 mbar_expect_tx(bar(SB_KQKFULL), 16384 + 32768);
                 for (int s = 0; s < 2; s++) tma_load_2d(base + kOffQK + s * kSlab64, &map_qk, s * 64, hc * kC, bar(SB_KQKFULL));
                 for (int s = 0; s < 2; s++) tma_load_2d(base + kOffKT + s * kSlab128, &map_kt, s * 64, hc * kDH, bar(SB_KQKFULL));
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == 9) {
         // ================= MMA issuer =================
         if (lane == 0) {
             constexpr uint32_t id64 = idesc_dense(128, 64, false, 0), id128 = idesc_dense(128, 128, false, 0);
@@ -473,19 +480,20 @@ gdn_scan_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             }
         }
     } else {
-        // ================= state rows: one value dim per thread =================
-        const int r = tid;  // state row = TMEM lane
-        const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-        float *Srow = p.ssm + ((size_t)vh * kDH + r) * kDH;
+        // ================= state threads: row r = TMEM lane, half h of the columns =================
+        const int r = tid & 127, h = tid >> 7;
+        const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+        float *Srow = p.ssm + ((size_t)vh * kDH + r) * kDH + h * 64;  // this thread's 64 state columns
         const int total_v = p.Hv * kDH;
         const float *cv0 = p.cv + (size_t)vh * nchunks * kC;
+        const float *sUcol = sU + (r >> 5) * (kSlab64 / 4) + (r & 31);  // U[t][r] at sUcol[t * 32]
         // decay sums of the chunk at hand: lane l holds c_l and c_{32+l}
         float c_lo = __ldg(cv0 + lane), c_hi = __ldg(cv0 + 32 + lane);
         {
             // S -> its two-term copy; the accumulator starts scaled by the first chunk's total decay
             const float eC = expf(__shfl_sync(0xffffffffu, c_hi, 31));
 #pragma unroll 1
-            for (int c = 0; c < kDH; c += 32) {
+            for (int c = 0; c < 64; c += 32) {
                 uint32_t x[32], hi[16], lo[16];
 #pragma unroll
                 for (int i = 0; i < 8; i++) {
@@ -495,9 +503,9 @@ gdn_scan_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                     x[4 * i] = __float_as_uint(v.x * eC); x[4 * i + 1] = __float_as_uint(v.y * eC);
                     x[4 * i + 2] = __float_as_uint(v.z * eC); x[4 * i + 3] = __float_as_uint(v.w * eC);
                 }
-                tc_st32(tmem + lane_base + kTcS + c, x);
-                tc_st16(tmem + lane_base + kTcSh + (c >> 1), hi);
-                tc_st16(tmem + lane_base + kTcSl + (c >> 1), lo);
+                tc_st32(tmem + lane_base + kTcS + h * 64 + c, x);
+                tc_st16(tmem + lane_base + kTcSh + h * 32 + (c >> 1), hi);
+                tc_st16(tmem + lane_base + kTcSl + h * 32 + (c >> 1), lo);
             }
             tc_wait_st();
             tc_fence_before();
@@ -506,38 +514,33 @@ gdn_scan_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         bool ok = true;
         for (int j = 0; j < nchunks; j++) {
             const uint32_t ph = j & 1;
-            const int t0 = j * kC;
-            const float *Ug = p.U + ((size_t)vh * nchunks + j) * kC * kDH + r;
+            const int t0 = j * kC + h * 32;  // this thread's 32 tokens of the chunk
             // output scales e^{c_t} of this chunk, and the decay sums of the next one
-            const float e_lo = expf(c_lo), e_hi = expf(c_hi);
+            const float ev = expf(h == 0 ? c_lo : c_hi);
             float eC_next = 1.0f;  // the last update leaves the state unscaled
             if (j + 1 < nchunks) {
                 c_lo = __ldg(cv0 + (size_t)(j + 1) * kC + lane);
                 c_hi = __ldg(cv0 + (size_t)(j + 1) * kC + 32 + lane);
                 eC_next = expf(__shfl_sync(0xffffffffu, c_hi, 31));
             }
-            // Dt = U - acc, as two fp16 terms
+            // Dt = U - acc for tokens h*32 .. h*32+31, as two fp16 terms
             {
-                float u[kC];
-#pragma unroll
-                for (int t = 0; t < kC; t++) u[t] = __ldg(Ug + (size_t)t * kDH);
-                ok = __all_sync(0xffffffffu, mbar_wait(bar(SB_DACC), ph, abortp));
+                ok = __all_sync(0xffffffffu, mbar_wait(bar(SB_UFULL), ph, abortp) && mbar_wait(bar(SB_DACC), ph, abortp));
                 if (!ok) break;
                 tc_fence_after();
                 if (tid == 0) SC_TR(8);
-                uint32_t a0[32], a1[32];
-                tc_ld32(tmem + lane_base + kTcAcc, a0);
-                tc_ld32(tmem + lane_base + kTcAcc + 32, a1);
-                tc_wait_ld();
-                uint32_t dh[32], dl[32];
+                uint32_t a0[32];
+                tc_ld32(tmem + lane_base + kTcAcc + h * 32, a0);
+                float u[32];
 #pragma unroll
-                for (int i = 0; i < 16; i++) {
+                for (int t = 0; t < 32; t++) u[t] = sUcol[(h * 32 + t) * 32];
+                tc_wait_ld();
+                uint32_t dh[16], dl[16];
+#pragma unroll
+                for (int i = 0; i < 16; i++)
                     split2_f16(u[2 * i] - __uint_as_float(a0[2 * i]), u[2 * i + 1] - __uint_as_float(a0[2 * i + 1]), dh[i], dl[i]);
-                    split2_f16(u[32 + 2 * i] - __uint_as_float(a1[2 * i]), u[32 + 2 * i + 1] - __uint_as_float(a1[2 * i + 1]), dh[16 + i],
-                               dl[16 + i]);
-                }
-                tc_st32(tmem + lane_base + kTcDh, dh);
-                tc_st32(tmem + lane_base + kTcDl, dl);
+                tc_st16(tmem + lane_base + kTcDh + h * 16, dh);
+                tc_st16(tmem + lane_base + kTcDl + h * 16, dl);
                 tc_wait_st();
                 tc_fence_before();
                 mbar_arrive(bar(SB_DFULL));
@@ -549,9 +552,9 @@ gdn_scan_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             tc_fence_after();
             if (tid == 0) SC_TR(12);
 #pragma unroll 1
-            for (int c = 0; c < kDH; c += 32) {
+            for (int c = 0; c < 64; c += 32) {
                 uint32_t x[32], hi[16], lo[16];
-                tc_ld32(tmem + lane_base + kTcS + c, x);
+                tc_ld32(tmem + lane_base + kTcS + h * 64 + c, x);
                 tc_wait_ld();
 #pragma unroll
                 for (int i = 0; i < 16; i++) {
@@ -560,9 +563,9 @@ gdn_scan_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                     x[2 * i] = __float_as_uint(v0 * eC_next);
                     x[2 * i + 1] = __float_as_uint(v1 * eC_next);
                 }
-                tc_st16(tmem + lane_base + kTcSh + (c >> 1), hi);
-                tc_st16(tmem + lane_base + kTcSl + (c >> 1), lo);
-                if (j + 1 < nchunks) tc_st32(tmem + lane_base + kTcS + c, x);
+                tc_st16(tmem + lane_base + kTcSh + h * 32 + (c >> 1), hi);
+                tc_st16(tmem + lane_base + kTcSl + h * 32 + (c >> 1), lo);
+                if (j + 1 < nchunks) tc_st32(tmem + lane_base + kTcS + h * 64 + c, x);
             }
             tc_wait_st();
             tc_fence_before();
@@ -571,29 +574,26 @@ gdn_scan_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             // output rows of this chunk (off the critical path: the next chunk's first products run meanwhile)
             {
                 uint32_t o1[32], o2[32];
-#pragma unroll 1
-                for (int c = 0; c < kC; c += 32) {
-                    tc_ld32(tmem + lane_base + kTcO1 + c, o1);
-                    tc_ld32(tmem + lane_base + kTcO2 + c, o2);
-                    tc_wait_ld();
-                    const float ev = c == 0 ? e_lo : e_hi;
-                    float *orow = p.out + (size_t)(t0 + c) * total_v + (size_t)vh * kDH + r;
-#pragma unroll
-                    for (int i = 0; i < 32; i++) {
-                        const float sc = __shfl_sync(0xffffffffu, ev, i);
-                        if (t0 + c + i < p.n) orow[(size_t)i * total_v] = sc * __uint_as_float(o1[i]) + __uint_as_float(o2[i]);
-                    }
-                }
+                tc_ld32(tmem + lane_base + kTcO1 + h * 32, o1);
+                tc_ld32(tmem + lane_base + kTcO2 + h * 32, o2);
+                tc_wait_ld();
                 tc_fence_before();
-                mbar_arrive(bar(SB_OFREE));
+                mbar_arrive(bar(SB_OFREE));  // the accumulators are in registers
                 if (tid == 0) SC_TR(14);
+                float *orow = p.out + (size_t)t0 * total_v + (size_t)vh * kDH + r;
+#pragma unroll
+                for (int i = 0; i < 32; i++) {
+                    const float sc = __shfl_sync(0xffffffffu, ev, i);
+                    if (t0 + i < p.n) orow[(size_t)i * total_v] = sc * __uint_as_float(o1[i]) + __uint_as_float(o2[i]);
+                }
+                if (tid == 0) SC_TR(15);
             }
         }
         if (ok) {  // final state back to memory
 #pragma unroll 1
-            for (int c = 0; c < kDH; c += 32) {
+            for (int c = 0; c < 64; c += 32) {
                 uint32_t x[32];
-                tc_ld32(tmem + lane_base + kTcS + c, x);
+                tc_ld32(tmem + lane_base + kTcS + h * 64 + c, x);
                 tc_wait_ld();
 #pragma unroll
                 for (int i = 0; i < 8; i++)
@@ -606,7 +606,7 @@ gdn_scan_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     tc_fence_before();
     __syncthreads();
     if (s_abort && tid == 0) atomicCAS(p.err, 0, (3 << 16) | (blockIdx.x & 0xffff));
-    if (warp == 5) {
+    if (warp == 9) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(512u) : "memory");
     }
@@ -686,11 +686,12 @@ int launch_gdn_prefill(const GdnDims &g, int n, int chunk, int step0, float *con
     gdn_ring_kernel<<<dim3(12, 3), 256, 0, st>>>(g.conv_dim, n, step0, conv_state, qkv);
     gdn_chunk_kernel<<<dim3(nchunks, g.Hv), 256, kChunkSmem, st>>>(g, n, w, nchunks);
     {
-        CUtensorMap mw, mq, mqk, mkt;
+        CUtensorMap mw, mq, mqk, mkt, mu;
         if (!make_map_2d(&mw, w.W16, (uint64_t)g.Hv * nchunks * kC, 2 * kDH, kC, false) ||
             !make_map_2d(&mq, w.q16, (uint64_t)n, (uint64_t)g.Hk * 2 * kDH, kC, false) ||
             !make_map_2d(&mqk, w.QK16, (uint64_t)g.Hv * nchunks * kC, 2 * kC, kC, false) ||
-            !make_map_2d(&mkt, w.KT16, (uint64_t)g.Hv * nchunks * kDH, 2 * kC, kDH, false))
+            !make_map_2d(&mkt, w.KT16, (uint64_t)g.Hv * nchunks * kDH, 2 * kC, kDH, false) ||
+            !make_map_2d(&mu, w.U, (uint64_t)g.Hv * nchunks * kC, kDH, kC, true, /*swizzle=*/false))
             return -1;
         ScanParams sp;
         sp.n = n; sp.nchunks = nchunks; sp.Hv = g.Hv; sp.Hk = g.Hk;
@@ -700,7 +701,7 @@ int launch_gdn_prefill(const GdnDims &g, int n, int chunk, int step0, float *con
 #else
         sp.trace = nullptr;
 #endif
-        gdn_scan_kernel<<<g.Hv, kScThreads, kScSmem, st>>>(mw, mq, mqk, mkt, sp);
+        gdn_scan_kernel<<<g.Hv, kScThreads, kScSmem, st>>>(mw, mq, mqk, mkt, mu, sp);
     }
     int launches = 4;
     if (norm_w != nullptr) {
