@@ -13,8 +13,9 @@
 // Launch sequence:
 //   gdn_prep_kernel    per token   : conv + SiLU, q/k normalisation, ln(decay), beta  -> workspace
 //   gdn_ring_kernel                : last three raw inputs -> conv history ring
-//   gdn_chunk_kernel   per (head, chunk), all chunks in parallel: K K^T, Q K^T, A, then U and W by
-//                      forward substitution -> workspace
+//   gdn_kk_kernel      per (key head, chunk): K K^T and Q K^T
+//   gdn_chunk_kernel   per (value head, chunk), all chunks in parallel: A, then U and W by forward
+//                      substitution, and the scan's operands as fp16 pairs -> workspace
 //   gdn_scan_kernel    per head, chunks in sequence: D, O, S on tcgen05 with the state in tensor memory
 //   gdn_norm_kernel    per token: gated RMS-norm in place
 // The chunk kernel's contractions run as split tf32 (mma.sync m16n8k8, two terms per operand), the
@@ -78,6 +79,7 @@ struct GdnWork {  // workspace carved by the host
     float *lg, *bt;       // [n][Hv]  ln(decay), beta
     float *U;             // [Hv][nchunks][64][128]
     float *cv;            // [Hv][nchunks][64]  inclusive running sum of ln(decay)
+    float *KKr, *QKr;     // [Hk][nchunks][64][64]  k k^T and q k^T of a chunk (shared by the value heads of a key head)
     // operands of the scan, each value as two fp16 terms laid side by side (hi | lo):
     __half *q16;          // [n][Hk][128 | 128]             normalised, scaled q
     __half *W16;          // [Hv][nchunks][64][128 | 128]
@@ -170,33 +172,90 @@ __global__ void gdn_ring_kernel(int C, int n, int step0, float *__restrict__ rin
             ring[(size_t)((step0 + t) & 3) * C + ch] = qkv[(size_t)t * C + ch];
 }
 
-// ---- per (head, chunk): everything that does not depend on the state ---------------------------
+// Optional clock trace (development builds only: -DFM_GDN_TRACE): scan CTA 0 [chunk][16 events], then one row of
+// the chunk kernel's CTA (0, 0)
+#ifdef FM_GDN_TRACE
+extern "C" {
+long long *fm_gdn_trace = nullptr;
+}
+__device__ long long *fm_gdn_trace_dev = nullptr;
+#define SC_TR(slot)                                                                              \
+    do {                                                                                         \
+        if (p.trace && blockIdx.x == 0 && j < 64) p.trace[j * 16 + (slot)] = clock64();          \
+    } while (0)
+#define CH_TR(slot)                                                                              \
+    do {                                                                                         \
+        if (fm_gdn_trace_dev && blockIdx.x == 1 && blockIdx.y == 0 && threadIdx.x == 0) fm_gdn_trace_dev[64 * 16 + (slot)] = clock64(); \
+    } while (0)
+#else
+#define SC_TR(slot) do { } while (0)
+#define CH_TR(slot) do { } while (0)
+#endif
+
+// ---- per (key head, chunk): K K^T and Q K^T (64 x 64 x 128), shared by the value heads -------------
 constexpr int kLdK = kDH + 4;   // [row][k] operands read as (row g, k t): stride = 4 mod 32
+constexpr int kKkSmem = 2 * kC * kLdK * 4;
+
+// grid (nchunks, Hk), 256 threads: warp = (16-row tile, 32-column half)
+__global__ void __launch_bounds__(256)
+gdn_kk_kernel(GdnDims g, int n, GdnWork w, int nchunks) {
+    extern __shared__ __align__(16) float sm[];
+    float *sK = sm, *sQ = sK + kC * kLdK;
+    const int chunk = blockIdx.x, kh = blockIdx.y;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int t0 = chunk * kC, total_k = g.Hk * kDH;
+    for (int i = tid; i < kC * (kDH / 4); i += 256) {
+        const int r = i >> 5, c4 = (i & 31) * 4;
+        float4 k4 = make_float4(0.f, 0.f, 0.f, 0.f), q4 = k4;
+        if (t0 + r < n) {
+            k4 = __ldg(reinterpret_cast<const float4 *>(w.kn + (size_t)(t0 + r) * total_k + (size_t)kh * kDH + c4));
+            q4 = __ldg(reinterpret_cast<const float4 *>(w.qn + (size_t)(t0 + r) * total_k + (size_t)kh * kDH + c4));
+        }
+        *reinterpret_cast<float4 *>(sK + r * kLdK + c4) = k4;
+        *reinterpret_cast<float4 *>(sQ + r * kLdK + c4) = q4;
+    }
+    __syncthreads();
+    const int mt = warp & 3, nh = warp >> 2;
+    float akk[4][4] = {}, aqk[4][4] = {};
+    const float *Ka = sK + (mt * 16) * kLdK, *Qa = sQ + (mt * 16) * kLdK, *Kb = sK + (nh * 32) * kLdK;
+    auto fb = [&](int k, int nn) { return Kb[nn * kLdK + k]; };
+    warp_gemm_tf32<4>(akk, kDH, [&](int m, int k) { return Ka[m * kLdK + k]; }, fb, lane);
+    warp_gemm_tf32<4>(aqk, kDH, [&](int m, int k) { return Qa[m * kLdK + k]; }, fb, lane);
+    float *kk_out = w.KKr + ((size_t)kh * nchunks + chunk) * kC * kC, *qk_out = w.QKr + ((size_t)kh * nchunks + chunk) * kC * kC;
+    const int gq = lane >> 2, tq = lane & 3;
+#pragma unroll
+    for (int nt = 0; nt < 4; nt++) {
+        const int r = mt * 16 + gq, c = nh * 32 + nt * 8 + 2 * tq;
+        *reinterpret_cast<float2 *>(kk_out + r * kC + c) = make_float2(akk[nt][0], akk[nt][1]);
+        *reinterpret_cast<float2 *>(kk_out + (r + 8) * kC + c) = make_float2(akk[nt][2], akk[nt][3]);
+        *reinterpret_cast<float2 *>(qk_out + r * kC + c) = make_float2(aqk[nt][0], aqk[nt][1]);
+        *reinterpret_cast<float2 *>(qk_out + (r + 8) * kC + c) = make_float2(aqk[nt][2], aqk[nt][3]);
+    }
+}
+
+// ---- per (head, chunk): everything that does not depend on the state ---------------------------
 constexpr int kLdT = kC + 4;
-constexpr int kChunkSmem = (2 * kC * kLdK + kC * kLdT + 3 * kC) * 4;  // 85 KB: two CTAs per SM overlap their phases
+constexpr int kChunkSmem = (kC * kLdK + kC * kLdT + 3 * kC) * 4;  // 51 KB: several CTAs per SM overlap their phases
 
 // grid (nchunks, Hv), 256 threads
 __global__ void __launch_bounds__(256, 2)
 gdn_chunk_kernel(GdnDims g, int n, GdnWork w, int nchunks) {
     extern __shared__ __align__(16) float sm[];
-    float *sK = sm, *sQ = sK + kC * kLdK;
-    float *sA = sQ + kC * kLdK, *sT = sA + kC * kLdT;
+    float *sK = sm;
+    float *sA = sK + kC * kLdK, *sT = sA + kC * kLdT;
     float *sc = sT + kC, *sb = sc + kC;
     const int chunk = blockIdx.x, vh = blockIdx.y, kh = vh / (g.Hv / g.Hk);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int t0 = chunk * kC;
     const int total_k = g.Hk * kDH, total_v = g.Hv * kDH;
 
+    CH_TR(0);
     // rows past the end of the run are zero (beta 0, decay 1: they leave the state alone)
     for (int i = tid; i < kC * (kDH / 4); i += 256) {
         const int r = i >> 5, c4 = (i & 31) * 4;
-        float4 k4 = make_float4(0.f, 0.f, 0.f, 0.f), q4 = k4;
-        if (t0 + r < n) {
-            k4 = *reinterpret_cast<const float4 *>(w.kn + (size_t)(t0 + r) * total_k + (size_t)kh * kDH + c4);
-            q4 = *reinterpret_cast<const float4 *>(w.qn + (size_t)(t0 + r) * total_k + (size_t)kh * kDH + c4);
-        }
+        float4 k4 = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (t0 + r < n) k4 = __ldg(reinterpret_cast<const float4 *>(w.kn + (size_t)(t0 + r) * total_k + (size_t)kh * kDH + c4));
         *reinterpret_cast<float4 *>(sK + r * kLdK + c4) = k4;
-        *reinterpret_cast<float4 *>(sQ + r * kLdK + c4) = q4;
     }
     if (warp == 0) {  // inclusive scan of ln(decay) over the 64 rows, two per lane
         float a = (t0 + lane < n) ? w.lg[(size_t)(t0 + lane) * g.Hv + vh] : 0.f;
@@ -214,6 +273,7 @@ gdn_chunk_kernel(GdnDims g, int n, GdnWork w, int nchunks) {
         cv[lane] = a; cv[32 + lane] = b;
     }
     __syncthreads();
+    CH_TR(1);
     {   // k transposed and scaled for the state update of the scan: Ks[k][i] = e^{cC - c_i} k_i[k], hi | lo
         __half *kt = w.KT16 + ((size_t)vh * nchunks + chunk) * kDH * 2 * kC;
         const float cC = sc[kC - 1];
@@ -226,34 +286,34 @@ gdn_chunk_kernel(GdnDims g, int n, GdnWork w, int nchunks) {
         }
     }
 
-    // K K^T and Q K^T (64 x 64 x 128): warp = (16-row tile, 32-column half)
+    CH_TR(2);
+    // A = beta_t e^{c_t - c_i} (k_t . k_i) below the diagonal, and the decay-masked q k^T for the scan, from the
+    // key head's products: a thread takes 4 consecutive columns of a row
     {
-        const int mt = warp & 3, nh = warp >> 2;
-        float akk[4][4] = {}, aqk[4][4] = {};
-        const float *Ka = sK + (mt * 16) * kLdK, *Qa = sQ + (mt * 16) * kLdK, *Kb = sK + (nh * 32) * kLdK;
-        auto fb = [&](int k, int nn) { return Kb[nn * kLdK + k]; };
-        warp_gemm_tf32<4>(akk, kDH, [&](int m, int k) { return Ka[m * kLdK + k]; }, fb, lane);
-        warp_gemm_tf32<4>(aqk, kDH, [&](int m, int k) { return Qa[m * kLdK + k]; }, fb, lane);
+        const float *kk = w.KKr + ((size_t)kh * nchunks + chunk) * kC * kC, *qk = w.QKr + ((size_t)kh * nchunks + chunk) * kC * kC;
         __half *qk_out = w.QK16 + ((size_t)vh * nchunks + chunk) * kC * 2 * kC;
-        const int gq = lane >> 2, tq = lane & 3;
-#pragma unroll
-        for (int nt = 0; nt < 4; nt++)
+        for (int i = tid; i < kC * (kC / 4); i += 256) {
+            const int r = i >> 4, c = (i & 15) * 4;
+            const float4 a = __ldg(reinterpret_cast<const float4 *>(kk + r * kC + c));
+            const float4 q = __ldg(reinterpret_cast<const float4 *>(qk + r * kC + c));
+            const float av[4] = {a.x, a.y, a.z, a.w}, qv[4] = {q.x, q.y, q.z, q.w};
+            __half h[4], l[4];
 #pragma unroll
             for (int e = 0; e < 4; e++) {
-                const int r = mt * 16 + gq + (e >> 1) * 8, c = nh * 32 + nt * 8 + 2 * tq + (e & 1);
-                const float dec = c <= r ? expf(sc[r] - sc[c]) : 0.f;
-                sA[r * kLdT + c] = c < r ? sb[r] * dec * akk[nt][e] : 0.f;
-                __half h, l;
-                split_f16(dec * aqk[nt][e], h, l);
-                qk_out[r * 2 * kC + c] = h;
-                qk_out[r * 2 * kC + kC + c] = l;
+                const float dec = c + e <= r ? expf(sc[r] - sc[c + e]) : 0.f;
+                sA[r * kLdT + c + e] = c + e < r ? sb[r] * dec * av[e] : 0.f;
+                split_f16(dec * qv[e], h[e], l[e]);
             }
+            *reinterpret_cast<uint2 *>(qk_out + r * 2 * kC + c) = *reinterpret_cast<const uint2 *>(h);
+            *reinterpret_cast<uint2 *>(qk_out + r * 2 * kC + kC + c) = *reinterpret_cast<const uint2 *>(l);
+        }
     }
     __syncthreads();
     // (I + A) X = [beta V | beta e^c K] by forward substitution: thread c owns column c of X (a column
     // of U for c < 128, of W otherwise) and keeps its 64 entries in registers; A is read as broadcast
     // 128-bit loads and four partial sums shorten the dependent chain.  This replaces forming
     // T = (I + A)^-1 and multiplying by it.
+    CH_TR(3);
     if (tid < kC) sT[tid] = sb[tid] * expf(sc[tid]);  // row scale of the K block
     __syncthreads();
     {
@@ -282,6 +342,7 @@ gdn_chunk_kernel(GdnDims g, int n, GdnWork w, int nchunks) {
             for (int i = r & ~3; i < r; i++) a0 += Ar[i] * x[i];
             x[r] -= (a0 + a1) + (a2 + a3);
         }
+        CH_TR(4);
         if (is_u) {
             float *dst = w.U + ((size_t)vh * nchunks + chunk) * kC * kDH + c;
 #pragma unroll
@@ -297,6 +358,7 @@ gdn_chunk_kernel(GdnDims g, int n, GdnWork w, int nchunks) {
             }
         }
     }
+    CH_TR(5);
 }
 
 // ---- the chunk scan on the 5th-generation tensor cores ------------------------------------------
@@ -339,19 +401,6 @@ __device__ __forceinline__ void split2_f16(float x0, float x1, uint32_t &hi, uin
     hi = *reinterpret_cast<const uint32_t *>(&hh);
     lo = *reinterpret_cast<const uint32_t *>(&ll);
 }
-
-// Optional clock trace of CTA 0 (development builds only: -DFM_GDN_TRACE): [chunk][16 events]
-#ifdef FM_GDN_TRACE
-extern "C" {
-long long *fm_gdn_trace = nullptr;
-}
-#define SC_TR(slot)                                                                              \
-    do {                                                                                         \
-        if (p.trace && blockIdx.x == 0 && j < 64) p.trace[j * 16 + (slot)] = clock64();          \
-    } while (0)
-#else
-#define SC_TR(slot) do { } while (0)
-#endif
 
 struct ScanParams {
     long long *trace;
@@ -652,6 +701,8 @@ static size_t carve(const GdnDims &g, int n, void *base, GdnWork *w) {
     t.bt = take((size_t)n * g.Hv);
     t.U = take((size_t)g.Hv * nchunks * kC * kDH);
     t.cv = take((size_t)g.Hv * nchunks * kC);
+    t.KKr = take((size_t)g.Hk * nchunks * kC * kC);
+    t.QKr = take((size_t)g.Hk * nchunks * kC * kC);
     // fp16 pairs: two halves per value = one float's worth of bytes
     t.q16 = reinterpret_cast<__half *>(take((size_t)n * g.Hk * kDH));
     t.W16 = reinterpret_cast<__half *>(take((size_t)g.Hv * nchunks * kC * kDH));
@@ -677,13 +728,18 @@ int launch_gdn_prefill(const GdnDims &g, int n, int chunk, int step0, float *con
     if (!configured) {
         if (cudaFuncSetAttribute(gdn_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, g.conv_dim * 4) != cudaSuccess ||
             cudaFuncSetAttribute(gdn_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kChunkSmem) != cudaSuccess ||
+            cudaFuncSetAttribute(gdn_kk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kKkSmem) != cudaSuccess ||
             cudaFuncSetAttribute(gdn_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kScSmem) != cudaSuccess)
             return -1;
         configured = true;
     }
     const int nchunks = (n + kC - 1) / kC;
+#ifdef FM_GDN_TRACE
+    cudaMemcpyToSymbolAsync(fm_gdn_trace_dev, &fm_gdn_trace, sizeof(long long *), 0, cudaMemcpyHostToDevice, st);
+#endif
     gdn_prep_kernel<<<n, 512, g.conv_dim * 4, st>>>(g, n, step0, conv_state, qkv, beta, alpha, conv_w, A_log, dt_bias, w);
     gdn_ring_kernel<<<dim3(12, 3), 256, 0, st>>>(g.conv_dim, n, step0, conv_state, qkv);
+    gdn_kk_kernel<<<dim3(nchunks, g.Hk), 256, kKkSmem, st>>>(g, n, w, nchunks);
     gdn_chunk_kernel<<<dim3(nchunks, g.Hv), 256, kChunkSmem, st>>>(g, n, w, nchunks);
     {
         CUtensorMap mw, mq, mqk, mkt, mu;
@@ -703,7 +759,7 @@ int launch_gdn_prefill(const GdnDims &g, int n, int chunk, int step0, float *con
 #endif
         gdn_scan_kernel<<<g.Hv, kScThreads, kScSmem, st>>>(mw, mq, mqk, mkt, mu, sp);
     }
-    int launches = 4;
+    int launches = 5;
     if (norm_w != nullptr) {
         gdn_norm_kernel<<<n, 256, 0, st>>>(g, z, norm_w, out);
         launches++;
