@@ -430,32 +430,39 @@ def _probe_sweep(pkg, torch, dev, peak, gen):
     ctx.set_stream(torch.cuda.current_stream().cuda_stream)
     K = torch.randn((Lmax, HKV * D), device=dev, generator=gen).bfloat16().float()
     V = torch.randn((Lmax, HKV * D), device=dev, generator=gen).bfloat16().float()
-    qp = torch.randn((1, H * 2 * D), device=dev, generator=gen)
-    kn = torch.randn((1, HKV * D), device=dev, generator=gen)
-    out = torch.empty((1, H * D), device=dev)
+    qp = torch.randn((NL, 1, H * 2 * D), device=dev, generator=gen)
+    kn = torch.randn((NL, 1, HKV * D), device=dev, generator=gen)
+    out = torch.empty((NL, 1, H * D), device=dev)
+    sq, skv, so = H * 2 * D, HKV * D, H * D
+
+    def token(pos):  # one token through the NL layers: one C call, consecutive layers' launches overlapping
+        ctx.attn_decode_layers(0, NL, [0], [pos], out, qp, kn, kn, sq, skv, so)
+
     for L in (4096, 8192, 16384, 32768, 65536, 131072):
         for layer in range(NL):
             ctx.kv_import(layer, 0, K, V, L)
         reps = 6 if L >= 65536 else 20
         pos = L
-        for layer in range(NL):
-            ctx.attn_decode(layer, [0], [pos], out, q_proj_out=qp, k=kn, v=kn)
+        for _ in range(3):
+            token(pos); pos += 1
         torch.cuda.synchronize()
-        ctx.profile_read(); ctx.profile_enable(True)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for r in range(reps):
-            for layer in range(NL):
-                ctx.attn_decode(layer, [0], [pos + 1 + r], out, q_proj_out=qp, k=kn, v=kn)
+            token(pos); pos += 1
         e1.record()
         torch.cuda.synchronize()
-        n_k, k_ms = ctx.profile_read(); ctx.profile_enable(False)
         us_layer = e0.elapsed_time(e1) * 1e3 / (reps * NL)
+        # the same launches bracketed one by one (no overlap between layers while events sit between them)
+        ctx.profile_read(); ctx.profile_enable(True)
+        for r in range(3):
+            token(pos); pos += 1
+        torch.cuda.synchronize()
+        n_k, k_ms = ctx.profile_read(); ctx.profile_enable(False)
         us_kernel = k_ms * 1e3 / max(n_k, 1)
-        kvb = 2 * (L + 1 + reps / 2) * HKV * D * 2
-        sweep[str(L)] = {"us_per_layer": us_layer, "kv_gbps": kvb / us_layer / 1e3,
-                         "us_decode_kernel": us_kernel, "kv_gbps_kernel": kvb / us_kernel / 1e3,
-                         "frac_of_peak_kernel": kvb / us_kernel / 1e3 / peak}
+        kvb = 2 * (L + 4 + reps / 2) * HKV * D * 2
+        sweep[str(L)] = {"us_per_layer": us_layer, "kv_gbps": kvb / us_layer / 1e3, "frac_of_peak": kvb / us_layer / 1e3 / peak,
+                         "us_decode_kernel_bracketed_alone": us_kernel}
     res["decode_b1_sweep"] = sweep
     ctx.close()
     del K, V

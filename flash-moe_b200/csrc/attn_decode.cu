@@ -15,12 +15,10 @@
 //     mantissa bits: K and V are exact in bf16, so the result tracks the fp32 reference to ~1e-4;
 //   * each CTA writes an un-normalised partial (O, max, sum); a second kernel merges the partials
 //     and applies the gate.
-#include <cooperative_groups.h>
 
 #include "fm_device.cuh"
 #include "fm_internal.h"
 
-namespace cg = cooperative_groups;
 
 namespace fm {
 
@@ -74,10 +72,10 @@ __device__ __forceinline__ void named_barrier(int id, int nthreads) {
 //   * append: the CTA whose last tile holds the step's new row forms that row itself (k: RMS-norm +
 //     RoPE), stores it to the page and patches its shared-memory tile -- no separate append launch;
 //   * tail: with one split per (KV head, sequence) the CTA finishes its rows itself; with several, the
-//     grid (launched cooperatively, at most one CTA per SM) meets at a grid barrier and the (token,
-//     head) rows are merged by all CTAs -- no separate merge launch.  tail = 1: normalise, gate,
+//     last CTA to arrive at the unit's counter merges the splits (in two levels when there are many)
+//     -- no separate merge launch, no grid barrier.  tail = 1: normalise, gate,
 //     write the output; 2: un-normalised row and (max, sum) for the caller to exchange; 3: store the
-//     row into every peer's exchange buffer and publish the step; 4 (ordinary launch only): store the
+//     row into every peer's exchange buffer and publish the step; 4: store the
 //     rows of this (token, KV head) into every peer's buffer, publish that unit, wait -- bounded --
 //     for every peer's rows of the same unit, merge them by log-sum-exp, gate, write the output: the
 //     whole sequence-sharded step in this one kernel.
@@ -90,9 +88,9 @@ struct DecodeFused {
     float *ml_out;
     XchgView x;
     uint32_t step;
-    unsigned int *counters;  // [tokens*Hkv] arrivals per (token, KV head) + [1] finished groups; self-resetting
-    int coop;                // 1: cooperative launch, the splits are merged grid-wide after a grid barrier;
-                             // 0: ordinary launch, the last CTA to arrive for a (token, KV head) merges its splits
+    unsigned int *counters;  // [tokens*Hkv] arrivals per (token, KV head) + [1] finished units; self-resetting
+    unsigned int *group_counters;  // [tokens*Hkv][kDecMaxGroups] arrivals per group of splits (many splits only)
+    float *group_o, *group_ml;     // [tokens][H][kDecMaxGroups][D] / [..][2]: the groups' merged partials
     int *err;                // tail 4: device error word (a peer never published)
     long long *trace;  // development builds only (-DFM_DEC_TRACE)
 };
@@ -131,8 +129,8 @@ attn_decode_kernel(KvView kv, RopeParams rope, TokSpec toks, int H, const float 
     const int split = blockIdx.x, kvh = blockIdx.y, tok = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     DEC_TR(0);
-    // A following launch marked as programmatically dependent may start filling free SMs now; it
-    // holds back its own writes to the shared scratch until this grid has completed (dep_wait below).
+    // A following launch marked as programmatically dependent (another layer's step) may start filling
+    // free SMs now.
     if (kFused) dep_launch_dependents();
     const int pw = warp & 3;   // which 16 rows of the tile
     const int hs = warp >> 2;  // which share of the head dim
@@ -437,9 +435,10 @@ attn_decode_kernel(KvView kv, RopeParams rope, TokSpec toks, int H, const float 
         }
     };
     const bool direct = kFused && nsplits == 1;  // this CTA is the only split: finish the rows here
-    // From here on the kernel writes what the previous launch may still be reading (partials,
-    // arrival counters, exchange slots): wait for it to complete.  No effect for an ordinary launch.
-    if (kFused) dep_wait();
+    // The exchange tails write slots that the previous launch's peers may still be reading: wait for
+    // the previous launch to complete.  (Partials and counters are per layer, and a launch is only ever
+    // overlapped with another layer's.)  No effect for an ordinary launch.
+    if (kFused && f.tail >= 3) dep_wait();
     for (int r = warp; r < group; r += kDecWarps) {
         float mw[4], M = kNegBig;
 #pragma unroll
@@ -476,81 +475,84 @@ attn_decode_kernel(KvView kv, RopeParams rope, TokSpec toks, int H, const float 
         }
     }
     if (!kFused) return;
-    // work unit of the split merge = (token, head, eighth of the head dim), one warp each: 8 lanes of 4
-    // dims x 4 groups of splits, warp shuffles only
-    const int sg = lane >> 3, dl = lane & 7;
-    if (!direct && f.coop) {
-        // ---- every CTA's partials are written: meet, then merge the (token, head) rows grid-wide ----
-        cg::grid_group grid = cg::this_grid();
-        __threadfence();
-        DEC_TR(3);
-        grid.sync();
-        DEC_TR(4);
-        const int ncta = gridDim.x * gridDim.y * gridDim.z;
-        const int cta = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
-        const int units = gridDim.z * H * 8;
-        for (int u = cta * kDecWarps + warp; u < units; u += ncta * kDecWarps) {
-            const int item = u >> 3, e8 = u & 7;
-            const int tk = item / H, head = item - tk * H;
-            const size_t prow0 = ((size_t)tk * H + head) * nsplits;
-            const float2 *mlp = reinterpret_cast<const float2 *>(part_ml) + prow0;
-            float M = kNegBig;
-            for (int j = lane; j < nsplits; j += 32) M = fmaxf(M, __ldcg(mlp + j).x);
-            M = warp_max(M);
-            float lt = 0.f;
-            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 4
-            for (int j = sg; j < nsplits; j += 4) {
-                const float4 v = __ldcg(reinterpret_cast<const float4 *>(part_o + (prow0 + j) * kD + e8 * 32) + dl);
-                const float2 ml2 = __ldcg(mlp + j);
-                const float w = fast_exp2(ml2.x - M);
-                lt += w * ml2.y;
-                acc.x += w * v.x; acc.y += w * v.y; acc.z += w * v.z; acc.w += w * v.w;
-            }
-#pragma unroll
-            for (int o = 8; o <= 16; o <<= 1) {
-                acc.x += __shfl_xor_sync(0xffffffffu, acc.x, o);
-                acc.y += __shfl_xor_sync(0xffffffffu, acc.y, o);
-                acc.z += __shfl_xor_sync(0xffffffffu, acc.z, o);
-                acc.w += __shfl_xor_sync(0xffffffffu, acc.w, o);
-                lt += __shfl_xor_sync(0xffffffffu, lt, o);
-            }
-            if (sg == 0) emit(tk, head, e8 * 32 + dl * 4, acc, M, lt);
-        }
-    } else if (!direct) {
-        // ---- the last CTA to arrive for this (token, KV head) merges its splits ----
+    if (!direct) {
+        // ---- merge of the splits by the last CTA to arrive -------------------------------------------
+        // Up to kDecMaxLastCtaSplits splits per (token, KV head): the last CTA of the unit merges them all.
+        // More (small batch, long context): the splits form groups of kDecGroup; the last CTA of a group
+        // merges the group into one partial per head, the last group to finish merges the groups.  Either
+        // way a warp takes whole heads: lane j holds the (max, sum) of part j, the weights travel by
+        // shuffle, and all row loads of a head are in flight together.
         __shared__ int s_last;
-        __threadfence();
-        __syncthreads();
-        if (tid == 0) {
-            unsigned int *cnt = f.counters + tok * kv.Hkv + kvh;
-            const unsigned int old = atomicAdd(cnt, 1u);
-            s_last = old == (unsigned int)nsplits - 1;
-            if (s_last) *cnt = 0;
-        }
-        __syncthreads();
-        if (!s_last) return;
-        __threadfence();
-        // a warp takes whole heads: lane j holds the (max, sum) of split j (at most 24 splits on this
-        // path), the weights travel by shuffle, and all row loads of a head are in flight together
-        for (int r = warp; r < group; r += kDecWarps) {
-            const int head = kvh * group + r;
-            const size_t prow0 = ((size_t)tok * H + head) * nsplits;
-            const float2 mlj = lane < nsplits ? __ldcg(reinterpret_cast<const float2 *>(part_ml) + prow0 + lane) : make_float2(kNegBig, 0.f);
-            const float M = warp_max(mlj.x);
+        auto merge_head = [&](const float *po, const float *pml, int cnt, float4 &a0, float4 &a1, float &M, float &lt) {
+            const float2 mlj = lane < cnt ? __ldcg(reinterpret_cast<const float2 *>(pml) + lane) : make_float2(kNegBig, 0.f);
+            M = warp_max(mlj.x);
             const float wj = fast_exp2(mlj.x - M);
-            const float lt = warp_sum(wj * mlj.y);
-            float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0;
-            const float4 *src = reinterpret_cast<const float4 *>(part_o + prow0 * kD) + lane * 2;
+            lt = warp_sum(wj * mlj.y);
+            a0 = make_float4(0.f, 0.f, 0.f, 0.f);
+            a1 = a0;
+            const float4 *src = reinterpret_cast<const float4 *>(po) + lane * 2;
 #pragma unroll 8
-            for (int j = 0; j < nsplits; j++) {
+            for (int j = 0; j < cnt; j++) {
                 const float w = __shfl_sync(0xffffffffu, wj, j);
                 const float4 v0 = __ldcg(src + (size_t)j * (kD / 4)), v1 = __ldcg(src + (size_t)j * (kD / 4) + 1);
                 a0.x += w * v0.x; a0.y += w * v0.y; a0.z += w * v0.z; a0.w += w * v0.w;
                 a1.x += w * v1.x; a1.y += w * v1.y; a1.z += w * v1.z; a1.w += w * v1.w;
             }
-            emit(tok, head, lane * 8, a0, M, lt);
-            emit(tok, head, lane * 8 + 4, a1, M, lt);
+        };
+        // arrival at a counter; true for the CTA that completes it (which also resets it)
+        auto arrive_last = [&](unsigned int *cnt, int expected) {
+            __threadfence();
+            __syncthreads();
+            if (tid == 0) {
+                const unsigned int old = atomicAdd(cnt, 1u);
+                s_last = old == (unsigned int)expected - 1;
+                if (s_last) *cnt = 0;
+            }
+            __syncthreads();
+            const bool last = s_last != 0;
+            if (last) __threadfence();
+            return last;
+        };
+        const int unit = tok * kv.Hkv + kvh;
+        if (nsplits <= kDecMaxLastCtaSplits) {
+            if (!arrive_last(f.counters + unit, nsplits)) return;
+            for (int r = warp; r < group; r += kDecWarps) {
+                const int head = kvh * group + r;
+                const size_t prow0 = ((size_t)tok * H + head) * nsplits;
+                float4 a0, a1;
+                float M, lt;
+                merge_head(part_o + prow0 * kD, part_ml + prow0 * 2, nsplits, a0, a1, M, lt);
+                emit(tok, head, lane * 8, a0, M, lt);
+                emit(tok, head, lane * 8 + 4, a1, M, lt);
+            }
+        } else {
+            const int gi = split / kDecGroup, gfirst = gi * kDecGroup;
+            const int gcount = min(kDecGroup, nsplits - gfirst), ngroups = (nsplits + kDecGroup - 1) / kDecGroup;
+            if (!arrive_last(f.group_counters + unit * kDecMaxGroups + gi, gcount)) return;
+            DEC_TR(3);
+            for (int r = warp; r < group; r += kDecWarps) {
+                const int head = kvh * group + r;
+                const size_t prow0 = ((size_t)tok * H + head) * nsplits + gfirst;
+                float4 a0, a1;
+                float M, lt;
+                merge_head(part_o + prow0 * kD, part_ml + prow0 * 2, gcount, a0, a1, M, lt);
+                const size_t g2 = ((size_t)tok * H + head) * kDecMaxGroups + gi;
+                float4 *dst = reinterpret_cast<float4 *>(f.group_o + g2 * kD) + lane * 2;
+                dst[0] = a0;
+                dst[1] = a1;
+                if (lane == 0) *reinterpret_cast<float2 *>(f.group_ml + g2 * 2) = make_float2(M, lt);
+            }
+            if (!arrive_last(f.counters + unit, ngroups)) return;
+            DEC_TR(4);
+            for (int r = warp; r < group; r += kDecWarps) {
+                const int head = kvh * group + r;
+                const size_t g2 = ((size_t)tok * H + head) * kDecMaxGroups;
+                float4 a0, a1;
+                float M, lt;
+                merge_head(f.group_o + g2 * kD, f.group_ml + g2 * 2, ngroups, a0, a1, M, lt);
+                emit(tok, head, lane * 8, a0, M, lt);
+                emit(tok, head, lane * 8 + 4, a1, M, lt);
+            }
         }
     }
     DEC_TR(5);
@@ -612,14 +614,14 @@ attn_decode_kernel(KvView kv, RopeParams rope, TokSpec toks, int H, const float 
         }
         return;
     }
-    if (f.tail == 3 && !f.coop) {
-        // this (token, KV head) is in every peer's buffer; the last group to get here publishes the step
+    if (f.tail == 3) {
+        // this (token, KV head) is in every peer's buffer; the last unit to get here publishes the step
         __threadfence_system();
         __syncthreads();
         if (tid == 0) {
             unsigned int *done = f.counters + gridDim.z * kv.Hkv;
-            const unsigned int groups = gridDim.y * gridDim.z;
-            if (atomicAdd(done, 1u) == groups - 1) {
+            const unsigned int units = gridDim.y * gridDim.z;
+            if (atomicAdd(done, 1u) == units - 1) {
                 *done = 0;
                 __threadfence_system();
                 for (int r = 0; r < f.x.nranks; r++) {
@@ -627,17 +629,6 @@ attn_decode_kernel(KvView kv, RopeParams rope, TokSpec toks, int H, const float 
                     st_release_sys(flags + (f.step & 1) * f.x.nranks + f.x.me, f.step);
                 }
             }
-        }
-        return;
-    }
-    if (f.tail == 3) {
-        // every row is in every peer's buffer before the step is published
-        cg::grid_group grid = cg::this_grid();
-        __threadfence_system();
-        grid.sync();
-        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && tid < f.x.nranks) {
-            uint32_t *flags = reinterpret_cast<uint32_t *>(f.x.peer[tid] + f.x.flag_offset_floats);
-            st_release_sys(flags + (f.step & 1) * f.x.nranks + f.x.me, f.step);
         }
     }
 }
@@ -658,13 +649,12 @@ int launch_attn_decode(const KvView &kv, const RopeParams &rope, const TokSpec &
     return cudaGetLastError() == cudaSuccess ? 1 : -1;
 }
 
-// The whole decode step in one launch (see DecodeFused).  With several splits the launch is
-// cooperative: the grid never exceeds one CTA per SM, so all CTAs are resident for the grid barrier.
+// The whole decode step in one launch (see DecodeFused).
 int launch_attn_decode_fused(const KvView &kv, const RopeParams &rope, const TokSpec &toks, int H,
                              const float *q_proj_out, const float *q, const uint16_t *q_norm_w, float eps,
                              float *part_o, float *part_ml, int nsplits, const float *k_new, const float *v_new,
                              const uint16_t *k_norm_w, int tail, const float *gate, float *out, float *ml_out,
-                             const XchgView *x, uint32_t step, unsigned int *counters, int *err, bool overlap_prev,
+                             const XchgView *x, uint32_t step, const DecodeScratch &scr, int *err, bool overlap_prev,
                              cudaStream_t st) {
     static bool configured = false;
     if (!configured) {
@@ -672,6 +662,7 @@ int launch_attn_decode_fused(const KvView &kv, const RopeParams &rope, const Tok
             return -1;
         configured = true;
     }
+    if (nsplits > kDecMaxLastCtaSplits && (toks.n > scr.group_tokens || nsplits > kDecGroup * kDecMaxGroups)) return -1;
     dim3 grid(nsplits, kv.Hkv, toks.n);
     DecodeFused f = {};
     f.k_new = k_new; f.v_new = v_new; f.knw = k_norm_w;
@@ -681,31 +672,22 @@ int launch_attn_decode_fused(const KvView &kv, const RopeParams &rope, const Tok
 #ifdef FM_DEC_TRACE
     f.trace = fm_dec_trace;
 #endif
-    f.counters = counters;
+    f.counters = scr.counters;
+    f.group_counters = scr.group_counters;
+    f.group_o = scr.group_o;
+    f.group_ml = scr.group_ml;
     f.err = err;
-    // Few splits per (KV head, sequence): an ordinary launch, the last CTA of each group merges (a
-    // cooperative launch costs ~10 us more to start).  Many splits (small batch): one CTA could not
-    // merge them quickly, so the grid meets at a barrier and every warp takes a share.
-    f.coop = nsplits > kDecMaxLastCtaSplits;
-    if (tail == 4 && f.coop) return -1;  // the caller picks tail 3 + the separate merge for many splits
-    KvView kv_ = kv; RopeParams rope_ = rope; TokSpec toks_ = toks;
-    if (!f.coop) {
-        // overlap_prev: the caller vouches that this launch reads nothing the previous kernel in the
-        // stream writes except through the scratch the kernel guards itself (another layer's step).
-        // Its CTAs then take SMs as the previous grid's CTAs retire instead of after the grid drains.
-        cudaLaunchConfig_t lc = {};
-        lc.gridDim = grid; lc.blockDim = dim3(kDecThreads); lc.dynamicSmemBytes = kDecSmem; lc.stream = st;
-        cudaLaunchAttribute at[1];
-        at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        at[0].val.programmaticStreamSerializationAllowed = 1;
-        lc.attrs = at; lc.numAttrs = overlap_prev ? 1 : 0;
-        const cudaError_t e = cudaLaunchKernelEx(&lc, attn_decode_kernel<true>, kv_, rope_, toks_, H, q_proj_out, q, q_norm_w, eps,
-                                                 part_o, part_ml, nsplits, f);
-        return e == cudaSuccess ? 1 : -1;
-    }
-    void *args[] = {&kv_, &rope_, &toks_, &H, &q_proj_out, &q, &q_norm_w, &eps, &part_o, &part_ml, &nsplits, &f};
-    const cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<void *>(attn_decode_kernel<true>), grid, dim3(kDecThreads), args,
-                                                      kDecSmem, st);
+    // overlap_prev: the caller vouches that this launch reads nothing the previous kernel in the
+    // stream writes except through the scratch the kernel guards itself (another layer's step).
+    // Its CTAs then take SMs as the previous grid's CTAs retire instead of after the grid drains.
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = grid; lc.blockDim = dim3(kDecThreads); lc.dynamicSmemBytes = kDecSmem; lc.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = at; lc.numAttrs = overlap_prev ? 1 : 0;
+    const cudaError_t e = cudaLaunchKernelEx(&lc, attn_decode_kernel<true>, kv, rope, toks, H, q_proj_out, q, q_norm_w, eps, part_o, part_ml,
+                                             nsplits, f);
     return e == cudaSuccess ? 1 : -1;
 }
 

@@ -8,6 +8,8 @@
 #include <algorithm>
 #include <new>
 
+#include <cstdlib>
+
 #include "fm_internal.h"
 
 using namespace fm;
@@ -155,13 +157,30 @@ extern "C" fm_status fm_create(const FmConfig *cfg, FmCtx **out) {
         for (int64_t i = 0; i < ctx->pool_pages; i++) ctx->free_pages[(size_t)i] = (int)(ctx->pool_pages - 1 - i);
         ctx->kv_len.assign((size_t)c.num_full_layers * c.max_seqs, 0);
 
-        // split partials: at most ~2 CTAs per SM plus one per (KV head, sequence), 16 head rows each
+        // Split partials: at most ~2 CTAs per SM plus one per (KV head, sequence), 16 head rows each.  Every layer
+        // has its own set of partials and arrival counters, so the launches of consecutive layers never share
+        // scratch and need no ordering among themselves (fm_attn_decode_layers overlaps them).
         ctx->max_splits = std::max(1, ctx->sm_count);
+        const size_t nsets = (size_t)c.num_full_layers;
         const size_t rows = ((size_t)2 * ctx->sm_count + (size_t)c.num_kv_heads * c.max_batch_tokens) * 16 + 64;
-        CREATE_CUDA(cudaMalloc(&ctx->d_part_o, rows * c.head_dim * sizeof(float)));
-        CREATE_CUDA(cudaMalloc(&ctx->d_part_ml, rows * 2 * sizeof(float)));
-        CREATE_CUDA(cudaMalloc(&ctx->d_dec_counters, ((size_t)kMaxList * c.num_kv_heads + 1) * sizeof(unsigned int)));
-        CREATE_CUDA(cudaMemset(ctx->d_dec_counters, 0, ((size_t)kMaxList * c.num_kv_heads + 1) * sizeof(unsigned int)));
+        ctx->part_rows = rows;
+        ctx->counter_stride = (size_t)kMaxList * c.num_kv_heads + 1;
+        CREATE_CUDA(cudaMalloc(&ctx->d_part_o, nsets * rows * c.head_dim * sizeof(float)));
+        CREATE_CUDA(cudaMalloc(&ctx->d_part_ml, nsets * rows * 2 * sizeof(float)));
+        CREATE_CUDA(cudaMalloc(&ctx->d_dec_counters, nsets * ctx->counter_stride * sizeof(unsigned int)));
+        CREATE_CUDA(cudaMemset(ctx->d_dec_counters, 0, nsets * ctx->counter_stride * sizeof(unsigned int)));
+        // second-level scratch of the split merge, needed only when few sequences are split many ways
+        DecodeScratch &ds = ctx->dec_scr;
+        ds.counters = ctx->d_dec_counters;
+        ds.group_tokens = 8;
+        const size_t gc = (size_t)ds.group_tokens * c.num_kv_heads * kDecMaxGroups;
+        const size_t grows = (size_t)ds.group_tokens * c.num_attn_heads * kDecMaxGroups;
+        ctx->group_counter_stride = gc;
+        ctx->group_rows = grows;
+        CREATE_CUDA(cudaMalloc(&ds.group_counters, nsets * gc * sizeof(unsigned int)));
+        CREATE_CUDA(cudaMemset(ds.group_counters, 0, nsets * gc * sizeof(unsigned int)));
+        CREATE_CUDA(cudaMalloc(&ds.group_o, nsets * grows * c.head_dim * sizeof(float)));
+        CREATE_CUDA(cudaMalloc(&ds.group_ml, nsets * grows * 2 * sizeof(float)));
         if (c.seq_shard_count == 1) {  // prefill needs the whole sequence on one context
             CREATE_CUDA(cudaMalloc(&ctx->d_pf_q16, (size_t)c.max_batch_tokens * c.num_attn_heads * c.head_dim * 2 * 2));  // hi | lo
             CREATE_CUDA(cudaMalloc(&ctx->d_pf_k16, (size_t)c.max_seq_len * c.num_kv_heads * c.head_dim * 2));
@@ -200,6 +219,7 @@ extern "C" void fm_destroy(FmCtx *ctx) {
     cudaSetDevice(ctx->cfg.device);
     cudaDeviceSynchronize();
     cudaFree(ctx->pool); cudaFree(ctx->d_page_table); cudaFree(ctx->d_conv_state); cudaFree(ctx->d_ssm_state);
+    cudaFree(ctx->dec_scr.group_counters); cudaFree(ctx->dec_scr.group_o); cudaFree(ctx->dec_scr.group_ml);
     cudaFree(ctx->d_part_o); cudaFree(ctx->d_part_ml); cudaFree(ctx->d_dec_counters); cudaFree(ctx->d_xchg_counter); cudaFree(ctx->d_pf_q16); cudaFree(ctx->d_pf_k16); cudaFree(ctx->d_pf_v16); cudaFree(ctx->d_err);
     if (ctx->h_err) cudaFreeHost(ctx->h_err); cudaFree(ctx->d_work);
     cudaFree(ctx->d_stage);
@@ -492,10 +512,39 @@ static int pick_splits(const FmCtx *ctx, int batch, int max_len) {
     const int gpages = (max_len + c.page_size - 1) / c.page_size;
     const int slots = (gpages + c.seq_shard_count - 1) / c.seq_shard_count;
     want = std::min(want, std::max(1, slots));
+    if (ctx->overlap_layers) {
+        // Launches of consecutive layers overlap.  When a full-width launch would be short (under ~64 tiles
+        // per CTA) its start-up and merge tail are a large share of it and, holding every SM, it keeps the
+        // next layer from starting: a quarter of the width with at least 8 tiles per CTA lets about four
+        // layers stream side by side, each hiding the others' prologues and tails (batch 1: 17.6 -> 5.1 us
+        // per layer at 4K, 48.9 -> 40.9 at 128K).  Long launches keep the full width.
+        const int tiles_full = (slots + want - 1) / want;
+        if (tiles_full < 64) want = std::max(1, std::min(want / 4, (slots + 7) / 8));
+    }
+    want = std::min(want, kDecGroup * kDecMaxGroups);
+    if (batch > ctx->dec_scr.group_tokens) want = std::min(want, kDecMaxLastCtaSplits);  // no second-level scratch for that many tokens
     return std::max(1, std::min(want, ctx->max_splits));
 }
 
 static inline bool sg_host(const FmCtx *ctx) { return ctx->ptr_mode == FM_PTR_HOST; }
+
+// Scratch set of one full-attention layer.
+struct LayerScratch {
+    float *part_o, *part_ml;
+    DecodeScratch scr;
+};
+static LayerScratch layer_scratch(const FmCtx *ctx, int fa_idx) {
+    LayerScratch ls;
+    const size_t s = (size_t)fa_idx, D = (size_t)ctx->cfg.head_dim;
+    ls.part_o = ctx->d_part_o + s * ctx->part_rows * D;
+    ls.part_ml = ctx->d_part_ml + s * ctx->part_rows * 2;
+    ls.scr = ctx->dec_scr;
+    ls.scr.counters += s * ctx->counter_stride;
+    ls.scr.group_counters += s * ctx->group_counter_stride;
+    ls.scr.group_o += s * ctx->group_rows * D;
+    ls.scr.group_ml += s * ctx->group_rows * 2;
+    return ls;
+}
 
 // Shared body of fm_attn_decode / fm_attn_decode_partial (device pointers).
 static fm_status decode_core(FmCtx *ctx, int fa_idx, const int *seq, const int *pos, int batch,
@@ -533,9 +582,10 @@ static fm_status decode_core(FmCtx *ctx, int fa_idx, const int *seq, const int *
         float *mlp = ml_part ? ml_part + (size_t)i0 * H * 2 : nullptr;
         // one launch: append of the new rows, split-KV attention, merge of the splits, gate
         ProfScope prof(ctx);
-        fm_status st = launched(ctx, launch_attn_decode_fused(kv, ctx->rope, t, H, qp, qq, qnw, c.rms_norm_eps, ctx->d_part_o, ctx->d_part_ml, ns,
+        const LayerScratch ls = layer_scratch(ctx, fa_idx);
+        fm_status st = launched(ctx, launch_attn_decode_fused(kv, ctx->rope, t, H, qp, qq, qnw, c.rms_norm_eps, ls.part_o, ls.part_ml, ns,
                                                               k ? k + i0 * kvd : nullptr, v ? v + i0 * kvd : nullptr, knw, out ? 1 : 2, gp, op, mlp,
-                                                              nullptr, 0, ctx->d_dec_counters, ctx->d_err, ctx->overlap_prev && i0 == 0 && !sg_host(ctx),
+                                                              nullptr, 0, ls.scr, ctx->d_err, ctx->overlap_prev && i0 == 0 && !sg_host(ctx),
                                                               ctx->stream), "attn_decode");
         if (st) return st;
     }
@@ -946,7 +996,7 @@ static fm_status xchg_push(FmCtx *ctx, const char *fn, int fa_idx, const int *se
     int max_len = 1;
     for (int i = 0; i < batch; i++) max_len = std::max(max_len, ctx->kv_len[lidx(ctx, fa_idx, seq[i])] + (k ? 1 : 0));
     const int ns = pick_splits(ctx, batch, max_len);
-    const bool whole = out != nullptr && ns <= kDecMaxLastCtaSplits;
+    const bool whole = out != nullptr;
     const float *d_g = whole ? sg.in(q_proj_out ? nullptr : gate, batch * qd, &ok) : nullptr;
     size_t w_out = 0;
     float *d_out = whole ? sg.out(out, batch * qd, &ok, &w_out) : nullptr;
@@ -970,9 +1020,10 @@ static fm_status xchg_push(FmCtx *ctx, const char *fn, int fa_idx, const int *se
         // one launch: append, split-KV attention, merge of the splits, rows into every peer's buffer; then either the
         // step is published for the separate merge, or the peers' rows are awaited, merged and gated right there
         ProfScope prof(ctx);
-        st = launched(ctx, launch_attn_decode_fused(kv_view(ctx, fa_idx), ctx->rope, t, H, d_qp, d_q, d_qn, c.rms_norm_eps, ctx->d_part_o,
-                                                    ctx->d_part_ml, ns, d_k, d_v, d_kn, whole ? 4 : 3, d_g, d_out, nullptr, &ctx->xchg,
-                                                    ctx->xchg_step, ctx->d_dec_counters, ctx->d_err, ctx->overlap_prev && !sg.host,
+        const LayerScratch ls = layer_scratch(ctx, fa_idx);
+        st = launched(ctx, launch_attn_decode_fused(kv_view(ctx, fa_idx), ctx->rope, t, H, d_qp, d_q, d_qn, c.rms_norm_eps, ls.part_o,
+                                                    ls.part_ml, ns, d_k, d_v, d_kn, whole ? 4 : 3, d_g, d_out, nullptr, &ctx->xchg,
+                                                    ctx->xchg_step, ls.scr, ctx->d_err, ctx->overlap_prev && !sg.host,
                                                     ctx->stream),
                       "attn_decode");
     }
@@ -1115,10 +1166,13 @@ extern "C" fm_status fm_attn_decode_layers(FmCtx *ctx, int first_layer, int n_la
     // timing events, and not in host-pointer mode (copies sit between the launches anyway).
     struct Overlap {
         FmCtx *c;
-        ~Overlap() { c->overlap_prev = c->overlap_merge = false; }
+        ~Overlap() { c->overlap_prev = c->overlap_merge = c->overlap_layers = false; }
     } guard{ctx};
+    // (layers whose outputs would alias are kept in full stream order)
+    const bool distinct = layer_stride_out >= (size_t)std::max(batch, 0) * ctx->cfg.num_attn_heads * ctx->cfg.head_dim;
+    ctx->overlap_layers = !ctx->prof_on && n_layers > 1 && distinct;
     for (int l = 0; l < n_layers; l++) {
-        ctx->overlap_prev = l > 0 && !ctx->prof_on;
+        ctx->overlap_prev = l > 0 && ctx->overlap_layers;
         ctx->overlap_merge = !ctx->prof_on;
         const float *qp = q_proj_out + (size_t)l * layer_stride_q;
         const float *kk = k ? k + (size_t)l * layer_stride_kv : nullptr, *vv = v ? v + (size_t)l * layer_stride_kv : nullptr;

@@ -64,6 +64,15 @@ struct RopeParams {
 
 }  // namespace fm
 
+constexpr int kDecGroup = 16;      // splits per first-level merge group
+constexpr int kDecMaxGroups = 16;  // so up to 256 splits per (KV head, sequence)
+struct DecodeScratch {
+    unsigned int *counters;        // [kMaxList * Hkv + 1]
+    unsigned int *group_counters;  // [group_tokens * Hkv * kDecMaxGroups]
+    float *group_o, *group_ml;     // [group_tokens][H][kDecMaxGroups][D] and [..][2]
+    int group_tokens;              // tokens the two-level merge has room for (it is only needed at small batch)
+};
+
 struct FmCtx {
     FmConfig cfg;
     cudaStream_t stream = nullptr;
@@ -95,6 +104,8 @@ struct FmCtx {
     float *d_part_ml = nullptr;  // [batch][H][max_splits][2]
     int max_splits = 0;
     unsigned int *d_dec_counters = nullptr;  // arrival counters of the fused decode kernel
+    DecodeScratch dec_scr = {};              // set 0; layer l uses the pointers advanced by l strides
+    size_t part_rows = 0, counter_stride = 0, group_counter_stride = 0, group_rows = 0;
 
     // prefill scratch: fp16 copies of q (normalised, rotated, scaled) and of the sequence's K, V rows
     void *d_pf_q16 = nullptr;  // [max_batch_tokens][H*D]
@@ -114,7 +125,7 @@ struct FmCtx {
     bool prof_on = false;
     // set by fm_attn_decode_layers between layers: the next decode launch may start while the previous
     // layer's kernel drains (different layers touch different pages, inputs and outputs)
-    bool overlap_prev = false, overlap_merge = false;
+    bool overlap_prev = false, overlap_merge = false, overlap_layers = false;
     std::vector<cudaEvent_t> prof_ev;  // pairs (start, stop)
     size_t prof_used = 0;
 
@@ -141,9 +152,9 @@ int launch_attn_decode_fused(const KvView &kv, const RopeParams &rope, const Tok
                              const float *q_proj_out, const float *q, const uint16_t *q_norm_w, float eps,
                              float *part_o, float *part_ml, int nsplits, const float *k_new, const float *v_new,
                              const uint16_t *k_norm_w, int tail, const float *gate, float *out, float *ml_out,
-                             const XchgView *x, uint32_t step, unsigned int *counters, int *err, bool overlap_prev,
+                             const XchgView *x, uint32_t step, const DecodeScratch &scr, int *err, bool overlap_prev,
                              cudaStream_t st);
-constexpr int kDecMaxLastCtaSplits = 24;  // more splits per (KV head, sequence): cooperative launch, grid-wide merge
+constexpr int kDecMaxLastCtaSplits = 24;  // more splits per (KV head, sequence): merged in two levels
 
 // merges [nparts] partials per (token, head) laid out with strides, applies the gate
 int launch_attn_merge(const float *part_o, const float *part_ml, int nparts, long long part_stride_o,
