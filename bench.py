@@ -509,37 +509,42 @@ def _gdn_weights(pkg, torch, dev):
 
 
 def _probe_gdn_decode(pkg, torch, dev, peak, gen):
+    """GatedDeltaNet decode step, one launch per layer, cycling layers so that the states read exceed L2:
+    batch 1 over the 45 layers (180 MiB), batch 8 over 45 layers, batch 64 over 8 layers (2 GiB)."""
     res = {}
-    # ---- GatedDeltaNet decode, batch 1, cycling the 45 layers (180 MiB of state > L2) ----
-    cfg = pkg.default_config(num_full_layers=0, num_linear_layers=45, max_seqs=1)
-    ctx = pkg.Context(cfg)
-    ctx.set_stream(torch.cuda.current_stream().cuda_stream)
     tw = _gdn_weights(pkg, torch, dev)
-    qkv = torch.randn((1, 12288), device=dev, generator=gen)
-    z = torch.randn((1, 8192), device=dev, generator=gen)
-    be = torch.randn((1, 64), device=dev, generator=gen)
-    al = torch.randn((1, 64), device=dev, generator=gen)
-    go = torch.empty((1, 8192), device=dev)
+    for B, NL, reps in ((1, 45, 20), (8, 45, 10), (64, 8, 10)):
+        cfg = pkg.default_config(num_full_layers=0, num_linear_layers=NL, max_seqs=B, max_batch_tokens=max(B, 64))
+        ctx = pkg.Context(cfg)
+        ctx.set_stream(torch.cuda.current_stream().cuda_stream)
+        qkv = torch.randn((B, 12288), device=dev, generator=gen)
+        z = torch.randn((B, 8192), device=dev, generator=gen)
+        be = torch.randn((B, 64), device=dev, generator=gen)
+        al = torch.randn((B, 64), device=dev, generator=gen)
+        go = torch.empty((B, 8192), device=dev)
+        seqs = list(range(B))
 
-    def gdn_pass():
-        for li in range(45):
-            ctx.gdn_decode(li, [0], qkv, z, be, al, go, tw["conv_w"], tw["A_log"], tw["dt_bias"], tw["norm_w"])
+        def gdn_pass():
+            for li in range(NL):
+                ctx.gdn_decode(li, seqs, qkv, z, be, al, go, tw["conv_w"], tw["A_log"], tw["dt_bias"], tw["norm_w"])
 
-    for _ in range(3):
-        gdn_pass()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    reps = 20
-    for _ in range(reps):
-        gdn_pass()
-    e1.record()
-    torch.cuda.synchronize()
-    us = e0.elapsed_time(e1) * 1e3 / (reps * 45)
-    gdn_bytes = 2 * 4194304 + 2 * 147456 + (12288 + 8192 + 128 + 8192) * 4 + 98304 + 768
-    res["gdn_decode_b1"] = {"us_per_layer": us, "state_gbps": gdn_bytes / us / 1e3, "frac_of_peak": gdn_bytes / us / 1e3 / peak,
-                            "algorithmic_bytes_per_layer": gdn_bytes}
-    ctx.close()
+        for _ in range(3):
+            gdn_pass()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            gdn_pass()
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / (reps * NL)
+        # per sequence: state read + written, conv ring rows, inputs and output; weights once per launch
+        gdn_bytes = B * (2 * 4194304 + 2 * 147456 + (12288 + 8192 + 128 + 8192) * 4) + 98304 + 768
+        res[f"gdn_decode_b{B}"] = {"us_per_layer": us, "state_gbps": gdn_bytes / us / 1e3, "frac_of_peak": gdn_bytes / us / 1e3 / peak,
+                                   "algorithmic_bytes_per_layer": gdn_bytes, "layers_cycled": NL}
+        ctx.close()
+        del ctx
+        torch.cuda.empty_cache()
     return res
 
 
