@@ -498,7 +498,7 @@ def _probe_prefill(pkg, torch, dev, gen):
     ctx.attn_prefill(0, 0, 0, T, o, q=q, gate=g, k=k, v=v)
     n_k, k_ms = ctx.profile_read(); ctx.profile_enable(False)
     res["prefill_attn_T2048"] = {"ms": ms, "tflops": flops / ms / 1e9, "algorithmic_gflop": flops / 1e9,
-                                 "ms_kernels_after_append": k_ms, "tflops_kernels_after_append": flops / k_ms / 1e9}
+                                 "ms_launches_bracketed": k_ms, "tflops_launches_bracketed": flops / k_ms / 1e9}
     ctx.close()
     return res
 

@@ -3,11 +3,12 @@
 // Math of the Metal kernels prefill_q_rope_norm_bf16 / prefill_causal_attn
 // (metal_infer/shaders.metal:2228-2397; dispatch metal_infer/batched_prefill.h:574-668): q is
 // normalised and rotated, token t of the run attends to cache rows [0, row0 + t] (the run's own rows
-// were appended before this kernel runs), the result is multiplied by sigmoid(gate).
+// are appended by the preparation launch), the result is multiplied by sigmoid(gate).
 //
 // Organisation
-//   attn_q_prep_kernel    q -> RMS-norm, partial RoPE, * (1/sqrt(D)) * log2(e) -> fp16 hi | lo workspace
-//   attn_kv_f16_kernel    K, V rows of the sequence: bf16 pages -> contiguous fp16 workspace
+//   attn_prefill_prep_kernel   one launch: q -> RMS-norm, partial RoPE, * (1/sqrt(D)) * log2(e) -> fp16 hi | lo
+//                         workspace; the run's k, v rows -> bf16 pages (the append) and fp16 workspace; cached
+//                         prefix rows -> fp16 workspace
 //   attn_prefill_kernel   one CTA per (128 query tokens, query head):
 //       warp 4 (one lane)  TMA producer: q_hi tile once, then K / V tiles of 64 rows into 2-stage rings
 //       warp 5 (one lane)  issues tcgen05.mma: S = q_hi K^T + q_lo K^T (M128 N64 K256 each; q_hi from
@@ -63,36 +64,99 @@ __host__ __device__ constexpr uint32_t idesc_f16(int M, int N, bool b_mn_major) 
            | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 
-// ---- q preparation: norm, RoPE, scale -> fp16 [n][H][hi(256) | lo(256)] ------------------------
-// grid (n), 256 threads: the rotation table of the token is built once, then each warp walks heads
-// (a lane holds 8 consecutive dims of the head).
+// ---- operand preparation, one launch, three kinds of CTA (256 threads each) ------------------------
+//   blocks [0, n)                q of token t: RMS-norm, partial RoPE, * (1/sqrt(D)) * log2(e) -> fp16
+//                                [n][H][hi(256) | lo(256)]; a warp walks heads, a lane holds 8 dims
+//   blocks [n, n + n*Hkv)        k, v of token t, KV head h: k RMS-norm + RoPE, then the row goes to its bf16
+//                                page (the store proper) and, converted bf16 -> fp16, to the workspace the
+//                                attention kernel reads (math of metal_infer/layer_forward.h:574-629)
+//   blocks [n + n*Hkv, + row0)   one cached row of the prefix: bf16 page -> fp16 workspace
+// K and V are exact in fp16 (bf16 -> fp16 is lossless inside fp16's range; values beyond +-65504 are clamped).
+struct PrepParams {
+    int n, row0, start_pos, seq, H;
+    const float *q_proj_out, *q_in, *k, *v;
+    const uint16_t *qnw, *knw;
+    float eps;
+    __half *q16, *k16, *v16;
+};
+
+__device__ __forceinline__ float clamp_f16(float x) { return fminf(fmaxf(x, -65504.f), 65504.f); }
+
 __global__ void __launch_bounds__(256)
-attn_q_prep_kernel(RopeParams rope, int H, int start_pos, const float *__restrict__ q_proj_out,
-                   const float *__restrict__ q_in, const uint16_t *__restrict__ qnw, float eps,
-                   __half *__restrict__ q16) {
+attn_prefill_prep_kernel(KvView kv, RopeParams rope, PrepParams p) {
     __shared__ float s_cos[64], s_sin[64];
     __shared__ float s_x[8][kHD];
-    const int t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    __shared__ float s_red[8];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int half = rope.rotary_dim / 2;
-    if (tid < half) {
-        sincos_reduced(((float)(start_pos + t) / rope.pos_div) * rope.inv_freq[tid], s_sin[tid], s_cos[tid]);
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");  // the attention launch may begin its set-up
+    int b = blockIdx.x;
+    if (b >= p.n + p.n * kv.Hkv) {
+        // ---- prefix row: pages -> fp16 workspace ----
+        const int row = b - p.n - p.n * kv.Hkv;
+        const int page = kv.page_table[(size_t)p.seq * kv.max_slots + row / kv.page_size];
+        const int r = row % kv.page_size;
+        const size_t page_elems = (size_t)2 * kv.Hkv * kv.page_size * kHD;
+        for (int e = tid; e < kv.Hkv * kHD; e += 256) {
+            const int kvh = e / kHD, d = e - kvh * kHD;
+            const __nv_bfloat16 *kp = kv.pool + (size_t)page * page_elems + ((size_t)kvh * kv.page_size + r) * kHD + d;
+            const __nv_bfloat16 *vp = kp + (size_t)kv.Hkv * kv.page_size * kHD;
+            p.k16[(size_t)row * kv.Hkv * kHD + e] = __float2half_rn(clamp_f16(__bfloat162float(*kp)));
+            p.v16[(size_t)row * kv.Hkv * kHD + e] = __float2half_rn(clamp_f16(__bfloat162float(*vp)));
+        }
+        return;
     }
+    const bool is_q = b < p.n;
+    const int t = is_q ? b : (b - p.n) / kv.Hkv;
+    if (tid < half) sincos_reduced(((float)(p.start_pos + t) / rope.pos_div) * rope.inv_freq[tid], s_sin[tid], s_cos[tid]);
     __syncthreads();
+    if (!is_q) {
+        // ---- append: thread d owns dim d of (token t, KV head kvh) ----
+        const int kvh = (b - p.n) % kv.Hkv, d = tid, row = p.row0 + t;
+        const size_t src = ((size_t)t * kv.Hkv + kvh) * kHD + d;
+        float x = p.k[src];
+        float *sx = s_x[0];
+        if (p.knw != nullptr) {
+            const float ss = warp_sum(x * x);
+            if (lane == 0) s_red[warp] = ss;
+            __syncthreads();
+            float tot = 0.f;
+#pragma unroll
+            for (int w = 0; w < 8; w++) tot += s_red[w];
+            x = x * (1.0f / sqrtf(tot / kHD + p.eps)) * bf16_bits_to_float(p.knw[d]);
+        }
+        sx[d] = x;
+        __syncthreads();
+        if (d < rope.rotary_dim) {
+            const int i = d < half ? d : d - half;
+            x = d < half ? x * s_cos[i] - sx[d + half] * s_sin[i] : sx[d - half] * s_sin[i] + x * s_cos[i];
+        }
+        const __nv_bfloat16 kb = __float2bfloat16_rn(x), vb = __float2bfloat16_rn(p.v[src]);
+        const int gpage = row / kv.page_size, r = row - gpage * kv.page_size;
+        const int page = kv.page_table[(size_t)p.seq * kv.max_slots + gpage];
+        __nv_bfloat16 *pg = kv.pool + (size_t)page * ((size_t)2 * kv.Hkv * kv.page_size * kHD);
+        pg[((size_t)kvh * kv.page_size + r) * kHD + d] = kb;
+        pg[((size_t)(kv.Hkv + kvh) * kv.page_size + r) * kHD + d] = vb;
+        p.k16[((size_t)row * kv.Hkv + kvh) * kHD + d] = __float2half_rn(clamp_f16(__bfloat162float(kb)));
+        p.v16[((size_t)row * kv.Hkv + kvh) * kHD + d] = __float2half_rn(clamp_f16(__bfloat162float(vb)));
+        return;
+    }
+    // ---- q of token t ----
     const float qscale = rope.logit_scale * kLog2e;
     float w8[8];
 #pragma unroll
-    for (int j = 0; j < 8; j++) w8[j] = qnw ? bf16_bits_to_float(qnw[lane * 8 + j]) : 1.0f;
-    for (int h = warp; h < H; h += 8) {
-        const float *src = q_proj_out ? q_proj_out + ((size_t)t * H + h) * 2 * kHD : q_in + ((size_t)t * H + h) * kHD;
+    for (int j = 0; j < 8; j++) w8[j] = p.qnw ? bf16_bits_to_float(p.qnw[lane * 8 + j]) : 1.0f;
+    for (int h = warp; h < p.H; h += 8) {
+        const float *src = p.q_proj_out ? p.q_proj_out + ((size_t)t * p.H + h) * 2 * kHD : p.q_in + ((size_t)t * p.H + h) * kHD;
         const float4 a = __ldg(reinterpret_cast<const float4 *>(src + lane * 8));
-        const float4 b = __ldg(reinterpret_cast<const float4 *>(src + lane * 8 + 4));
-        float x[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-        if (qnw != nullptr) {
+        const float4 bq = __ldg(reinterpret_cast<const float4 *>(src + lane * 8 + 4));
+        float x[8] = {a.x, a.y, a.z, a.w, bq.x, bq.y, bq.z, bq.w};
+        if (p.qnw != nullptr) {
             float ss = 0.f;
 #pragma unroll
             for (int j = 0; j < 8; j++) ss += x[j] * x[j];
             ss = warp_sum(ss);
-            const float inv = 1.0f / sqrtf(ss / kHD + eps);
+            const float inv = 1.0f / sqrtf(ss / kHD + p.eps);
 #pragma unroll
             for (int j = 0; j < 8; j++) x[j] = x[j] * inv * w8[j];
         }
@@ -119,27 +183,9 @@ attn_q_prep_kernel(RopeParams rope, int H, int start_pos, const float *__restric
             hi[j] = *reinterpret_cast<const uint32_t *>(&hh);
             lo[j] = *reinterpret_cast<const uint32_t *>(&ll);
         }
-        __half *dst = q16 + ((size_t)t * H + h) * 2 * kHD + lane * 8;
+        __half *dst = p.q16 + ((size_t)t * p.H + h) * 2 * kHD + lane * 8;
         *reinterpret_cast<uint4 *>(dst) = make_uint4(hi[0], hi[1], hi[2], hi[3]);        // q_hi
         *reinterpret_cast<uint4 *>(dst + kHD) = make_uint4(lo[0], lo[1], lo[2], lo[3]);  // q_lo
-    }
-}
-
-// ---- K, V rows [0, L) of one sequence: bf16 pages -> fp16 [L][Hkv*256] --------------------------
-// grid (L), 256 threads
-__global__ void attn_kv_f16_kernel(KvView kv, int seq, int L, __half *__restrict__ k16, __half *__restrict__ v16) {
-    const int row = blockIdx.x;
-    const int page = kv.page_table[(size_t)seq * kv.max_slots + row / kv.page_size];
-    const int r = row % kv.page_size;
-    const size_t page_elems = (size_t)2 * kv.Hkv * kv.page_size * kHD;
-    for (int e = threadIdx.x; e < kv.Hkv * kHD; e += blockDim.x) {
-        const int kvh = e / kHD, d = e - kvh * kHD;
-        const __nv_bfloat16 *kp = kv.pool + (size_t)page * page_elems + ((size_t)kvh * kv.page_size + r) * kHD + d;
-        const __nv_bfloat16 *vp = kp + (size_t)kv.Hkv * kv.page_size * kHD;
-        const float kf = fminf(fmaxf(__bfloat162float(*kp), -65504.f), 65504.f);
-        const float vf = fminf(fmaxf(__bfloat162float(*vp), -65504.f), 65504.f);
-        k16[(size_t)row * kv.Hkv * kHD + e] = __float2half_rn(kf);
-        v16[(size_t)row * kv.Hkv * kHD + e] = __float2half_rn(vf);
     }
 }
 
@@ -233,6 +279,9 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     tc_fence_after();
     const uint32_t tmem = s_tmem_base;
     volatile int *abortp = &s_abort;
+    // Launched as a programmatic dependent of the preparation kernel: everything above overlapped its
+    // tail; its outputs (q16, k16, v16) are read from here on.
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
 
     if (warp == 4) {
         // ================= TMA producer =================
@@ -488,8 +537,9 @@ static bool make_map(CUtensorMap *m, const void *base, uint64_t rows, uint64_t c
 }
 
 int launch_attn_prefill(const KvView &kv, const RopeParams &rope, int seq, int start_pos, int row0, int n, int H,
-                        const float *q_proj_out, const float *q, const float *gate, const uint16_t *q_norm_w, float eps,
-                        const PrefillWork &wk, float *out, cudaStream_t st) {
+                        const float *q_proj_out, const float *q, const float *gate, const float *k, const float *v,
+                        const uint16_t *q_norm_w, const uint16_t *k_norm_w, float eps, const PrefillWork &wk, float *out,
+                        cudaStream_t st) {
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmem) != cudaSuccess) return -1;
@@ -500,8 +550,12 @@ int launch_attn_prefill(const KvView &kv, const RopeParams &rope, int seq, int s
     if (!make_map(&mq, wk.q16, (uint64_t)n, (uint64_t)H * 2 * kHD, kBM) || !make_map(&mk, wk.k16, (uint64_t)L, (uint64_t)kv.Hkv * kHD, kBN) ||
         !make_map(&mv, wk.v16, (uint64_t)L, (uint64_t)kv.Hkv * kHD, kBN))
         return -1;
-    attn_q_prep_kernel<<<n, 256, 0, st>>>(rope, H, start_pos, q_proj_out, q, q_norm_w, eps, reinterpret_cast<__half *>(wk.q16));
-    attn_kv_f16_kernel<<<L, 256, 0, st>>>(kv, seq, L, reinterpret_cast<__half *>(wk.k16), reinterpret_cast<__half *>(wk.v16));
+    PrepParams pp;
+    pp.n = n; pp.row0 = row0; pp.start_pos = start_pos; pp.seq = seq; pp.H = H;
+    pp.q_proj_out = q_proj_out; pp.q_in = q; pp.k = k; pp.v = v; pp.qnw = q_norm_w; pp.knw = k_norm_w; pp.eps = eps;
+    pp.q16 = reinterpret_cast<__half *>(wk.q16); pp.k16 = reinterpret_cast<__half *>(wk.k16); pp.v16 = reinterpret_cast<__half *>(wk.v16);
+    attn_prefill_prep_kernel<<<n + n * kv.Hkv + row0, 256, 0, st>>>(kv, rope, pp);
+    if (cudaGetLastError() != cudaSuccess) return -1;
     PfParams p;
     p.n = n; p.row0 = row0; p.H = H; p.Hkv = kv.Hkv;
 #ifdef FM_PF_TRACE
@@ -511,8 +565,14 @@ int launch_attn_prefill(const KvView &kv, const RopeParams &rope, int seq, int s
 #endif
     p.q16 = reinterpret_cast<const __half *>(wk.q16);
     p.q_proj_out = q_proj_out; p.gate = gate; p.out = out; p.err = wk.err;
-    attn_prefill_kernel<<<dim3(H, (n + kBM - 1) / kBM), kPfThreads, kPfSmem, st>>>(mq, mk, mv, p);
-    return cudaGetLastError() == cudaSuccess ? 3 : -1;
+    // the attention launch overlaps its set-up (barriers, TMEM allocation) with the end of the preparation
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3(H, (n + kBM - 1) / kBM); lc.blockDim = dim3(kPfThreads); lc.dynamicSmemBytes = kPfSmem; lc.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = at; lc.numAttrs = 1;
+    return cudaLaunchKernelEx(&lc, attn_prefill_kernel, mq, mk, mv, p) == cudaSuccess ? 2 : -1;
 }
 
 }  // namespace fm

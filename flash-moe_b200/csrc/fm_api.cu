@@ -703,15 +703,12 @@ extern "C" fm_status fm_attn_prefill(FmCtx *ctx, int fa_idx, int seq, int start_
     ctx->kv_len[lidx(ctx, fa_idx, seq)] = row0 + n;
     FM_CUDA(ctx, sg.push());
     const KvView kv = kv_view(ctx, fa_idx);
-    TokSpec t;
-    t.mode = 1; t.n = n; t.seq0 = seq; t.pos0 = start_pos; t.row0 = row0;
-    st = launched(ctx, launch_kv_append(kv, ctx->rope, t, d_k, d_v, d_kn, c.rms_norm_eps, ctx->stream), "kv_append");
-    if (st) return st;
     {
+        // two launches: operand preparation (which is also the append), then the attention kernel
         ProfScope prof(ctx);
         const PrefillWork wk{ctx->d_pf_q16, ctx->d_pf_k16, ctx->d_pf_v16, ctx->d_err};
-        st = launched(ctx, launch_attn_prefill(kv, ctx->rope, seq, start_pos, row0, n, c.num_attn_heads, d_qp, d_q, d_g, d_qn,
-                                               c.rms_norm_eps, wk, d_out, ctx->stream), "attn_prefill");
+        st = launched(ctx, launch_attn_prefill(kv, ctx->rope, seq, start_pos, row0, n, c.num_attn_heads, d_qp, d_q, d_g, d_k, d_v, d_qn,
+                                               d_kn, c.rms_norm_eps, wk, d_out, ctx->stream), "attn_prefill");
     }
     if (st) return st;
     if (sg.host) FM_CUDA(ctx, cudaMemcpyAsync(ctx->h_err, ctx->d_err, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));

@@ -175,9 +175,9 @@ struct PrefillWork {
     void *q16, *k16, *v16;
     int *err;
 };
-int launch_attn_prefill(const KvView &kv, const RopeParams &rope, int seq, int start_pos, int row0,
-                        int n, int H, const float *q_proj_out, const float *q, const float *gate,
-                        const uint16_t *q_norm_w, float eps, const PrefillWork &wk, float *out,
+int launch_attn_prefill(const KvView &kv, const RopeParams &rope, int seq, int start_pos, int row0, int n, int H,
+                        const float *q_proj_out, const float *q, const float *gate, const float *k, const float *v,
+                        const uint16_t *q_norm_w, const uint16_t *k_norm_w, float eps, const PrefillWork &wk, float *out,
                         cudaStream_t st);
 
 struct GdnDims {

@@ -87,6 +87,15 @@ struct GdnWork {  // workspace carved by the host
     __half *KT16;         // [Hv][nchunks][128][64 | 64]    k transposed, column i scaled by e^{cC - c_i}
 };
 
+// x -> (hi, lo) fp16 with hi + lo = x to 22 bits; two values per 32-bit word (first value in the low half)
+__device__ __forceinline__ void split2_f16(float x0, float x1, uint32_t &hi, uint32_t &lo) {
+    const __half2 hh = __floats2half2_rn(x0, x1);
+    const float2 hf = __half22float2(hh);
+    const __half2 ll = __floats2half2_rn(x0 - hf.x, x1 - hf.y);
+    hi = *reinterpret_cast<const uint32_t *>(&hh);
+    lo = *reinterpret_cast<const uint32_t *>(&ll);
+}
+
 __device__ __forceinline__ void split_f16(float x, __half &hi, __half &lo) {
     hi = __float2half_rn(x);
     lo = __float2half_rn(x - __half2float(hi));
@@ -365,11 +374,14 @@ gdn_chunk_kernel(GdnDims g, int n, GdnWork w, int nchunks) {
 // One CTA per value head walks the chunks with the state in tensor memory, transposed so that the
 // state row (value dim v) is the TMEM lane; every product has its A operand in TMEM and a K-major
 // B tile brought by TMA:
-//     acc[v][t] = sum_k S[v][k] W[t][k]              Dt = U^T - acc            (M128 N64  K128)
-//     O1[v][t]  = sum_k S[v][k] Q[t][k]                                         (M128 N64  K128)
-//     O2[v][t]  = sum_i Dt[v][i] QKm[t][i]                                      (M128 N64  K64)
-//     S[v][k]   = e^{cC} S[v][k] + sum_i Dt[v][i] Ks[k][i]                      (M128 N128 K64)
+//     acc[v][t] = sum_k S[v][k] W[t][k]              Dt = U^T - acc   }  one product M128 N128 K128 with
+//     O1[v][t]  = sum_k S[v][k] Q[t][k]                               }  B = [W ; Q] stacked along N
+//     O2[v][t]  = sum_i Dt[v][i] QKm[t][i]                            }  one product M128 N192 K64 with
+//     S[v][k]   = e^{cC} S[v][k] + sum_i Dt[v][i] Ks[k][i]            }  B = [Ks ; QKm] stacked along N
 //     out[t][v] = e^{c_t} O1[v][t] + O2[v][t]
+// (an M128 MMA costs about the same ~60 cycles for N = 64 as for N = 128, so the products that share their
+// A operand are stacked: 36 MMAs per chunk instead of 72; their accumulators are adjacent TMEM columns, and
+// O2, which must start from zero next to the accumulating S, is zeroed by the state threads beforehand)
 // Precision: fp16 has 11 significant bits, so every operand enters as two fp16 terms (x = hi + lo,
 // 22 bits) and every product as three MMAs into the same fp32 accumulator (hi*hi, lo*hi, hi*lo):
 // the B tiles arrive from the chunk kernel already split (hi | lo side by side), the TMEM operands S
@@ -378,29 +390,23 @@ gdn_chunk_kernel(GdnDims g, int n, GdnWork w, int nchunks) {
 // scales the accumulator by the next chunk's total decay, so the next update accumulates on top.
 //   warps 0-7   state threads, two per state row (each takes half of the columns of every pass):
 //               S -> TMEM, per chunk Dt = U - acc (split), the pass over the new S, the output rows
-//   warp 8      TMA producer (single-buffered tiles: W | Q are free again after the first two product
-//               groups, U after Dt is formed, QKm | Ks after the last two)
+//   warp 8      TMA producer (single-buffered tiles: [W ; Q] is free again after the first product, U after
+//               Dt is formed, [Ks ; QKm] after the second)
 //   warp 9      MMA issuer
-// TMEM: S 128 + S hi 64 + S lo 64 + acc 64 + Dt hi 32 + Dt lo 32 + O1 64 + O2 64 = 512 columns.
+// TMEM: S 128 | O2 64 | S hi 64 | S lo 64 | acc 64 | O1 64 | Dt hi 32 | Dt lo 32 = 512 columns.
 // Every mbarrier wait is bounded; on expiry the CTA records an error code and winds down.
 constexpr int kScThreads = 320;
-constexpr uint32_t kTcS = 0, kTcSh = 128, kTcSl = 192, kTcAcc = 256, kTcDh = 320, kTcDl = 352, kTcO1 = 384, kTcO2 = 448;
+constexpr uint32_t kTcS = 0, kTcO2 = 128, kTcSh = 192, kTcSl = 256, kTcAcc = 320, kTcO1 = 384, kTcDh = 448, kTcDl = 480;
 constexpr int kSlab64 = 64 * 128;    // bytes of one 64-element-wide slab of a 64-row fp16 tile
-constexpr int kSlab128 = 128 * 128;  // ... of a 128-row tile
+constexpr int kSlab128 = 128 * 128;  // ... of a 128-row tile ([W ; Q])
+constexpr int kSlab192 = 192 * 128;  // ... of a 192-row tile ([Ks ; QKm])
 // shared-memory tiles (fp16, 128-byte swizzle): [hi | lo] pairs
-constexpr int kOffW = 0, kOffQ = 32768, kOffQK = 65536, kOffKT = 81920, kOffU = 114688 /*fp32 [64][128], unswizzled slabs*/,
-              kOffBar = 147456;
-enum ScBar { SB_SREADY = 0, SB_WQFULL, SB_UFULL, SB_KQKFULL, SB_DACC, SB_WEMPTY, SB_DFULL, SB_CDONE, SB_KEMPTY, SB_OFREE, SB_COUNT };
+// [W ; Q]: 4 slabs (hi k 0-63, hi k 64-127, lo, lo) of 128 rows, W in rows 0-63; [Ks ; QKm]: 2 slabs (hi, lo) of 192
+// rows, Ks in rows 0-127
+constexpr int kOffWQ = 0, kOffKQ = 65536, kOffU = 114688 /*fp32 [64][128], unswizzled slabs*/, kOffBar = 147456;
+enum ScBar { SB_SREADY = 0, SB_WQFULL, SB_UFULL, SB_KQKFULL, SB_DACC, SB_WEMPTY, SB_DFULL, SB_CDONE, SB_KEMPTY, SB_COUNT };
 constexpr int kScSmem = kOffBar + SB_COUNT * 8 + 1024 /*alignment slack*/;
 
-// x -> (hi, lo) fp16 with hi + lo = x to 22 bits; two values per 32-bit word (first value in the low half)
-__device__ __forceinline__ void split2_f16(float x0, float x1, uint32_t &hi, uint32_t &lo) {
-    const __half2 hh = __floats2half2_rn(x0, x1);
-    const float2 hf = __half22float2(hh);
-    const __half2 ll = __floats2half2_rn(x0 - hf.x, x1 - hf.y);
-    hi = *reinterpret_cast<const uint32_t *>(&hh);
-    lo = *reinterpret_cast<const uint32_t *>(&ll);
-}
 
 struct ScanParams {
     long long *trace;
@@ -436,7 +442,6 @@ gdn_scan_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         mbar_init(bar(SB_DFULL), 256);
         mbar_init(bar(SB_CDONE), 1);
         mbar_init(bar(SB_KEMPTY), 1);
-        mbar_init(bar(SB_OFREE), 256);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     if (warp == 9) {
@@ -456,73 +461,55 @@ gdn_scan_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                 const int hc = vh * nchunks + j;
                 if (j > 0 && !mbar_wait(bar(SB_WEMPTY), (j - 1) & 1, abortp)) break;
                 mbar_expect_tx(bar(SB_WQFULL), 65536);
-                for (int s = 0; s < 4; s++) tma_load_2d(base + kOffW + s * kSlab64, &map_w, s * 64, hc * kC, bar(SB_WQFULL));
-                for (int s = 0; s < 4; s++) tma_load_2d(base + kOffQ + s * kSlab64, &map_q, kh * 2 * kDH + s * 64, j * kC, bar(SB_WQFULL));
+                for (int s = 0; s < 4; s++) tma_load_2d(base + kOffWQ + s * kSlab128, &map_w, s * 64, hc * kC, bar(SB_WQFULL));
+                for (int s = 0; s < 4; s++)
+                    tma_load_2d(base + kOffWQ + s * kSlab128 + kSlab64, &map_q, kh * 2 * kDH + s * 64, j * kC, bar(SB_WQFULL));
                 if (j > 0 && !mbar_wait(bar(SB_DFULL), (j - 1) & 1, abortp)) break;  // U of the previous chunk has been read
                 mbar_expect_tx(bar(SB_UFULL), 32768);
                 for (int s = 0; s < 4; s++) tma_load_2d(base + kOffU + s * kSlab64, &map_u, s * 32, hc * kC, bar(SB_UFULL));
                 if (j > 0 && !mbar_wait(bar(SB_KEMPTY), (j - 1) & 1, abortp)) break;
                 mbar_expect_tx(bar(SB_KQKFULL), 16384 + 32768);
-                for (int s = 0; s < 2; s++) tma_load_2d(base + kOffQK + s * kSlab64, &map_qk, s * 64, hc * kC, bar(SB_KQKFULL));
-                for (int s = 0; s < 2; s++) tma_load_2d(base + kOffKT + s * kSlab128, &map_kt, s * 64, hc * kDH, bar(SB_KQKFULL));
+                for (int s = 0; s < 2; s++) tma_load_2d(base + kOffKQ + s * kSlab192, &map_kt, s * 64, hc * kDH, bar(SB_KQKFULL));
+                for (int s = 0; s < 2; s++) tma_load_2d(base + kOffKQ + s * kSlab192 + kSlab128, &map_qk, s * 64, hc * kC, bar(SB_KQKFULL));
             }
         }
     } else if (warp == 9) {
         // ================= MMA issuer =================
         if (lane == 0) {
-            constexpr uint32_t id64 = idesc_dense(128, 64, false, 0), id128 = idesc_dense(128, 128, false, 0);
-            // tiles: W hi = slabs 0,1 and lo = slabs 2,3 (same for Q); QKm hi = slab 0, lo = slab 1; Ks likewise
-            const uint64_t dWh = smem_desc(base + kOffW, 16, 1024), dWl = smem_desc(base + kOffW + 2 * kSlab64, 16, 1024);
-            const uint64_t dQh = smem_desc(base + kOffQ, 16, 1024), dQl = smem_desc(base + kOffQ + 2 * kSlab64, 16, 1024);
-            const uint64_t dQKh = smem_desc(base + kOffQK, 16, 1024), dQKl = smem_desc(base + kOffQK + kSlab64, 16, 1024);
-            const uint64_t dKh = smem_desc(base + kOffKT, 16, 1024), dKl = smem_desc(base + kOffKT + kSlab128, 16, 1024);
+            constexpr uint32_t id128 = idesc_dense(128, 128, false, 0), id192 = idesc_dense(128, 192, false, 0);
+            const uint64_t dWQh = smem_desc(base + kOffWQ, 16, 1024), dWQl = smem_desc(base + kOffWQ + 2 * kSlab128, 16, 1024);
+            const uint64_t dKQh = smem_desc(base + kOffKQ, 16, 1024), dKQl = smem_desc(base + kOffKQ + kSlab192, 16, 1024);
             // k-step of 16 elements = 32 bytes inside a 64-element slab, then the next slab
-            auto k64 = [](int ks) { return (uint64_t)((((ks >> 2) * kSlab64) + (ks & 3) * 32) >> 4); };
+            auto k128 = [](int ks) { return (uint64_t)((((ks >> 2) * kSlab128) + (ks & 3) * 32) >> 4); };
             auto kin = [](int ks) { return (uint64_t)((ks * 32) >> 4); };
             for (int j = 0; j < nchunks; j++) {
                 const uint32_t ph = j & 1;
+                // S (two-term copy) is ready, the previous chunk's output accumulators have been read out
                 bool ok = mbar_wait(bar(SB_SREADY), ph, abortp) && mbar_wait(bar(SB_WQFULL), ph, abortp);
                 if (!ok) break;
                 tc_fence_after();
                 SC_TR(0);
-                // acc = S W^T, three terms
+                // [acc | O1] = S [W ; Q]^T, three terms
 #pragma unroll
-                for (int ks = 0; ks < 8; ks++) tc_mma_f16_ta(tmem + kTcAcc, tmem + kTcSh + ks * 8, dWh + k64(ks), id64, ks > 0);
+                for (int ks = 0; ks < 8; ks++) tc_mma_f16_ta(tmem + kTcAcc, tmem + kTcSh + ks * 8, dWQh + k128(ks), id128, ks > 0);
 #pragma unroll
-                for (int ks = 0; ks < 8; ks++) tc_mma_f16_ta(tmem + kTcAcc, tmem + kTcSl + ks * 8, dWh + k64(ks), id64, 1);
+                for (int ks = 0; ks < 8; ks++) tc_mma_f16_ta(tmem + kTcAcc, tmem + kTcSl + ks * 8, dWQh + k128(ks), id128, 1);
 #pragma unroll
-                for (int ks = 0; ks < 8; ks++) tc_mma_f16_ta(tmem + kTcAcc, tmem + kTcSh + ks * 8, dWl + k64(ks), id64, 1);
+                for (int ks = 0; ks < 8; ks++) tc_mma_f16_ta(tmem + kTcAcc, tmem + kTcSh + ks * 8, dWQl + k128(ks), id128, 1);
                 tc_commit(bar(SB_DACC));
-                SC_TR(1);
-                // O1 = S Q^T: the output accumulators of the previous chunk must have been read out
-                if (j > 0 && !mbar_wait(bar(SB_OFREE), (j - 1) & 1, abortp)) break;
-                tc_fence_after();
-                SC_TR(2);
-#pragma unroll
-                for (int ks = 0; ks < 8; ks++) tc_mma_f16_ta(tmem + kTcO1, tmem + kTcSh + ks * 8, dQh + k64(ks), id64, ks > 0);
-#pragma unroll
-                for (int ks = 0; ks < 8; ks++) tc_mma_f16_ta(tmem + kTcO1, tmem + kTcSl + ks * 8, dQh + k64(ks), id64, 1);
-#pragma unroll
-                for (int ks = 0; ks < 8; ks++) tc_mma_f16_ta(tmem + kTcO1, tmem + kTcSh + ks * 8, dQl + k64(ks), id64, 1);
                 tc_commit(bar(SB_WEMPTY));
-                SC_TR(3);
-                // O2 = Dt QKm^T and S += Dt Ks^T, three terms each
+                SC_TR(1);
+                // [S | O2] += Dt [Ks ; QKm]^T, three terms (S pre-scaled, O2 zeroed by the state threads)
                 ok = mbar_wait(bar(SB_DFULL), ph, abortp) && mbar_wait(bar(SB_KQKFULL), ph, abortp);
                 if (!ok) break;
                 tc_fence_after();
                 SC_TR(4);
 #pragma unroll
-                for (int ks = 0; ks < 4; ks++) tc_mma_f16_ta(tmem + kTcO2, tmem + kTcDh + ks * 8, dQKh + kin(ks), id64, ks > 0);
+                for (int ks = 0; ks < 4; ks++) tc_mma_f16_ta(tmem + kTcS, tmem + kTcDh + ks * 8, dKQh + kin(ks), id192, 1);
 #pragma unroll
-                for (int ks = 0; ks < 4; ks++) tc_mma_f16_ta(tmem + kTcO2, tmem + kTcDl + ks * 8, dQKh + kin(ks), id64, 1);
+                for (int ks = 0; ks < 4; ks++) tc_mma_f16_ta(tmem + kTcS, tmem + kTcDl + ks * 8, dKQh + kin(ks), id192, 1);
 #pragma unroll
-                for (int ks = 0; ks < 4; ks++) tc_mma_f16_ta(tmem + kTcO2, tmem + kTcDh + ks * 8, dQKl + kin(ks), id64, 1);
-#pragma unroll
-                for (int ks = 0; ks < 4; ks++) tc_mma_f16_ta(tmem + kTcS, tmem + kTcDh + ks * 8, dKh + kin(ks), id128, 1);
-#pragma unroll
-                for (int ks = 0; ks < 4; ks++) tc_mma_f16_ta(tmem + kTcS, tmem + kTcDl + ks * 8, dKh + kin(ks), id128, 1);
-#pragma unroll
-                for (int ks = 0; ks < 4; ks++) tc_mma_f16_ta(tmem + kTcS, tmem + kTcDh + ks * 8, dKl + kin(ks), id128, 1);
+                for (int ks = 0; ks < 4; ks++) tc_mma_f16_ta(tmem + kTcS, tmem + kTcDh + ks * 8, dKQl + kin(ks), id192, 1);
                 tc_commit(bar(SB_CDONE));
                 tc_commit(bar(SB_KEMPTY));
                 SC_TR(5);
@@ -590,6 +577,12 @@ gdn_scan_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                     split2_f16(u[2 * i] - __uint_as_float(a0[2 * i]), u[2 * i + 1] - __uint_as_float(a0[2 * i + 1]), dh[i], dl[i]);
                 tc_st16(tmem + lane_base + kTcDh + h * 16, dh);
                 tc_st16(tmem + lane_base + kTcDl + h * 16, dl);
+                {   // O2 starts from zero (its product accumulates next to S)
+                    uint32_t zz[32];
+#pragma unroll
+                    for (int i = 0; i < 32; i++) zz[i] = 0u;
+                    tc_st32(tmem + lane_base + kTcO2 + h * 32, zz);
+                }
                 tc_wait_st();
                 tc_fence_before();
                 mbar_arrive(bar(SB_DFULL));
@@ -600,6 +593,10 @@ gdn_scan_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             if (!ok) break;
             tc_fence_after();
             if (tid == 0) SC_TR(12);
+            // the output accumulators go to registers first: the next chunk's first product overwrites O1
+            uint32_t o1[32], o2[32];
+            tc_ld32(tmem + lane_base + kTcO1 + h * 32, o1);
+            tc_ld32(tmem + lane_base + kTcO2 + h * 32, o2);
 #pragma unroll 1
             for (int c = 0; c < 64; c += 32) {
                 uint32_t x[32], hi[16], lo[16];
@@ -620,15 +617,8 @@ gdn_scan_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             tc_fence_before();
             mbar_arrive(bar(SB_SREADY));
             if (tid == 0) SC_TR(13);
-            // output rows of this chunk (off the critical path: the next chunk's first products run meanwhile)
+            // output rows of this chunk (off the critical path: the next chunk's first product runs meanwhile)
             {
-                uint32_t o1[32], o2[32];
-                tc_ld32(tmem + lane_base + kTcO1 + h * 32, o1);
-                tc_ld32(tmem + lane_base + kTcO2 + h * 32, o2);
-                tc_wait_ld();
-                tc_fence_before();
-                mbar_arrive(bar(SB_OFREE));  // the accumulators are in registers
-                if (tid == 0) SC_TR(14);
                 float *orow = p.out + (size_t)t0 * total_v + (size_t)vh * kDH + r;
 #pragma unroll
                 for (int i = 0; i < 32; i++) {
