@@ -505,7 +505,7 @@ extern "C" fm_status fm_kv_append_rope(FmCtx *ctx, int fa_idx, const int *seq, c
 // Splits per (KV head, sequence): one CTA per SM is resident (shared memory), so the grid should be
 // as close to the SM count as possible without exceeding it -- a few CTAs over would run as a
 // second, nearly empty wave.
-static int pick_splits(const FmCtx *ctx, int batch, int max_len) {
+static int pick_splits(const FmCtx *ctx, int batch, int max_len, bool exchange = false) {
     const FmConfig &c = ctx->cfg;
     const int units = c.num_kv_heads * batch;
     int want = std::max(1, ctx->sm_count / units);
@@ -518,8 +518,11 @@ static int pick_splits(const FmCtx *ctx, int batch, int max_len) {
         // next layer from starting: a quarter of the width with at least 8 tiles per CTA lets about four
         // layers stream side by side, each hiding the others' prologues and tails (batch 1: 17.6 -> 5.1 us
         // per layer at 4K, 48.9 -> 40.9 at 128K).  Long launches keep the full width.
+        // With the peer exchange in the tail the launches complete in order, and a narrow launch whose CTAs
+        // have to wait for their turn holds its SMs meanwhile: measured at batch 8 x 128K, full width is better
+        // at 57 tiles per CTA (4 GPUs: 91 vs 101 us per layer), a quarter at 29 (8 GPUs: 56 vs 64).
         const int tiles_full = (slots + want - 1) / want;
-        if (tiles_full < 64) want = std::max(1, std::min(want / 4, (slots + 7) / 8));
+        if (tiles_full < (exchange ? 40 : 64)) want = std::max(1, std::min(want / 4, (slots + 7) / 8));
     }
     want = std::min(want, kDecGroup * kDecMaxGroups);
     if (batch > ctx->dec_scr.group_tokens) want = std::min(want, kDecMaxLastCtaSplits);  // no second-level scratch for that many tokens
@@ -992,7 +995,7 @@ static fm_status xchg_push(FmCtx *ctx, const char *fn, int fa_idx, const int *se
     std::vector<int> rows(batch);
     int max_len = 1;
     for (int i = 0; i < batch; i++) max_len = std::max(max_len, ctx->kv_len[lidx(ctx, fa_idx, seq[i])] + (k ? 1 : 0));
-    const int ns = pick_splits(ctx, batch, max_len);
+    const int ns = pick_splits(ctx, batch, max_len, /*exchange=*/true);
     const bool whole = out != nullptr;
     const float *d_g = whole ? sg.in(q_proj_out ? nullptr : gate, batch * qd, &ok) : nullptr;
     size_t w_out = 0;
