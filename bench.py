@@ -397,9 +397,9 @@ def run_ours(args):
 
 
 # DRAM bytes (read + write) of one attn_decode_kernel launch for ONE sequence at 131073 rows, from
-# the committed ncu capture (profiles/attn_decode_kernel_b1_ctx128k_ncu.md): 268.96 MB + 5.49 MB.
+# the committed ncu capture (profiles/attn_decode_kernel_b1_ctx128k_ncu.md): 268.76 MB + 4.43 MB.
 # Traffic grows in proportion to rows x sequences, so the bench launch is scaled from it.
-TRAFFIC_NCU_1SEQ_128K = 274.45e6
+TRAFFIC_NCU_1SEQ_128K = 273.18e6
 
 
 def extra_measurements(pkg, torch, dev, peak, only=None):
