@@ -39,6 +39,7 @@ class FmConfig(C.Structure):
         ("max_seqs", C.c_int), ("max_seq_len", C.c_int), ("page_size", C.c_int),
         ("kv_pool_pages", C.c_int64), ("max_batch_tokens", C.c_int),
         ("seq_shard_rank", C.c_int), ("seq_shard_count", C.c_int), ("device", C.c_int),
+        ("sliding_window", C.c_int),
     ]
 
 

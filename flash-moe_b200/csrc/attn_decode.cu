@@ -138,7 +138,7 @@ attn_decode_kernel(KvView kv, RopeParams rope, TokSpec toks, int H, const float 
 
     int seq, pos, row_new;
     tok_get(toks, tok, seq, pos, row_new);
-    const int L = row_new + 1;  // rows attended, the new one included
+    const int L = tok_rows(toks, tok);  // rows attended, the new one included (row_new + 1 unless the window wrapped)
 
     // ---- which page slots this CTA walks ----
     const int gpages = (L + kPage - 1) / kPage;

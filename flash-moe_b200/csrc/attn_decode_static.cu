@@ -118,6 +118,7 @@ extern "C" fm_status fm_attn_decode_static(const FmStaticDecodeArgs *a, char *er
         t.seq[i] = i;
         t.pos[i] = a->pos[i];
         t.row[i] = a->kv_len[i] - 1;
+        t.nrows[i] = a->kv_len[i];
         max_len = std::max(max_len, a->kv_len[i]);
     }
     // splits: fill the SMs, stay within the pages available and within the fixed scratch

@@ -98,6 +98,8 @@ extern "C" fm_status fm_create(const FmConfig *cfg, FmCtx **out) {
         if (c.rotary_dim < 0 || c.rotary_dim > 128 || c.rotary_dim % 2 != 0 || c.rotary_dim > c.head_dim)
             return fail(nullptr, FM_ERR_UNSUPPORTED, "fm_create: rotary_dim %d (even, <= 128)", c.rotary_dim);
         if (c.max_seq_len < 1) return fail(nullptr, FM_ERR_INVALID, "fm_create: max_seq_len %d", c.max_seq_len);
+        if (c.sliding_window < 0 || c.sliding_window > c.max_seq_len)
+            return fail(nullptr, FM_ERR_INVALID, "fm_create: sliding_window %d (0, or 1..max_seq_len)", c.sliding_window);
     }
     if (has_gdn) {
         if (c.linear_key_dim != 128 || c.linear_value_dim != 128 || c.conv_kernel_size != 4)
@@ -141,7 +143,9 @@ extern "C" fm_status fm_create(const FmConfig *cfg, FmCtx **out) {
         if (c.rope_scaling_mode == 3 && c.rope_scale_factor > 1.0f) yarn = sqrtf(0.1f * logf(c.rope_scale_factor) + 1.0f);
         ctx->rope.logit_scale = (1.0f / sqrtf((float)c.head_dim)) * yarn;
 
-        const int gpages = (c.max_seq_len + c.page_size - 1) / c.page_size;
+        // a sliding window bounds the rows a sequence can hold, whatever max_seq_len says
+        const int max_rows = c.sliding_window > 0 ? std::min(c.max_seq_len, c.sliding_window) : c.max_seq_len;
+        const int gpages = (max_rows + c.page_size - 1) / c.page_size;
         ctx->max_slots = (gpages + c.seq_shard_count - 1) / c.seq_shard_count;
         ctx->page_elems = (size_t)2 * c.num_kv_heads * c.page_size * c.head_dim;
         ctx->pool_pages = c.kv_pool_pages > 0 ? c.kv_pool_pages
@@ -322,10 +326,15 @@ static KvView kv_view(const FmCtx *ctx, int fa_idx) {
 }
 
 // Makes sure the locally-held pages covering rows [0, new_len) of (layer, seq) exist.
+// Rows of the store a sequence occupies after `count` tokens, and the row token number `count` goes to.
+static inline int rows_held(const FmConfig &c, int count) { return c.sliding_window > 0 ? std::min(count, c.sliding_window) : count; }
+static inline int row_of(const FmConfig &c, int count) { return c.sliding_window > 0 ? count % c.sliding_window : count; }
+
 static fm_status ensure_pages(FmCtx *ctx, int fa_idx, int seq, int new_len) {
     const FmConfig &c = ctx->cfg;
-    if (new_len > c.max_seq_len)
+    if (c.sliding_window == 0 && new_len > c.max_seq_len)
         return fail(ctx, FM_ERR_CAPACITY, "KV cache overflow (pos=%d >= cap=%d)", new_len - 1, c.max_seq_len);
+    new_len = rows_held(c, new_len);
     const int gpages = (new_len + c.page_size - 1) / c.page_size;
     const int nslots = gpages > c.seq_shard_rank ? (gpages - c.seq_shard_rank + c.seq_shard_count - 1) / c.seq_shard_count : 0;
     int *tab = &ctx->h_page_table[((size_t)fa_idx * c.max_seqs + seq) * ctx->max_slots];
@@ -439,7 +448,7 @@ static fm_status append_list(FmCtx *ctx, int fa_idx, const int *seq, const int *
         TokSpec t;
         t.mode = 0;
         t.n = std::min(kMaxList, n - i0);
-        for (int i = 0; i < t.n; i++) { t.seq[i] = seq[i0 + i]; t.pos[i] = pos[i0 + i]; t.row[i] = rows[i0 + i]; }
+        for (int i = 0; i < t.n; i++) { t.seq[i] = seq[i0 + i]; t.pos[i] = pos[i0 + i]; t.row[i] = rows[i0 + i]; t.nrows[i] = rows[i0 + i] + 1; }
         fm_status st = launched(ctx, launch_kv_append(kv, ctx->rope, t, k + i0 * kv_dim, v + i0 * kv_dim, knw, ctx->cfg.rms_norm_eps, ctx->stream), "kv_append");
         if (st) return st;
     }
@@ -447,21 +456,25 @@ static fm_status append_list(FmCtx *ctx, int fa_idx, const int *seq, const int *
 }
 
 // Reserves rows for n tokens (token i goes to sequence seq[i]); fills rows[]. All-or-nothing.
-static fm_status reserve_rows(FmCtx *ctx, int fa_idx, const int *seq, int n, std::vector<int> &rows) {
+// With a sliding window the row is the token count modulo the window and nothing ever overflows.
+static fm_status reserve_rows(FmCtx *ctx, int fa_idx, const int *seq, int n, std::vector<int> &rows, std::vector<int> *nrows = nullptr) {
     const FmConfig &c = ctx->cfg;
     rows.resize(n);
+    if (nrows) nrows->resize(n);
     std::vector<int> add(c.max_seqs, 0);
     for (int i = 0; i < n; i++) {
-        rows[i] = ctx->kv_len[lidx(ctx, fa_idx, seq[i])] + add[seq[i]];
+        const int count = ctx->kv_len[lidx(ctx, fa_idx, seq[i])] + add[seq[i]];
         add[seq[i]]++;
-        if (rows[i] >= c.max_seq_len)
-            return fail(ctx, FM_ERR_CAPACITY, "KV cache overflow (pos=%d >= cap=%d)", rows[i], c.max_seq_len);
+        if (c.sliding_window == 0 && count >= c.max_seq_len)
+            return fail(ctx, FM_ERR_CAPACITY, "KV cache overflow (pos=%d >= cap=%d)", count, c.max_seq_len);
+        rows[i] = row_of(c, count);
+        if (nrows) (*nrows)[i] = rows_held(c, count + 1);
     }
     // page demand check before touching anything
     size_t need = 0;
     for (int s = 0; s < c.max_seqs; s++) {
         if (!add[s]) continue;
-        const int new_len = ctx->kv_len[lidx(ctx, fa_idx, s)] + add[s];
+        const int new_len = rows_held(c, ctx->kv_len[lidx(ctx, fa_idx, s)] + add[s]);
         const int gpages = (new_len + c.page_size - 1) / c.page_size;
         const int nslots = gpages > c.seq_shard_rank ? (gpages - c.seq_shard_rank + c.seq_shard_count - 1) / c.seq_shard_count : 0;
         const int *tab = &ctx->h_page_table[((size_t)fa_idx * c.max_seqs + s) * ctx->max_slots];
@@ -556,14 +569,16 @@ static fm_status decode_core(FmCtx *ctx, int fa_idx, const int *seq, const int *
                              float *o_part, float *ml_part) {
     const FmConfig &c = ctx->cfg;
     const int H = c.num_attn_heads, D = c.head_dim;
-    std::vector<int> rows(batch);
+    std::vector<int> rows(batch), nrows(batch);
     if (k != nullptr) {
-        fm_status st = reserve_rows(ctx, fa_idx, seq, batch, rows);  // pages and lengths; the kernel writes the rows
+        fm_status st = reserve_rows(ctx, fa_idx, seq, batch, rows, &nrows);  // pages and lengths; the kernel writes the rows
         if (st) return st;
     } else {
         for (int i = 0; i < batch; i++) {
-            rows[i] = ctx->kv_len[lidx(ctx, fa_idx, seq[i])] - 1;
-            if (rows[i] < 0) return fail(ctx, FM_ERR_INVALID, "fm_attn_decode: sequence %d is empty and no k/v given", seq[i]);
+            const int count = ctx->kv_len[lidx(ctx, fa_idx, seq[i])];
+            if (count < 1) return fail(ctx, FM_ERR_INVALID, "fm_attn_decode: sequence %d is empty and no k/v given", seq[i]);
+            rows[i] = row_of(c, count - 1);
+            nrows[i] = rows_held(c, count);
         }
     }
     const KvView kv = kv_view(ctx, fa_idx);
@@ -574,8 +589,8 @@ static fm_status decode_core(FmCtx *ctx, int fa_idx, const int *seq, const int *
         t.n = std::min(kMaxList, batch - i0);
         int max_len = 1;
         for (int i = 0; i < t.n; i++) {
-            t.seq[i] = seq[i0 + i]; t.pos[i] = pos[i0 + i]; t.row[i] = rows[i0 + i];
-            max_len = std::max(max_len, rows[i0 + i] + 1);
+            t.seq[i] = seq[i0 + i]; t.pos[i] = pos[i0 + i]; t.row[i] = rows[i0 + i]; t.nrows[i] = nrows[i0 + i];
+            max_len = std::max(max_len, nrows[i0 + i]);
         }
         const int ns = pick_splits(ctx, t.n, max_len);
         const float *qp = q_proj_out ? q_proj_out + (size_t)i0 * H * 2 * D : nullptr;
@@ -700,6 +715,8 @@ extern "C" fm_status fm_attn_prefill(FmCtx *ctx, int fa_idx, int seq, int start_
     float *d_out = sg.out(out, n * qd, &ok, &w_out);
     if (!ok) return fail(ctx, FM_ERR_INVALID, "fm_attn_prefill: staging buffer too small");
     const int row0 = ctx->kv_len[lidx(ctx, fa_idx, seq)];
+    if (c.sliding_window > 0 && row0 + n > c.sliding_window)
+        return fail(ctx, FM_ERR_UNSUPPORTED, "fm_attn_prefill: the run would wrap the sliding window (%d + %d > %d); feed it through fm_attn_decode", row0, n, c.sliding_window);
     if (row0 + n > c.max_seq_len) return fail(ctx, FM_ERR_CAPACITY, "KV cache overflow (pos=%d >= cap=%d)", row0 + n - 1, c.max_seq_len);
     fm_status st = ensure_pages(ctx, fa_idx, seq, row0 + n);
     if (st) return st;
@@ -817,7 +834,7 @@ extern "C" fm_status fm_kv_export(FmCtx *ctx, int fa_idx, int seq, float *k, flo
     const FmConfig &c = ctx->cfg;
     if (fa_idx < 0 || fa_idx >= c.num_full_layers || seq < 0 || seq >= c.max_seqs || !k || !v)
         return fail(ctx, FM_ERR_INVALID, "fm_kv_export: bad argument");
-    const int len = ctx->kv_len[lidx(ctx, fa_idx, seq)];
+    const int len = rows_held(c, ctx->kv_len[lidx(ctx, fa_idx, seq)]);  // rows in store order (a wrapped window is not unrolled)
     if (len_out) *len_out = len;
     if (len > max_rows) return fail(ctx, FM_ERR_INVALID, "fm_kv_export: %d rows held, room for %d", len, max_rows);
     if (len == 0) return FM_OK;
@@ -847,6 +864,8 @@ extern "C" fm_status fm_kv_import(FmCtx *ctx, int fa_idx, int seq, const float *
     if (fa_idx < 0 || fa_idx >= c.num_full_layers || seq < 0 || seq >= c.max_seqs || len < 0 || (len > 0 && (!k || !v)))
         return fail(ctx, FM_ERR_INVALID, "fm_kv_import: bad argument");
     if (len > c.max_seq_len) return fail(ctx, FM_ERR_CAPACITY, "KV cache overflow (pos=%d >= cap=%d)", len - 1, c.max_seq_len);
+    if (c.sliding_window > 0 && len > c.sliding_window)
+        return fail(ctx, FM_ERR_INVALID, "fm_kv_import: %d rows do not fit the sliding window of %d", len, c.sliding_window);
     FM_CUDA(ctx, cudaSetDevice(c.device));
     // drop pages beyond the new length, then make sure the needed ones exist
     {
@@ -992,9 +1011,9 @@ static fm_status xchg_push(FmCtx *ctx, const char *fn, int fa_idx, const int *se
     const float *d_q = sg.in(q_proj_out ? nullptr : q, batch * qd, &ok);
     const float *d_k = sg.in(k, batch * kvd, &ok), *d_v = sg.in(v, batch * kvd, &ok);
     const uint16_t *d_qn = sg.in(q_norm_w, (size_t)D, &ok), *d_kn = sg.in(k_norm_w, (size_t)D, &ok);
-    std::vector<int> rows(batch);
+    std::vector<int> rows(batch), nrows(batch);
     int max_len = 1;
-    for (int i = 0; i < batch; i++) max_len = std::max(max_len, ctx->kv_len[lidx(ctx, fa_idx, seq[i])] + (k ? 1 : 0));
+    for (int i = 0; i < batch; i++) max_len = std::max(max_len, rows_held(c, ctx->kv_len[lidx(ctx, fa_idx, seq[i])] + (k ? 1 : 0)));
     const int ns = pick_splits(ctx, batch, max_len, /*exchange=*/true);
     const bool whole = out != nullptr;
     const float *d_g = whole ? sg.in(q_proj_out ? nullptr : gate, batch * qd, &ok) : nullptr;
@@ -1002,19 +1021,21 @@ static fm_status xchg_push(FmCtx *ctx, const char *fn, int fa_idx, const int *se
     float *d_out = whole ? sg.out(out, batch * qd, &ok, &w_out) : nullptr;
     if (!ok) return fail(ctx, FM_ERR_INVALID, "%s: staging buffer too small", fn);
     if (k != nullptr) {
-        st = reserve_rows(ctx, fa_idx, seq, batch, rows);
+        st = reserve_rows(ctx, fa_idx, seq, batch, rows, &nrows);
         if (st) return st;
     } else {
         for (int i = 0; i < batch; i++) {
-            rows[i] = ctx->kv_len[lidx(ctx, fa_idx, seq[i])] - 1;
-            if (rows[i] < 0) return fail(ctx, FM_ERR_INVALID, "%s: sequence %d is empty and no k/v given", fn, seq[i]);
+            const int count = ctx->kv_len[lidx(ctx, fa_idx, seq[i])];
+            if (count < 1) return fail(ctx, FM_ERR_INVALID, "%s: sequence %d is empty and no k/v given", fn, seq[i]);
+            rows[i] = row_of(c, count - 1);
+            nrows[i] = rows_held(c, count);
         }
     }
     FM_CUDA(ctx, sg.push());
     TokSpec t;
     t.mode = 0;
     t.n = batch;
-    for (int i = 0; i < batch; i++) { t.seq[i] = seq[i]; t.pos[i] = pos[i]; t.row[i] = rows[i]; }
+    for (int i = 0; i < batch; i++) { t.seq[i] = seq[i]; t.pos[i] = pos[i]; t.row[i] = rows[i]; t.nrows[i] = nrows[i]; }
     ctx->xchg_step++;
     {
         // one launch: append, split-KV attention, merge of the splits, rows into every peer's buffer; then either the

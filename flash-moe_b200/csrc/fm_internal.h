@@ -20,6 +20,7 @@ struct TokSpec {
     int n;
     int seq0, pos0, row0;  // mode 1: token t has pos0 + t, cache row row0 + t
     int seq[kMaxList], pos[kMaxList], row[kMaxList];
+    int nrows[kMaxList];   // mode 0: cache rows the token attends to (row + 1, or the window once it has wrapped)
 };
 
 __host__ __device__ inline void tok_get(const TokSpec &t, int i, int &seq, int &pos, int &row) {
@@ -29,6 +30,8 @@ __host__ __device__ inline void tok_get(const TokSpec &t, int i, int &seq, int &
         seq = t.seq[i]; pos = t.pos[i]; row = t.row[i];
     }
 }
+
+__host__ __device__ inline int tok_rows(const TokSpec &t, int i) { return t.mode == 1 ? t.row0 + i + 1 : t.nrows[i]; }
 
 // The paged bf16 KV store of one layer as a kernel sees it.
 // Page layout: [2 (K,V)][Hkv][page_size][D] bf16, so one (K or V, head) tile is contiguous.

@@ -84,6 +84,11 @@ typedef struct FmConfig {
     int seq_shard_rank;      /* 0 */
     int seq_shard_count;     /* 1 */
     int device;              /* CUDA device ordinal */
+    /* long-context policy of the KV store (decode): 0 = keep every position; W > 0 = sliding window,
+     * the store of a sequence is a circular buffer of W rows -- the token count keeps growing, row
+     * count % W is overwritten, attention sees the last min(count, W) tokens
+     * (g_sliding_window / KVCache.window_size: layer_forward.h:130-131,148-161,600-601,649-650,673-677) */
+    int sliding_window;
 } FmConfig;
 
 typedef struct FmCtx FmCtx;

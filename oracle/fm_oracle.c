@@ -113,7 +113,10 @@ int fmo_attn_step(const FmoDims *d, float *k_cache, float *v_cache, int *len, in
                   int threads) {
     const int H = d->num_attn_heads, Hkv = d->num_kv_heads, D = d->head_dim;
     const int q_dim = H * D, kv_dim = Hkv * D;
-    if (*len >= capacity) return -1; /* metal_infer/layer_forward.h:603-607 */
+    const int W = d->sliding_window;
+    if (W > 0 && capacity != W) return -1;        /* metal_infer/layer_forward.h:154-161 */
+    if (W == 0 && *len >= capacity) return -1;     /* metal_infer/layer_forward.h:603-607 */
+    const int cache_pos = W > 0 ? *len % capacity : *len; /* :600-601 circular write */
 
     float *q = malloc((size_t)q_dim * sizeof(float));
     float *k = malloc((size_t)kv_dim * sizeof(float));
@@ -127,17 +130,20 @@ int fmo_attn_step(const FmoDims *d, float *k_cache, float *v_cache, int *len, in
 
     /* append, then attend over the cache including the new row
        (metal_infer/layer_forward.h:591-646) */
-    memcpy(k_cache + (size_t)*len * kv_dim, k, (size_t)kv_dim * sizeof(float));
-    memcpy(v_cache + (size_t)*len * kv_dim, v_in, (size_t)kv_dim * sizeof(float));
+    memcpy(k_cache + (size_t)cache_pos * kv_dim, k, (size_t)kv_dim * sizeof(float));
+    memcpy(v_cache + (size_t)cache_pos * kv_dim, v_in, (size_t)kv_dim * sizeof(float));
     if (d->store_bf16) {
-        float *kr = k_cache + (size_t)*len * kv_dim, *vr = v_cache + (size_t)*len * kv_dim;
+        float *kr = k_cache + (size_t)cache_pos * kv_dim, *vr = v_cache + (size_t)cache_pos * kv_dim;
         for (int i = 0; i < kv_dim; i++) {
             kr[i] = round_bf16f(kr[i]);
             vr[i] = round_bf16f(vr[i]);
         }
     }
     *len += 1;
-    const int L = *len;
+    /* rows attended and where row i of the window lives (metal_infer/layer_forward.h:649-650, 673-677) */
+    const int wrapped = W > 0 && *len > W;
+    const int L = wrapped ? W : *len;
+    const int first = wrapped ? *len - W : 0;
     const int group = H / Hkv;
     const float scale = (1.0f / sqrtf((float)D)) * yarn_logit_factor(d);
 
@@ -149,7 +155,8 @@ int fmo_attn_step(const FmoDims *d, float *k_cache, float *v_cache, int *len, in
         const float *qh = q + (size_t)h * D;
         float *s = malloc((size_t)L * sizeof(float));
         for (int i = 0; i < L; i++) {
-            const float *kp = k_cache + (size_t)i * kv_dim + (size_t)kvh * D;
+            const int p = wrapped ? (first + i) % capacity : i;
+            const float *kp = k_cache + (size_t)p * kv_dim + (size_t)kvh * D;
             float dot = 0.0f;
             for (int e = 0; e < D; e++) dot += qh[e] * kp[e];
             s[i] = dot * scale;
@@ -157,7 +164,8 @@ int fmo_attn_step(const FmoDims *d, float *k_cache, float *v_cache, int *len, in
         softmax_inplace(s, L);
         float *oh = out + (size_t)h * D;
         for (int i = 0; i < L; i++) {
-            const float *vp = v_cache + (size_t)i * kv_dim + (size_t)kvh * D;
+            const int p = wrapped ? (first + i) % capacity : i;
+            const float *vp = v_cache + (size_t)p * kv_dim + (size_t)kvh * D;
             for (int e = 0; e < D; e++) oh[e] += s[i] * vp[e];
         }
         free(s);

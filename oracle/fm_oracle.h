@@ -39,6 +39,9 @@ typedef struct {
     int store_bf16;          /* restatement only (the reference harness ignores it): round the
                                 normalised, rotated k and the v to bf16 (nearest even) before the
                                 append, i.e. reference arithmetic on top of a bf16 KV store */
+    int sliding_window;      /* 0 unlimited; > 0: the cache is a circular buffer of that many rows
+                                (capacity must equal it), metal_infer/layer_forward.h:130-161,600-601,
+                                649-650,673-677; *len keeps counting every appended token */
 } FmoDims;
 
 #define FMO_API(prefix)                                                                         \

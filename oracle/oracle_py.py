@@ -23,7 +23,7 @@ class FmoDims(C.Structure):
         ("rope_scaling_mode", C.c_int), ("rope_scale_factor", C.c_float), ("max_seq_len", C.c_int),
         ("linear_num_v_heads", C.c_int), ("linear_num_k_heads", C.c_int),
         ("linear_key_dim", C.c_int), ("linear_value_dim", C.c_int), ("conv_kernel_size", C.c_int),
-        ("store_bf16", C.c_int),
+        ("store_bf16", C.c_int), ("sliding_window", C.c_int),
     ]
 
 
@@ -31,7 +31,7 @@ def make_dims(**kw) -> FmoDims:
     d = dict(num_attn_heads=32, num_kv_heads=2, head_dim=256, rotary_dim=64, rope_theta=1e7,
              rms_norm_eps=1e-6, rope_scaling_mode=0, rope_scale_factor=1.0, max_seq_len=262144,
              linear_num_v_heads=64, linear_num_k_heads=16, linear_key_dim=128,
-             linear_value_dim=128, conv_kernel_size=4, store_bf16=0)
+             linear_value_dim=128, conv_kernel_size=4, store_bf16=0, sliding_window=0)
     d.update(kw)
     return FmoDims(**d)
 

@@ -124,6 +124,8 @@ int fmr_attn_step(const FmoDims *d, float *k_cache, float *v_cache, int *len, in
     kv.v_cache = v_cache;
     kv.len = *len;
     kv.capacity = capacity;
+    kv.window_size = d->sliding_window; /* as kv_cache_new() sets it from g_sliding_window */
+    if (kv.window_size > 0 && capacity != kv.window_size) return -1;
     g_tensors.q_norm = q_norm_w;
     g_tensors.k_norm = k_norm_w;
     /* the body normalises / rotates q and k in place: work on copies */

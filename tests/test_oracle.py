@@ -144,3 +144,32 @@ def test_first_token_attends_to_itself_only(port):
     want = np.tile(v, (1, 2)) * (1.0 / (1.0 + np.exp(-g)))
     assert ln == 1
     np.testing.assert_allclose(out, want, rtol=1e-6, atol=1e-7)
+
+
+@pytest.mark.parametrize("window", [5, 37])
+def test_port_equals_reference_sliding_window(port, ref, synth, window):
+    """Circular KV cache of `window` rows (metal_infer/layer_forward.h:600-601, 649-650, 673-677): 3 * window
+    steps from an empty cache wrap the buffer twice; restatement and reference agree bit for bit, and once
+    wrapped the output equals plain attention over the last `window` tokens."""
+    heads, kvh, D = 8, 2, 256
+    steps = 3 * window
+    dims = make_dims(num_attn_heads=heads, num_kv_heads=kvh, sliding_window=window)
+    q, g, k, v = synth.attn_step_inputs(21, steps, heads=heads, kv_heads=kvh)
+    res = []
+    for orc in (port, ref):
+        kc = np.zeros((window, kvh * D), np.float32); vc = np.zeros_like(kc)
+        out, ln = orc.attn_run(dims, kc, vc, 0, q, g, k, v, threads=2)
+        assert ln == steps
+        res.append((out, kc, vc))
+    np.testing.assert_array_equal(res[0][0], res[1][0])
+    np.testing.assert_array_equal(res[0][1], res[1][1])
+    # last step against an unbounded cache that holds only the last `window` tokens (already rotated rows
+    # are position-independent, so they can be replayed as a prefix)
+    plain = make_dims(num_attn_heads=heads, num_kv_heads=kvh)
+    kc = np.zeros((steps, kvh * D), np.float32); vc = np.zeros_like(kc)
+    full, _ = port.attn_run(plain, kc, vc, 0, q, g, k, v)
+    k_last, v_last = kc[steps - window:steps - 1].copy(), vc[steps - window:steps - 1].copy()
+    kc2 = np.zeros((window, kvh * D), np.float32); vc2 = np.zeros_like(kc2)
+    kc2[:window - 1] = k_last; vc2[:window - 1] = v_last
+    last, _ = port.attn_run(plain, kc2, vc2, window - 1, q[-1:], g[-1:], k[-1:], v[-1:], start_pos=steps - 1)
+    np.testing.assert_allclose(res[0][0][-1], last[0], rtol=2e-5, atol=2e-6)
