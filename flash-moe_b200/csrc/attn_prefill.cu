@@ -456,26 +456,27 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             mbar_arrive(bar(BAR_PFULL));
             if (tid == 0) PF_TR(3);
         }
-        // epilogue
+        // epilogue: the first two chunks of the gate row are requested before the wait for the last P V
+        const int t_row = t0 + r;
+        const bool live = t_row < p.n;
+        const float4 *gp = reinterpret_cast<const float4 *>(
+            p.q_proj_out ? p.q_proj_out + ((size_t)(live ? t_row : 0) * p.H + head) * 2 * kHD + kHD
+                         : p.gate + ((size_t)(live ? t_row : 0) * p.H + head) * kHD);
+        float4 gn[8], gn2[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) { gn[i] = __ldg(gp + i); gn2[i] = __ldg(gp + 8 + i); }
         if (ok && ntiles > 0) ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_PVDONE), (ntiles - 1) & 1, abortp));
         PF_CTA(2);
         if (ok) {
             // All MMAs have completed, so every K / V / q tile in shared memory is dead.  Each thread
             // gates its own row in registers -- the gate row comes straight from global memory through
-            // read-only 16-byte loads, one chunk ahead -- and parks the result in shared memory at a
+            // read-only 16-byte loads, two chunks ahead -- and parks the result in shared memory at a
             // pitch of 1040 bytes (conflict-free 128-bit stores, rows still contiguous); every row then
             // leaves through one 1 KB bulk asynchronous copy.
             tc_fence_after();
             constexpr uint32_t kPitch = 1040;
             const float inv = l_sum > 0.f ? 1.0f / l_sum : 0.f;
-            const int t = t0 + r;
-            const bool live = t < p.n;
-            const float4 *gp = reinterpret_cast<const float4 *>(
-                p.q_proj_out ? p.q_proj_out + ((size_t)(live ? t : 0) * p.H + head) * 2 * kHD + kHD
-                             : p.gate + ((size_t)(live ? t : 0) * p.H + head) * kHD);
-            float4 gn[8];
-#pragma unroll
-            for (int i = 0; i < 8; i++) gn[i] = __ldg(gp + i);
+            const int t = t_row;
             PF_CTA(4);
 #pragma unroll 1
             for (int c = 0; c < kHD; c += 32) {
@@ -483,10 +484,10 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 tc_ld32(tmem + lane_base + kColO + c, o);
                 float4 g[8];
 #pragma unroll
-                for (int i = 0; i < 8; i++) g[i] = gn[i];
-                if (c + 32 < kHD) {
+                for (int i = 0; i < 8; i++) { g[i] = gn[i]; gn[i] = gn2[i]; }
+                if (c + 64 < kHD) {  // two chunks ahead
 #pragma unroll
-                    for (int i = 0; i < 8; i++) gn[i] = __ldg(gp + ((c + 32) >> 2) + i);
+                    for (int i = 0; i < 8; i++) gn2[i] = __ldg(gp + ((c + 64) >> 2) + i);
                 }
                 tc_wait_ld();
 #pragma unroll
