@@ -18,7 +18,7 @@ FM_PTR_DEVICE, FM_PTR_HOST = 0, 1
 
 EXPORTS = [
     "fm_default_config", "fm_create", "fm_destroy", "fm_last_error", "fm_set_stream",
-    "fm_set_pointer_mode", "fm_synchronize", "fm_reset", "fm_kv_len", "fm_kv_append_rope",
+    "fm_set_pointer_mode", "fm_synchronize", "fm_reset", "fm_seq_fork", "fm_kv_free_pages", "fm_kv_len", "fm_kv_append_rope",
     "fm_attn_decode", "fm_attn_decode_partial", "fm_attn_merge_gate", "fm_attn_prefill",
     "fm_gdn_decode", "fm_gdn_prefill", "fm_kv_export", "fm_kv_import", "fm_state_export",
     "fm_state_import", "fm_launch_count", "fm_profile_enable", "fm_profile_read",
@@ -70,6 +70,8 @@ def load_library() -> C.CDLL:
     lib.fm_last_error.argtypes = [C.c_void_p]
     lib.fm_launch_count.restype = C.c_int64
     lib.fm_launch_count.argtypes = [C.c_void_p]
+    lib.fm_kv_free_pages.restype = C.c_int64
+    lib.fm_kv_free_pages.argtypes = [C.c_void_p]
     lib.fm_destroy.restype = None
     lib.fm_destroy.argtypes = [C.c_void_p]
     lib.fm_default_config.restype = None
@@ -150,6 +152,12 @@ class Context:
 
     def reset(self, seq: int = -1):
         self._check(self.lib.fm_reset(self.h, C.c_int(seq)))
+
+    def seq_fork(self, src: int, dst: int):
+        self._check(self.lib.fm_seq_fork(self.h, C.c_int(src), C.c_int(dst)))
+
+    def kv_free_pages(self) -> int:
+        return self.lib.fm_kv_free_pages(self.h)
 
     def kv_len(self, fa_idx: int, seq: int = 0) -> int:
         return self.lib.fm_kv_len(self.h, C.c_int(fa_idx), C.c_int(seq))

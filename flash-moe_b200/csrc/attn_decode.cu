@@ -636,11 +636,10 @@ attn_decode_kernel(KvView kv, RopeParams rope, TokSpec toks, int H, const float 
 int launch_attn_decode(const KvView &kv, const RopeParams &rope, const TokSpec &toks, int H,
                        const float *q_proj_out, const float *q, const uint16_t *q_norm_w, float eps,
                        float *part_o, float *part_ml, int nsplits, cudaStream_t st) {
-    static bool configured = false;
-    if (!configured) {
+    static unsigned long long configured = 0;  // one bit per device
+    if (first_use_on_device(&configured)) {
         if (cudaFuncSetAttribute(attn_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmem) != cudaSuccess)
             return -1;
-        configured = true;
     }
     dim3 grid(nsplits, kv.Hkv, toks.n);
     DecodeFused f = {};
@@ -656,11 +655,10 @@ int launch_attn_decode_fused(const KvView &kv, const RopeParams &rope, const Tok
                              const uint16_t *k_norm_w, int tail, const float *gate, float *out, float *ml_out,
                              const XchgView *x, uint32_t step, const DecodeScratch &scr, int *err, bool overlap_prev,
                              cudaStream_t st) {
-    static bool configured = false;
-    if (!configured) {
+    static unsigned long long configured = 0;  // one bit per device
+    if (first_use_on_device(&configured)) {
         if (cudaFuncSetAttribute(attn_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmem) != cudaSuccess)
             return -1;
-        configured = true;
     }
     if (nsplits > kDecMaxLastCtaSplits && (toks.n > scr.group_tokens || nsplits > kDecGroup * kDecMaxGroups)) return -1;
     dim3 grid(nsplits, kv.Hkv, toks.n);

@@ -541,10 +541,9 @@ int launch_attn_prefill(const KvView &kv, const RopeParams &rope, int seq, int s
                         const float *q_proj_out, const float *q, const float *gate, const float *k, const float *v,
                         const uint16_t *q_norm_w, const uint16_t *k_norm_w, float eps, const PrefillWork &wk, float *out,
                         cudaStream_t st) {
-    static bool configured = false;
-    if (!configured) {
+    static unsigned long long configured = 0;  // one bit per device
+    if (first_use_on_device(&configured)) {
         if (cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmem) != cudaSuccess) return -1;
-        configured = true;
     }
     const int L = row0 + n;
     CUtensorMap mq, mk, mv;

@@ -159,6 +159,7 @@ extern "C" fm_status fm_create(const FmConfig *cfg, FmCtx **out) {
         CREATE_CUDA(cudaMemset(ctx->d_page_table, 0, nent * sizeof(int)));
         ctx->free_pages.resize((size_t)ctx->pool_pages);
         for (int64_t i = 0; i < ctx->pool_pages; i++) ctx->free_pages[(size_t)i] = (int)(ctx->pool_pages - 1 - i);
+        ctx->page_refs.assign((size_t)ctx->pool_pages, 0);
         ctx->kv_len.assign((size_t)c.num_full_layers * c.max_seqs, 0);
 
         // Split partials: at most ~2 CTAs per SM plus one per (KV head, sequence), 16 head rows each.  Every layer
@@ -326,6 +327,17 @@ static KvView kv_view(const FmCtx *ctx, int fa_idx) {
 }
 
 // Makes sure the locally-held pages covering rows [0, new_len) of (layer, seq) exist.
+// Pages are reference-counted: a forked sequence shares the full pages of its source.
+static inline int take_page(FmCtx *ctx) {
+    const int p = ctx->free_pages.back();
+    ctx->free_pages.pop_back();
+    ctx->page_refs[(size_t)p] = 1;
+    return p;
+}
+static inline void release_page(FmCtx *ctx, int p) {
+    if (--ctx->page_refs[(size_t)p] == 0) ctx->free_pages.push_back(p);
+}
+
 // Rows of the store a sequence occupies after `count` tokens, and the row token number `count` goes to.
 static inline int rows_held(const FmConfig &c, int count) { return c.sliding_window > 0 ? std::min(count, c.sliding_window) : count; }
 static inline int row_of(const FmConfig &c, int count) { return c.sliding_window > 0 ? count % c.sliding_window : count; }
@@ -345,7 +357,7 @@ static fm_status ensure_pages(FmCtx *ctx, int fa_idx, int seq, int new_len) {
     if ((size_t)need > ctx->free_pages.size())
         return fail(ctx, FM_ERR_CAPACITY, "KV page pool exhausted (%d more pages needed, %zu free)", need, ctx->free_pages.size());
     for (int s = first_new; s < nslots; s++)
-        if (tab[s] < 0) { tab[s] = ctx->free_pages.back(); ctx->free_pages.pop_back(); }
+        if (tab[s] < 0) tab[s] = take_page(ctx);
     int *dtab = ctx->d_page_table + ((size_t)fa_idx * c.max_seqs + seq) * ctx->max_slots;
     // pageable-source copies are staged by the runtime before the call returns, so `tab` may change later
     FM_CUDA(ctx, cudaMemcpyAsync(dtab + first_new, tab + first_new, (size_t)(nslots - first_new) * sizeof(int),
@@ -368,7 +380,7 @@ extern "C" fm_status fm_reset(FmCtx *ctx, int seq) {
         for (int s = s0; s < s1; s++) {
             int *tab = &ctx->h_page_table[((size_t)l * c.max_seqs + s) * ctx->max_slots];
             for (int i = 0; i < ctx->max_slots; i++)
-                if (tab[i] >= 0) { ctx->free_pages.push_back(tab[i]); tab[i] = -1; }
+                if (tab[i] >= 0) { release_page(ctx, tab[i]); tab[i] = -1; }
             ctx->kv_len[lidx(ctx, l, s)] = 0;
         }
     for (int l = 0; l < c.num_linear_layers; l++)
@@ -379,6 +391,62 @@ extern "C" fm_status fm_reset(FmCtx *ctx, int seq) {
             FM_CUDA(ctx, cudaMemsetAsync(ctx->d_ssm_state + lidx(ctx, l, s) * sn, 0, sn * sizeof(float), ctx->stream));
             ctx->gdn_steps[lidx(ctx, l, s)] = 0;
         }
+    return FM_OK;
+}
+
+extern "C" int64_t fm_kv_free_pages(const FmCtx *ctx) { return ctx ? (int64_t)ctx->free_pages.size() : -1; }
+
+// dst becomes a copy of src without copying what cannot change: the full pages of src are shared by
+// reference (appends never touch a full page), the partly filled last page and the recurrent state are
+// copied.  Work is ordered on the context's stream.
+extern "C" fm_status fm_seq_fork(FmCtx *ctx, int src, int dst) {
+    if (!ctx) return FM_ERR_INVALID;
+    const FmConfig &c = ctx->cfg;
+    if (src < 0 || src >= c.max_seqs || dst < 0 || dst >= c.max_seqs || src == dst)
+        return fail(ctx, FM_ERR_INVALID, "fm_seq_fork: sequences %d -> %d of %d", src, dst, c.max_seqs);
+    if (c.sliding_window > 0 && c.num_full_layers > 0)
+        return fail(ctx, FM_ERR_UNSUPPORTED, "fm_seq_fork: pages of a sliding-window store are rewritten in place and cannot be shared");
+    fm_status st = fm_reset(ctx, dst);
+    if (st) return st;
+    // pages to copy: one per layer whose last local page is partly filled
+    size_t need = 0;
+    for (int l = 0; l < c.num_full_layers; l++) {
+        const int len = ctx->kv_len[lidx(ctx, l, src)];
+        const int gp = len / c.page_size;  // the partly filled global page, if any
+        if (len % c.page_size != 0 && gp % c.seq_shard_count == c.seq_shard_rank) need++;
+    }
+    if (need > ctx->free_pages.size())
+        return fail(ctx, FM_ERR_CAPACITY, "KV page pool exhausted (%zu more pages needed, %zu free)", need, ctx->free_pages.size());
+    const size_t page_bytes = ctx->page_elems * sizeof(__nv_bfloat16);
+    for (int l = 0; l < c.num_full_layers; l++) {
+        const int len = ctx->kv_len[lidx(ctx, l, src)];
+        int *stab = &ctx->h_page_table[((size_t)l * c.max_seqs + src) * ctx->max_slots];
+        int *dtab = &ctx->h_page_table[((size_t)l * c.max_seqs + dst) * ctx->max_slots];
+        for (int s = 0; s < ctx->max_slots; s++) {
+            if (stab[s] < 0) continue;
+            const int gp = s * c.seq_shard_count + c.seq_shard_rank;
+            if ((gp + 1) * c.page_size <= len) {
+                dtab[s] = stab[s];
+                ctx->page_refs[(size_t)stab[s]]++;
+            } else if (gp * c.page_size < len) {
+                dtab[s] = take_page(ctx);
+                FM_CUDA(ctx, cudaMemcpyAsync(ctx->pool + (size_t)dtab[s] * ctx->page_elems, ctx->pool + (size_t)stab[s] * ctx->page_elems,
+                                             page_bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+            }
+        }
+        FM_CUDA(ctx, cudaMemcpyAsync(ctx->d_page_table + ((size_t)l * c.max_seqs + dst) * ctx->max_slots, dtab,
+                                     (size_t)ctx->max_slots * sizeof(int), cudaMemcpyHostToDevice, ctx->stream));
+        ctx->kv_len[lidx(ctx, l, dst)] = len;
+    }
+    const size_t cn = (size_t)c.conv_kernel_size * ctx->conv_dim;
+    const size_t sn = (size_t)c.linear_num_v_heads * c.linear_value_dim * c.linear_key_dim;
+    for (int l = 0; l < c.num_linear_layers; l++) {
+        FM_CUDA(ctx, cudaMemcpyAsync(ctx->d_conv_state + lidx(ctx, l, dst) * cn, ctx->d_conv_state + lidx(ctx, l, src) * cn,
+                                     cn * sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream));
+        FM_CUDA(ctx, cudaMemcpyAsync(ctx->d_ssm_state + lidx(ctx, l, dst) * sn, ctx->d_ssm_state + lidx(ctx, l, src) * sn,
+                                     sn * sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream));
+        ctx->gdn_steps[lidx(ctx, l, dst)] = ctx->gdn_steps[lidx(ctx, l, src)];
+    }
     return FM_OK;
 }
 
@@ -867,13 +935,11 @@ extern "C" fm_status fm_kv_import(FmCtx *ctx, int fa_idx, int seq, const float *
     if (c.sliding_window > 0 && len > c.sliding_window)
         return fail(ctx, FM_ERR_INVALID, "fm_kv_import: %d rows do not fit the sliding window of %d", len, c.sliding_window);
     FM_CUDA(ctx, cudaSetDevice(c.device));
-    // drop pages beyond the new length, then make sure the needed ones exist
+    // drop the sequence's pages (some may be shared with a fork and must not be overwritten), then take fresh ones
     {
-        const int gpages = (len + c.page_size - 1) / c.page_size;
-        const int nslots = gpages > c.seq_shard_rank ? (gpages - c.seq_shard_rank + c.seq_shard_count - 1) / c.seq_shard_count : 0;
         int *tab = &ctx->h_page_table[((size_t)fa_idx * c.max_seqs + seq) * ctx->max_slots];
-        for (int i = nslots; i < ctx->max_slots; i++)
-            if (tab[i] >= 0) { ctx->free_pages.push_back(tab[i]); tab[i] = -1; }
+        for (int i = 0; i < ctx->max_slots; i++)
+            if (tab[i] >= 0) { release_page(ctx, tab[i]); tab[i] = -1; }
     }
     fm_status st = ensure_pages(ctx, fa_idx, seq, len);
     if (st) return st;

@@ -94,6 +94,7 @@ struct FmCtx {
     int *d_page_table = nullptr;       // [layers][seqs][max_slots]
     std::vector<int> h_page_table;
     std::vector<int> free_pages;
+    std::vector<int> page_refs;   // sequences holding each page (0 = free); > 1 after fm_seq_fork
     std::vector<int> kv_len;           // [layers][seqs] global rows
 
     // GatedDeltaNet state
@@ -198,5 +199,16 @@ int launch_gdn_prefill(const GdnDims &g, int n, int chunk, int step0, float *con
                        const uint16_t *norm_w, float *out, void *work, size_t work_bytes, int *err,
                        cudaStream_t st);
 size_t gdn_prefill_work_bytes(const GdnDims &g, int max_tokens, int chunk);
+
+// True the first time it is called for the current device with a given per-call-site flag word: function
+// attributes (dynamic shared memory limits) are per device, and one process may hold contexts on several.
+inline bool first_use_on_device(unsigned long long *done_mask) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return true;
+    const unsigned long long bit = 1ull << dev;
+    if (*done_mask & bit) return false;
+    *done_mask |= bit;
+    return true;
+}
 
 }  // namespace fm

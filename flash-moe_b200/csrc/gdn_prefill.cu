@@ -714,14 +714,13 @@ int launch_gdn_prefill(const GdnDims &g, int n, int chunk, int step0, float *con
     (void)chunk;
     GdnWork w;
     if (carve(g, n, work, &w) > work_bytes) return -1;
-    static bool configured = false;
-    if (!configured) {
+    static unsigned long long configured = 0;  // one bit per device
+    if (first_use_on_device(&configured)) {
         if (cudaFuncSetAttribute(gdn_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, g.conv_dim * 4) != cudaSuccess ||
             cudaFuncSetAttribute(gdn_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kChunkSmem) != cudaSuccess ||
             cudaFuncSetAttribute(gdn_kk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kKkSmem) != cudaSuccess ||
             cudaFuncSetAttribute(gdn_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kScSmem) != cudaSuccess)
             return -1;
-        configured = true;
     }
     const int nchunks = (n + kC - 1) / kC;
 #ifdef FM_GDN_TRACE

@@ -117,6 +117,18 @@ fm_status fm_synchronize(FmCtx *ctx);
  * (FlashMoE-iOS/FlashMoEEngine/FlashMoEEngine.m:1239-1258). */
 fm_status fm_reset(FmCtx *ctx, int seq);
 
+/* Sequence `dst` becomes a copy of `src` (it is reset first): the reference's system-prompt cache
+ * saves every layer's KV rows and recurrent state after the prompt and copies them back for each
+ * request (metal_infer/generate.h:708-764, 887-947).  In the paged store the full pages of `src` are
+ * shared by reference -- appends never touch a full page, so no copy is ever needed for them -- and
+ * only the partly filled last page of each layer and the GatedDeltaNet state are copied.  Resetting
+ * either sequence leaves the other intact.  Not available with a sliding window (pages are
+ * rewritten in place).  With sequence sharding every rank calls it. */
+fm_status fm_seq_fork(FmCtx *ctx, int src, int dst);
+
+/* Pages of the KV pool not held by any sequence. */
+int64_t fm_kv_free_pages(const FmCtx *ctx);
+
 /* Rows held for (layer, sequence) -- KVCache.len (metal_infer/layer_forward.h:128). */
 int fm_kv_len(const FmCtx *ctx, int fa_idx, int seq);
 
