@@ -416,6 +416,66 @@ def extra_measurements(pkg, torch, dev, peak, only=None):
         res.update(_probe_gdn_decode(pkg, torch, dev, peak, gen))
     if want("gdn_prefill"):
         res.update(_probe_gdn_prefill(pkg, torch, dev, gen))
+    if want("hybrid"):
+        res.update(_probe_hybrid(pkg, torch, dev, peak, gen))
+    return res
+
+
+def _probe_hybrid(pkg, torch, dev, peak, gen):
+    """One decode token through the token-mixing part of the full hybrid stack: 60 layers arranged as 15 x (3
+    GatedDeltaNet + 1 gated GQA), each layer's entry point called in model order (the projections and MoE between
+    them are outside this library).  Batch x context combinations that fit one GPU."""
+    res = {}
+    tw = _gdn_weights(pkg, torch, dev)
+    out = {}
+    for B, L in ((1, 32768), (1, 131072), (8, 32768), (8, 131072), (64, 32768)):
+        cfg = pkg.default_config(num_full_layers=15, num_linear_layers=45, max_seqs=B, max_seq_len=L + 64,
+                                 max_batch_tokens=max(B, 64))
+        ctx = pkg.Context(cfg)
+        ctx.set_stream(torch.cuda.current_stream().cuda_stream)
+        K = torch.randn((L, HKV * D), device=dev, generator=gen).bfloat16().float()
+        for layer in range(15):
+            for s in range(B):
+                ctx.kv_import(layer, s, K, K, L)
+        del K
+        qp = torch.randn((B, H * 2 * D), device=dev, generator=gen)
+        kn = torch.randn((B, HKV * D), device=dev, generator=gen)
+        ao = torch.empty((B, H * D), device=dev)
+        qkv = torch.randn((B, 12288), device=dev, generator=gen)
+        z = torch.randn((B, 8192), device=dev, generator=gen)
+        be = torch.randn((B, 64), device=dev, generator=gen)
+        al = torch.randn((B, 64), device=dev, generator=gen)
+        go = torch.empty((B, 8192), device=dev)
+        seqs = list(range(B))
+        pos = [L]
+
+        def token():
+            p = [pos[0]] * B
+            for blk in range(15):
+                for j in range(3):
+                    ctx.gdn_decode(3 * blk + j, seqs, qkv, z, be, al, go, tw["conv_w"], tw["A_log"], tw["dt_bias"], tw["norm_w"])
+                ctx.attn_decode(blk, seqs, p, ao, q_proj_out=qp, k=kn, v=kn)
+            pos[0] += 1
+
+        for _ in range(3):
+            token()
+        torch.cuda.synchronize()
+        reps = 10 if B * L <= 262144 else 4
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            token()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / reps
+        kv_bytes = 15 * B * (L + 4) * KV_BYTES_PER_ROW
+        gdn_bytes = 45 * (B * (2 * 4194304 + 2 * 147456 + (12288 + 8192 + 128 + 8192) * 4) + 98304 + 768)
+        out[f"b{B}_ctx{L}"] = {"ms_per_token": ms, "bytes_per_token": kv_bytes + gdn_bytes,
+                               "gbps": (kv_bytes + gdn_bytes) / ms / 1e6, "frac_of_peak": (kv_bytes + gdn_bytes) / ms / 1e6 / peak}
+        ctx.close()
+        del ctx
+        torch.cuda.empty_cache()
+    res["hybrid_stack_token_mixing"] = out
     return res
 
 
@@ -592,7 +652,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"],
                     help="how sequence shards exchange partial results: the library's peer-memory kernels, or NCCL all-gathers")
-    ap.add_argument("--probe", default=None, choices=["sweep", "prefill", "gdn_decode", "gdn_prefill"],
+    ap.add_argument("--probe", default=None, choices=["sweep", "prefill", "gdn_decode", "gdn_prefill", "hybrid"],
                     help="run only one of the extra measurements and print it (for profiling one kernel)")
     args = ap.parse_args()
     if args.probe:
