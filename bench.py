@@ -446,16 +446,20 @@ def _probe_hybrid(pkg, torch, dev, peak, gen):
         be = torch.randn((B, 64), device=dev, generator=gen)
         al = torch.randn((B, 64), device=dev, generator=gen)
         go = torch.empty((B, 8192), device=dev)
-        seqs = list(range(B))
-        pos = [L]
+        # the calls of one token, arguments converted once (a C host pays no per-call conversion either)
+        seq_arr = np.arange(B, dtype=np.int32)
+        pos_arr = np.full(B, L, dtype=np.int32)
+        calls = []
+        for blk in range(15):
+            for j in range(3):
+                calls.append(ctx.prepared("fm_gdn_decode", 3 * blk + j, seq_arr, B, qkv, z, be, al, tw["conv_w"], tw["A_log"],
+                                          tw["dt_bias"], tw["norm_w"], go))
+            calls.append(ctx.prepared("fm_attn_decode", blk, seq_arr, pos_arr, B, qp, None, None, kn, kn, None, None, ao))
 
         def token():
-            p = [pos[0]] * B
-            for blk in range(15):
-                for j in range(3):
-                    ctx.gdn_decode(3 * blk + j, seqs, qkv, z, be, al, go, tw["conv_w"], tw["A_log"], tw["dt_bias"], tw["norm_w"])
-                ctx.attn_decode(blk, seqs, p, ao, q_proj_out=qp, k=kn, v=kn)
-            pos[0] += 1
+            for f in calls:
+                f()
+            pos_arr[:] += 1
 
         for _ in range(3):
             token()
@@ -582,11 +586,13 @@ def _probe_gdn_decode(pkg, torch, dev, peak, gen):
         be = torch.randn((B, 64), device=dev, generator=gen)
         al = torch.randn((B, 64), device=dev, generator=gen)
         go = torch.empty((B, 8192), device=dev)
-        seqs = list(range(B))
+        seq_arr = np.arange(B, dtype=np.int32)
+        calls = [ctx.prepared("fm_gdn_decode", li, seq_arr, B, qkv, z, be, al, tw["conv_w"], tw["A_log"], tw["dt_bias"],
+                              tw["norm_w"], go) for li in range(NL)]
 
         def gdn_pass():
-            for li in range(NL):
-                ctx.gdn_decode(li, seqs, qkv, z, be, al, go, tw["conv_w"], tw["A_log"], tw["dt_bias"], tw["norm_w"])
+            for f in calls:
+                f()
 
         for _ in range(3):
             gdn_pass()

@@ -153,6 +153,31 @@ class Context:
     def reset(self, seq: int = -1):
         self._check(self.lib.fm_reset(self.h, C.c_int(seq)))
 
+    def prepared(self, entry: str, *args):
+        """A zero-argument callable for `entry(ctx, *args)` with the arguments converted once: Python ints become
+        C ints, int32 numpy arrays `const int *` (mutate them in place between calls, e.g. positions), other arrays
+        and tensors pointers.  For callers that step layers in a tight loop and do not want the per-call
+        conversions of the convenience methods in the way."""
+        fn = getattr(self.lib, entry)
+        conv, keep = [], []
+        for a in args:
+            if a is None:
+                conv.append(None)
+            elif isinstance(a, (int, np.integer)):
+                conv.append(C.c_int(int(a)))
+            elif isinstance(a, np.ndarray) and a.dtype == np.int32:
+                assert a.flags.c_contiguous
+                keep.append(a)
+                conv.append(a.ctypes.data_as(C.POINTER(C.c_int)))
+            else:
+                keep.append(a)
+                conv.append(_ptr(a))
+        h, check = self.h, self._check
+
+        def call(_conv=tuple(conv), _keep=keep):
+            check(fn(h, *_conv))
+        return call
+
     def seq_fork(self, src: int, dst: int):
         self._check(self.lib.fm_seq_fork(self.h, C.c_int(src), C.c_int(dst)))
 
