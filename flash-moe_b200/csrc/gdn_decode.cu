@@ -41,8 +41,8 @@ __device__ __forceinline__ float conv_silu(const float *ring, int conv_dim, int 
     return acc / (1.0f + expf(-acc));
 }
 
-template <int S>  // CTAs (row slices) per head
-__global__ void __launch_bounds__(kGdnThreads)
+template <int S, int W>  // CTAs (row slices) per head; warps per CTA (8, or 16 for whole-head CTAs at large batch)
+__global__ void __launch_bounds__(32 * W)
 gdn_decode_kernel(GdnDims g, TokSpec toks, float *__restrict__ conv_ring, float *__restrict__ ssm,
                   long long conv_seq_stride, long long ssm_seq_stride, const float *__restrict__ qkv,
                   const float *__restrict__ z, const float *__restrict__ beta,
@@ -50,12 +50,12 @@ gdn_decode_kernel(GdnDims g, TokSpec toks, float *__restrict__ conv_ring, float 
                   const float *__restrict__ A_log, const uint16_t *__restrict__ dt_bias,
                   const uint16_t *__restrict__ norm_w, float *__restrict__ out) {
     constexpr int kRows = kDv / S;          // state rows of this CTA
-    constexpr int kRowsPerWarp = kRows / 8;  // 8 warps
+    constexpr int kRowsPerWarp = kRows / W;
     __shared__ __align__(16) float s_q[kDk];
     __shared__ __align__(16) float s_k[kDk];
     __shared__ float s_v[kRows];
     __shared__ float s_o[kRows];
-    __shared__ float s_red[16];
+    __shared__ float s_red[8 + W];
     __shared__ float s_ss;  // this CTA's share of sum(o^2); read by the cluster peers
 
     const int slice = blockIdx.x, vh = blockIdx.y, tok = blockIdx.z;
@@ -78,7 +78,7 @@ gdn_decode_kernel(GdnDims g, TokSpec toks, float *__restrict__ conv_ring, float 
     const bool has_w = conv_w != nullptr;
     const bool own_qk = (slice == 0) && (vh % rep == 0);
     float my = 0.f;
-    {
+    if (tid < 2 * kDk) {
         // threads 0..127: q channel, 128..255: k channel
         const int ch = (tid < kDk ? 0 : total_k) + kh * kDk + (tid & (kDk - 1));
         const float x = x_in[ch];
@@ -102,7 +102,7 @@ gdn_decode_kernel(GdnDims g, TokSpec toks, float *__restrict__ conv_ring, float 
         const float inv_scale = 1.0f / sqrtf((float)kDk);
         if (tid < kDk)
             s_q[tid] = my * inv * (inv_scale * inv_scale);
-        else
+        else if (tid < 2 * kDk)
             s_k[tid - kDk] = my * inv * inv_scale;
     }
     // decay and beta of this head
@@ -136,7 +136,7 @@ gdn_decode_kernel(GdnDims g, TokSpec toks, float *__restrict__ conv_ring, float 
     __syncthreads();
     if (tid == 0) {
         float t = 0.f;
-        for (int w = 0; w < 8; w++) t += s_red[8 + w];
+        for (int w = 0; w < W; w++) t += s_red[8 + w];
         s_ss = t;
     }
     float total_ss;
@@ -164,7 +164,7 @@ gdn_decode_kernel(GdnDims g, TokSpec toks, float *__restrict__ conv_ring, float 
     }
 }
 
-template <int S>
+template <int S, int W>
 static int launch_gdn_decode_s(const GdnDims &g, const TokSpec &toks, float *conv_state, float *ssm_state,
                                long long conv_seq_stride, long long ssm_seq_stride, const float *qkv,
                                const float *z, const float *beta, const float *alpha,
@@ -172,7 +172,7 @@ static int launch_gdn_decode_s(const GdnDims &g, const TokSpec &toks, float *con
                                const uint16_t *norm_w, float *out, cudaStream_t st) {
     cudaLaunchConfig_t lc = {};
     lc.gridDim = dim3(S, g.Hv, toks.n);
-    lc.blockDim = dim3(kGdnThreads);
+    lc.blockDim = dim3(32 * W);
     lc.dynamicSmemBytes = 0;
     lc.stream = st;
     cudaLaunchAttribute attr[1];
@@ -182,7 +182,7 @@ static int launch_gdn_decode_s(const GdnDims &g, const TokSpec &toks, float *con
     attr[0].val.clusterDim.z = 1;
     lc.attrs = attr;
     lc.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&lc, gdn_decode_kernel<S>, g, toks, conv_state, ssm_state,
+    cudaError_t e = cudaLaunchKernelEx(&lc, gdn_decode_kernel<S, W>, g, toks, conv_state, ssm_state,
                                        conv_seq_stride, ssm_seq_stride, qkv, z, beta, alpha, conv_w,
                                        A_log, dt_bias, norm_w, out);
     return e == cudaSuccess ? 1 : -1;
@@ -197,12 +197,12 @@ int launch_gdn_decode(const GdnDims &g, const TokSpec &toks, float *conv_state, 
     // enough CTAs to cover the machine at small batch, whole heads per CTA at large batch
     const int ctas_whole = g.Hv * toks.n;
     if (ctas_whole >= 512)
-        return launch_gdn_decode_s<1>(g, toks, conv_state, ssm_state, conv_seq_stride, ssm_seq_stride, qkv, z,
+        return launch_gdn_decode_s<1, 16>(g, toks, conv_state, ssm_state, conv_seq_stride, ssm_seq_stride, qkv, z,
                                       beta, alpha, conv_w, A_log, dt_bias, norm_w, out, st);
     if (ctas_whole >= 256)
-        return launch_gdn_decode_s<2>(g, toks, conv_state, ssm_state, conv_seq_stride, ssm_seq_stride, qkv, z,
+        return launch_gdn_decode_s<2, 8>(g, toks, conv_state, ssm_state, conv_seq_stride, ssm_seq_stride, qkv, z,
                                       beta, alpha, conv_w, A_log, dt_bias, norm_w, out, st);
-    return launch_gdn_decode_s<4>(g, toks, conv_state, ssm_state, conv_seq_stride, ssm_seq_stride, qkv, z,
+    return launch_gdn_decode_s<4, 8>(g, toks, conv_state, ssm_state, conv_seq_stride, ssm_seq_stride, qkv, z,
                                   beta, alpha, conv_w, A_log, dt_bias, norm_w, out, st);
 }
 
