@@ -67,3 +67,30 @@ def test_window_batch_and_limits(pkg, port, synth):
     c.close()
     with pytest.raises(pkg.FmError):
         attn_ctx(pkg, heads, kvh, max_seq_len=128, sliding_window=500)
+
+
+def test_window_on_a_sequence_sharded_store(pkg, port, synth):
+    """Sliding window of 300 rows held by two sequence-shard contexts (alternating pages of the circular buffer):
+    every step both compute their partial result, merged by log-sum-exp + gate, through a wrap of the window."""
+    heads, kvh, window, steps = 32, 2, 300, 420
+    dims = make_dims(num_attn_heads=heads, num_kv_heads=kvh, sliding_window=window, store_bf16=1)
+    q, g, k, v = synth.attn_step_inputs(51, steps)
+    kc = np.zeros((window, kvh * 256), np.float32); vc = np.zeros_like(kc)
+    ref, _ = port.attn_run(dims, kc, vc, 0, q, g, k, v, threads=8)
+    shards = [attn_ctx(pkg, heads, kvh, max_seq_len=2048, shard=(r, 2), sliding_window=window) for r in range(2)]
+    merger = attn_ctx(pkg, heads, kvh, max_seq_len=128)
+    worst = 0.0
+    for t in range(steps):
+        po, pml = [], []
+        for c in shards:
+            o = np.empty((1, heads, 256), np.float32); ml = np.empty((1, heads, 2), np.float32)
+            c.attn_decode_partial(0, [0], [t], o, ml, q=q[t:t + 1].copy(), k=k[t:t + 1].copy(), v=v[t:t + 1].copy())
+            po.append(o); pml.append(ml)
+        out = np.empty((1, heads * 256), np.float32)
+        merger.attn_merge_gate(2, np.stack(po), np.stack(pml), 1, out, gate=g[t:t + 1].copy())
+        gated, _, _ = rel_errors(out[0], ref[t])
+        worst = max(worst, gated)
+        assert gated <= TOL, (t, gated)
+    for c in shards + [merger]:
+        c.close()
+    print("sharded window worst gated", worst)
