@@ -481,22 +481,30 @@ attn_decode_kernel(KvView kv, RopeParams rope, TokSpec toks, int H, const float 
         // More (small batch, long context): the splits form groups of kDecGroup; the last CTA of a group
         // merges the group into one partial per head, the last group to finish merges the groups.  Either
         // way a warp takes whole heads: lane j holds the (max, sum) of part j, the weights travel by
-        // shuffle, and all row loads of a head are in flight together.
+        // shuffle, and the row loads of its heads are in flight together.
         __shared__ int s_last;
-        auto merge_head = [&](const float *po, const float *pml, int cnt, float4 &a0, float4 &a1, float &M, float &lt) {
-            const float2 mlj = lane < cnt ? __ldcg(reinterpret_cast<const float2 *>(pml) + lane) : make_float2(kNegBig, 0.f);
-            M = warp_max(mlj.x);
-            const float wj = fast_exp2(mlj.x - M);
-            lt = warp_sum(wj * mlj.y);
-            a0 = make_float4(0.f, 0.f, 0.f, 0.f);
-            a1 = a0;
-            const float4 *src = reinterpret_cast<const float4 *>(po) + lane * 2;
-#pragma unroll 8
+        // two heads at a time (with 16 heads per KV head and 8 warps that is the whole share of a warp), so that
+        // the loads of both are in flight together; `two` false: the second head is a dummy copy of the first
+        struct Merged { float4 a0, a1; float M, lt; };
+        auto merge_heads = [&](const float *po0, const float *pml0, const float *po1, const float *pml1, int cnt, Merged &x, Merged &y) {
+            const float2 ml0 = lane < cnt ? __ldcg(reinterpret_cast<const float2 *>(pml0) + lane) : make_float2(kNegBig, 0.f);
+            const float2 ml1 = lane < cnt ? __ldcg(reinterpret_cast<const float2 *>(pml1) + lane) : make_float2(kNegBig, 0.f);
+            x.M = warp_max(ml0.x);
+            y.M = warp_max(ml1.x);
+            const float w0 = fast_exp2(ml0.x - x.M), w1 = fast_exp2(ml1.x - y.M);
+            x.lt = warp_sum(w0 * ml0.y);
+            y.lt = warp_sum(w1 * ml1.y);
+            x.a0 = x.a1 = y.a0 = y.a1 = make_float4(0.f, 0.f, 0.f, 0.f);
+            const float4 *s0 = reinterpret_cast<const float4 *>(po0) + lane * 2, *s1 = reinterpret_cast<const float4 *>(po1) + lane * 2;
+#pragma unroll 4
             for (int j = 0; j < cnt; j++) {
-                const float w = __shfl_sync(0xffffffffu, wj, j);
-                const float4 v0 = __ldcg(src + (size_t)j * (kD / 4)), v1 = __ldcg(src + (size_t)j * (kD / 4) + 1);
-                a0.x += w * v0.x; a0.y += w * v0.y; a0.z += w * v0.z; a0.w += w * v0.w;
-                a1.x += w * v1.x; a1.y += w * v1.y; a1.z += w * v1.z; a1.w += w * v1.w;
+                const float wa = __shfl_sync(0xffffffffu, w0, j), wb = __shfl_sync(0xffffffffu, w1, j);
+                const float4 p0 = __ldcg(s0 + (size_t)j * (kD / 4)), p1 = __ldcg(s0 + (size_t)j * (kD / 4) + 1);
+                const float4 q0 = __ldcg(s1 + (size_t)j * (kD / 4)), q1 = __ldcg(s1 + (size_t)j * (kD / 4) + 1);
+                x.a0.x += wa * p0.x; x.a0.y += wa * p0.y; x.a0.z += wa * p0.z; x.a0.w += wa * p0.w;
+                x.a1.x += wa * p1.x; x.a1.y += wa * p1.y; x.a1.z += wa * p1.z; x.a1.w += wa * p1.w;
+                y.a0.x += wb * q0.x; y.a0.y += wb * q0.y; y.a0.z += wb * q0.z; y.a0.w += wb * q0.w;
+                y.a1.x += wb * q1.x; y.a1.y += wb * q1.y; y.a1.z += wb * q1.z; y.a1.w += wb * q1.w;
             }
         };
         // arrival at a counter; true for the CTA that completes it (which also resets it)
@@ -516,42 +524,54 @@ attn_decode_kernel(KvView kv, RopeParams rope, TokSpec toks, int H, const float 
         const int unit = tok * kv.Hkv + kvh;
         if (nsplits <= kDecMaxLastCtaSplits) {
             if (!arrive_last(f.counters + unit, nsplits)) return;
-            for (int r = warp; r < group; r += kDecWarps) {
-                const int head = kvh * group + r;
-                const size_t prow0 = ((size_t)tok * H + head) * nsplits;
-                float4 a0, a1;
-                float M, lt;
-                merge_head(part_o + prow0 * kD, part_ml + prow0 * 2, nsplits, a0, a1, M, lt);
-                emit(tok, head, lane * 8, a0, M, lt);
-                emit(tok, head, lane * 8 + 4, a1, M, lt);
+            for (int r = warp; r < group; r += 2 * kDecWarps) {
+                const bool two = r + kDecWarps < group;
+                const int h0 = kvh * group + r, h1 = two ? h0 + kDecWarps : h0;
+                const size_t p0 = ((size_t)tok * H + h0) * nsplits, p1 = ((size_t)tok * H + h1) * nsplits;
+                Merged x, y;
+                merge_heads(part_o + p0 * kD, part_ml + p0 * 2, part_o + p1 * kD, part_ml + p1 * 2, nsplits, x, y);
+                emit(tok, h0, lane * 8, x.a0, x.M, x.lt);
+                emit(tok, h0, lane * 8 + 4, x.a1, x.M, x.lt);
+                if (two) {
+                    emit(tok, h1, lane * 8, y.a0, y.M, y.lt);
+                    emit(tok, h1, lane * 8 + 4, y.a1, y.M, y.lt);
+                }
             }
         } else {
             const int gi = split / kDecGroup, gfirst = gi * kDecGroup;
             const int gcount = min(kDecGroup, nsplits - gfirst), ngroups = (nsplits + kDecGroup - 1) / kDecGroup;
             if (!arrive_last(f.group_counters + unit * kDecMaxGroups + gi, gcount)) return;
             DEC_TR(3);
-            for (int r = warp; r < group; r += kDecWarps) {
-                const int head = kvh * group + r;
-                const size_t prow0 = ((size_t)tok * H + head) * nsplits + gfirst;
-                float4 a0, a1;
-                float M, lt;
-                merge_head(part_o + prow0 * kD, part_ml + prow0 * 2, gcount, a0, a1, M, lt);
+            auto put_group = [&](int head, const Merged &m) {
                 const size_t g2 = ((size_t)tok * H + head) * kDecMaxGroups + gi;
                 float4 *dst = reinterpret_cast<float4 *>(f.group_o + g2 * kD) + lane * 2;
-                dst[0] = a0;
-                dst[1] = a1;
-                if (lane == 0) *reinterpret_cast<float2 *>(f.group_ml + g2 * 2) = make_float2(M, lt);
+                dst[0] = m.a0;
+                dst[1] = m.a1;
+                if (lane == 0) *reinterpret_cast<float2 *>(f.group_ml + g2 * 2) = make_float2(m.M, m.lt);
+            };
+            for (int r = warp; r < group; r += 2 * kDecWarps) {
+                const bool two = r + kDecWarps < group;
+                const int h0 = kvh * group + r, h1 = two ? h0 + kDecWarps : h0;
+                const size_t p0 = ((size_t)tok * H + h0) * nsplits + gfirst, p1 = ((size_t)tok * H + h1) * nsplits + gfirst;
+                Merged x, y;
+                merge_heads(part_o + p0 * kD, part_ml + p0 * 2, part_o + p1 * kD, part_ml + p1 * 2, gcount, x, y);
+                put_group(h0, x);
+                if (two) put_group(h1, y);
             }
             if (!arrive_last(f.counters + unit, ngroups)) return;
             DEC_TR(4);
-            for (int r = warp; r < group; r += kDecWarps) {
-                const int head = kvh * group + r;
-                const size_t g2 = ((size_t)tok * H + head) * kDecMaxGroups;
-                float4 a0, a1;
-                float M, lt;
-                merge_head(f.group_o + g2 * kD, f.group_ml + g2 * 2, ngroups, a0, a1, M, lt);
-                emit(tok, head, lane * 8, a0, M, lt);
-                emit(tok, head, lane * 8 + 4, a1, M, lt);
+            for (int r = warp; r < group; r += 2 * kDecWarps) {
+                const bool two = r + kDecWarps < group;
+                const int h0 = kvh * group + r, h1 = two ? h0 + kDecWarps : h0;
+                const size_t g0 = ((size_t)tok * H + h0) * kDecMaxGroups, g1 = ((size_t)tok * H + h1) * kDecMaxGroups;
+                Merged x, y;
+                merge_heads(f.group_o + g0 * kD, f.group_ml + g0 * 2, f.group_o + g1 * kD, f.group_ml + g1 * 2, ngroups, x, y);
+                emit(tok, h0, lane * 8, x.a0, x.M, x.lt);
+                emit(tok, h0, lane * 8 + 4, x.a1, x.M, x.lt);
+                if (two) {
+                    emit(tok, h1, lane * 8, y.a0, y.M, y.lt);
+                    emit(tok, h1, lane * 8 + 4, y.a1, y.M, y.lt);
+                }
             }
         }
     }
