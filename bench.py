@@ -237,13 +237,10 @@ def run_ours(args):
             cur[0] += 1
             return
         for layer in range(NL):
-            if False:
-                pass
-            else:
-                ctx.attn_decode_partial(layer, seqs, pos, o_part, ml_part, q_proj_out=qp[layer], k=kn[layer], v=vn[layer])
-                dist.all_gather_into_tensor(o_all, o_part, group=seq_group)
-                dist.all_gather_into_tensor(ml_all, ml_part, group=seq_group)
-                ctx.attn_merge_gate(ss, o_all, ml_all, B, out[layer], q_proj_out=qp[layer])
+            ctx.attn_decode_partial(layer, seqs, pos, o_part, ml_part, q_proj_out=qp[layer], k=kn[layer], v=vn[layer])
+            dist.all_gather_into_tensor(o_all, o_part, group=seq_group)
+            dist.all_gather_into_tensor(ml_all, ml_part, group=seq_group)
+            ctx.attn_merge_gate(ss, o_all, ml_all, B, out[layer], q_proj_out=qp[layer])
         cur[0] += 1
 
     def barrier():
@@ -329,17 +326,14 @@ def run_ours(args):
                 cur[0] += 1
                 return
             for layer in range(NL):
-                if False:
-                    pass
-                else:
-                    ctx.attn_decode_partial(layer, seqs, pos, h_o, h_ml, q_proj_out=h_qp[layer], k=h_k[layer], v=h_v[layer])
-                    o_part.copy_(torch.from_numpy(h_o)); ml_part.copy_(torch.from_numpy(h_ml))
-                    dist.all_gather_into_tensor(o_all, o_part, group=seq_group)
-                    dist.all_gather_into_tensor(ml_all, ml_part, group=seq_group)
-                    ctx.set_pointer_mode(pkg.binding.FM_PTR_DEVICE)
-                    ctx.attn_merge_gate(ss, o_all, ml_all, B, out[layer], q_proj_out=qp[layer])
-                    ctx.set_pointer_mode(pkg.binding.FM_PTR_HOST)
-                    h_out[layer] = out[layer].cpu().numpy()
+                ctx.attn_decode_partial(layer, seqs, pos, h_o, h_ml, q_proj_out=h_qp[layer], k=h_k[layer], v=h_v[layer])
+                o_part.copy_(torch.from_numpy(h_o)); ml_part.copy_(torch.from_numpy(h_ml))
+                dist.all_gather_into_tensor(o_all, o_part, group=seq_group)
+                dist.all_gather_into_tensor(ml_all, ml_part, group=seq_group)
+                ctx.set_pointer_mode(pkg.binding.FM_PTR_DEVICE)
+                ctx.attn_merge_gate(ss, o_all, ml_all, B, out[layer], q_proj_out=qp[layer])
+                ctx.set_pointer_mode(pkg.binding.FM_PTR_HOST)
+                h_out[layer] = out[layer].cpu().numpy()
             cur[0] += 1
 
         step_host()
@@ -362,6 +356,13 @@ def run_ours(args):
                "note": "fm_attn_decode_layers in host-pointer mode: every step copies q_proj_out, k, v of all layers "
                        "from page-locked host memory to the device and the gated outputs back; the KV cache is resident state"}
         ctx.set_pointer_mode(pkg.binding.FM_PTR_DEVICE)
+
+    # ---- correctness of what was timed: one more step of the same workload, one (layer, sequence) of it against
+    # the CPU checker on every rank (each rank holds one KV-head group; the ranks of a sequence group put their
+    # shards of the cache together first).  Outside every timed region.
+    parity = None
+    if not args.no_check:
+        parity = parity_check(args, pkg, torch, dist, ctx, step, cur, qp, kn, vn, out, dev, world, ss, seq_group, Hl, Hkvl)
 
     extra = {}
     if rank == 0 and world == 1 and not args.no_extra:
@@ -387,18 +388,60 @@ def run_ours(args):
                        "l2": "inputs larger than L2 (KV streamed per step: %.1f GB)" % (kv_bytes_step / 1e9)},
             "us_per_layer": ms_step * 1e3 / NL,
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches),
-            "clocks": clocks, "extra": extra,
+            "clocks": clocks, "parity": parity, "extra": extra,
         }
         print(json.dumps(line))
     if ctx is not None:
         ctx.close()
     if world > 1:
         dist.destroy_process_group()
+    if parity is not None and not parity["ok"]:
+        sys.exit(3)
+
+
+PARITY_TOL = 2e-3
+
+
+def parity_check(args, pkg, torch, dist, ctx, step, cur, qp, kn, vn, out, dev, world, ss, seq_group, Hl, Hkvl):
+    """Runs one more step of the timed workload and compares the last layer's output for the last sequence with
+    the CPU checker fed the same cache rows and inputs (tolerance of the attention parity tests).  The checker
+    is used as a checker only; nothing here is timed."""
+    from oracle.oracle_py import Oracle, host_threads, make_dims
+    B, NL = args.batch, args.layers
+    layer, s = NL - 1, B - 1
+    n = ctx.kv_len(layer, s)
+    kd = torch.zeros((n + 1, Hkvl * D), device=dev); vd = torch.zeros_like(kd)
+    ctx.kv_export(layer, s, kd, vd, n + 1)          # on a sequence-sharded store: the rows this rank owns
+    torch.cuda.synchronize()
+    if ss > 1:
+        dist.all_reduce(kd, group=seq_group); dist.all_reduce(vd, group=seq_group)
+    kc, vc = kd.cpu().numpy(), vd.cpu().numpy()
+    del kd, vd
+    pos = cur[0]
+    step()
+    torch.cuda.synchronize()
+    got = out[layer, s].cpu().numpy()
+    x = qp[layer, s].cpu().numpy().reshape(Hl, 2, D)
+    q, gate = np.ascontiguousarray(x[:, 0].reshape(1, -1)), np.ascontiguousarray(x[:, 1].reshape(1, -1))
+    k, v = kn[layer, s:s + 1].cpu().numpy(), vn[layer, s:s + 1].cpu().numpy()
+    dims = make_dims(num_attn_heads=Hl, num_kv_heads=Hkvl, store_bf16=1)
+    want, _ = Oracle("port").attn_run(dims, kc, vc, n, q, gate, k, v, start_pos=pos, threads=host_threads())
+    a, r = got.astype(np.float64).ravel(), want.astype(np.float64).ravel()
+    err = float((np.abs(a - r) / np.maximum(np.abs(r), np.sqrt(np.mean(r * r)))).max())
+    t = torch.tensor([err], device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    err = float(t.item())
+    return {"gated": err, "tol": PARITY_TOL, "ok": bool(err <= PARITY_TOL), "rows": n + 1,
+            "checked": f"layer {layer}, sequence {s} of one more step of the timed workload, on every rank (max over ranks), "
+                       "against the CPU checker"}
 
 
 # DRAM bytes (read + write) of one attn_decode_kernel launch for ONE sequence at 131073 rows, from
 # the committed ncu capture (profiles/attn_decode_kernel_b1_ctx128k_ncu.md): 268.76 MB + 4.43 MB.
-# Traffic grows in proportion to rows x sequences, so the bench launch is scaled from it.
+# Traffic grows in proportion to rows x sequences, so the bench launch is scaled from it.  Captured on the kernel
+# as of commit 9d09feb (two-level merge with a warp merging its two heads together); refresh when the kernel's
+# memory behaviour changes.
 TRAFFIC_NCU_1SEQ_128K = 273.18e6
 
 
@@ -499,34 +542,44 @@ def _probe_sweep(pkg, torch, dev, peak, gen):
     out = torch.empty((NL, 1, H * D), device=dev)
     sq, skv, so = H * 2 * D, HKV * D, H * D
 
-    def token(pos):  # one token through the NL layers: one C call, consecutive layers' launches overlapping
-        ctx.attn_decode_layers(0, NL, [0], [pos], out, qp, kn, kn, sq, skv, so)
+    seq_arr = np.zeros(1, dtype=np.int32)
+    pos_arr = np.zeros(1, dtype=np.int32)
+    # model order: one fm_attn_decode call per layer, each an ordinary launch that starts when the previous one has
+    # finished (in the model, layer l+1's projections depend on layer l's output)
+    calls = [ctx.prepared("fm_attn_decode", l, seq_arr, pos_arr, 1, qp[l], None, None, kn[l], kn[l], None, None, out[l])
+             for l in range(NL)]
+
+    def token(pos):
+        pos_arr[0] = pos
+        for f in calls:
+            f()
+
+    def token_overlapped(pos):  # one C call for all layers: consecutive layers' launches overlap (needs every layer's
+        ctx.attn_decode_layers(0, NL, [0], [pos], out, qp, kn, kn, sq, skv, so)  # inputs up front: a throughput figure)
+
+    def timed(fn, pos, reps):
+        for _ in range(3):
+            fn(pos); pos += 1
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for r in range(reps):
+            fn(pos); pos += 1
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / (reps * NL), pos
 
     for L in (4096, 8192, 16384, 32768, 65536, 131072):
         for layer in range(NL):
             ctx.kv_import(layer, 0, K, V, L)
         reps = 6 if L >= 65536 else 20
-        pos = L
-        for _ in range(3):
-            token(pos); pos += 1
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for r in range(reps):
-            token(pos); pos += 1
-        e1.record()
-        torch.cuda.synchronize()
-        us_layer = e0.elapsed_time(e1) * 1e3 / (reps * NL)
-        # the same launches bracketed one by one (no overlap between layers while events sit between them)
-        ctx.profile_read(); ctx.profile_enable(True)
-        for r in range(3):
-            token(pos); pos += 1
-        torch.cuda.synchronize()
-        n_k, k_ms = ctx.profile_read(); ctx.profile_enable(False)
-        us_kernel = k_ms * 1e3 / max(n_k, 1)
+        us_layer, pos = timed(token, L, reps)
+        us_overlapped, pos = timed(token_overlapped, pos, reps)
         kvb = 2 * (L + 4 + reps / 2) * HKV * D * 2
         sweep[str(L)] = {"us_per_layer": us_layer, "kv_gbps": kvb / us_layer / 1e3, "frac_of_peak": kvb / us_layer / 1e3 / peak,
-                         "us_decode_kernel_bracketed_alone": us_kernel}
+                         "how": "one fm_attn_decode call per layer in model order (no overlap between layers)",
+                         "us_per_layer_all_layers_in_one_call": us_overlapped,
+                         "kv_gbps_all_layers_in_one_call": kvb / us_overlapped / 1e3}
     res["decode_b1_sweep"] = sweep
     ctx.close()
     del K, V
@@ -656,6 +709,7 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=10)
     ap.add_argument("--no-extra", action="store_true", help="skip the context sweep / prefill / GatedDeltaNet figures")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-check", action="store_true", help="skip the comparison of one step's output with the CPU checker")
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"],
                     help="how sequence shards exchange partial results: the library's peer-memory kernels, or NCCL all-gathers")
     ap.add_argument("--probe", default=None, choices=["sweep", "prefill", "gdn_decode", "gdn_prefill", "hybrid"],

@@ -92,27 +92,8 @@ struct DecodeFused {
     unsigned int *group_counters;  // [tokens*Hkv][kDecMaxGroups] arrivals per group of splits (many splits only)
     float *group_o, *group_ml;     // [tokens][H][kDecMaxGroups][D] / [..][2]: the groups' merged partials
     int *err;                // tail 4: device error word (a peer never published)
-    long long *trace;  // development builds only (-DFM_DEC_TRACE)
 };
 
-#ifdef FM_DEC_TRACE
-extern "C" {
-long long *fm_dec_trace = nullptr;  // device buffer [CTAs][8]
-}
-__device__ long long *g_dec_trace = nullptr;
-__device__ __forceinline__ long long dec_gtime() {
-    long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-#define DEC_TR(k)                                                                                          \
-    do {                                                                                                   \
-        if (f.trace && threadIdx.x == 0)                                                                   \
-            f.trace[((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 8 + (k)] = dec_gtime(); \
-    } while (0)
-#else
-#define DEC_TR(k) do { } while (0)
-#endif
 
 template <bool kFused>
 __global__ void __launch_bounds__(kDecThreads, 1)
@@ -128,7 +109,6 @@ attn_decode_kernel(KvView kv, RopeParams rope, TokSpec toks, int H, const float 
 
     const int split = blockIdx.x, kvh = blockIdx.y, tok = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    DEC_TR(0);
     // A following launch marked as programmatically dependent (another layer's step) may start filling
     // free SMs now.
     if (kFused) dep_launch_dependents();
@@ -239,7 +219,6 @@ attn_decode_kernel(KvView kv, RopeParams rope, TokSpec toks, int H, const float 
     const float4 *xslice = reinterpret_cast<const float4 *>(s_x) + (size_t)(pw * kNS) * 64 + lane;
     // this warp's q fragments (its share of the head dim, hi and lo terms) stay in registers
     __syncthreads();
-    DEC_TR(1);
     uint32_t qh[kKSteps][4], ql[kKSteps][4];
 #pragma unroll
     for (int k8 = 0; k8 < kKSteps; k8++) {
@@ -383,7 +362,6 @@ attn_decode_kernel(KvView kv, RopeParams rope, TokSpec toks, int H, const float 
     }
     cp_async_wait<0>();
     __syncthreads();
-    DEC_TR(2);
 
     // ---- merge the four row-slices through shared memory (the ring is free now) ----
 #pragma unroll
@@ -435,10 +413,13 @@ attn_decode_kernel(KvView kv, RopeParams rope, TokSpec toks, int H, const float 
         }
     };
     const bool direct = kFused && nsplits == 1;  // this CTA is the only split: finish the rows here
-    // The exchange tails write slots that the previous launch's peers may still be reading: wait for
-    // the previous launch to complete.  (Partials and counters are per layer, and a launch is only ever
-    // overlapped with another layer's.)  No effect for an ordinary launch.
-    if (kFused && f.tail >= 3) dep_wait();
+    // A launch that was started as a programmatic dependent of the previous one (another layer's step) has
+    // streamed its pages while that launch drained; from here on it writes what later work reads (partials,
+    // counters, exchange slots, the output), so every CTA waits for the previous launch to have completed and
+    // flushed.  A dependent of a grid that uses launch_dependents has to execute this wait, and with it the
+    // launches of one fm_attn_decode_layers call complete in order: whatever follows the last layer in the
+    // stream follows all of them.  No effect for an ordinary launch.
+    if (kFused) dep_wait();
     for (int r = warp; r < group; r += kDecWarps) {
         float mw[4], M = kNegBig;
 #pragma unroll
@@ -541,7 +522,6 @@ attn_decode_kernel(KvView kv, RopeParams rope, TokSpec toks, int H, const float 
             const int gi = split / kDecGroup, gfirst = gi * kDecGroup;
             const int gcount = min(kDecGroup, nsplits - gfirst), ngroups = (nsplits + kDecGroup - 1) / kDecGroup;
             if (!arrive_last(f.group_counters + unit * kDecMaxGroups + gi, gcount)) return;
-            DEC_TR(3);
             auto put_group = [&](int head, const Merged &m) {
                 const size_t g2 = ((size_t)tok * H + head) * kDecMaxGroups + gi;
                 float4 *dst = reinterpret_cast<float4 *>(f.group_o + g2 * kD) + lane * 2;
@@ -559,7 +539,6 @@ attn_decode_kernel(KvView kv, RopeParams rope, TokSpec toks, int H, const float 
                 if (two) put_group(h1, y);
             }
             if (!arrive_last(f.counters + unit, ngroups)) return;
-            DEC_TR(4);
             for (int r = warp; r < group; r += 2 * kDecWarps) {
                 const bool two = r + kDecWarps < group;
                 const int h0 = kvh * group + r, h1 = two ? h0 + kDecWarps : h0;
@@ -575,7 +554,6 @@ attn_decode_kernel(KvView kv, RopeParams rope, TokSpec toks, int H, const float 
             }
         }
     }
-    DEC_TR(5);
     if (f.tail == 4) {
         // ---- this CTA has stored the unit's rows into every rank's buffer: publish, wait, merge ----
         __shared__ int s_ok;
@@ -687,9 +665,6 @@ int launch_attn_decode_fused(const KvView &kv, const RopeParams &rope, const Tok
     f.tail = tail; f.gate = gate; f.out = out; f.ml_out = ml_out;
     if (x) f.x = *x;
     f.step = step;
-#ifdef FM_DEC_TRACE
-    f.trace = fm_dec_trace;
-#endif
     f.counters = scr.counters;
     f.group_counters = scr.group_counters;
     f.group_o = scr.group_o;

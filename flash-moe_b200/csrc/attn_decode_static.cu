@@ -50,6 +50,11 @@ extern "C" fm_status fm_attn_decode_static(const FmStaticDecodeArgs *a, char *er
         set_err(err, err_cap, "fm_attn_decode_static: batch %d (1..%d)", a->batch, kMaxList);
         return FM_ERR_INVALID;
     }
+    if (a->num_attn_heads < 1 || a->max_pages_per_seq < 1 || (a->rotary_dim > 0 && !(a->rope_theta > 0.f))) {
+        set_err(err, err_cap, "fm_attn_decode_static: %d query heads, %d pages per sequence, or rope_theta <= 0", a->num_attn_heads,
+                a->max_pages_per_seq);
+        return FM_ERR_INVALID;
+    }
     if (a->num_kv_heads < 1 || a->num_attn_heads % a->num_kv_heads != 0 || a->num_attn_heads / a->num_kv_heads > 16 ||
         a->rotary_dim < 0 || a->rotary_dim > 128 || (a->rotary_dim & 1)) {
         set_err(err, err_cap, "fm_attn_decode_static: %d query / %d KV heads, rotary %d not supported", a->num_attn_heads,
@@ -132,7 +137,7 @@ extern "C" fm_status fm_attn_decode_static(const FmStaticDecodeArgs *a, char *er
     if (launch_attn_decode(kv, rope, t, H, a->q_proj_out, a->q, a->q_norm_w, a->rms_norm_eps, part_o, part_ml, ns, st) < 0 ||
         launch_attn_merge(part_o, part_ml, ns, D, 2, (long long)H * ns * D, (long long)H * ns * 2, (long long)ns * D,
                           (long long)ns * 2, t.n, H, D, a->q_proj_out, a->gate, a->out, nullptr, st) < 0) {
-        set_err(err, err_cap, "fm_attn_decode_static: kernel launch failed (%d)", (int)cudaGetLastError());
+        set_err(err, err_cap, "fm_attn_decode_static: kernel launch failed");
         return FM_ERR_CUDA;
     }
     return FM_OK;

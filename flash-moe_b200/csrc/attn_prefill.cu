@@ -190,31 +190,8 @@ attn_prefill_prep_kernel(KvView kv, RopeParams rope, PrepParams p) {
 }
 
 // ---- the attention kernel ----------------------------------------------------------------------
-// Optional per-tile clock trace of one CTA (development builds only: -DFM_PF_TRACE).
-#ifdef FM_PF_TRACE
-extern "C" {
-long long *fm_pf_trace = nullptr;  // device buffer, [64 tiles][8 events]
-}
-#define PF_TR(slot)                                                                           \
-    do {                                                                                      \
-        if (p.trace && blockIdx.x == 0 && blockIdx.y == 0 && j < 64) p.trace[j * 8 + (slot)] = clock64(); \
-    } while (0)
-__device__ __forceinline__ long long pf_gtime() {
-    long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-#define PF_CTA(k)                                                                                  \
-    do {                                                                                           \
-        if (p.trace && threadIdx.x == 0) p.trace[512 + (blockIdx.x * gridDim.y + blockIdx.y) * 8 + (k)] = pf_gtime(); \
-    } while (0)
-#else
-#define PF_TR(slot) do { } while (0)
-#define PF_CTA(k) do { } while (0)
-#endif
 
 struct PfParams {
-    long long *trace;
     int n;         // tokens in the run
     int row0;      // cache rows before the run
     int H, Hkv;
@@ -241,7 +218,6 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     auto bar = [&](int i) { return sBar + 8u * (uint32_t)i; };
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    PF_CTA(0);
     // heavy tiles first: CTAs are handed out in linear order (x fastest), so x walks the heads and
     // y = 0 is the last (longest) query tile of every head
     const int nqt = gridDim.y;
@@ -336,21 +312,17 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     ok = mbar_wait(bar(BAR_KFULL + ((j + 1) & 1)), ((j + 1) >> 1) & 1, abortp) && mbar_wait(bar(BAR_SFREE), j & 1, abortp);
                     if (!ok) break;
                     tc_fence_after();
-                    PF_TR(4);
                     issue_s(j + 1);
-                    PF_TR(5);
                 }
                 ok = mbar_wait(bar(BAR_PFULL), j & 1, abortp) && mbar_wait(bar(BAR_VFULL + b), u & 1, abortp);
                 if (!ok) break;
                 tc_fence_after();
-                PF_TR(6);
                 const uint64_t dv = dv0 + (uint64_t)((b * kKVBytesPf) >> 4);
 #pragma unroll
                 for (int ks = 0; ks < 2 * kBN / 16; ks++)  // p_hi (4 k-steps) then p_lo (4) against the same V tile
                     tc_mma_f16_ta(tmem + kColO, tmem + kColP + ks * 8, dv + (uint64_t)(((ks & 3) * 2048) >> 4), idesc_o, (j > 0 || ks > 0));
                 tc_commit(bar(BAR_PVDONE));
                 tc_commit(bar(BAR_VEMPTY + b));
-                PF_TR(7);
             }
         }
     } else {
@@ -381,12 +353,10 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         }
         float m_ref = kNegBig, l_sum = 0.f;
         bool ok = true;
-        PF_CTA(1);
         for (int j = 0; j < ntiles; j++) {
             ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_SFULL), j & 1, abortp));
             if (!ok) break;  // warp-uniform: the tcgen05.ld / st below are warp-collective
             tc_fence_after();
-            if (tid == 0) PF_TR(0);
             uint32_t sr[64];
             {
                 uint32_t lo[32], hi[32];
@@ -398,7 +368,6 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             }
             tc_fence_before();
             mbar_arrive(bar(BAR_SFREE));
-            if (tid == 0) PF_TR(1);
             // causal mask and row maximum
             float mx = kNegBig;
             const int col0 = j * kBN;
@@ -418,7 +387,6 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 if (!ok) break;
                 tc_fence_after();
             }
-            if (tid == 0) PF_TR(2);
             if (any_grow) {  // lazy rescale, warp-uniform because tcgen05.ld/st are warp-collective
                 const float m_new = grow ? mx : m_ref;
                 const float corr = fast_exp2(m_ref - m_new);
@@ -454,7 +422,6 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             tc_wait_st();
             tc_fence_before();
             mbar_arrive(bar(BAR_PFULL));
-            if (tid == 0) PF_TR(3);
         }
         // epilogue: the first two chunks of the gate row are requested before the wait for the last P V
         const int t_row = t0 + r;
@@ -466,7 +433,6 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #pragma unroll
         for (int i = 0; i < 8; i++) { gn[i] = __ldg(gp + i); gn2[i] = __ldg(gp + 8 + i); }
         if (ok && ntiles > 0) ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_PVDONE), (ntiles - 1) & 1, abortp));
-        PF_CTA(2);
         if (ok) {
             // All MMAs have completed, so every K / V / q tile in shared memory is dead.  Each thread
             // gates its own row in registers -- the gate row comes straight from global memory through
@@ -477,7 +443,6 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             constexpr uint32_t kPitch = 1040;
             const float inv = l_sum > 0.f ? 1.0f / l_sum : 0.f;
             const int t = t_row;
-            PF_CTA(4);
 #pragma unroll 1
             for (int c = 0; c < kHD; c += 32) {
                 uint32_t o[32];
@@ -502,7 +467,6 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 }
             }
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-            PF_CTA(5);
             if (live) {
                 float *orow = p.out + ((size_t)t * p.H + head) * kHD;
                 asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], 1024;\n" ::"l"(orow), "r"(sQ + r * kPitch) : "memory");
@@ -513,10 +477,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         }
     }
     // ---- wind down: everyone meets, TMEM goes back ----
-    PF_CTA(6);
     tc_fence_before();
     __syncthreads();
-    PF_CTA(3);
     if (s_abort && tid == 0) atomicCAS(p.err, 0, (1 << 16) | ((blockIdx.y & 0xff) << 8) | (blockIdx.x & 0xff));
     if (warp == 5) {
         tc_fence_after();
@@ -558,11 +520,6 @@ int launch_attn_prefill(const KvView &kv, const RopeParams &rope, int seq, int s
     if (cudaGetLastError() != cudaSuccess) return -1;
     PfParams p;
     p.n = n; p.row0 = row0; p.H = H; p.Hkv = kv.Hkv;
-#ifdef FM_PF_TRACE
-    p.trace = fm_pf_trace;
-#else
-    p.trace = nullptr;
-#endif
     p.q16 = reinterpret_cast<const __half *>(wk.q16);
     p.q_proj_out = q_proj_out; p.gate = gate; p.out = out; p.err = wk.err;
     // the attention launch overlaps its set-up (barriers, TMEM allocation) with the end of the preparation

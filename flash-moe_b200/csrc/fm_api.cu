@@ -406,17 +406,21 @@ extern "C" fm_status fm_seq_fork(FmCtx *ctx, int src, int dst) {
         return fail(ctx, FM_ERR_INVALID, "fm_seq_fork: sequences %d -> %d of %d", src, dst, c.max_seqs);
     if (c.sliding_window > 0 && c.num_full_layers > 0)
         return fail(ctx, FM_ERR_UNSUPPORTED, "fm_seq_fork: pages of a sliding-window store are rewritten in place and cannot be shared");
-    fm_status st = fm_reset(ctx, dst);
-    if (st) return st;
-    // pages to copy: one per layer whose last local page is partly filled
-    size_t need = 0;
+    // pages to copy: one per layer whose last local page is partly filled.  The demand is checked before dst is
+    // touched (an error changes no state); the pages dst alone holds come back to the pool when it is reset.
+    size_t need = 0, reclaim = 0;
     for (int l = 0; l < c.num_full_layers; l++) {
         const int len = ctx->kv_len[lidx(ctx, l, src)];
         const int gp = len / c.page_size;  // the partly filled global page, if any
         if (len % c.page_size != 0 && gp % c.seq_shard_count == c.seq_shard_rank) need++;
+        const int *dtab = &ctx->h_page_table[((size_t)l * c.max_seqs + dst) * ctx->max_slots];
+        for (int s = 0; s < ctx->max_slots; s++)
+            if (dtab[s] >= 0 && ctx->page_refs[(size_t)dtab[s]] == 1) reclaim++;
     }
-    if (need > ctx->free_pages.size())
-        return fail(ctx, FM_ERR_CAPACITY, "KV page pool exhausted (%zu more pages needed, %zu free)", need, ctx->free_pages.size());
+    if (need > ctx->free_pages.size() + reclaim)
+        return fail(ctx, FM_ERR_CAPACITY, "KV page pool exhausted (%zu more pages needed, %zu free)", need, ctx->free_pages.size() + reclaim);
+    fm_status st = fm_reset(ctx, dst);
+    if (st) return st;
     const size_t page_bytes = ctx->page_elems * sizeof(__nv_bfloat16);
     for (int l = 0; l < c.num_full_layers; l++) {
         const int len = ctx->kv_len[lidx(ctx, l, src)];
@@ -844,7 +848,7 @@ extern "C" fm_status fm_gdn_decode(FmCtx *ctx, int li, const int *seq, int batch
         t.n = std::min(kMaxList, batch - i0);
         for (int i = 0; i < t.n; i++) {
             t.seq[i] = seq[i0 + i];
-            t.pos[i] = ctx->gdn_steps[lidx(ctx, li, seq[i0 + i])]++;
+            t.pos[i] = ctx->gdn_steps[lidx(ctx, li, seq[i0 + i])];
             t.row[i] = 0;
         }
         ProfScope prof(ctx);
@@ -852,6 +856,7 @@ extern "C" fm_status fm_gdn_decode(FmCtx *ctx, int li, const int *seq, int batch
                                              (long long)cn, (long long)sn, d_qkv + (size_t)i0 * ctx->conv_dim, d_z + i0 * vd, d_b + i0 * hv,
                                              d_a + i0 * hv, d_cw, d_al, d_db, d_nw, d_out + i0 * vd, ctx->stream), "gdn_decode");
         if (st) return st;
+        for (int i = 0; i < t.n; i++) ctx->gdn_steps[lidx(ctx, li, seq[i0 + i])]++;  // only once the step is queued
     }
     FM_CUDA(ctx, sg.pull(out, w_out, batch * vd));
     return FM_OK;
@@ -935,9 +940,17 @@ extern "C" fm_status fm_kv_import(FmCtx *ctx, int fa_idx, int seq, const float *
     if (c.sliding_window > 0 && len > c.sliding_window)
         return fail(ctx, FM_ERR_INVALID, "fm_kv_import: %d rows do not fit the sliding window of %d", len, c.sliding_window);
     FM_CUDA(ctx, cudaSetDevice(c.device));
-    // drop the sequence's pages (some may be shared with a fork and must not be overwritten), then take fresh ones
+    // drop the sequence's pages (some may be shared with a fork and must not be overwritten), then take fresh
+    // ones -- after checking that the pool, with the pages this sequence alone holds, covers the demand
     {
         int *tab = &ctx->h_page_table[((size_t)fa_idx * c.max_seqs + seq) * ctx->max_slots];
+        size_t reclaim = 0;
+        for (int i = 0; i < ctx->max_slots; i++)
+            if (tab[i] >= 0 && ctx->page_refs[(size_t)tab[i]] == 1) reclaim++;
+        const int gpages = (rows_held(c, len) + c.page_size - 1) / c.page_size;
+        const size_t need = gpages > c.seq_shard_rank ? (size_t)(gpages - c.seq_shard_rank + c.seq_shard_count - 1) / c.seq_shard_count : 0;
+        if (need > ctx->free_pages.size() + reclaim)
+            return fail(ctx, FM_ERR_CAPACITY, "KV page pool exhausted (%zu pages needed, %zu free)", need, ctx->free_pages.size() + reclaim);
         for (int i = 0; i < ctx->max_slots; i++)
             if (tab[i] >= 0) { release_page(ctx, tab[i]); tab[i] = -1; }
     }

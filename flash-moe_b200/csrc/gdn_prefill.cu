@@ -181,25 +181,6 @@ __global__ void gdn_ring_kernel(int C, int n, int step0, float *__restrict__ rin
             ring[(size_t)((step0 + t) & 3) * C + ch] = qkv[(size_t)t * C + ch];
 }
 
-// Optional clock trace (development builds only: -DFM_GDN_TRACE): scan CTA 0 [chunk][16 events], then one row of
-// the chunk kernel's CTA (0, 0)
-#ifdef FM_GDN_TRACE
-extern "C" {
-long long *fm_gdn_trace = nullptr;
-}
-__device__ long long *fm_gdn_trace_dev = nullptr;
-#define SC_TR(slot)                                                                              \
-    do {                                                                                         \
-        if (p.trace && blockIdx.x == 0 && j < 64) p.trace[j * 16 + (slot)] = clock64();          \
-    } while (0)
-#define CH_TR(slot)                                                                              \
-    do {                                                                                         \
-        if (fm_gdn_trace_dev && blockIdx.x == 1 && blockIdx.y == 0 && threadIdx.x == 0) fm_gdn_trace_dev[64 * 16 + (slot)] = clock64(); \
-    } while (0)
-#else
-#define SC_TR(slot) do { } while (0)
-#define CH_TR(slot) do { } while (0)
-#endif
 
 // ---- per (key head, chunk): K K^T and Q K^T (64 x 64 x 128), shared by the value heads -------------
 constexpr int kLdK = kDH + 4;   // [row][k] operands read as (row g, k t): stride = 4 mod 32
@@ -258,7 +239,6 @@ gdn_chunk_kernel(GdnDims g, int n, GdnWork w, int nchunks) {
     const int t0 = chunk * kC;
     const int total_k = g.Hk * kDH, total_v = g.Hv * kDH;
 
-    CH_TR(0);
     // rows past the end of the run are zero (beta 0, decay 1: they leave the state alone)
     for (int i = tid; i < kC * (kDH / 4); i += 256) {
         const int r = i >> 5, c4 = (i & 31) * 4;
@@ -282,7 +262,6 @@ gdn_chunk_kernel(GdnDims g, int n, GdnWork w, int nchunks) {
         cv[lane] = a; cv[32 + lane] = b;
     }
     __syncthreads();
-    CH_TR(1);
     {   // k transposed and scaled for the state update of the scan: Ks[k][i] = e^{cC - c_i} k_i[k], hi | lo
         __half *kt = w.KT16 + ((size_t)vh * nchunks + chunk) * kDH * 2 * kC;
         const float cC = sc[kC - 1];
@@ -295,7 +274,6 @@ gdn_chunk_kernel(GdnDims g, int n, GdnWork w, int nchunks) {
         }
     }
 
-    CH_TR(2);
     // A = beta_t e^{c_t - c_i} (k_t . k_i) below the diagonal, and the decay-masked q k^T for the scan, from the
     // key head's products: a thread takes 4 consecutive columns of a row
     {
@@ -322,7 +300,6 @@ gdn_chunk_kernel(GdnDims g, int n, GdnWork w, int nchunks) {
     // of U for c < 128, of W otherwise) and keeps its 64 entries in registers; A is read as broadcast
     // 128-bit loads and four partial sums shorten the dependent chain.  This replaces forming
     // T = (I + A)^-1 and multiplying by it.
-    CH_TR(3);
     if (tid < kC) sT[tid] = sb[tid] * expf(sc[tid]);  // row scale of the K block
     __syncthreads();
     {
@@ -351,7 +328,6 @@ gdn_chunk_kernel(GdnDims g, int n, GdnWork w, int nchunks) {
             for (int i = r & ~3; i < r; i++) a0 += Ar[i] * x[i];
             x[r] -= (a0 + a1) + (a2 + a3);
         }
-        CH_TR(4);
         if (is_u) {
             float *dst = w.U + ((size_t)vh * nchunks + chunk) * kC * kDH + c;
 #pragma unroll
@@ -367,7 +343,6 @@ gdn_chunk_kernel(GdnDims g, int n, GdnWork w, int nchunks) {
             }
         }
     }
-    CH_TR(5);
 }
 
 // ---- the chunk scan on the 5th-generation tensor cores ------------------------------------------
@@ -409,7 +384,6 @@ constexpr int kScSmem = kOffBar + SB_COUNT * 8 + 1024 /*alignment slack*/;
 
 
 struct ScanParams {
-    long long *trace;
     int n, nchunks, Hv, Hk;
     const float *U, *cv;
     float *ssm, *out;
@@ -488,7 +462,6 @@ gdn_scan_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                 bool ok = mbar_wait(bar(SB_SREADY), ph, abortp) && mbar_wait(bar(SB_WQFULL), ph, abortp);
                 if (!ok) break;
                 tc_fence_after();
-                SC_TR(0);
                 // [acc | O1] = S [W ; Q]^T, three terms
 #pragma unroll
                 for (int ks = 0; ks < 8; ks++) tc_mma_f16_ta(tmem + kTcAcc, tmem + kTcSh + ks * 8, dWQh + k128(ks), id128, ks > 0);
@@ -498,12 +471,10 @@ gdn_scan_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                 for (int ks = 0; ks < 8; ks++) tc_mma_f16_ta(tmem + kTcAcc, tmem + kTcSh + ks * 8, dWQl + k128(ks), id128, 1);
                 tc_commit(bar(SB_DACC));
                 tc_commit(bar(SB_WEMPTY));
-                SC_TR(1);
                 // [S | O2] += Dt [Ks ; QKm]^T, three terms (S pre-scaled, O2 zeroed by the state threads)
                 ok = mbar_wait(bar(SB_DFULL), ph, abortp) && mbar_wait(bar(SB_KQKFULL), ph, abortp);
                 if (!ok) break;
                 tc_fence_after();
-                SC_TR(4);
 #pragma unroll
                 for (int ks = 0; ks < 4; ks++) tc_mma_f16_ta(tmem + kTcS, tmem + kTcDh + ks * 8, dKQh + kin(ks), id192, 1);
 #pragma unroll
@@ -512,7 +483,6 @@ gdn_scan_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                 for (int ks = 0; ks < 4; ks++) tc_mma_f16_ta(tmem + kTcS, tmem + kTcDh + ks * 8, dKQl + kin(ks), id192, 1);
                 tc_commit(bar(SB_CDONE));
                 tc_commit(bar(SB_KEMPTY));
-                SC_TR(5);
             }
         }
     } else {
@@ -564,7 +534,6 @@ gdn_scan_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                 ok = __all_sync(0xffffffffu, mbar_wait(bar(SB_UFULL), ph, abortp) && mbar_wait(bar(SB_DACC), ph, abortp));
                 if (!ok) break;
                 tc_fence_after();
-                if (tid == 0) SC_TR(8);
                 uint32_t a0[32];
                 tc_ld32(tmem + lane_base + kTcAcc + h * 32, a0);
                 float u[32];
@@ -586,13 +555,11 @@ gdn_scan_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                 tc_wait_st();
                 tc_fence_before();
                 mbar_arrive(bar(SB_DFULL));
-                if (tid == 0) SC_TR(9);
             }
             // the new state: two-term copy for the next chunk's products, accumulator pre-scaled for its update
             ok = __all_sync(0xffffffffu, mbar_wait(bar(SB_CDONE), ph, abortp));
             if (!ok) break;
             tc_fence_after();
-            if (tid == 0) SC_TR(12);
             // the output accumulators go to registers first: the next chunk's first product overwrites O1
             uint32_t o1[32], o2[32];
             tc_ld32(tmem + lane_base + kTcO1 + h * 32, o1);
@@ -616,7 +583,6 @@ gdn_scan_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             tc_wait_st();
             tc_fence_before();
             mbar_arrive(bar(SB_SREADY));
-            if (tid == 0) SC_TR(13);
             // output rows of this chunk (off the critical path: the next chunk's first product runs meanwhile)
             {
                 float *orow = p.out + (size_t)t0 * total_v + (size_t)vh * kDH + r;
@@ -625,7 +591,6 @@ gdn_scan_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                     const float sc = __shfl_sync(0xffffffffu, ev, i);
                     if (t0 + i < p.n) orow[(size_t)i * total_v] = sc * __uint_as_float(o1[i]) + __uint_as_float(o2[i]);
                 }
-                if (tid == 0) SC_TR(15);
             }
         }
         if (ok) {  // final state back to memory
@@ -723,9 +688,6 @@ int launch_gdn_prefill(const GdnDims &g, int n, int chunk, int step0, float *con
             return -1;
     }
     const int nchunks = (n + kC - 1) / kC;
-#ifdef FM_GDN_TRACE
-    cudaMemcpyToSymbolAsync(fm_gdn_trace_dev, &fm_gdn_trace, sizeof(long long *), 0, cudaMemcpyHostToDevice, st);
-#endif
     gdn_prep_kernel<<<n, 512, g.conv_dim * 4, st>>>(g, n, step0, conv_state, qkv, beta, alpha, conv_w, A_log, dt_bias, w);
     gdn_ring_kernel<<<dim3(12, 3), 256, 0, st>>>(g.conv_dim, n, step0, conv_state, qkv);
     gdn_kk_kernel<<<dim3(nchunks, g.Hk), 256, kKkSmem, st>>>(g, n, w, nchunks);
@@ -741,11 +703,6 @@ int launch_gdn_prefill(const GdnDims &g, int n, int chunk, int step0, float *con
         ScanParams sp;
         sp.n = n; sp.nchunks = nchunks; sp.Hv = g.Hv; sp.Hk = g.Hk;
         sp.U = w.U; sp.cv = w.cv; sp.ssm = ssm_state; sp.out = out; sp.err = err;
-#ifdef FM_GDN_TRACE
-        sp.trace = fm_gdn_trace;
-#else
-        sp.trace = nullptr;
-#endif
         gdn_scan_kernel<<<g.Hv, kScThreads, kScSmem, st>>>(mw, mq, mqk, mkt, mu, sp);
     }
     int launches = 5;

@@ -208,6 +208,46 @@ def test_overflow_and_bad_arguments(pkg, synth):
     assert e.value.status == pkg.binding.FM_ERR_UNSUPPORTED
 
 
+@pytest.mark.parametrize("batch,ctx", [(1, 32768), (1, 131072), (8, 32768), (8, 131072)])
+def test_quoted_sizes_against_checker(pkg, port, batch, ctx):
+    """The contexts and batch sizes the throughput figures are quoted on, compared with the CPU checker
+    directly: batch 1 (every split of the sequence on its own SM, the splits merged in two levels) and batch 8
+    (the bench's launch shape, one layer).  Rows are made on the device (seeded), copied to the host for the
+    checker one sequence at a time."""
+    import torch
+    from oracle.oracle_py import host_threads
+    dev = torch.device("cuda:0")
+    cfg = pkg.default_config(num_full_layers=1, num_linear_layers=0, max_seqs=batch, max_seq_len=ctx + 64,
+                             max_batch_tokens=64)
+    c = pkg.Context(cfg)
+    c.set_stream(torch.cuda.current_stream().cuda_stream)
+    gen = torch.Generator(device=dev); gen.manual_seed(1000 + ctx + batch)
+    q = torch.randn((batch, 8192), device=dev, generator=gen)
+    g = torch.randn((batch, 8192), device=dev, generator=gen)
+    k = torch.randn((batch, 512), device=dev, generator=gen).bfloat16().float()
+    v = torch.randn((batch, 512), device=dev, generator=gen).bfloat16().float()
+    qh, gh, kh, vh = (t.cpu().numpy() for t in (q, g, k, v))
+    refs = []
+    for s in range(batch):
+        K = torch.randn((ctx, 512), device=dev, generator=gen).bfloat16().float()
+        V = torch.randn((ctx, 512), device=dev, generator=gen).bfloat16().float()
+        c.kv_import(0, s, K, V, ctx)
+        r, _, _ = oracle_attn(port, 32, 2, K.cpu().numpy(), V.cpu().numpy(), qh[s:s + 1], gh[s:s + 1], kh[s:s + 1],
+                              vh[s:s + 1], threads=host_threads())
+        refs.append(r)
+        del K, V
+    out = torch.empty((batch, 8192), device=dev)
+    c.attn_decode(0, list(range(batch)), [ctx] * batch, out, q=q, gate=g, k=k, v=v)
+    c.synchronize()
+    got = out.cpu().numpy()
+    for s in range(batch):
+        gated, mom, rr = rel_errors(got[s], refs[s])
+        print("batch", batch, "ctx", ctx, "seq", s, "gated", gated, "rms-rel", rr)
+        assert gated <= TOL
+        assert c.kv_len(0, s) == ctx + 1
+    c.close()
+
+
 def test_full_size_properties_128k(pkg, synth):
     """Size-independent checks at the largest context: softmax weights sum to one (V = 1 gives
     out = sigmoid(gate)) and the result is linear in V."""

@@ -20,7 +20,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("world", [2, 4, 8])
 def test_layers_call_with_peer_exchange_matches_checker(world):
     import torch
     if torch.cuda.device_count() < world:
