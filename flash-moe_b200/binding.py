@@ -15,6 +15,7 @@ LIB_PATH = HERE / "libfm_b200.so"
 
 FM_OK, FM_ERR_INVALID, FM_ERR_CAPACITY, FM_ERR_NOMEM, FM_ERR_CUDA, FM_ERR_TIMEOUT, FM_ERR_UNSUPPORTED = range(7)
 FM_PTR_DEVICE, FM_PTR_HOST = 0, 1
+FM_KV_BF16, FM_KV_FP8_E4M3 = 0, 1
 
 EXPORTS = [
     "fm_default_config", "fm_create", "fm_destroy", "fm_last_error", "fm_set_stream",
@@ -24,6 +25,7 @@ EXPORTS = [
     "fm_state_import", "fm_launch_count", "fm_profile_enable", "fm_profile_read",
     "fm_attn_decode_static", "fm_exchange_bytes", "fm_exchange_attach", "fm_attn_decode_exchange_push",
     "fm_attn_decode_exchange_merge", "fm_attn_decode_exchange", "fm_attn_decode_layers",
+    "fm_kv_export_fp8", "fm_kv_import_fp8",
 ]
 
 
@@ -39,7 +41,7 @@ class FmConfig(C.Structure):
         ("max_seqs", C.c_int), ("max_seq_len", C.c_int), ("page_size", C.c_int),
         ("kv_pool_pages", C.c_int64), ("max_batch_tokens", C.c_int),
         ("seq_shard_rank", C.c_int), ("seq_shard_count", C.c_int), ("device", C.c_int),
-        ("sliding_window", C.c_int),
+        ("sliding_window", C.c_int), ("kv_dtype", C.c_int),
     ]
 
 
@@ -284,6 +286,16 @@ class Context:
     def kv_import(self, fa_idx, seq, k, v, length):
         self._check(self.lib.fm_kv_import(self.h, C.c_int(fa_idx), C.c_int(seq), _ptr(k), _ptr(v),
                                           C.c_int(length)))
+
+    def kv_export_fp8(self, fa_idx, seq, k8, v8, k_scales, v_scales, max_rows) -> int:
+        n = C.c_int(0)
+        self._check(self.lib.fm_kv_export_fp8(self.h, C.c_int(fa_idx), C.c_int(seq), _ptr(k8), _ptr(v8), _ptr(k_scales),
+                                              _ptr(v_scales), C.c_int(max_rows), C.byref(n)))
+        return n.value
+
+    def kv_import_fp8(self, fa_idx, seq, k8, v8, k_scales, v_scales, length):
+        self._check(self.lib.fm_kv_import_fp8(self.h, C.c_int(fa_idx), C.c_int(seq), _ptr(k8), _ptr(v8), _ptr(k_scales),
+                                              _ptr(v_scales), C.c_int(length)))
 
     def state_export(self, li, seq, conv, ssm):
         self._check(self.lib.fm_state_export(self.h, C.c_int(li), C.c_int(seq), _ptr(conv), _ptr(ssm)))

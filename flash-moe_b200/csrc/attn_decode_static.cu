@@ -101,7 +101,9 @@ extern "C" fm_status fm_attn_decode_static(const FmStaticDecodeArgs *a, char *er
     rope.logit_scale = 1.0f / sqrtf(256.0f);
 
     KvView kv;
-    kv.pool = reinterpret_cast<__nv_bfloat16 *>(const_cast<void *>(a->kv_pages));
+    kv.pool = reinterpret_cast<unsigned char *>(const_cast<void *>(a->kv_pages));
+    kv.page_bytes = fm::kv_page_bytes(0, a->num_kv_heads, 64, 256);
+    kv.fp8 = 0;
     kv.page_table = a->page_table;
     kv.max_slots = a->max_pages_per_seq;
     kv.page_size = 64;
@@ -120,10 +122,7 @@ extern "C" fm_status fm_attn_decode_static(const FmStaticDecodeArgs *a, char *er
                     a->max_pages_per_seq);
             return FM_ERR_INVALID;
         }
-        t.seq[i] = i;
-        t.pos[i] = a->pos[i];
-        t.row[i] = a->kv_len[i] - 1;
-        t.nrows[i] = a->kv_len[i];
+        t.set(i, i, a->pos[i], a->kv_len[i] - 1, a->kv_len[i]);
         max_len = std::max(max_len, a->kv_len[i]);
     }
     // splits: fill the SMs, stay within the pages available and within the fixed scratch

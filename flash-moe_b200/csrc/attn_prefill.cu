@@ -96,11 +96,11 @@ attn_prefill_prep_kernel(KvView kv, RopeParams rope, PrepParams p) {
         const int row = b - p.n - p.n * kv.Hkv;
         const int page = kv.page_table[(size_t)p.seq * kv.max_slots + row / kv.page_size];
         const int r = row % kv.page_size;
-        const size_t page_elems = (size_t)2 * kv.Hkv * kv.page_size * kHD;
+        const unsigned char *pgb = kv_page(kv, page);
         for (int e = tid; e < kv.Hkv * kHD; e += 256) {
             const int kvh = e / kHD, d = e - kvh * kHD;
-            const __nv_bfloat16 *kp = kv.pool + (size_t)page * page_elems + ((size_t)kvh * kv.page_size + r) * kHD + d;
-            const __nv_bfloat16 *vp = kp + (size_t)kv.Hkv * kv.page_size * kHD;
+            const __nv_bfloat16 *kp = reinterpret_cast<const __nv_bfloat16 *>(pgb + kv_tile_offset(kv, 0, kvh)) + (size_t)r * kHD + d;
+            const __nv_bfloat16 *vp = reinterpret_cast<const __nv_bfloat16 *>(pgb + kv_tile_offset(kv, 1, kvh)) + (size_t)r * kHD + d;
             p.k16[(size_t)row * kv.Hkv * kHD + e] = __float2half_rn(clamp_f16(__bfloat162float(*kp)));
             p.v16[(size_t)row * kv.Hkv * kHD + e] = __float2half_rn(clamp_f16(__bfloat162float(*vp)));
         }
@@ -134,9 +134,9 @@ attn_prefill_prep_kernel(KvView kv, RopeParams rope, PrepParams p) {
         const __nv_bfloat16 kb = __float2bfloat16_rn(x), vb = __float2bfloat16_rn(p.v[src]);
         const int gpage = row / kv.page_size, r = row - gpage * kv.page_size;
         const int page = kv.page_table[(size_t)p.seq * kv.max_slots + gpage];
-        __nv_bfloat16 *pg = kv.pool + (size_t)page * ((size_t)2 * kv.Hkv * kv.page_size * kHD);
-        pg[((size_t)kvh * kv.page_size + r) * kHD + d] = kb;
-        pg[((size_t)(kv.Hkv + kvh) * kv.page_size + r) * kHD + d] = vb;
+        unsigned char *pg = kv_page(kv, page);
+        reinterpret_cast<__nv_bfloat16 *>(pg + kv_tile_offset(kv, 0, kvh))[(size_t)r * kHD + d] = kb;
+        reinterpret_cast<__nv_bfloat16 *>(pg + kv_tile_offset(kv, 1, kvh))[(size_t)r * kHD + d] = vb;
         p.k16[((size_t)row * kv.Hkv + kvh) * kHD + d] = __float2half_rn(clamp_f16(__bfloat162float(kb)));
         p.v16[((size_t)row * kv.Hkv + kvh) * kHD + d] = __float2half_rn(clamp_f16(__bfloat162float(vb)));
         return;

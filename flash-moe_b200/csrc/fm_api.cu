@@ -50,6 +50,7 @@ extern "C" void fm_default_config(FmConfig *c) {
     c->max_seqs = 1; c->max_seq_len = 8192; c->page_size = 64; c->kv_pool_pages = 0;
     c->max_batch_tokens = 64;
     c->seq_shard_rank = 0; c->seq_shard_count = 1; c->device = 0;
+    c->kv_dtype = FM_KV_BF16;
 }
 
 // RoPE frequency of pair i under the scaling modes of metal_infer/layer_forward.h:22-63, evaluated
@@ -100,6 +101,10 @@ extern "C" fm_status fm_create(const FmConfig *cfg, FmCtx **out) {
         if (c.max_seq_len < 1) return fail(nullptr, FM_ERR_INVALID, "fm_create: max_seq_len %d", c.max_seq_len);
         if (c.sliding_window < 0 || c.sliding_window > c.max_seq_len)
             return fail(nullptr, FM_ERR_INVALID, "fm_create: sliding_window %d (0, or 1..max_seq_len)", c.sliding_window);
+        if (c.kv_dtype != FM_KV_BF16 && c.kv_dtype != FM_KV_FP8_E4M3)
+            return fail(nullptr, FM_ERR_INVALID, "fm_create: kv_dtype %d (FM_KV_BF16 or FM_KV_FP8_E4M3)", c.kv_dtype);
+        if (c.kv_dtype == FM_KV_FP8_E4M3 && c.num_kv_heads > 8)
+            return fail(nullptr, FM_ERR_UNSUPPORTED, "fm_create: an FP8 store takes at most 8 KV heads per context (%d)", c.num_kv_heads);
     }
     if (has_gdn) {
         if (c.linear_key_dim != 128 || c.linear_value_dim != 128 || c.conv_kernel_size != 4)
@@ -147,12 +152,12 @@ extern "C" fm_status fm_create(const FmConfig *cfg, FmCtx **out) {
         const int max_rows = c.sliding_window > 0 ? std::min(c.max_seq_len, c.sliding_window) : c.max_seq_len;
         const int gpages = (max_rows + c.page_size - 1) / c.page_size;
         ctx->max_slots = (gpages + c.seq_shard_count - 1) / c.seq_shard_count;
-        ctx->page_elems = (size_t)2 * c.num_kv_heads * c.page_size * c.head_dim;
+        ctx->page_bytes = kv_page_bytes(c.kv_dtype == FM_KV_FP8_E4M3, c.num_kv_heads, c.page_size, c.head_dim);
         ctx->pool_pages = c.kv_pool_pages > 0 ? c.kv_pool_pages
                                               : (int64_t)ctx->max_slots * c.max_seqs * c.num_full_layers;
-        CREATE_CUDA(cudaMalloc(&ctx->pool, (size_t)ctx->pool_pages * ctx->page_elems * sizeof(__nv_bfloat16)));
+        CREATE_CUDA(cudaMalloc(&ctx->pool, (size_t)ctx->pool_pages * ctx->page_bytes));
         // zero so that rows past a sequence's end hold finite values (they meet zero weights)
-        CREATE_CUDA(cudaMemset(ctx->pool, 0, (size_t)ctx->pool_pages * ctx->page_elems * sizeof(__nv_bfloat16)));
+        CREATE_CUDA(cudaMemset(ctx->pool, 0, (size_t)ctx->pool_pages * ctx->page_bytes));
         const size_t nent = (size_t)c.num_full_layers * c.max_seqs * ctx->max_slots;
         ctx->h_page_table.assign(nent, -1);
         CREATE_CUDA(cudaMalloc(&ctx->d_page_table, nent * sizeof(int)));
@@ -316,6 +321,8 @@ static inline size_t lidx(const FmCtx *ctx, int layer, int seq) { return (size_t
 static KvView kv_view(const FmCtx *ctx, int fa_idx) {
     KvView v;
     v.pool = ctx->pool;
+    v.page_bytes = ctx->page_bytes;
+    v.fp8 = ctx->cfg.kv_dtype == FM_KV_FP8_E4M3;
     v.page_table = ctx->d_page_table + (size_t)fa_idx * ctx->cfg.max_seqs * ctx->max_slots;
     v.max_slots = ctx->max_slots;
     v.page_size = ctx->cfg.page_size;
@@ -421,7 +428,7 @@ extern "C" fm_status fm_seq_fork(FmCtx *ctx, int src, int dst) {
         return fail(ctx, FM_ERR_CAPACITY, "KV page pool exhausted (%zu more pages needed, %zu free)", need, ctx->free_pages.size() + reclaim);
     fm_status st = fm_reset(ctx, dst);
     if (st) return st;
-    const size_t page_bytes = ctx->page_elems * sizeof(__nv_bfloat16);
+    const size_t page_bytes = ctx->page_bytes;
     for (int l = 0; l < c.num_full_layers; l++) {
         const int len = ctx->kv_len[lidx(ctx, l, src)];
         int *stab = &ctx->h_page_table[((size_t)l * c.max_seqs + src) * ctx->max_slots];
@@ -434,7 +441,7 @@ extern "C" fm_status fm_seq_fork(FmCtx *ctx, int src, int dst) {
                 ctx->page_refs[(size_t)stab[s]]++;
             } else if (gp * c.page_size < len) {
                 dtab[s] = take_page(ctx);
-                FM_CUDA(ctx, cudaMemcpyAsync(ctx->pool + (size_t)dtab[s] * ctx->page_elems, ctx->pool + (size_t)stab[s] * ctx->page_elems,
+                FM_CUDA(ctx, cudaMemcpyAsync(ctx->pool + (size_t)dtab[s] * page_bytes, ctx->pool + (size_t)stab[s] * page_bytes,
                                              page_bytes, cudaMemcpyDeviceToDevice, ctx->stream));
             }
         }
@@ -520,7 +527,7 @@ static fm_status append_list(FmCtx *ctx, int fa_idx, const int *seq, const int *
         TokSpec t;
         t.mode = 0;
         t.n = std::min(kMaxList, n - i0);
-        for (int i = 0; i < t.n; i++) { t.seq[i] = seq[i0 + i]; t.pos[i] = pos[i0 + i]; t.row[i] = rows[i0 + i]; t.nrows[i] = rows[i0 + i] + 1; }
+        for (int i = 0; i < t.n; i++) t.set(i, seq[i0 + i], pos[i0 + i], rows[i0 + i], rows[i0 + i] + 1);
         fm_status st = launched(ctx, launch_kv_append(kv, ctx->rope, t, k + i0 * kv_dim, v + i0 * kv_dim, knw, ctx->cfg.rms_norm_eps, ctx->stream), "kv_append");
         if (st) return st;
     }
@@ -661,7 +668,7 @@ static fm_status decode_core(FmCtx *ctx, int fa_idx, const int *seq, const int *
         t.n = std::min(kMaxList, batch - i0);
         int max_len = 1;
         for (int i = 0; i < t.n; i++) {
-            t.seq[i] = seq[i0 + i]; t.pos[i] = pos[i0 + i]; t.row[i] = rows[i0 + i]; t.nrows[i] = nrows[i0 + i];
+            t.set(i, seq[i0 + i], pos[i0 + i], rows[i0 + i], nrows[i0 + i]);
             max_len = std::max(max_len, nrows[i0 + i]);
         }
         const int ns = pick_splits(ctx, t.n, max_len);
@@ -670,14 +677,22 @@ static fm_status decode_core(FmCtx *ctx, int fa_idx, const int *seq, const int *
         const float *gp = gate ? gate + (size_t)i0 * H * D : nullptr;
         float *op = (out ? out : o_part) + (size_t)i0 * H * D;
         float *mlp = ml_part ? ml_part + (size_t)i0 * H * 2 : nullptr;
-        // one launch: append of the new rows, split-KV attention, merge of the splits, gate
+        // One launch: append of the new rows, split-KV attention, merge of the splits, gate.  When a sequence is split
+        // over the whole machine (small batch) one CTA cannot merge all the parts quickly -- it would pull more than
+        // a megabyte through a single SM -- so the launch stops at the parts (tail 0) and a merge launch with a CTA
+        // per (head, token) follows as its programmatic dependent.
         ProfScope prof(ctx);
         const LayerScratch ls = layer_scratch(ctx, fa_idx);
+        const bool wide = ns > kDecMaxLastCtaSplits;
         fm_status st = launched(ctx, launch_attn_decode_fused(kv, ctx->rope, t, H, qp, qq, qnw, c.rms_norm_eps, ls.part_o, ls.part_ml, ns,
-                                                              k ? k + i0 * kvd : nullptr, v ? v + i0 * kvd : nullptr, knw, out ? 1 : 2, gp, op, mlp,
-                                                              nullptr, 0, ls.scr, ctx->d_err, ctx->overlap_prev && i0 == 0 && !sg_host(ctx),
-                                                              ctx->stream), "attn_decode");
+                                                              k ? k + i0 * kvd : nullptr, v ? v + i0 * kvd : nullptr, knw, wide ? 0 : (out ? 1 : 2),
+                                                              gp, op, mlp, nullptr, 0, ls.scr, ctx->d_err,
+                                                              ctx->overlap_prev && i0 == 0 && !sg_host(ctx), ctx->stream), "attn_decode");
         if (st) return st;
+        if (wide) {
+            st = launched(ctx, launch_attn_merge_wide(ls.part_o, ls.part_ml, ns, t.n, H, qp, gp, op, mlp, ctx->stream), "attn_merge");
+            if (st) return st;
+        }
     }
     return FM_OK;
 }
@@ -773,6 +788,7 @@ extern "C" fm_status fm_attn_prefill(FmCtx *ctx, int fa_idx, int seq, int start_
     if (fa_idx < 0 || fa_idx >= c.num_full_layers || seq < 0 || seq >= c.max_seqs) return fail(ctx, FM_ERR_INVALID, "fm_attn_prefill: layer %d / seq %d", fa_idx, seq);
     if (n < 0 || n > c.max_batch_tokens) return fail(ctx, FM_ERR_INVALID, "fm_attn_prefill: n=%d exceeds max_batch_tokens=%d", n, c.max_batch_tokens);
     if (c.seq_shard_count != 1) return fail(ctx, FM_ERR_UNSUPPORTED, "fm_attn_prefill: needs the whole sequence on one context (seq_shard_count=1)");
+    if (c.kv_dtype != FM_KV_BF16) return fail(ctx, FM_ERR_UNSUPPORTED, "fm_attn_prefill: the store is FP8; feed the prompt through fm_attn_decode");
     if (n == 0) return FM_OK;
     FM_CUDA(ctx, cudaSetDevice(c.device));
     const size_t qd = (size_t)c.num_attn_heads * c.head_dim, kvd = (size_t)c.num_kv_heads * c.head_dim;
@@ -847,9 +863,7 @@ extern "C" fm_status fm_gdn_decode(FmCtx *ctx, int li, const int *seq, int batch
         t.mode = 0;
         t.n = std::min(kMaxList, batch - i0);
         for (int i = 0; i < t.n; i++) {
-            t.seq[i] = seq[i0 + i];
-            t.pos[i] = ctx->gdn_steps[lidx(ctx, li, seq[i0 + i])];
-            t.row[i] = 0;
+            t.set(i, seq[i0 + i], ctx->gdn_steps[lidx(ctx, li, seq[i0 + i])], 0, 0);
         }
         ProfScope prof(ctx);
         st = launched(ctx, launch_gdn_decode(g, t, ctx->d_conv_state + (size_t)li * c.max_seqs * cn, ctx->d_ssm_state + (size_t)li * c.max_seqs * sn,
@@ -902,75 +916,167 @@ extern "C" fm_status fm_gdn_prefill(FmCtx *ctx, int li, int seq, int n, int chun
 }
 
 // ---- snapshot / restore -----------------------------------------------------------------------
+// Host-pointer mode moves the rows through the context's own staging pair in chunks (no allocation per call:
+// the reference takes and restores this snapshot per request, metal_infer/generate.h:897-939).
+template <typename Row>  // Row(row0, n, d_k, d_v, d_ks, d_vs, h_k, h_v, h_ks, h_vs, to_device) handles one chunk
+static fm_status staged_rows(FmCtx *ctx, int len, size_t row_bytes_each, bool with_scales, Row chunk_fn) {
+    // staging layout per chunk of n rows: k | v | k_scales | v_scales
+    const size_t per_row = 2 * row_bytes_each + (with_scales ? 8 : 0);
+    const int chunk = (int)std::min<size_t>((size_t)len, std::max<size_t>(1, (ctx->stage_bytes - 1024) / per_row));
+    for (int row0 = 0; row0 < len; row0 += chunk) {
+        const int n = std::min(chunk, len - row0);
+        const size_t o_v = ((size_t)n * row_bytes_each + 255) & ~(size_t)255, o_ks = 2 * o_v, o_vs = o_ks + (((size_t)n * 4 + 255) & ~(size_t)255);
+        const fm_status st = chunk_fn(row0, n, o_v, o_ks, o_vs);
+        if (st) return st;
+    }
+    return FM_OK;
+}
+
+static fm_status kv_export_check(FmCtx *ctx, const char *fn, int fa_idx, int seq, bool ptrs_ok, int max_rows, int *len_out, int *len) {
+    const FmConfig &c = ctx->cfg;
+    if (fa_idx < 0 || fa_idx >= c.num_full_layers || seq < 0 || seq >= c.max_seqs || !ptrs_ok)
+        return fail(ctx, FM_ERR_INVALID, "%s: bad argument", fn);
+    *len = rows_held(c, ctx->kv_len[lidx(ctx, fa_idx, seq)]);  // rows in store order (a wrapped window is not unrolled)
+    if (len_out) *len_out = *len;
+    if (*len > max_rows) return fail(ctx, FM_ERR_INVALID, "%s: %d rows held, room for %d", fn, *len, max_rows);
+    return FM_OK;
+}
+
 extern "C" fm_status fm_kv_export(FmCtx *ctx, int fa_idx, int seq, float *k, float *v, int max_rows, int *len_out) {
     if (!ctx) return FM_ERR_INVALID;
     const FmConfig &c = ctx->cfg;
-    if (fa_idx < 0 || fa_idx >= c.num_full_layers || seq < 0 || seq >= c.max_seqs || !k || !v)
-        return fail(ctx, FM_ERR_INVALID, "fm_kv_export: bad argument");
-    const int len = rows_held(c, ctx->kv_len[lidx(ctx, fa_idx, seq)]);  // rows in store order (a wrapped window is not unrolled)
-    if (len_out) *len_out = len;
-    if (len > max_rows) return fail(ctx, FM_ERR_INVALID, "fm_kv_export: %d rows held, room for %d", len, max_rows);
-    if (len == 0) return FM_OK;
+    int len = 0;
+    fm_status st = kv_export_check(ctx, "fm_kv_export", fa_idx, seq, k && v, max_rows, len_out, &len);
+    if (st || len == 0) return st;
     FM_CUDA(ctx, cudaSetDevice(c.device));
     const size_t kvd = (size_t)c.num_kv_heads * c.head_dim;
     const KvView kv = kv_view(ctx, fa_idx);
     if (ctx->ptr_mode == FM_PTR_DEVICE)
-        return launched(ctx, launch_kv_export(kv, seq, len, k, v, ctx->stream), "kv_export");
-    // host pointers: go through a temporary device image (snapshot path, not a hot path)
-    float *tmp = nullptr;
-    FM_CUDA(ctx, cudaMalloc(&tmp, 2 * (size_t)len * kvd * sizeof(float)));
-    cudaMemsetAsync(tmp, 0, 2 * (size_t)len * kvd * sizeof(float), ctx->stream);
-    fm_status st = launched(ctx, launch_kv_export(kv, seq, len, tmp, tmp + (size_t)len * kvd, ctx->stream), "kv_export");
-    if (st == FM_OK) {
-        cudaError_t e = cudaMemcpyAsync(k, tmp, (size_t)len * kvd * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream);
-        if (e == cudaSuccess) e = cudaMemcpyAsync(v, tmp + (size_t)len * kvd, (size_t)len * kvd * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream);
-        if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
-        if (e != cudaSuccess) st = fail(ctx, FM_ERR_CUDA, "fm_kv_export: %s", cudaGetErrorString(e));
-    }
-    cudaFree(tmp);
-    return st;
+        return launched(ctx, launch_kv_export(kv, seq, 0, len, k, v, ctx->stream), "kv_export");
+    return staged_rows(ctx, len, kvd * 4, false, [&](int row0, int n, size_t o_v, size_t, size_t) -> fm_status {
+        float *dk = reinterpret_cast<float *>(ctx->d_stage), *dv = reinterpret_cast<float *>(ctx->d_stage + o_v);
+        // rows another shard holds are left alone in the caller's arrays: start from what is there
+        memcpy(ctx->h_stage, k + (size_t)row0 * kvd, (size_t)n * kvd * 4);
+        memcpy(ctx->h_stage + o_v, v + (size_t)row0 * kvd, (size_t)n * kvd * 4);
+        FM_CUDA(ctx, cudaMemcpyAsync(ctx->d_stage, ctx->h_stage, o_v + (size_t)n * kvd * 4, cudaMemcpyHostToDevice, ctx->stream));
+        const fm_status s2 = launched(ctx, launch_kv_export(kv, seq, row0, n, dk, dv, ctx->stream), "kv_export");
+        if (s2) return s2;
+        FM_CUDA(ctx, cudaMemcpyAsync(ctx->h_stage, ctx->d_stage, o_v + (size_t)n * kvd * 4, cudaMemcpyDeviceToHost, ctx->stream));
+        FM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        memcpy(k + (size_t)row0 * kvd, ctx->h_stage, (size_t)n * kvd * 4);
+        memcpy(v + (size_t)row0 * kvd, ctx->h_stage + o_v, (size_t)n * kvd * 4);
+        return FM_OK;
+    });
+}
+
+// Drops the sequence's pages of one layer (some may be shared with a fork and must not be overwritten) and takes
+// fresh ones for `len` rows -- after checking that the pool, with the pages this sequence alone holds, covers the
+// demand, so that an error changes nothing.
+static fm_status kv_import_prepare(FmCtx *ctx, const char *fn, int fa_idx, int seq, bool ptrs_ok, int len) {
+    const FmConfig &c = ctx->cfg;
+    if (fa_idx < 0 || fa_idx >= c.num_full_layers || seq < 0 || seq >= c.max_seqs || len < 0 || (len > 0 && !ptrs_ok))
+        return fail(ctx, FM_ERR_INVALID, "%s: bad argument", fn);
+    if (len > c.max_seq_len) return fail(ctx, FM_ERR_CAPACITY, "KV cache overflow (pos=%d >= cap=%d)", len - 1, c.max_seq_len);
+    if (c.sliding_window > 0 && len > c.sliding_window)
+        return fail(ctx, FM_ERR_INVALID, "%s: %d rows do not fit the sliding window of %d", fn, len, c.sliding_window);
+    FM_CUDA(ctx, cudaSetDevice(c.device));
+    int *tab = &ctx->h_page_table[((size_t)fa_idx * c.max_seqs + seq) * ctx->max_slots];
+    size_t reclaim = 0;
+    for (int i = 0; i < ctx->max_slots; i++)
+        if (tab[i] >= 0 && ctx->page_refs[(size_t)tab[i]] == 1) reclaim++;
+    const int gpages = (rows_held(c, len) + c.page_size - 1) / c.page_size;
+    const size_t need = gpages > c.seq_shard_rank ? (size_t)(gpages - c.seq_shard_rank + c.seq_shard_count - 1) / c.seq_shard_count : 0;
+    if (need > ctx->free_pages.size() + reclaim)
+        return fail(ctx, FM_ERR_CAPACITY, "KV page pool exhausted (%zu pages needed, %zu free)", need, ctx->free_pages.size() + reclaim);
+    for (int i = 0; i < ctx->max_slots; i++)
+        if (tab[i] >= 0) { release_page(ctx, tab[i]); tab[i] = -1; }
+    const fm_status st = ensure_pages(ctx, fa_idx, seq, len);
+    if (st) return st;
+    ctx->kv_len[lidx(ctx, fa_idx, seq)] = len;
+    return FM_OK;
 }
 
 extern "C" fm_status fm_kv_import(FmCtx *ctx, int fa_idx, int seq, const float *k, const float *v, int len) {
     if (!ctx) return FM_ERR_INVALID;
     const FmConfig &c = ctx->cfg;
-    if (fa_idx < 0 || fa_idx >= c.num_full_layers || seq < 0 || seq >= c.max_seqs || len < 0 || (len > 0 && (!k || !v)))
-        return fail(ctx, FM_ERR_INVALID, "fm_kv_import: bad argument");
-    if (len > c.max_seq_len) return fail(ctx, FM_ERR_CAPACITY, "KV cache overflow (pos=%d >= cap=%d)", len - 1, c.max_seq_len);
-    if (c.sliding_window > 0 && len > c.sliding_window)
-        return fail(ctx, FM_ERR_INVALID, "fm_kv_import: %d rows do not fit the sliding window of %d", len, c.sliding_window);
-    FM_CUDA(ctx, cudaSetDevice(c.device));
-    // drop the sequence's pages (some may be shared with a fork and must not be overwritten), then take fresh
-    // ones -- after checking that the pool, with the pages this sequence alone holds, covers the demand
-    {
-        int *tab = &ctx->h_page_table[((size_t)fa_idx * c.max_seqs + seq) * ctx->max_slots];
-        size_t reclaim = 0;
-        for (int i = 0; i < ctx->max_slots; i++)
-            if (tab[i] >= 0 && ctx->page_refs[(size_t)tab[i]] == 1) reclaim++;
-        const int gpages = (rows_held(c, len) + c.page_size - 1) / c.page_size;
-        const size_t need = gpages > c.seq_shard_rank ? (size_t)(gpages - c.seq_shard_rank + c.seq_shard_count - 1) / c.seq_shard_count : 0;
-        if (need > ctx->free_pages.size() + reclaim)
-            return fail(ctx, FM_ERR_CAPACITY, "KV page pool exhausted (%zu pages needed, %zu free)", need, ctx->free_pages.size() + reclaim);
-        for (int i = 0; i < ctx->max_slots; i++)
-            if (tab[i] >= 0) { release_page(ctx, tab[i]); tab[i] = -1; }
-    }
-    fm_status st = ensure_pages(ctx, fa_idx, seq, len);
-    if (st) return st;
-    ctx->kv_len[lidx(ctx, fa_idx, seq)] = len;
-    if (len == 0) return FM_OK;
+    fm_status st = kv_import_prepare(ctx, "fm_kv_import", fa_idx, seq, k && v, len);
+    if (st || len == 0) return st;
     const size_t kvd = (size_t)c.num_kv_heads * c.head_dim;
     const KvView kv = kv_view(ctx, fa_idx);
     if (ctx->ptr_mode == FM_PTR_DEVICE)
-        return launched(ctx, launch_kv_import(kv, seq, len, k, v, ctx->stream), "kv_import");
-    float *tmp = nullptr;
-    FM_CUDA(ctx, cudaMalloc(&tmp, 2 * (size_t)len * kvd * sizeof(float)));
-    cudaError_t e = cudaMemcpyAsync(tmp, k, (size_t)len * kvd * sizeof(float), cudaMemcpyHostToDevice, ctx->stream);
-    if (e == cudaSuccess) e = cudaMemcpyAsync(tmp + (size_t)len * kvd, v, (size_t)len * kvd * sizeof(float), cudaMemcpyHostToDevice, ctx->stream);
-    st = e == cudaSuccess ? launched(ctx, launch_kv_import(kv, seq, len, tmp, tmp + (size_t)len * kvd, ctx->stream), "kv_import")
-                          : fail(ctx, FM_ERR_CUDA, "fm_kv_import: %s", cudaGetErrorString(e));
-    cudaStreamSynchronize(ctx->stream);
-    cudaFree(tmp);
-    return st;
+        return launched(ctx, launch_kv_import(kv, seq, 0, len, k, v, ctx->stream), "kv_import");
+    return staged_rows(ctx, len, kvd * 4, false, [&](int row0, int n, size_t o_v, size_t, size_t) -> fm_status {
+        memcpy(ctx->h_stage, k + (size_t)row0 * kvd, (size_t)n * kvd * 4);
+        memcpy(ctx->h_stage + o_v, v + (size_t)row0 * kvd, (size_t)n * kvd * 4);
+        FM_CUDA(ctx, cudaMemcpyAsync(ctx->d_stage, ctx->h_stage, o_v + (size_t)n * kvd * 4, cudaMemcpyHostToDevice, ctx->stream));
+        const fm_status s2 = launched(ctx, launch_kv_import(kv, seq, row0, n, reinterpret_cast<const float *>(ctx->d_stage),
+                                                            reinterpret_cast<const float *>(ctx->d_stage + o_v), ctx->stream), "kv_import");
+        if (s2) return s2;
+        FM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));  // the staging pair is reused by the next chunk
+        return FM_OK;
+    });
+}
+
+extern "C" fm_status fm_kv_export_fp8(FmCtx *ctx, int fa_idx, int seq, uint8_t *k8, uint8_t *v8, float *k_scales, float *v_scales,
+                                      int max_rows, int *len_out) {
+    if (!ctx) return FM_ERR_INVALID;
+    const FmConfig &c = ctx->cfg;
+    if (c.kv_dtype != FM_KV_FP8_E4M3) return fail(ctx, FM_ERR_INVALID, "fm_kv_export_fp8: the store is not FP8");
+    int len = 0;
+    fm_status st = kv_export_check(ctx, "fm_kv_export_fp8", fa_idx, seq, k8 && v8 && k_scales && v_scales, max_rows, len_out, &len);
+    if (st || len == 0) return st;
+    FM_CUDA(ctx, cudaSetDevice(c.device));
+    const size_t kvd = (size_t)c.num_kv_heads * c.head_dim;
+    const KvView kv = kv_view(ctx, fa_idx);
+    if (ctx->ptr_mode == FM_PTR_DEVICE)
+        return launched(ctx, launch_kv_copy_fp8(kv, seq, 0, len, k8, v8, k_scales, v_scales, false, ctx->stream), "kv_export_fp8");
+    return staged_rows(ctx, len, kvd, true, [&](int row0, int n, size_t o_v, size_t o_ks, size_t o_vs) -> fm_status {
+        char *hs = ctx->h_stage, *ds = ctx->d_stage;
+        memcpy(hs, k8 + (size_t)row0 * kvd, (size_t)n * kvd);
+        memcpy(hs + o_v, v8 + (size_t)row0 * kvd, (size_t)n * kvd);
+        memcpy(hs + o_ks, k_scales + row0, (size_t)n * 4);
+        memcpy(hs + o_vs, v_scales + row0, (size_t)n * 4);
+        FM_CUDA(ctx, cudaMemcpyAsync(ds, hs, o_vs + (size_t)n * 4, cudaMemcpyHostToDevice, ctx->stream));
+        const fm_status s2 = launched(ctx, launch_kv_copy_fp8(kv, seq, row0, n, reinterpret_cast<uint8_t *>(ds), reinterpret_cast<uint8_t *>(ds + o_v),
+                                                              reinterpret_cast<float *>(ds + o_ks), reinterpret_cast<float *>(ds + o_vs), false,
+                                                              ctx->stream), "kv_export_fp8");
+        if (s2) return s2;
+        FM_CUDA(ctx, cudaMemcpyAsync(hs, ds, o_vs + (size_t)n * 4, cudaMemcpyDeviceToHost, ctx->stream));
+        FM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        memcpy(k8 + (size_t)row0 * kvd, hs, (size_t)n * kvd);
+        memcpy(v8 + (size_t)row0 * kvd, hs + o_v, (size_t)n * kvd);
+        memcpy(k_scales + row0, hs + o_ks, (size_t)n * 4);
+        memcpy(v_scales + row0, hs + o_vs, (size_t)n * 4);
+        return FM_OK;
+    });
+}
+
+extern "C" fm_status fm_kv_import_fp8(FmCtx *ctx, int fa_idx, int seq, const uint8_t *k8, const uint8_t *v8, const float *k_scales,
+                                      const float *v_scales, int len) {
+    if (!ctx) return FM_ERR_INVALID;
+    const FmConfig &c = ctx->cfg;
+    if (c.kv_dtype != FM_KV_FP8_E4M3) return fail(ctx, FM_ERR_INVALID, "fm_kv_import_fp8: the store is not FP8");
+    fm_status st = kv_import_prepare(ctx, "fm_kv_import_fp8", fa_idx, seq, k8 && v8 && k_scales && v_scales, len);
+    if (st || len == 0) return st;
+    const size_t kvd = (size_t)c.num_kv_heads * c.head_dim;
+    const KvView kv = kv_view(ctx, fa_idx);
+    if (ctx->ptr_mode == FM_PTR_DEVICE)
+        return launched(ctx, launch_kv_copy_fp8(kv, seq, 0, len, const_cast<uint8_t *>(k8), const_cast<uint8_t *>(v8), const_cast<float *>(k_scales),
+                                                const_cast<float *>(v_scales), true, ctx->stream), "kv_import_fp8");
+    return staged_rows(ctx, len, kvd, true, [&](int row0, int n, size_t o_v, size_t o_ks, size_t o_vs) -> fm_status {
+        char *hs = ctx->h_stage, *ds = ctx->d_stage;
+        memcpy(hs, k8 + (size_t)row0 * kvd, (size_t)n * kvd);
+        memcpy(hs + o_v, v8 + (size_t)row0 * kvd, (size_t)n * kvd);
+        memcpy(hs + o_ks, k_scales + row0, (size_t)n * 4);
+        memcpy(hs + o_vs, v_scales + row0, (size_t)n * 4);
+        FM_CUDA(ctx, cudaMemcpyAsync(ds, hs, o_vs + (size_t)n * 4, cudaMemcpyHostToDevice, ctx->stream));
+        const fm_status s2 = launched(ctx, launch_kv_copy_fp8(kv, seq, row0, n, reinterpret_cast<uint8_t *>(ds), reinterpret_cast<uint8_t *>(ds + o_v),
+                                                              reinterpret_cast<float *>(ds + o_ks), reinterpret_cast<float *>(ds + o_vs), true,
+                                                              ctx->stream), "kv_import_fp8");
+        if (s2) return s2;
+        FM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        return FM_OK;
+    });
 }
 
 // conv history: the reference keeps [(ks-1)][conv_dim], oldest first; the device keeps a ring of ks
@@ -1114,7 +1220,7 @@ static fm_status xchg_push(FmCtx *ctx, const char *fn, int fa_idx, const int *se
     TokSpec t;
     t.mode = 0;
     t.n = batch;
-    for (int i = 0; i < batch; i++) { t.seq[i] = seq[i]; t.pos[i] = pos[i]; t.row[i] = rows[i]; t.nrows[i] = nrows[i]; }
+    for (int i = 0; i < batch; i++) t.set(i, seq[i], pos[i], rows[i], nrows[i]);
     ctx->xchg_step++;
     {
         // one launch: append, split-KV attention, merge of the splits, rows into every peer's buffer; then either the

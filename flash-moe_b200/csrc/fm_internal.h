@@ -15,30 +15,42 @@ constexpr int kMaxList = 64;  // tokens a kernel takes by value in one launch
 
 // Which tokens a launch works on.  mode 0: an explicit list (decode: one token per sequence);
 // mode 1: a run of n consecutive tokens of one sequence (prefill).
+// A listed token's four numbers sit together (one 16-byte read of the kernel's parameter space).
+struct TokEntry {
+    int seq, pos, row;
+    int nrows;  // cache rows the token attends to (row + 1, or the window once it has wrapped)
+};
 struct TokSpec {
     int mode;
     int n;
     int seq0, pos0, row0;  // mode 1: token t has pos0 + t, cache row row0 + t
-    int seq[kMaxList], pos[kMaxList], row[kMaxList];
-    int nrows[kMaxList];   // mode 0: cache rows the token attends to (row + 1, or the window once it has wrapped)
+    int pad[3];
+    TokEntry e[kMaxList];  // mode 0
+    void set(int i, int seq, int pos, int row, int nrows) { e[i].seq = seq; e[i].pos = pos; e[i].row = row; e[i].nrows = nrows; }
 };
 
 __host__ __device__ inline void tok_get(const TokSpec &t, int i, int &seq, int &pos, int &row) {
     if (t.mode == 1) {
         seq = t.seq0; pos = t.pos0 + i; row = t.row0 + i;
     } else {
-        seq = t.seq[i]; pos = t.pos[i]; row = t.row[i];
+        const TokEntry x = t.e[i];
+        seq = x.seq; pos = x.pos; row = x.row;
     }
 }
 
-__host__ __device__ inline int tok_rows(const TokSpec &t, int i) { return t.mode == 1 ? t.row0 + i + 1 : t.nrows[i]; }
+__host__ __device__ inline int tok_rows(const TokSpec &t, int i) { return t.mode == 1 ? t.row0 + i + 1 : t.e[i].nrows; }
 
-// The paged bf16 KV store of one layer as a kernel sees it.
-// Page layout: [2 (K,V)][Hkv][page_size][D] bf16, so one (K or V, head) tile is contiguous.
+// The paged KV store of one layer as a kernel sees it.
+// bf16 page:  [2 (K,V)][Hkv][page_size][D] bf16, so one (K or V, head) tile is contiguous.
+// FP8 page:   [2 (K,V)][Hkv][page_size][D] E4M3 bytes, then the rows' scales, float k_scale[page_size] and
+//             v_scale[page_size] (one scale per position over all KV heads, as KVCache.k_scales / v_scales of
+//             metal_infer/layer_forward.h:124-127).
 // Row r of a sequence lives in global page r / page_size; a context holds the pages with
 // (page % shard_count) == shard_rank, at local slot page / shard_count of its page table.
 struct KvView {
-    __nv_bfloat16 *pool;
+    unsigned char *pool;
+    size_t page_bytes;
+    int fp8;                // 0: bf16 pages, 1: E4M3 pages with per-row scales
     const int *page_table;  // [max_seqs][max_slots] of this layer
     int max_slots;
     int page_size;
@@ -46,6 +58,20 @@ struct KvView {
     int D;
     int shard_rank, shard_count;
 };
+
+__host__ __device__ inline size_t kv_page_bytes(int fp8, int Hkv, int page_size, int D) {
+    return fp8 ? (size_t)2 * Hkv * page_size * D + (size_t)2 * page_size * sizeof(float)
+               : (size_t)2 * Hkv * page_size * D * 2;
+}
+__host__ __device__ inline unsigned char *kv_page(const KvView &kv, int page) { return kv.pool + (size_t)page * kv.page_bytes; }
+// start of the (which = 0 K / 1 V, head) tile inside a page, in bytes
+__host__ __device__ inline size_t kv_tile_offset(const KvView &kv, int which, int kvh) {
+    return (size_t)(which * kv.Hkv + kvh) * kv.page_size * kv.D * (kv.fp8 ? 1 : 2);
+}
+// FP8 pages: the page's k_scale[page_size] (which = 0) or v_scale[page_size] (which = 1)
+__host__ __device__ inline float *kv_page_scales(const KvView &kv, unsigned char *page_base, int which) {
+    return reinterpret_cast<float *>(page_base + (size_t)2 * kv.Hkv * kv.page_size * kv.D) + (size_t)which * kv.page_size;
+}
 
 // Exchange buffers of a sequence group as a kernel sees them (see attn_decode.cu).
 constexpr int kMaxXchgRanks = 8;
@@ -87,9 +113,9 @@ struct FmCtx {
     fm::RopeParams rope;
 
     // KV store
-    __nv_bfloat16 *pool = nullptr;
+    unsigned char *pool = nullptr;
     int64_t pool_pages = 0;
-    size_t page_elems = 0;  // bf16 elements per page
+    size_t page_bytes = 0;
     int max_slots = 0;      // local page slots per sequence
     int *d_page_table = nullptr;       // [layers][seqs][max_slots]
     std::vector<int> h_page_table;
@@ -167,13 +193,22 @@ int launch_attn_merge(const float *part_o, const float *part_ml, int nparts, lon
                       const float *q_proj_out, const float *gate, float *out, float *ml_out,
                       cudaStream_t st);
 
+// merge of many split partials of (token, head), laid out [tok][H][nparts][..], as a programmatic dependent of the
+// launch that writes them
+int launch_attn_merge_wide(const float *part_o, const float *part_ml, int nparts, int ntok, int H, const float *q_proj_out,
+                           const float *gate, float *out, float *ml_out, cudaStream_t st);
+
 int launch_attn_merge_push(const float *part_o, const float *part_ml, int nsplits, int ntok, int H, const XchgView &x,
                            uint32_t step, unsigned int *done_counter, cudaStream_t st);
 int launch_attn_wait_merge(const XchgView &x, uint32_t step, int ntok, int H, const float *q_proj_out, const float *gate,
                            float *out, int *err, bool overlap_prev, cudaStream_t st);
 
-int launch_kv_export(const KvView &kv, int seq, int len, float *k, float *v, cudaStream_t st);
-int launch_kv_import(const KvView &kv, int seq, int len, const float *k, const float *v, cudaStream_t st);
+// rows [row0, row0 + n) of a sequence to / from fp32 [n][Hkv*D] buffers that start at row0
+int launch_kv_export(const KvView &kv, int seq, int row0, int n, float *k, float *v, cudaStream_t st);
+int launch_kv_import(const KvView &kv, int seq, int row0, int n, const float *k, const float *v, cudaStream_t st);
+// FP8 store: the stored bytes [n][Hkv*D] and per-row scales [n] themselves
+int launch_kv_copy_fp8(const KvView &kv, int seq, int row0, int n, uint8_t *k, uint8_t *v, float *ks, float *vs, bool import,
+                       cudaStream_t st);
 
 struct PrefillWork {
     void *q16, *k16, *v16;

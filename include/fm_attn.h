@@ -50,6 +50,9 @@ typedef enum fm_status {
 
 enum { FM_PTR_DEVICE = 0, FM_PTR_HOST = 1 };
 
+/* Element type of the KV store (FmConfig.kv_dtype). */
+enum { FM_KV_BF16 = 0, FM_KV_FP8_E4M3 = 1 };
+
 /* Plain-data configuration; replaces the ModelConfig fields this path reads
  * (metal_infer/config.h:9-75) and the feature globals set before metal_setup()
  * (metal_infer/timing.h:82-111).  Head counts are those HELD BY THIS CONTEXT:
@@ -89,6 +92,14 @@ typedef struct FmConfig {
      * count % W is overwritten, attention sees the last min(count, W) tokens
      * (g_sliding_window / KVCache.window_size: layer_forward.h:130-131,148-161,600-601,649-650,673-677) */
     int sliding_window;
+    /* FM_KV_BF16 (default): rows are stored as bf16.  FM_KV_FP8_E4M3: rows are stored as E4M3 bytes with one
+     * scale per position and tensor (K, V), scale = absmax over the row / 240, the reference's FP8 cache
+     * (g_use_fp8_kv; metal_infer/fp8.h:19-118, KVCache fields metal_infer/layer_forward.h:124-127, append
+     * :609-616, CPU attention :679-712, Metal kernels metal_infer/shaders.metal:1067-1143,1320-1430).  The
+     * bytes and scales are the reference's, quirks of its encoder included, so a row decodes to what its CPU
+     * attention would have read.  The absmax runs over the KV heads THIS CONTEXT holds (all of them on one
+     * GPU, as in the reference).  Half the bytes per row of bf16. */
+    int kv_dtype;
 } FmConfig;
 
 typedef struct FmCtx FmCtx;
@@ -241,6 +252,14 @@ fm_status fm_gdn_prefill(FmCtx *ctx, int li, int seq, int n, int chunk, const fl
  * caller's arrays are left alone / ignored).  Pointers follow the pointer mode. */
 fm_status fm_kv_export(FmCtx *ctx, int fa_idx, int seq, float *k, float *v, int max_rows, int *len_out);
 fm_status fm_kv_import(FmCtx *ctx, int fa_idx, int seq, const float *k, const float *v, int len);
+/* FP8 store only: the stored bytes and scales themselves, k8 / v8 [len][Hkv*D] E4M3 bytes and k_scales /
+ * v_scales [len] -- KVCache.k_cache_fp8 / v_cache_fp8 / k_scales / v_scales (metal_infer/layer_forward.h:124-127),
+ * what the reference's snapshot copies for an FP8 cache.  Unlike the fp32 pair above (which decodes on export
+ * and quantises again on import) this round trip is exact. */
+fm_status fm_kv_export_fp8(FmCtx *ctx, int fa_idx, int seq, uint8_t *k8, uint8_t *v8, float *k_scales, float *v_scales,
+                           int max_rows, int *len_out);
+fm_status fm_kv_import_fp8(FmCtx *ctx, int fa_idx, int seq, const uint8_t *k8, const uint8_t *v8, const float *k_scales,
+                           const float *v_scales, int len);
 fm_status fm_state_export(FmCtx *ctx, int li, int seq, float *conv, float *ssm);
 fm_status fm_state_import(FmCtx *ctx, int li, int seq, const float *conv, const float *ssm);
 

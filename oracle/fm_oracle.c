@@ -312,3 +312,229 @@ int fmo_gdn_run(const FmoDims *d, float *conv_state, float *ssm_state, const flo
     }
     return 0;
 }
+
+/* ------------------------------------------------------------------------ */
+/* FP8 E4M3 codec of the KV cache (metal_infer/fp8.h:19-118), restated: per-row scale = absmax / 240
+   (1 for an all-zero row); 3-bit mantissa rounded half up; magnitudes below 2^-6 that are not below 2^-9 go
+   through the normal-number branch with the exponent clamped to -6, whose negative mantissa term is OR-ed into
+   the byte as a two's-complement int; the decoder knows 0x7F as the only NaN. */
+static uint8_t e4m3_encode(float x, float inv_scale) {
+    float scaled = x * inv_scale;
+    if (scaled != scaled) return 0x7F;
+    scaled = fminf(fmaxf(scaled, -448.0f), 448.0f);
+    uint32_t bits;
+    memcpy(&bits, &scaled, sizeof bits);
+    const uint8_t sign = (bits >> 31) & 1;
+    const float mag = fabsf(scaled);
+    if (mag < 0.001953125f) {
+        int m = (int)(mag / 0.001953125f + 0.5f);
+        if (m > 7) m = 7;
+        return (uint8_t)((sign << 7) | m);
+    }
+    int e = (int)floorf(log2f(mag));
+    if (e < -6) e = -6;
+    if (e > 8) e = 8;
+    const float frac = mag / powf(2.0f, (float)e) - 1.0f;
+    int mant = (int)(frac * 8.0f + 0.5f);
+    if (mant > 7) { mant = 0; e++; }
+    int eb = e + 7;
+    if (eb < 0) { eb = 0; mant = 0; }
+    if (eb > 15) { eb = 15; mant = 6; }
+    if (eb == 15 && mant >= 7) mant = 6;
+    return (uint8_t)((sign << 7) | (eb << 3) | mant);
+}
+
+static float e4m3_value(uint8_t x) { /* the byte's value before the scale (NaN for 0x7F) */
+    if (x == 0x7F) return NAN;
+    const int eb = (x >> 3) & 0xF, mant = x & 7;
+    float val = eb == 0 ? (float)mant * 0.001953125f : (1.0f + (float)mant / 8.0f) * powf(2.0f, (float)eb - 7.0f);
+    return (x & 0x80) ? -val : val;
+}
+
+void fmo_fp8_encode_rows(const float *src, int n, int kv_dim, uint8_t *dst, float *scales) {
+    for (int i = 0; i < n; i++) {
+        const float *r = src + (size_t)i * kv_dim;
+        float amax = 0.0f;
+        for (int j = 0; j < kv_dim; j++) {
+            const float a = fabsf(r[j]);
+            if (a > amax) amax = a;
+        }
+        const float scale = amax > 0.0f ? amax / 240.0f : 1.0f;
+        const float inv = 1.0f / scale;
+        for (int j = 0; j < kv_dim; j++) dst[(size_t)i * kv_dim + j] = e4m3_encode(r[j], inv);
+        scales[i] = scale;
+    }
+}
+
+void fmo_fp8_decode_rows(const uint8_t *src, const float *scales, int n, int kv_dim, float *dst) {
+    for (int i = 0; i < n; i++)
+        for (int j = 0; j < kv_dim; j++) dst[(size_t)i * kv_dim + j] = e4m3_value(src[(size_t)i * kv_dim + j]) * scales[i];
+}
+
+/* H2O eviction (metal_infer/layer_forward.h:265-383): keep the first `sinks` rows, the last `recent` rows and,
+   of the rows between, the `budget - sinks - recent` with the largest accumulated attention mass (selection in
+   the reference's order: repeated arg-max with strict >, so ties go to the earlier row), compacted in
+   temporal order. */
+static void h2o_evict(const FmoDims *d, FmoCache *c) {
+    if (c->h2o_num_valid <= c->h2o_budget) return;
+    const int num_valid = c->h2o_num_valid, budget = c->h2o_budget;
+    int sinks = c->h2o_num_sinks, recent = c->h2o_num_recent;
+    if (sinks > budget) sinks = budget;
+    if (sinks + recent > budget) recent = budget - sinks;
+    const int heavy = budget - sinks - recent;
+    const int ev0 = sinks, ev1 = num_valid - recent, nev = ev1 - ev0;
+    if (nev <= 0 || heavy >= nev) return;
+    int *idx = malloc((size_t)nev * sizeof(int));
+    float *sc = malloc((size_t)nev * sizeof(float));
+    for (int i = 0; i < nev; i++) { idx[i] = ev0 + i; sc[i] = c->attn_scores_accum[ev0 + i]; }
+    for (int i = 0; i < heavy && i < nev; i++) {
+        int mi = i;
+        for (int j = i + 1; j < nev; j++)
+            if (sc[j] > sc[mi]) mi = j;
+        if (mi != i) {
+            const float ts = sc[i]; sc[i] = sc[mi]; sc[mi] = ts;
+            const int ti = idx[i]; idx[i] = idx[mi]; idx[mi] = ti;
+        }
+    }
+    int *keep = malloc((size_t)budget * sizeof(int));
+    int nk = 0;
+    for (int i = 0; i < sinks && i < num_valid; i++) keep[nk++] = i;
+    for (int i = 0; i < heavy - 1; i++)          /* heavy hitters back in temporal order */
+        for (int j = i + 1; j < heavy; j++)
+            if (idx[j] < idx[i]) { const int t = idx[i]; idx[i] = idx[j]; idx[j] = t; }
+    for (int i = 0; i < heavy; i++) keep[nk++] = idx[i];
+    for (int i = num_valid - recent; i < num_valid; i++) keep[nk++] = i;
+    const size_t kv_dim = (size_t)d->num_kv_heads * d->head_dim;
+    for (int dst = 0; dst < nk; dst++) {
+        const int src = keep[dst];
+        if (src == dst) continue;
+        if (c->use_fp8) {
+            memmove(c->k8 + dst * kv_dim, c->k8 + src * kv_dim, kv_dim);
+            memmove(c->v8 + dst * kv_dim, c->v8 + src * kv_dim, kv_dim);
+            c->k_scales[dst] = c->k_scales[src];
+            c->v_scales[dst] = c->v_scales[src];
+        } else {
+            memmove(c->k_cache + dst * kv_dim, c->k_cache + src * kv_dim, kv_dim * sizeof(float));
+            memmove(c->v_cache + dst * kv_dim, c->v_cache + src * kv_dim, kv_dim * sizeof(float));
+        }
+        c->attn_scores_accum[dst] = c->attn_scores_accum[src];
+        c->token_positions[dst] = c->token_positions[src];
+    }
+    c->h2o_num_valid = nk;
+    free(idx); free(sc); free(keep);
+}
+
+/* One decode step with the cache policies of metal_infer/layer_forward.h:591-727: where the row goes (H2O: the
+   next compacted slot; window: len % capacity; else len), FP8 quantisation of the appended row, rows attended,
+   per-position softmax mass summed over heads for H2O, eviction after the step. */
+int fmo_attn_step_cache(const FmoDims *d, FmoCache *c, const float *q_in, const float *gate, const float *k_in,
+                        const float *v_in, const uint16_t *q_norm_w, const uint16_t *k_norm_w, int pos, float *out,
+                        int threads) {
+    const int H = d->num_attn_heads, Hkv = d->num_kv_heads, D = d->head_dim;
+    const int q_dim = H * D, kv_dim = Hkv * D;
+    const int h2o = c->h2o_budget > 0;
+    const int W = h2o ? 0 : c->window_size;
+    if (W > 0 && c->capacity != W) return -1;
+    int cache_pos;
+    if (h2o) {
+        cache_pos = c->h2o_num_valid;
+        if (cache_pos >= c->capacity) return -1;
+    } else if (W > 0) {
+        cache_pos = c->len % c->capacity;
+    } else {
+        cache_pos = c->len;
+        if (cache_pos >= c->capacity) return -1;
+    }
+    float *q = malloc((size_t)q_dim * sizeof(float));
+    float *k = malloc((size_t)kv_dim * sizeof(float));
+    memcpy(q, q_in, (size_t)q_dim * sizeof(float));
+    memcpy(k, k_in, (size_t)kv_dim * sizeof(float));
+    head_rms_norm(q, H, D, q_norm_w, d->rms_norm_eps);
+    head_rms_norm(k, Hkv, D, k_norm_w, d->rms_norm_eps);
+    rope_heads(d, q, H, pos);
+    rope_heads(d, k, Hkv, pos);
+    if (c->use_fp8) {
+        fmo_fp8_encode_rows(k, 1, kv_dim, c->k8 + (size_t)cache_pos * kv_dim, c->k_scales + cache_pos);
+        fmo_fp8_encode_rows(v_in, 1, kv_dim, c->v8 + (size_t)cache_pos * kv_dim, c->v_scales + cache_pos);
+    } else {
+        float *kr = c->k_cache + (size_t)cache_pos * kv_dim, *vr = c->v_cache + (size_t)cache_pos * kv_dim;
+        memcpy(kr, k, (size_t)kv_dim * sizeof(float));
+        memcpy(vr, v_in, (size_t)kv_dim * sizeof(float));
+        if (d->store_bf16)
+            for (int i = 0; i < kv_dim; i++) { kr[i] = round_bf16f(kr[i]); vr[i] = round_bf16f(vr[i]); }
+    }
+    if (h2o) {
+        c->token_positions[cache_pos] = c->len;
+        c->attn_scores_accum[cache_pos] = 0.0f;
+        c->h2o_num_valid++;
+    }
+    c->len++;
+    const int wrapped = !h2o && W > 0 && c->len > W;
+    const int L = h2o ? c->h2o_num_valid : (wrapped ? W : c->len);
+    const int first = wrapped ? c->len - W : 0;
+    const int group = H / Hkv;
+    const float scale = (1.0f / sqrtf((float)D)) * yarn_logit_factor(d);
+    float lut[256];
+    for (int i = 0; i < 256; i++) lut[i] = e4m3_value((uint8_t)i);
+
+    memset(out, 0, (size_t)q_dim * sizeof(float));
+    float *mass = h2o ? calloc((size_t)H * L, sizeof(float)) : NULL;  /* per head, summed in head order below */
+    if (threads < 1) threads = 1;
+#pragma omp parallel for num_threads(threads) schedule(static) if (threads > 1)
+    for (int h = 0; h < H; h++) {
+        const int kvh = h / group;
+        const float *qh = q + (size_t)h * D;
+        float *s = malloc((size_t)L * sizeof(float));
+        float *deq = c->use_fp8 ? malloc((size_t)D * sizeof(float)) : NULL;
+        for (int i = 0; i < L; i++) {
+            const int p = wrapped ? (first + i) % c->capacity : i;
+            const float *kp;
+            if (c->use_fp8) {
+                const uint8_t *kb = c->k8 + (size_t)p * kv_dim + (size_t)kvh * D;
+                const float sc = c->k_scales[p];
+                for (int e = 0; e < D; e++) deq[e] = lut[kb[e]] * sc;
+                kp = deq;
+            } else {
+                kp = c->k_cache + (size_t)p * kv_dim + (size_t)kvh * D;
+            }
+            float dot = 0.0f;
+            for (int e = 0; e < D; e++) dot += qh[e] * kp[e];
+            s[i] = dot * scale;
+        }
+        softmax_inplace(s, L);
+        if (mass) memcpy(mass + (size_t)h * L, s, (size_t)L * sizeof(float));
+        float *oh = out + (size_t)h * D;
+        for (int i = 0; i < L; i++) {
+            const int p = wrapped ? (first + i) % c->capacity : i;
+            const float *vp;
+            if (c->use_fp8) {
+                const uint8_t *vb = c->v8 + (size_t)p * kv_dim + (size_t)kvh * D;
+                const float sc = c->v_scales[p];
+                for (int e = 0; e < D; e++) deq[e] = lut[vb[e]] * sc;
+                vp = deq;
+            } else {
+                vp = c->v_cache + (size_t)p * kv_dim + (size_t)kvh * D;
+            }
+            for (int e = 0; e < D; e++) oh[e] += s[i] * vp[e];
+        }
+        free(s);
+        free(deq);
+    }
+    if (h2o) {
+        /* sum over heads in head order, then into the running totals (metal_infer/layer_forward.h:694-699, 256-261) */
+        for (int i = 0; i < L && i < c->h2o_num_valid; i++) {
+            float step = 0.0f;
+            for (int h = 0; h < H; h++) step += mass[(size_t)h * L + i];
+            c->attn_scores_accum[i] += step;
+        }
+        free(mass);
+        h2o_evict(d, c);
+    }
+    for (int i = 0; i < q_dim; i++) {
+        const float g = 1.0f / (1.0f + expf(-gate[i]));
+        out[i] *= g;
+    }
+    free(q);
+    free(k);
+    return 0;
+}

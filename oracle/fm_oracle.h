@@ -44,6 +44,22 @@ typedef struct {
                                 649-650,673-677; *len keeps counting every appended token */
 } FmoDims;
 
+/* A KV cache with the reference's optional policies (KVCache, metal_infer/layer_forward.h:121-141), caller-owned
+ * arrays.  fp32 store: k_cache / v_cache [capacity][kv_dim].  FP8 store (use_fp8): k8 / v8 [capacity][kv_dim]
+ * E4M3 bytes + k_scales / v_scales [capacity] (metal_infer/fp8.h:100-108).  window_size > 0: circular buffer
+ * (capacity == window_size).  h2o_budget > 0: heavy-hitter eviction (metal_infer/layer_forward.h:248-383);
+ * capacity >= budget + 1, attn_scores_accum / token_positions [capacity], num_recent = (budget - sinks) / 4 as
+ * kv_cache_new() sets it (:203). */
+typedef struct {
+    float *k_cache, *v_cache;
+    uint8_t *k8, *v8;
+    float *k_scales, *v_scales;
+    int len, capacity, use_fp8, window_size;
+    int h2o_budget, h2o_num_sinks, h2o_num_recent, h2o_num_valid;
+    float *attn_scores_accum;
+    int *token_positions;
+} FmoCache;
+
 #define FMO_API(prefix)                                                                         \
     /* One decode step. k_cache/v_cache: [capacity][kv_heads*head_dim] fp32, *len rows valid.   \
        q, gate: [heads*head_dim] (already de-interleaved); k, v: [kv_heads*head_dim].           \
@@ -72,6 +88,17 @@ typedef struct {
                         const float *qkv, const float *z, const float *beta,                    \
                         const float *alpha, const uint16_t *conv_w, const float *A_log,         \
                         const uint16_t *dt_bias, const uint16_t *norm_w, int n, float *out,     \
-                        int threads);
+                        int threads);                                                           \
+    /* One decode step on a cache with the optional policies (FP8 store, sliding window, H2O     \
+       eviction).  Same inputs and output as attn_step; the cache's len / h2o_num_valid move. */ \
+    int prefix##attn_step_cache(const FmoDims *d, FmoCache *c, const float *q, const float *gate, \
+                                const float *k, const float *v, const uint16_t *q_norm_w,       \
+                                const uint16_t *k_norm_w, int pos, float *out, int threads);     \
+    /* FP8 codec on n rows of kv_dim floats: bytes [n][kv_dim], scales [n]. */                   \
+    void prefix##fp8_encode_rows(const float *src, int n, int kv_dim, uint8_t *dst, float *scales); \
+    void prefix##fp8_decode_rows(const uint8_t *src, const float *scales, int n, int kv_dim, float *dst);
+
+FMO_API(fmo_)
+FMO_API(fmr_)
 
 #endif

@@ -27,6 +27,50 @@ class FmoDims(C.Structure):
     ]
 
 
+class FmoCache(C.Structure):
+    _fields_ = [
+        ("k_cache", C.POINTER(C.c_float)), ("v_cache", C.POINTER(C.c_float)),
+        ("k8", C.POINTER(C.c_uint8)), ("v8", C.POINTER(C.c_uint8)),
+        ("k_scales", C.POINTER(C.c_float)), ("v_scales", C.POINTER(C.c_float)),
+        ("len", C.c_int), ("capacity", C.c_int), ("use_fp8", C.c_int), ("window_size", C.c_int),
+        ("h2o_budget", C.c_int), ("h2o_num_sinks", C.c_int), ("h2o_num_recent", C.c_int),
+        ("h2o_num_valid", C.c_int),
+        ("attn_scores_accum", C.POINTER(C.c_float)), ("token_positions", C.POINTER(C.c_int)),
+    ]
+
+
+class Cache:
+    """A KV cache with the reference's optional policies, backed by numpy arrays the caller can read:
+    fp32 rows (k, v) or FP8 bytes + per-row scales (k8, v8, k_scales, v_scales); sliding window; H2O
+    (accum, token_positions, num_valid).  num_recent follows kv_cache_new(): (budget - sinks) // 4."""
+
+    def __init__(self, capacity: int, kv_dim: int, fp8: bool = False, window: int = 0, h2o_budget: int = 0,
+                 h2o_sinks: int = 4):
+        self.capacity, self.kv_dim, self.fp8 = capacity, kv_dim, fp8
+        f32p, u8p, i32p = C.POINTER(C.c_float), C.POINTER(C.c_uint8), C.POINTER(C.c_int)
+        self.k = np.zeros((capacity, kv_dim), np.float32) if not fp8 else None
+        self.v = np.zeros((capacity, kv_dim), np.float32) if not fp8 else None
+        self.k8 = np.zeros((capacity, kv_dim), np.uint8) if fp8 else None
+        self.v8 = np.zeros((capacity, kv_dim), np.uint8) if fp8 else None
+        self.k_scales = np.zeros((capacity,), np.float32) if fp8 else None
+        self.v_scales = np.zeros((capacity,), np.float32) if fp8 else None
+        self.accum = np.zeros((capacity,), np.float32) if h2o_budget > 0 else None
+        self.token_positions = np.zeros((capacity,), np.int32) if h2o_budget > 0 else None
+        p = lambda a, t: a.ctypes.data_as(t) if a is not None else None
+        self.c = FmoCache(p(self.k, f32p), p(self.v, f32p), p(self.k8, u8p), p(self.v8, u8p), p(self.k_scales, f32p),
+                          p(self.v_scales, f32p), 0, capacity, 1 if fp8 else 0, window, h2o_budget, h2o_sinks,
+                          (h2o_budget - h2o_sinks) // 4 if h2o_budget > 0 else 0, 0, p(self.accum, f32p),
+                          p(self.token_positions, i32p))
+
+    @property
+    def len(self):
+        return self.c.len
+
+    @property
+    def num_valid(self):
+        return self.c.h2o_num_valid
+
+
 def make_dims(**kw) -> FmoDims:
     d = dict(num_attn_heads=32, num_kv_heads=2, head_dim=256, rotary_dim=64, rope_theta=1e7,
              rms_norm_eps=1e-6, rope_scaling_mode=0, rope_scale_factor=1.0, max_seq_len=262144,
@@ -68,8 +112,49 @@ class Oracle:
             raise ValueError(kind)
         self.kind = kind
         self.lib = C.CDLL(str(path))
-        for name in ("attn_step", "attn_run", "gdn_step", "gdn_run"):
+        for name in ("attn_step", "attn_run", "gdn_step", "gdn_run", "attn_step_cache"):
             getattr(self.lib, self.prefix + name).restype = C.c_int
+        for name in ("fp8_encode_rows", "fp8_decode_rows"):
+            getattr(self.lib, self.prefix + name).restype = None
+
+    # -- cache policies: FP8 store, sliding window, H2O ------------------------
+    def attn_run_cache(self, dims: FmoDims, cache: Cache, q, gate, k, v, q_norm_w=None, k_norm_w=None,
+                       start_pos=None, threads: int = 1):
+        """n decode steps on a Cache (updated in place).  Returns out [n][q_dim]."""
+        q, _ = _f32(q); gate, _ = _f32(gate); k, _ = _f32(k); v, _ = _f32(v)
+        q, gate, k, v = (np.atleast_2d(a) for a in (q, gate, k, v))
+        n = q.shape[0]
+        out = np.empty((n, dims.num_attn_heads * dims.head_dim), np.float32)
+        _a, qn = _u16(q_norm_w); _b, kn = _u16(k_norm_w)
+        if start_pos is None:
+            start_pos = cache.len
+        f32p = C.POINTER(C.c_float)
+        fn = getattr(self.lib, self.prefix + "attn_step_cache")
+        for t in range(n):
+            rc = fn(C.byref(dims), C.byref(cache.c), q[t].ctypes.data_as(f32p), gate[t].ctypes.data_as(f32p),
+                    k[t].ctypes.data_as(f32p), v[t].ctypes.data_as(f32p), qn, kn, C.c_int(start_pos + t),
+                    out[t].ctypes.data_as(f32p), C.c_int(threads))
+            if rc != 0:
+                raise RuntimeError("KV cache overflow in oracle")
+        return out
+
+    def fp8_encode_rows(self, rows):
+        rows, rp = _f32(rows)
+        n, kv_dim = rows.shape
+        b = np.empty((n, kv_dim), np.uint8); sc = np.empty((n,), np.float32)
+        getattr(self.lib, self.prefix + "fp8_encode_rows")(rp, C.c_int(n), C.c_int(kv_dim),
+                                                            b.ctypes.data_as(C.POINTER(C.c_uint8)),
+                                                            sc.ctypes.data_as(C.POINTER(C.c_float)))
+        return b, sc
+
+    def fp8_decode_rows(self, b, sc):
+        b = np.ascontiguousarray(b, np.uint8); sc = np.ascontiguousarray(sc, np.float32)
+        n, kv_dim = b.shape
+        out = np.empty((n, kv_dim), np.float32)
+        getattr(self.lib, self.prefix + "fp8_decode_rows")(b.ctypes.data_as(C.POINTER(C.c_uint8)),
+                                                            sc.ctypes.data_as(C.POINTER(C.c_float)), C.c_int(n),
+                                                            C.c_int(kv_dim), out.ctypes.data_as(C.POINTER(C.c_float)))
+        return out
 
     # -- full attention ------------------------------------------------------
     def attn_run(self, dims: FmoDims, k_cache, v_cache, length: int, q, gate, k, v,

@@ -162,6 +162,58 @@ int fmr_attn_run(const FmoDims *d, float *k_cache, float *v_cache, int *len, int
     return 0;
 }
 
+/* ---- the same step on a cache with the reference's optional policies (FP8 store, sliding window, H2O) ---- */
+int fmr_attn_step_cache(const FmoDims *d, FmoCache *c, const float *q_in, const float *gate_in, const float *k_in,
+                        const float *v_in, const uint16_t *q_norm_w, const uint16_t *k_norm_w, int pos, float *out,
+                        int threads) {
+    load_cfg(d);
+    int q_dim = d->num_attn_heads * d->head_dim;
+    int kv_dim = d->num_kv_heads * d->head_dim;
+    KVCache kv;
+    memset(&kv, 0, sizeof(kv));
+    kv.k_cache = c->k_cache; kv.v_cache = c->v_cache;
+    kv.k_cache_fp8 = c->k8; kv.v_cache_fp8 = c->v8;
+    kv.k_scales = c->k_scales; kv.v_scales = c->v_scales;
+    kv.len = c->len; kv.capacity = c->capacity; kv.use_fp8 = c->use_fp8;
+    kv.window_size = c->h2o_budget > 0 ? 0 : c->window_size;     /* kv_cache_new(): H2O replaces the window */
+    if (kv.window_size > 0 && c->capacity != kv.window_size) return -1;
+    kv.h2o_active = c->h2o_budget > 0;
+    kv.h2o_budget = c->h2o_budget;
+    kv.h2o_num_sinks = c->h2o_num_sinks;
+    kv.h2o_num_recent = c->h2o_num_recent;
+    kv.h2o_num_valid = c->h2o_num_valid;
+    kv.attn_scores_accum = c->attn_scores_accum;
+    kv.token_positions = c->token_positions;
+    g_tensors.q_norm = q_norm_w;
+    g_tensors.k_norm = k_norm_w;
+    float *q = malloc((size_t)q_dim * sizeof(float));
+    float *g = malloc((size_t)q_dim * sizeof(float));
+    float *k = malloc((size_t)kv_dim * sizeof(float));
+    float *v = malloc((size_t)kv_dim * sizeof(float));
+    memcpy(q, q_in, (size_t)q_dim * sizeof(float));
+    memcpy(g, gate_in, (size_t)q_dim * sizeof(float));
+    memcpy(k, k_in, (size_t)kv_dim * sizeof(float));
+    memcpy(v, v_in, (size_t)kv_dim * sizeof(float));
+    int ok = 0;
+    /* The reference's per-head loop shares one dequantisation buffer (FP8) and one score accumulator (H2O)
+       between heads, so those two modes run it as written, on one thread. */
+    if (threads > 1 && !kv.use_fp8 && !kv.h2o_active)
+        fa_body_threaded(NULL, 0, q, g, k, v, &kv, pos, q_dim, kv_dim, out, &ok, threads);
+    else
+        fa_body_serial(NULL, 0, q, g, k, v, &kv, pos, q_dim, kv_dim, out, &ok);
+    c->len = kv.len;
+    c->h2o_num_valid = kv.h2o_num_valid;
+    free(q); free(g); free(k); free(v);
+    return ok ? 0 : -1;
+}
+
+void fmr_fp8_encode_rows(const float *src, int n, int kv_dim, uint8_t *dst, float *scales) {
+    for (int i = 0; i < n; i++) scales[i] = fp8_encode_vec(src + (size_t)i * kv_dim, dst + (size_t)i * kv_dim, kv_dim);
+}
+void fmr_fp8_decode_rows(const uint8_t *src, const float *scales, int n, int kv_dim, float *dst) {
+    for (int i = 0; i < n; i++) fp8_decode_vec(src + (size_t)i * kv_dim, dst + (size_t)i * kv_dim, kv_dim, scales[i]);
+}
+
 /* ---- GatedDeltaNet ---- */
 static void gdn_body_serial(WeightFile *wf, int layer_idx, LinearAttnState *state, float *qkv,
                             int qkv_dim, float *z, float *beta, float *alpha, float *out) {

@@ -63,7 +63,28 @@ def gdn_case(name, seed, v_heads, k_heads, dk, dv, steps, zero_state, bf16):
     print(name, out.shape, float(np.abs(out).max()), float(np.sqrt((ssm ** 2).mean())))
 
 
+def cache_policy_case(name, seed, heads, kv_heads, steps, fp8, h2o_budget):
+    """Decode steps from an empty cache with the FP8 store and / or H2O eviction switched on."""
+    from oracle.oracle_py import Cache
+    ref = Oracle("reference")
+    dims = make_dims(num_attn_heads=heads, num_kv_heads=kv_heads)
+    q, g, k, v = synth.attn_step_inputs(seed, steps, heads, kv_heads, 256)
+    capacity = h2o_budget + 1 if h2o_budget else steps
+    c = Cache(capacity, kv_heads * 256, fp8=fp8, h2o_budget=h2o_budget, h2o_sinks=4)
+    out = ref.attn_run_cache(dims, c, q, g, k, v)
+    z = np.zeros(0, np.float32)
+    np.savez_compressed(
+        OUT / f"{name}.npz", kind="attn_cache", heads=heads, kv_heads=kv_heads, steps=steps, fp8=fp8,
+        h2o_budget=h2o_budget, capacity=capacity, q=q, gate=g, k=k, v=v, out=out,
+        k8=c.k8 if fp8 else z, v8=c.v8 if fp8 else z, k_scales=c.k_scales if fp8 else z,
+        v_scales=c.v_scales if fp8 else z, token_positions=c.token_positions if h2o_budget else z,
+        accum=c.accum if h2o_budget else z)
+    print(name, out.shape, float(np.abs(out).max()))
+
+
 if __name__ == "__main__":
+    cache_policy_case("attn_fp8_h8_d256", 14, 8, 2, 12, fp8=True, h2o_budget=0)
+    cache_policy_case("attn_h2o_h8_d256", 15, 8, 2, 30, fp8=False, h2o_budget=16)
     # decode steps at the production head size, few heads (fp32 inputs, with norm weights)
     attn_case("attn_h8_d256_ctx37", 11, 8, 2, 256, 64, 1e7, 37, 3, norm=True, bf16=False)
     # bf16-representable inputs, GQA group 16 as in the production model, ragged context

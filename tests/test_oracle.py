@@ -173,3 +173,103 @@ def test_port_equals_reference_sliding_window(port, ref, synth, window):
     kc2[:window - 1] = k_last; vc2[:window - 1] = v_last
     last, _ = port.attn_run(plain, kc2, vc2, window - 1, q[-1:], g[-1:], k[-1:], v[-1:], start_pos=steps - 1)
     np.testing.assert_allclose(res[0][0][-1], last[0], rtol=2e-5, atol=2e-6)
+
+
+# ---- cache policies: FP8 store and H2O eviction -------------------------------------------------
+def test_fp8_codec_port_equals_reference(port, ref, synth):
+    """Bytes and scales of the FP8 E4M3 cache codec (metal_infer/fp8.h:19-118), including the values the
+    reference encodes oddly: magnitudes in [2^-9, 2^-6) of the scaled range, values one ulp either side of a
+    power of two, zeros, an all-zero row, the clamp at 448."""
+    rows = synth.normal(31, "fp8rows", (64, 512))
+    rows[1] = 0.0
+    rows[2, :] = np.linspace(-1.0, 1.0, 512, dtype=np.float32) * 240.0            # scale exactly 1
+    tiny = np.float32(2.0) ** np.arange(-12, -4, dtype=np.float32)
+    rows[3, :8] = tiny; rows[3, 8:16] = -tiny; rows[3, 16] = 240.0
+    pw = np.float32(2.0) ** np.arange(-8, 8, dtype=np.float32)
+    rows[4, :16] = pw; rows[4, 16:32] = np.nextafter(pw, np.float32(0)); rows[4, 32:48] = np.nextafter(pw, np.float32(1e9))
+    rows[4, 48] = 240.0
+    rows[5, :256] = np.linspace(0.0, 0.02, 256, dtype=np.float32); rows[5, 256] = 240.0; rows[5, 257:] = 0.0
+    b0, s0 = ref.fp8_encode_rows(rows)
+    b1, s1 = port.fp8_encode_rows(rows)
+    np.testing.assert_array_equal(b0, b1)
+    np.testing.assert_array_equal(s0, s1)
+    assert (b0 >= 0xFA).any(), "the sample must reach the reference's negative-mantissa bytes"
+    allb = np.arange(256, dtype=np.uint8).reshape(1, 256)
+    d0, d1 = ref.fp8_decode_rows(allb, np.array([0.37], np.float32)), port.fp8_decode_rows(allb, np.array([0.37], np.float32))
+    np.testing.assert_array_equal(d0, d1)            # NaN at 0x7F in both (array_equal treats NaNs as equal)
+    assert d0[0, 0xFF] == np.float32(-480.0) * np.float32(0.37)
+
+
+def _run_cache(orc, dims, kv_dim, capacity, q, g, k, v, threads=1, **cache_kw):
+    from oracle.oracle_py import Cache
+    c = Cache(capacity, kv_dim, **cache_kw)
+    out = orc.attn_run_cache(dims, c, q, g, k, v, threads=threads)
+    return out, c
+
+
+def test_port_equals_reference_fp8_cache(port, ref, synth):
+    """Decode steps on an FP8 cache from empty: outputs, stored bytes and scales agree bit for bit (the port
+    also with its per-head loop threaded: it keeps a dequantisation buffer per head)."""
+    heads, kvh, D, steps = 8, 2, 256, 40
+    dims = make_dims(num_attn_heads=heads, num_kv_heads=kvh)
+    q, g, k, v = synth.attn_step_inputs(41, steps, heads=heads, kv_heads=kvh)
+    kn = synth.to_bf16_bits(1.0 + synth.normal(41, "kn", (D,), std=0.1))
+    from oracle.oracle_py import Cache
+    res = []
+    for orc, threads in ((ref, 1), (port, 1), (port, 3)):
+        c = Cache(steps, kvh * D, fp8=True)
+        out = orc.attn_run_cache(dims, c, q, g, k, v, k_norm_w=kn, threads=threads)
+        res.append((out, c))
+    for out, c in res[1:]:
+        np.testing.assert_array_equal(out, res[0][0])
+        np.testing.assert_array_equal(c.k8, res[0][1].k8)
+        np.testing.assert_array_equal(c.v8, res[0][1].v8)
+        np.testing.assert_array_equal(c.k_scales, res[0][1].k_scales)
+        np.testing.assert_array_equal(c.v_scales, res[0][1].v_scales)
+
+
+@pytest.mark.parametrize("fp8", [False, True])
+def test_port_equals_reference_h2o(port, ref, synth, fp8):
+    """Heavy-hitter eviction (metal_infer/layer_forward.h:248-383): budget 24 with 4 sinks (so 5 recent, 15 heavy
+    hitters), 70 steps from empty -- the cache is compacted on every step past the budget.  Outputs, kept rows,
+    accumulated mass and original positions agree bit for bit."""
+    heads, kvh, D, steps, budget = 8, 2, 256, 70, 24
+    dims = make_dims(num_attn_heads=heads, num_kv_heads=kvh)
+    q, g, k, v = synth.attn_step_inputs(43, steps, heads=heads, kv_heads=kvh)
+    from oracle.oracle_py import Cache
+    res = []
+    for orc in (ref, port):
+        c = Cache(budget + 1, kvh * D, fp8=fp8, h2o_budget=budget, h2o_sinks=4)
+        out = orc.attn_run_cache(dims, c, q, g, k, v, threads=2)
+        assert c.len == steps and c.num_valid == budget
+        res.append((out, c))
+    (o0, c0), (o1, c1) = res
+    np.testing.assert_array_equal(o0, o1)
+    np.testing.assert_array_equal(c0.token_positions[:budget], c1.token_positions[:budget])
+    np.testing.assert_array_equal(c0.accum[:budget], c1.accum[:budget])
+    if fp8:
+        np.testing.assert_array_equal(c0.k8[:budget], c1.k8[:budget])
+        np.testing.assert_array_equal(c0.v_scales[:budget], c1.v_scales[:budget])
+    else:
+        np.testing.assert_array_equal(c0.k[:budget], c1.k[:budget])
+        np.testing.assert_array_equal(c0.v[:budget], c1.v[:budget])
+    assert list(c0.token_positions[:4]) == [0, 1, 2, 3]              # the sinks stay
+    assert list(c0.token_positions[budget - 5:budget]) == list(range(steps - 5, steps))   # and the recent rows
+
+
+@pytest.mark.parametrize("case", ["attn_fp8_h8_d256", "attn_h2o_h8_d256"])
+def test_cache_policy_golden(port, ref, case):
+    f = np.load(GOLD / f"{case}.npz")
+    from oracle.oracle_py import Cache
+    heads, kvh, D = int(f["heads"]), int(f["kv_heads"]), 256
+    dims = make_dims(num_attn_heads=heads, num_kv_heads=kvh)
+    for orc in (port, ref):
+        c = Cache(int(f["capacity"]), kvh * D, fp8=bool(f["fp8"]), h2o_budget=int(f["h2o_budget"]), h2o_sinks=4)
+        out = orc.attn_run_cache(dims, c, f["q"], f["gate"], f["k"], f["v"])
+        np.testing.assert_array_equal(out, f["out"])
+        if bool(f["fp8"]):
+            np.testing.assert_array_equal(c.k8, f["k8"])
+            np.testing.assert_array_equal(c.k_scales, f["k_scales"])
+        if int(f["h2o_budget"]):
+            np.testing.assert_array_equal(c.token_positions, f["token_positions"])
+            np.testing.assert_array_equal(c.accum, f["accum"])
