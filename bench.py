@@ -32,12 +32,20 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 H, HKV, D = 32, 2, 256
-KV_BYTES_PER_ROW = 2 * HKV * D * 2  # K and V, bf16, both KV heads
+KV_BYTES_PER_ROW = 2 * HKV * D * 2  # K and V, bf16, both KV heads (set_kv_dtype changes it for an FP8 store)
+KV_DTYPE = "bf16"
+
+
+def set_kv_dtype(name: str):
+    """bf16: 2 bytes per element.  fp8: one E4M3 byte per element plus the row's two fp32 scales."""
+    global KV_BYTES_PER_ROW, KV_DTYPE
+    KV_DTYPE = name
+    KV_BYTES_PER_ROW = 2 * HKV * D * 2 if name == "bf16" else 2 * HKV * D + 8
 
 
 def algorithmic_bytes_per_layer_seq(L: int) -> int:
-    """K+V rows once, q / gate / out once, the appended row (bf16 store)."""
-    return 2 * L * HKV * D * 2 + 3 * H * D * 4 + 2 * HKV * D * 2
+    """K+V rows once, q / gate / out once, the appended row."""
+    return L * KV_BYTES_PER_ROW + 3 * H * D * 4 + KV_BYTES_PER_ROW
 
 
 def load_peaks():
@@ -138,7 +146,7 @@ def run_reference(args):
 
 def workload_name(args):
     return (f"gated GQA decode attention, batch {args.batch}, context {args.ctx}, {args.layers} full-attention "
-            f"layers, {H}q/{HKV}kv heads x {D}, bf16 paged KV")
+            f"layers, {H}q/{HKV}kv heads x {D}, {'bf16' if KV_DTYPE == 'bf16' else 'FP8 E4M3 (per-row scales)'} paged KV")
 
 
 # ---------------------------------------------------------------------------------------------
@@ -197,7 +205,8 @@ def run_ours(args):
     total_steps = 2 * args.steps + args.warmup + args.e2e_steps + 4
     cfg = pkg.default_config(num_attn_heads=Hl, num_kv_heads=Hkvl, num_full_layers=NL, num_linear_layers=0,
                              max_seqs=B, max_seq_len=L + total_steps + 64, max_batch_tokens=max(B, 64),
-                             seq_shard_rank=my_ss, seq_shard_count=ss, device=local)
+                             seq_shard_rank=my_ss, seq_shard_count=ss, device=local,
+                             kv_dtype=pkg.binding.FM_KV_FP8_E4M3 if KV_DTYPE == "fp8" else pkg.binding.FM_KV_BF16)
     ctx = pkg.Context(cfg)
     ctx.set_stream(torch.cuda.current_stream().cuda_stream)
 
@@ -293,6 +302,7 @@ def run_ours(args):
     # roofline of the dominant kernel (split-KV decode) on this rank
     peak, peak_kind = load_peaks()
     alg_bytes_launch = algorithmic_bytes_per_layer_seq(int(L_mean)) * B / world
+    traffic_scale = 1.0 if KV_DTYPE == "bf16" else None  # the ncu capture below is of the bf16 kernel
     # The timed region holds nothing but launches of this kernel, consecutive ones overlapping at their
     # ends: its average launch duration is the region's device time over the launches in it.  The same
     # launches bracketed one by one (second pass) include each launch's start-up and drain.
@@ -306,8 +316,8 @@ def run_ours(args):
                 "us_per_launch": kern_s * 1e6, "launches_timed": n_dec,
                 "us_per_launch_bracketed_alone": iso_s * 1e6, "ms_per_step_with_launch_events": ms_profiled,
                 "algorithmic_bytes_per_launch": alg_bytes_launch,
-                "traffic": TRAFFIC_NCU_1SEQ_128K * (B / world) * (L_mean / 131073.0),
-                "traffic_source": "ncu capture at batch 1, scaled by sequences x rows per launch"}
+                "traffic": TRAFFIC_NCU_1SEQ_128K * (B / world) * (L_mean / 131073.0) if traffic_scale else None,
+                "traffic_source": "ncu capture at batch 1, scaled by sequences x rows per launch" if traffic_scale else None}
 
     # ---- end to end through the C-ABI with host buffers (rank-local copies inside the timed region) ----
     e2e = None
@@ -372,14 +382,14 @@ def run_ours(args):
         extra = extra_measurements(pkg, torch, dev, peak)
 
     cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu:
+    if rank == 0 and world == 1 and not args.no_cpu and KV_DTYPE == "bf16":  # the CPU leg times the reference's fp32 cache
         cpu = cpu_baseline(args, synth)
 
     if rank == 0:
         line = {
             "metric": "decode_attn_kv_stream", "value": value, "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16" if KV_DTYPE == "bf16" else "fp8_e4m3",
             "data": "synthetic",
             "config": {"workload": workload_name(args), "batch": B, "ctx": L, "layers": NL,
                        "parallelism": f"kv-head groups {hg} x sequence shards {ss}",
@@ -410,22 +420,42 @@ def parity_check(args, pkg, torch, dist, ctx, step, cur, qp, kn, vn, out, dev, w
     B, NL = args.batch, args.layers
     layer, s = NL - 1, B - 1
     n = ctx.kv_len(layer, s)
-    kd = torch.zeros((n + 1, Hkvl * D), device=dev); vd = torch.zeros_like(kd)
-    ctx.kv_export(layer, s, kd, vd, n + 1)          # on a sequence-sharded store: the rows this rank owns
-    torch.cuda.synchronize()
-    if ss > 1:
-        dist.all_reduce(kd, group=seq_group); dist.all_reduce(vd, group=seq_group)
-    kc, vc = kd.cpu().numpy(), vd.cpu().numpy()
-    del kd, vd
     pos = cur[0]
-    step()
-    torch.cuda.synchronize()
-    got = out[layer, s].cpu().numpy()
     x = qp[layer, s].cpu().numpy().reshape(Hl, 2, D)
     q, gate = np.ascontiguousarray(x[:, 0].reshape(1, -1)), np.ascontiguousarray(x[:, 1].reshape(1, -1))
     k, v = kn[layer, s:s + 1].cpu().numpy(), vn[layer, s:s + 1].cpu().numpy()
-    dims = make_dims(num_attn_heads=Hl, num_kv_heads=Hkvl, store_bf16=1)
-    want, _ = Oracle("port").attn_run(dims, kc, vc, n, q, gate, k, v, start_pos=pos, threads=host_threads())
+    if KV_DTYPE == "fp8":
+        from oracle.oracle_py import Cache
+        k8 = torch.zeros((n, Hkvl * D), dtype=torch.uint8, device=dev); v8 = torch.zeros_like(k8)
+        ks = torch.zeros(n, device=dev); vs = torch.zeros(n, device=dev)
+        ctx.kv_export_fp8(layer, s, k8, v8, ks, vs, n)   # on a sequence-sharded store: the rows this rank owns
+        torch.cuda.synchronize()
+        if ss > 1:
+            for t_ in (k8, v8, ks, vs):
+                dist.all_reduce(t_, group=seq_group)
+        cache = Cache(n + 1, Hkvl * D, fp8=True)
+        cache.k8[:n] = k8.cpu().numpy(); cache.v8[:n] = v8.cpu().numpy()
+        cache.k_scales[:n] = ks.cpu().numpy(); cache.v_scales[:n] = vs.cpu().numpy()
+        cache.c.len = n
+        del k8, v8
+        step()
+        torch.cuda.synchronize()
+        got = out[layer, s].cpu().numpy()
+        want = Oracle("port").attn_run_cache(make_dims(num_attn_heads=Hl, num_kv_heads=Hkvl), cache, q, gate, k, v, start_pos=pos,
+                                             threads=host_threads())
+    else:
+        kd = torch.zeros((n + 1, Hkvl * D), device=dev); vd = torch.zeros_like(kd)
+        ctx.kv_export(layer, s, kd, vd, n + 1)          # on a sequence-sharded store: the rows this rank owns
+        torch.cuda.synchronize()
+        if ss > 1:
+            dist.all_reduce(kd, group=seq_group); dist.all_reduce(vd, group=seq_group)
+        kc, vc = kd.cpu().numpy(), vd.cpu().numpy()
+        del kd, vd
+        step()
+        torch.cuda.synchronize()
+        got = out[layer, s].cpu().numpy()
+        dims = make_dims(num_attn_heads=Hl, num_kv_heads=Hkvl, store_bf16=1)
+        want, _ = Oracle("port").attn_run(dims, kc, vc, n, q, gate, k, v, start_pos=pos, threads=host_threads())
     a, r = got.astype(np.float64).ravel(), want.astype(np.float64).ravel()
     err = float((np.abs(a - r) / np.maximum(np.abs(r), np.sqrt(np.mean(r * r)))).max())
     t = torch.tensor([err], device=dev)
@@ -710,11 +740,13 @@ def main():
     ap.add_argument("--no-extra", action="store_true", help="skip the context sweep / prefill / GatedDeltaNet figures")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-check", action="store_true", help="skip the comparison of one step's output with the CPU checker")
+    ap.add_argument("--kv", default="bf16", choices=["bf16", "fp8"], help="element type of the KV store")
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"],
                     help="how sequence shards exchange partial results: the library's peer-memory kernels, or NCCL all-gathers")
     ap.add_argument("--probe", default=None, choices=["sweep", "prefill", "gdn_decode", "gdn_prefill", "hybrid"],
                     help="run only one of the extra measurements and print it (for profiling one kernel)")
     args = ap.parse_args()
+    set_kv_dtype(args.kv)
     if args.probe:
         import torch
         from __graft_entry__ import load_package

@@ -383,6 +383,7 @@ extern "C" fm_status fm_reset(FmCtx *ctx, int seq) {
     if (seq < -1 || seq >= c.max_seqs) return fail(ctx, FM_ERR_INVALID, "fm_reset: seq %d", seq);
     FM_CUDA(ctx, cudaSetDevice(c.device));
     const int s0 = seq < 0 ? 0 : seq, s1 = seq < 0 ? c.max_seqs : seq + 1;
+    ctx->pf_layer = -1;  // the prefill workspace may hold rows of a sequence that is going away
     for (int l = 0; l < c.num_full_layers; l++)
         for (int s = s0; s < s1; s++) {
             int *tab = &ctx->h_page_table[((size_t)l * c.max_seqs + s) * ctx->max_slots];
@@ -815,8 +816,11 @@ extern "C" fm_status fm_attn_prefill(FmCtx *ctx, int fa_idx, int seq, int start_
         // two launches: operand preparation (which is also the append), then the attention kernel
         ProfScope prof(ctx);
         const PrefillWork wk{ctx->d_pf_q16, ctx->d_pf_k16, ctx->d_pf_v16, ctx->d_err};
-        st = launched(ctx, launch_attn_prefill(kv, ctx->rope, seq, start_pos, row0, n, c.num_attn_heads, d_qp, d_q, d_g, d_k, d_v, d_qn,
+        const int prefix0 = (ctx->pf_layer == fa_idx && ctx->pf_seq == seq && ctx->pf_rows <= row0) ? ctx->pf_rows : 0;
+        ctx->pf_layer = -1;
+        st = launched(ctx, launch_attn_prefill(kv, ctx->rope, seq, start_pos, row0, prefix0, n, c.num_attn_heads, d_qp, d_q, d_g, d_k, d_v, d_qn,
                                                d_kn, c.rms_norm_eps, wk, d_out, ctx->stream), "attn_prefill");
+        if (st == FM_OK) { ctx->pf_layer = fa_idx; ctx->pf_seq = seq; ctx->pf_rows = row0 + n; }
     }
     if (st) return st;
     if (sg.host) FM_CUDA(ctx, cudaMemcpyAsync(ctx->h_err, ctx->d_err, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
@@ -980,6 +984,7 @@ static fm_status kv_import_prepare(FmCtx *ctx, const char *fn, int fa_idx, int s
     if (c.sliding_window > 0 && len > c.sliding_window)
         return fail(ctx, FM_ERR_INVALID, "%s: %d rows do not fit the sliding window of %d", fn, len, c.sliding_window);
     FM_CUDA(ctx, cudaSetDevice(c.device));
+    ctx->pf_layer = -1;
     int *tab = &ctx->h_page_table[((size_t)fa_idx * c.max_seqs + seq) * ctx->max_slots];
     size_t reclaim = 0;
     for (int i = 0; i < ctx->max_slots; i++)

@@ -141,6 +141,9 @@ struct FmCtx {
     void *d_pf_q16 = nullptr;  // [max_batch_tokens][H*D]
     void *d_pf_k16 = nullptr;  // [max_seq_len][Hkv*D]
     void *d_pf_v16 = nullptr;
+    // which (layer, sequence) the K / V workspace holds and how many of its rows: a prompt fed in several calls
+    // converts each cached row once, not once per call
+    int pf_layer = -1, pf_seq = -1, pf_rows = 0;
     int *d_err = nullptr;      // device-side error word written by kernels whose bounded waits expired
     int *h_err = nullptr;      // pinned copy
     void *d_work = nullptr;             // chunked GatedDeltaNet workspace
@@ -214,7 +217,8 @@ struct PrefillWork {
     void *q16, *k16, *v16;
     int *err;
 };
-int launch_attn_prefill(const KvView &kv, const RopeParams &rope, int seq, int start_pos, int row0, int n, int H,
+// prefix0: the fp16 workspace already holds cached rows [0, prefix0) of this (layer, sequence)
+int launch_attn_prefill(const KvView &kv, const RopeParams &rope, int seq, int start_pos, int row0, int prefix0, int n, int H,
                         const float *q_proj_out, const float *q, const float *gate, const float *k, const float *v,
                         const uint16_t *q_norm_w, const uint16_t *k_norm_w, float eps, const PrefillWork &wk, float *out,
                         cudaStream_t st);

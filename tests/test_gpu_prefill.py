@@ -34,6 +34,48 @@ def test_attn_prefill_matches_sequential_steps(pkg, port, synth, n, prefix):
     assert gated <= TOL
 
 
+def test_attn_prefill_in_small_calls(pkg, port, synth):
+    """A 4096-token prompt fed 32 tokens at a time (the reference's batch, MAX_PFB_GPU, metal_infer/shaders.metal:2130)
+    with a few decode steps in the middle: the result equals 4096 sequential CPU steps, and the cost of a call does not
+    grow with the rows already cached beyond what attending to them takes (each cached row is converted into the
+    kernel's operand workspace once, not once per call)."""
+    import time
+    import torch
+    T, step = 4096, 32
+    q, g, k, v = synth.attn_step_inputs(91, T, bf16=True)
+    dev = torch.device("cuda:0")
+    cfg = pkg.default_config(num_full_layers=1, num_linear_layers=0, max_seq_len=T + 8, max_batch_tokens=64)
+    c = pkg.Context(cfg)
+    c.set_stream(torch.cuda.current_stream().cuda_stream)
+    tq, tg, tk, tv = (torch.from_numpy(a).to(dev) for a in (q, g, k, v))
+    out = torch.empty((T, 8192), device=dev)
+    times = []
+    t = 0
+    while t < T:
+        if t == 2048:  # two decode steps in the middle of the prompt: the workspace has to pick their rows up
+            for _ in range(2):
+                c.attn_decode(0, [0], [t], out[t:t + 1], q=tq[t:t + 1], gate=tg[t:t + 1], k=tk[t:t + 1], v=tv[t:t + 1])
+                t += 1
+            continue
+        n = min(step, T - t)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        c.attn_prefill(0, 0, t, n, out[t:t + n], q=tq[t:t + n], gate=tg[t:t + n], k=tk[t:t + n], v=tv[t:t + n])
+        torch.cuda.synchronize()
+        times.append((t, time.perf_counter() - t0))
+        t += n
+    got = out.cpu().numpy()
+    c.close()
+    ref_out, _, _ = oracle_attn(port, 32, 2, np.zeros((0, 512), np.float32), np.zeros((0, 512), np.float32), q, g, k, v, start_pos=0,
+                                threads=16)
+    gated, _, rr = rel_errors(got, ref_out)
+    print("prefill in 32-token calls: gated", gated, "rms-rel", rr)
+    assert gated <= TOL
+    early = np.median([d for t_, d in times if 256 <= t_ < 768]); late = np.median([d for t_, d in times if t_ >= 3584])
+    print("seconds per call: early %.2e late %.2e" % (early, late))
+    assert late <= 3.0 * early + 30e-6
+
+
 @pytest.mark.parametrize("sizes", [(1,), (63,), (64,), (65,), (200,), (100, 70, 3), (4096,)])
 def test_gdn_prefill_matches_sequential_steps(pkg, port, synth, sizes):
     """Chunked GatedDeltaNet prefill against sequential CPU steps: output, final recurrent state and
