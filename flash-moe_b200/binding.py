@@ -25,7 +25,7 @@ EXPORTS = [
     "fm_state_import", "fm_launch_count", "fm_profile_enable", "fm_profile_read",
     "fm_attn_decode_static", "fm_exchange_bytes", "fm_exchange_attach", "fm_attn_decode_exchange_push",
     "fm_attn_decode_exchange_merge", "fm_attn_decode_exchange", "fm_attn_decode_layers",
-    "fm_kv_export_fp8", "fm_kv_import_fp8",
+    "fm_kv_export_fp8", "fm_kv_import_fp8", "fm_h2o_export",
 ]
 
 
@@ -41,7 +41,7 @@ class FmConfig(C.Structure):
         ("max_seqs", C.c_int), ("max_seq_len", C.c_int), ("page_size", C.c_int),
         ("kv_pool_pages", C.c_int64), ("max_batch_tokens", C.c_int),
         ("seq_shard_rank", C.c_int), ("seq_shard_count", C.c_int), ("device", C.c_int),
-        ("sliding_window", C.c_int), ("kv_dtype", C.c_int),
+        ("sliding_window", C.c_int), ("kv_dtype", C.c_int), ("h2o_budget", C.c_int), ("h2o_num_sinks", C.c_int),
     ]
 
 
@@ -296,6 +296,12 @@ class Context:
     def kv_import_fp8(self, fa_idx, seq, k8, v8, k_scales, v_scales, length):
         self._check(self.lib.fm_kv_import_fp8(self.h, C.c_int(fa_idx), C.c_int(seq), _ptr(k8), _ptr(v8), _ptr(k_scales),
                                               _ptr(v_scales), C.c_int(length)))
+
+    def h2o_export(self, fa_idx, seq, accum, token_positions, max_rows) -> int:
+        n = C.c_int(0)
+        self._check(self.lib.fm_h2o_export(self.h, C.c_int(fa_idx), C.c_int(seq), _ptr(accum), _ptr(token_positions),
+                                           C.c_int(max_rows), C.byref(n)))
+        return n.value
 
     def state_export(self, li, seq, conv, ssm):
         self._check(self.lib.fm_state_export(self.h, C.c_int(li), C.c_int(seq), _ptr(conv), _ptr(ssm)))

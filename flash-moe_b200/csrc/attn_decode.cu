@@ -134,6 +134,7 @@ struct DecodeFused {
     unsigned int *group_counters;  // [tokens*Hkv][kDecMaxGroups] arrivals per group of splits (many splits only)
     float *group_o, *group_ml;     // [tokens][H][kDecMaxGroups][D] / [..][2]: the groups' merged partials
     int *err;                // tail 4: device error word (a peer never published)
+    const int *h2o_slot;     // H2O store: [seqs] the physical row the new token takes (overrides the token list's row)
 };
 
 // kFp8: the store holds E4M3 bytes with one scale per row (fm_fp8.cuh).  The bytes go through the MMAs as fp16
@@ -164,6 +165,7 @@ __device__ __forceinline__ void attn_decode_body(const KvView &kv, const RopePar
 
     int seq, pos, row_new;
     tok_get(toks, tok, seq, pos, row_new);
+    if (kFused && f.h2o_slot != nullptr) row_new = f.h2o_slot[seq];
     const int L = tok_rows(toks, tok);  // rows attended, the new one included (row_new + 1 unless the window wrapped)
 
     // ---- which page slots this CTA walks ----
@@ -595,6 +597,10 @@ __device__ __forceinline__ void attn_decode_body(const KvView &kv, const RopePar
             *reinterpret_cast<float4 *>(f.out + ((size_t)tk * H + head) * kD + d) =
                 make_float4(acc.x * inv * fast_sigmoid(g.x), acc.y * inv * fast_sigmoid(g.y), acc.z * inv * fast_sigmoid(g.z),
                             acc.w * inv * fast_sigmoid(g.w));
+            if (f.ml_out != nullptr && d == 0) {  // the softmax's (max, sum), for the H2O mass accounting
+                f.ml_out[((size_t)tk * H + head) * 2 + 0] = M;
+                f.ml_out[((size_t)tk * H + head) * 2 + 1] = lt;
+            }
         } else if (f.tail == 2) {
             *reinterpret_cast<float4 *>(f.out + ((size_t)tk * H + head) * kD + d) = acc;
             if (d == 0) {
@@ -870,7 +876,7 @@ int launch_attn_decode_fused(const KvView &kv, const RopeParams &rope, const Tok
                              float *part_o, float *part_ml, int nsplits, const float *k_new, const float *v_new,
                              const uint16_t *k_norm_w, int tail, const float *gate, float *out, float *ml_out,
                              const XchgView *x, uint32_t step, const DecodeScratch &scr, int *err, bool overlap_prev,
-                             cudaStream_t st) {
+                             cudaStream_t st, const int *h2o_slot) {
     if (!(kv.fp8 ? configure_decode<true, true>() : configure_decode<true, false>())) return -1;
     if (tail != 0 && nsplits > kDecMaxLastCtaSplits && (toks.n > scr.group_tokens || nsplits > kDecGroup * kDecMaxGroups)) return -1;
     if (kv.fp8 && k_new != nullptr && kv.Hkv > 8) return -1;
@@ -885,6 +891,7 @@ int launch_attn_decode_fused(const KvView &kv, const RopeParams &rope, const Tok
     f.group_o = scr.group_o;
     f.group_ml = scr.group_ml;
     f.err = err;
+    f.h2o_slot = h2o_slot;
     // overlap_prev: the caller vouches that this launch reads nothing the previous kernel in the
     // stream writes except through the scratch the kernel guards itself (another layer's step).
     // Its CTAs then take SMs as the previous grid's CTAs retire instead of after the grid drains.
@@ -957,7 +964,7 @@ constexpr int kMergeWarps = 16;
 __global__ void __launch_bounds__(32 * kMergeWarps)
 attn_merge_wide_kernel(const float *__restrict__ part_o, const float *__restrict__ part_ml, int nparts, int H,
                        const float *__restrict__ q_proj_out, const float *__restrict__ gate, float *__restrict__ out,
-                       float *__restrict__ ml_out) {
+                       float *__restrict__ ml_out, float *__restrict__ ml_final) {
     __shared__ float4 s_acc[kMergeWarps][64];
     __shared__ float s_w[256];
     const int head = blockIdx.x, tok = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -1036,10 +1043,14 @@ attn_merge_wide_kernel(const float *__restrict__ part_o, const float *__restrict
     const float inv = lt > 0.f ? 1.0f / lt : 0.f;
     *reinterpret_cast<float4 *>(dst) = make_float4(acc.x * inv * fast_sigmoid(g.x), acc.y * inv * fast_sigmoid(g.y),
                                                    acc.z * inv * fast_sigmoid(g.z), acc.w * inv * fast_sigmoid(g.w));
+    if (ml_final != nullptr && threadIdx.x == 0) {
+        ml_final[((size_t)tok * H + head) * 2 + 0] = M;
+        ml_final[((size_t)tok * H + head) * 2 + 1] = lt;
+    }
 }
 
 int launch_attn_merge_wide(const float *part_o, const float *part_ml, int nparts, int ntok, int H, const float *q_proj_out,
-                           const float *gate, float *out, float *ml_out, cudaStream_t st) {
+                           const float *gate, float *out, float *ml_out, cudaStream_t st, float *ml_final) {
     if (ntok <= 0 || nparts < 1 || nparts > 256) return -1;
     cudaLaunchConfig_t lc = {};
     lc.gridDim = dim3(H, ntok); lc.blockDim = dim3(32 * kMergeWarps); lc.dynamicSmemBytes = 0; lc.stream = st;
@@ -1047,7 +1058,7 @@ int launch_attn_merge_wide(const float *part_o, const float *part_ml, int nparts
     at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     at[0].val.programmaticStreamSerializationAllowed = 1;
     lc.attrs = at; lc.numAttrs = 1;
-    return cudaLaunchKernelEx(&lc, attn_merge_wide_kernel, part_o, part_ml, nparts, H, q_proj_out, gate, out, ml_out) == cudaSuccess ? 1 : -1;
+    return cudaLaunchKernelEx(&lc, attn_merge_wide_kernel, part_o, part_ml, nparts, H, q_proj_out, gate, out, ml_out, ml_final) == cudaSuccess ? 1 : -1;
 }
 
 int launch_attn_merge(const float *part_o, const float *part_ml, int nparts, long long ps_o,

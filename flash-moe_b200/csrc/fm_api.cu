@@ -51,6 +51,7 @@ extern "C" void fm_default_config(FmConfig *c) {
     c->max_batch_tokens = 64;
     c->seq_shard_rank = 0; c->seq_shard_count = 1; c->device = 0;
     c->kv_dtype = FM_KV_BF16;
+    c->h2o_budget = 0; c->h2o_num_sinks = 4;
 }
 
 // RoPE frequency of pair i under the scaling modes of metal_infer/layer_forward.h:22-63, evaluated
@@ -103,6 +104,12 @@ extern "C" fm_status fm_create(const FmConfig *cfg, FmCtx **out) {
             return fail(nullptr, FM_ERR_INVALID, "fm_create: sliding_window %d (0, or 1..max_seq_len)", c.sliding_window);
         if (c.kv_dtype != FM_KV_BF16 && c.kv_dtype != FM_KV_FP8_E4M3)
             return fail(nullptr, FM_ERR_INVALID, "fm_create: kv_dtype %d (FM_KV_BF16 or FM_KV_FP8_E4M3)", c.kv_dtype);
+        if (c.h2o_budget < 0 || c.h2o_num_sinks < 0)
+            return fail(nullptr, FM_ERR_INVALID, "fm_create: h2o_budget %d / h2o_num_sinks %d", c.h2o_budget, c.h2o_num_sinks);
+        if (c.h2o_budget > 0 && c.seq_shard_count != 1)
+            return fail(nullptr, FM_ERR_UNSUPPORTED, "fm_create: H2O eviction needs the whole sequence on one context (seq_shard_count=1)");
+        if (c.h2o_budget > 0 && (size_t)c.num_attn_heads * c.head_dim * sizeof(float) > 96 * 1024)
+            return fail(nullptr, FM_ERR_UNSUPPORTED, "fm_create: H2O eviction takes at most 96 query heads per context (%d)", c.num_attn_heads);
         if (c.kv_dtype == FM_KV_FP8_E4M3 && c.num_kv_heads > 8)
             return fail(nullptr, FM_ERR_UNSUPPORTED, "fm_create: an FP8 store takes at most 8 KV heads per context (%d)", c.num_kv_heads);
     }
@@ -121,6 +128,7 @@ extern "C" fm_status fm_create(const FmConfig *cfg, FmCtx **out) {
     FmCtx *ctx = new (std::nothrow) FmCtx();
     if (!ctx) return fail(nullptr, FM_ERR_NOMEM, "fm_create: out of host memory");
     ctx->cfg = c;
+    if (c.h2o_budget > 0) ctx->cfg.sliding_window = 0;  // H2O replaces the window when both are set (layer_forward.h:148-152)
 #define CREATE_CUDA(call)                                                                               \
     do {                                                                                                \
         cudaError_t e__ = (call);                                                                       \
@@ -148,8 +156,9 @@ extern "C" fm_status fm_create(const FmConfig *cfg, FmCtx **out) {
         if (c.rope_scaling_mode == 3 && c.rope_scale_factor > 1.0f) yarn = sqrtf(0.1f * logf(c.rope_scale_factor) + 1.0f);
         ctx->rope.logit_scale = (1.0f / sqrtf((float)c.head_dim)) * yarn;
 
-        // a sliding window bounds the rows a sequence can hold, whatever max_seq_len says
-        const int max_rows = c.sliding_window > 0 ? std::min(c.max_seq_len, c.sliding_window) : c.max_seq_len;
+        // a sliding window or an H2O budget bounds the rows a sequence can hold, whatever max_seq_len says
+        const int max_rows = c.h2o_budget > 0 ? std::min(c.max_seq_len, c.h2o_budget + 1)
+                           : c.sliding_window > 0 ? std::min(c.max_seq_len, c.sliding_window) : c.max_seq_len;
         const int gpages = (max_rows + c.page_size - 1) / c.page_size;
         ctx->max_slots = (gpages + c.seq_shard_count - 1) / c.seq_shard_count;
         ctx->page_bytes = kv_page_bytes(c.kv_dtype == FM_KV_FP8_E4M3, c.num_kv_heads, c.page_size, c.head_dim);
@@ -191,6 +200,21 @@ extern "C" fm_status fm_create(const FmConfig *cfg, FmCtx **out) {
         CREATE_CUDA(cudaMemset(ds.group_counters, 0, nsets * gc * sizeof(unsigned int)));
         CREATE_CUDA(cudaMalloc(&ds.group_o, nsets * grows * c.head_dim * sizeof(float)));
         CREATE_CUDA(cudaMalloc(&ds.group_ml, nsets * grows * 2 * sizeof(float)));
+        if (c.h2o_budget > 0) {
+            ctx->h2o_cap = c.h2o_budget + 1;
+            const size_t ne = (size_t)c.num_full_layers * c.max_seqs * ctx->h2o_cap, ns = (size_t)c.num_full_layers * c.max_seqs;
+            CREATE_CUDA(cudaMalloc(&ctx->d_h2o_accum, ne * sizeof(float)));
+            CREATE_CUDA(cudaMalloc(&ctx->d_h2o_order, ne * sizeof(int)));
+            CREATE_CUDA(cudaMalloc(&ctx->d_h2o_tokpos, ne * sizeof(int)));
+            CREATE_CUDA(cudaMalloc(&ctx->d_h2o_slot, ns * sizeof(int)));
+            CREATE_CUDA(cudaMalloc(&ctx->d_h2o_counter, ns * sizeof(unsigned int)));
+            CREATE_CUDA(cudaMalloc(&ctx->d_h2o_ml, (size_t)kMaxList * c.num_attn_heads * 2 * sizeof(float)));
+            CREATE_CUDA(cudaMemset(ctx->d_h2o_accum, 0, ne * sizeof(float)));
+            CREATE_CUDA(cudaMemset(ctx->d_h2o_order, 0, ne * sizeof(int)));
+            CREATE_CUDA(cudaMemset(ctx->d_h2o_tokpos, 0, ne * sizeof(int)));
+            CREATE_CUDA(cudaMemset(ctx->d_h2o_slot, 0, ns * sizeof(int)));
+            CREATE_CUDA(cudaMemset(ctx->d_h2o_counter, 0, ns * sizeof(unsigned int)));
+        }
         if (c.seq_shard_count == 1) {  // prefill needs the whole sequence on one context
             CREATE_CUDA(cudaMalloc(&ctx->d_pf_q16, (size_t)c.max_batch_tokens * c.num_attn_heads * c.head_dim * 2 * 2));  // hi | lo
             CREATE_CUDA(cudaMalloc(&ctx->d_pf_k16, (size_t)c.max_seq_len * c.num_kv_heads * c.head_dim * 2));
@@ -232,6 +256,8 @@ extern "C" void fm_destroy(FmCtx *ctx) {
     cudaFree(ctx->dec_scr.group_counters); cudaFree(ctx->dec_scr.group_o); cudaFree(ctx->dec_scr.group_ml);
     cudaFree(ctx->d_part_o); cudaFree(ctx->d_part_ml); cudaFree(ctx->d_dec_counters); cudaFree(ctx->d_xchg_counter); cudaFree(ctx->d_pf_q16); cudaFree(ctx->d_pf_k16); cudaFree(ctx->d_pf_v16); cudaFree(ctx->d_err);
     if (ctx->h_err) cudaFreeHost(ctx->h_err); cudaFree(ctx->d_work);
+    cudaFree(ctx->d_h2o_accum); cudaFree(ctx->d_h2o_order); cudaFree(ctx->d_h2o_tokpos); cudaFree(ctx->d_h2o_slot);
+    cudaFree(ctx->d_h2o_counter); cudaFree(ctx->d_h2o_ml);
     cudaFree(ctx->d_stage);
     cudaFree(ctx->d_lstage);
     if (ctx->h_lstage) cudaFreeHost(ctx->h_lstage);
@@ -346,12 +372,32 @@ static inline void release_page(FmCtx *ctx, int p) {
 }
 
 // Rows of the store a sequence occupies after `count` tokens, and the row token number `count` goes to.
-static inline int rows_held(const FmConfig &c, int count) { return c.sliding_window > 0 ? std::min(count, c.sliding_window) : count; }
-static inline int row_of(const FmConfig &c, int count) { return c.sliding_window > 0 ? count % c.sliding_window : count; }
+// (H2O: `count` tokens occupy min(count, budget + 1) rows while the step that appended the last one runs and
+// min(count, budget) once it has evicted -- rows_kept; the row a token goes to is decided on the device.)
+static inline int rows_held(const FmConfig &c, int count) {
+    if (c.h2o_budget > 0) return std::min(count, c.h2o_budget + 1);
+    return c.sliding_window > 0 ? std::min(count, c.sliding_window) : count;
+}
+static inline int rows_kept(const FmConfig &c, int count) { return c.h2o_budget > 0 ? std::min(count, c.h2o_budget) : rows_held(c, count); }
+static inline int row_of(const FmConfig &c, int count) {
+    if (c.h2o_budget > 0) return std::min(count, c.h2o_budget);
+    return c.sliding_window > 0 ? count % c.sliding_window : count;
+}
+static H2oView h2o_view(const FmCtx *ctx, int fa_idx) {
+    H2oView h;
+    const size_t s = (size_t)fa_idx * ctx->cfg.max_seqs;
+    h.cap = ctx->h2o_cap;
+    h.accum = ctx->d_h2o_accum + s * h.cap;
+    h.order = ctx->d_h2o_order + s * h.cap;
+    h.tokpos = ctx->d_h2o_tokpos + s * h.cap;
+    h.slot = ctx->d_h2o_slot + s;
+    h.counter = ctx->d_h2o_counter + s;
+    return h;
+}
 
 static fm_status ensure_pages(FmCtx *ctx, int fa_idx, int seq, int new_len) {
     const FmConfig &c = ctx->cfg;
-    if (c.sliding_window == 0 && new_len > c.max_seq_len)
+    if (c.sliding_window == 0 && c.h2o_budget == 0 && new_len > c.max_seq_len)
         return fail(ctx, FM_ERR_CAPACITY, "KV cache overflow (pos=%d >= cap=%d)", new_len - 1, c.max_seq_len);
     new_len = rows_held(c, new_len);
     const int gpages = (new_len + c.page_size - 1) / c.page_size;
@@ -390,6 +436,10 @@ extern "C" fm_status fm_reset(FmCtx *ctx, int seq) {
             for (int i = 0; i < ctx->max_slots; i++)
                 if (tab[i] >= 0) { release_page(ctx, tab[i]); tab[i] = -1; }
             ctx->kv_len[lidx(ctx, l, s)] = 0;
+            if (c.h2o_budget > 0) {
+                fm_status st = launched(ctx, launch_h2o_init(h2o_view(ctx, l), s, 0, ctx->stream), "h2o_init");
+                if (st) return st;
+            }
         }
     for (int l = 0; l < c.num_linear_layers; l++)
         for (int s = s0; s < s1; s++) {
@@ -412,8 +462,8 @@ extern "C" fm_status fm_seq_fork(FmCtx *ctx, int src, int dst) {
     const FmConfig &c = ctx->cfg;
     if (src < 0 || src >= c.max_seqs || dst < 0 || dst >= c.max_seqs || src == dst)
         return fail(ctx, FM_ERR_INVALID, "fm_seq_fork: sequences %d -> %d of %d", src, dst, c.max_seqs);
-    if (c.sliding_window > 0 && c.num_full_layers > 0)
-        return fail(ctx, FM_ERR_UNSUPPORTED, "fm_seq_fork: pages of a sliding-window store are rewritten in place and cannot be shared");
+    if ((c.sliding_window > 0 || c.h2o_budget > 0) && c.num_full_layers > 0)
+        return fail(ctx, FM_ERR_UNSUPPORTED, "fm_seq_fork: pages of a sliding-window or H2O store are rewritten in place and cannot be shared");
     // pages to copy: one per layer whose last local page is partly filled.  The demand is checked before dst is
     // touched (an error changes no state); the pages dst alone holds come back to the pool when it is reset.
     size_t need = 0, reclaim = 0;
@@ -545,7 +595,7 @@ static fm_status reserve_rows(FmCtx *ctx, int fa_idx, const int *seq, int n, std
     for (int i = 0; i < n; i++) {
         const int count = ctx->kv_len[lidx(ctx, fa_idx, seq[i])] + add[seq[i]];
         add[seq[i]]++;
-        if (c.sliding_window == 0 && count >= c.max_seq_len)
+        if (c.sliding_window == 0 && c.h2o_budget == 0 && count >= c.max_seq_len)
             return fail(ctx, FM_ERR_CAPACITY, "KV cache overflow (pos=%d >= cap=%d)", count, c.max_seq_len);
         rows[i] = row_of(c, count);
         if (nrows) (*nrows)[i] = rows_held(c, count + 1);
@@ -578,6 +628,8 @@ extern "C" fm_status fm_kv_append_rope(FmCtx *ctx, int fa_idx, const int *seq, c
     fm_status st = check_layer_seq(ctx, "fm_kv_append_rope", fa_idx, ctx->cfg.num_full_layers, seq, n);
     if (st) return st;
     if (n == 0) return FM_OK;
+    if (ctx->cfg.h2o_budget > 0)
+        return fail(ctx, FM_ERR_UNSUPPORTED, "fm_kv_append_rope: with H2O eviction a row is appended by the decode step that attends to it");
     FM_CUDA(ctx, cudaSetDevice(ctx->cfg.device));
     const size_t kv_dim = (size_t)ctx->cfg.num_kv_heads * ctx->cfg.head_dim;
     Stager sg(ctx);
@@ -649,7 +701,11 @@ static fm_status decode_core(FmCtx *ctx, int fa_idx, const int *seq, const int *
                              float *o_part, float *ml_part) {
     const FmConfig &c = ctx->cfg;
     const int H = c.num_attn_heads, D = c.head_dim;
-    std::vector<int> rows(batch), nrows(batch);
+    const bool h2o = c.h2o_budget > 0;
+    if (h2o && (k == nullptr || out == nullptr))
+        return fail(ctx, FM_ERR_UNSUPPORTED, "fm_attn_decode: with H2O eviction a step appends its row and produces the final output");
+    std::vector<int> rows(batch), nrows(batch), tok_index(batch);
+    for (int i = 0; i < batch; i++) tok_index[i] = ctx->kv_len[lidx(ctx, fa_idx, seq[i])];  // tokens seen before this one
     if (k != nullptr) {
         fm_status st = reserve_rows(ctx, fa_idx, seq, batch, rows, &nrows);  // pages and lengths; the kernel writes the rows
         if (st) return st;
@@ -685,13 +741,23 @@ static fm_status decode_core(FmCtx *ctx, int fa_idx, const int *seq, const int *
         ProfScope prof(ctx);
         const LayerScratch ls = layer_scratch(ctx, fa_idx);
         const bool wide = ns > kDecMaxLastCtaSplits;
+        const H2oView hv = h2o ? h2o_view(ctx, fa_idx) : H2oView{};
         fm_status st = launched(ctx, launch_attn_decode_fused(kv, ctx->rope, t, H, qp, qq, qnw, c.rms_norm_eps, ls.part_o, ls.part_ml, ns,
                                                               k ? k + i0 * kvd : nullptr, v ? v + i0 * kvd : nullptr, knw, wide ? 0 : (out ? 1 : 2),
-                                                              gp, op, mlp, nullptr, 0, ls.scr, ctx->d_err,
-                                                              ctx->overlap_prev && i0 == 0 && !sg_host(ctx), ctx->stream), "attn_decode");
+                                                              gp, op, h2o ? ctx->d_h2o_ml : mlp, nullptr, 0, ls.scr, ctx->d_err,
+                                                              ctx->overlap_prev && i0 == 0 && !sg_host(ctx), ctx->stream, h2o ? hv.slot : nullptr),
+                                "attn_decode");
         if (st) return st;
         if (wide) {
-            st = launched(ctx, launch_attn_merge_wide(ls.part_o, ls.part_ml, ns, t.n, H, qp, gp, op, mlp, ctx->stream), "attn_merge");
+            st = launched(ctx, launch_attn_merge_wide(ls.part_o, ls.part_ml, ns, t.n, H, qp, gp, op, mlp, ctx->stream, h2o ? ctx->d_h2o_ml : nullptr),
+                          "attn_merge");
+            if (st) return st;
+        }
+        if (h2o) {
+            // the step's attention mass per cache row, and the eviction if the budget is exceeded (attn_h2o.cu)
+            const int recent = (c.h2o_budget - c.h2o_num_sinks) / 4;  // kv_cache_new(), metal_infer/layer_forward.h:203
+            st = launched(ctx, launch_h2o_mass(kv, ctx->rope, t, tok_index.data() + i0, hv, c.h2o_budget, c.h2o_num_sinks, recent, H, qp, qq, qnw,
+                                               c.rms_norm_eps, ctx->d_h2o_ml, max_len, ctx->stream), "h2o_mass");
             if (st) return st;
         }
     }
@@ -790,6 +856,7 @@ extern "C" fm_status fm_attn_prefill(FmCtx *ctx, int fa_idx, int seq, int start_
     if (n < 0 || n > c.max_batch_tokens) return fail(ctx, FM_ERR_INVALID, "fm_attn_prefill: n=%d exceeds max_batch_tokens=%d", n, c.max_batch_tokens);
     if (c.seq_shard_count != 1) return fail(ctx, FM_ERR_UNSUPPORTED, "fm_attn_prefill: needs the whole sequence on one context (seq_shard_count=1)");
     if (c.kv_dtype != FM_KV_BF16) return fail(ctx, FM_ERR_UNSUPPORTED, "fm_attn_prefill: the store is FP8; feed the prompt through fm_attn_decode");
+    if (c.h2o_budget > 0) return fail(ctx, FM_ERR_UNSUPPORTED, "fm_attn_prefill: H2O eviction works per decode step; feed the prompt through fm_attn_decode");
     if (n == 0) return FM_OK;
     FM_CUDA(ctx, cudaSetDevice(c.device));
     const size_t qd = (size_t)c.num_attn_heads * c.head_dim, kvd = (size_t)c.num_kv_heads * c.head_dim;
@@ -940,7 +1007,7 @@ static fm_status kv_export_check(FmCtx *ctx, const char *fn, int fa_idx, int seq
     const FmConfig &c = ctx->cfg;
     if (fa_idx < 0 || fa_idx >= c.num_full_layers || seq < 0 || seq >= c.max_seqs || !ptrs_ok)
         return fail(ctx, FM_ERR_INVALID, "%s: bad argument", fn);
-    *len = rows_held(c, ctx->kv_len[lidx(ctx, fa_idx, seq)]);  // rows in store order (a wrapped window is not unrolled)
+    *len = rows_kept(c, ctx->kv_len[lidx(ctx, fa_idx, seq)]);  // rows in store order (a wrapped window is not unrolled)
     if (len_out) *len_out = *len;
     if (*len > max_rows) return fail(ctx, FM_ERR_INVALID, "%s: %d rows held, room for %d", fn, *len, max_rows);
     return FM_OK;
@@ -955,15 +1022,16 @@ extern "C" fm_status fm_kv_export(FmCtx *ctx, int fa_idx, int seq, float *k, flo
     FM_CUDA(ctx, cudaSetDevice(c.device));
     const size_t kvd = (size_t)c.num_kv_heads * c.head_dim;
     const KvView kv = kv_view(ctx, fa_idx);
+    const int *order = c.h2o_budget > 0 ? h2o_view(ctx, fa_idx).order + (size_t)seq * ctx->h2o_cap : nullptr;  // cache order of an H2O store
     if (ctx->ptr_mode == FM_PTR_DEVICE)
-        return launched(ctx, launch_kv_export(kv, seq, 0, len, k, v, ctx->stream), "kv_export");
+        return launched(ctx, launch_kv_export(kv, seq, 0, len, k, v, order, ctx->stream), "kv_export");
     return staged_rows(ctx, len, kvd * 4, false, [&](int row0, int n, size_t o_v, size_t, size_t) -> fm_status {
         float *dk = reinterpret_cast<float *>(ctx->d_stage), *dv = reinterpret_cast<float *>(ctx->d_stage + o_v);
         // rows another shard holds are left alone in the caller's arrays: start from what is there
         memcpy(ctx->h_stage, k + (size_t)row0 * kvd, (size_t)n * kvd * 4);
         memcpy(ctx->h_stage + o_v, v + (size_t)row0 * kvd, (size_t)n * kvd * 4);
         FM_CUDA(ctx, cudaMemcpyAsync(ctx->d_stage, ctx->h_stage, o_v + (size_t)n * kvd * 4, cudaMemcpyHostToDevice, ctx->stream));
-        const fm_status s2 = launched(ctx, launch_kv_export(kv, seq, row0, n, dk, dv, ctx->stream), "kv_export");
+        const fm_status s2 = launched(ctx, launch_kv_export(kv, seq, row0, n, dk, dv, order, ctx->stream), "kv_export");
         if (s2) return s2;
         FM_CUDA(ctx, cudaMemcpyAsync(ctx->h_stage, ctx->d_stage, o_v + (size_t)n * kvd * 4, cudaMemcpyDeviceToHost, ctx->stream));
         FM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
@@ -983,6 +1051,8 @@ static fm_status kv_import_prepare(FmCtx *ctx, const char *fn, int fa_idx, int s
     if (len > c.max_seq_len) return fail(ctx, FM_ERR_CAPACITY, "KV cache overflow (pos=%d >= cap=%d)", len - 1, c.max_seq_len);
     if (c.sliding_window > 0 && len > c.sliding_window)
         return fail(ctx, FM_ERR_INVALID, "%s: %d rows do not fit the sliding window of %d", fn, len, c.sliding_window);
+    if (c.h2o_budget > 0 && len > c.h2o_budget)
+        return fail(ctx, FM_ERR_INVALID, "%s: %d rows exceed the H2O budget of %d", fn, len, c.h2o_budget);
     FM_CUDA(ctx, cudaSetDevice(c.device));
     ctx->pf_layer = -1;
     int *tab = &ctx->h_page_table[((size_t)fa_idx * c.max_seqs + seq) * ctx->max_slots];
@@ -995,9 +1065,13 @@ static fm_status kv_import_prepare(FmCtx *ctx, const char *fn, int fa_idx, int s
         return fail(ctx, FM_ERR_CAPACITY, "KV page pool exhausted (%zu pages needed, %zu free)", need, ctx->free_pages.size() + reclaim);
     for (int i = 0; i < ctx->max_slots; i++)
         if (tab[i] >= 0) { release_page(ctx, tab[i]); tab[i] = -1; }
-    const fm_status st = ensure_pages(ctx, fa_idx, seq, len);
+    fm_status st = ensure_pages(ctx, fa_idx, seq, len);
     if (st) return st;
     ctx->kv_len[lidx(ctx, fa_idx, seq)] = len;
+    if (c.h2o_budget > 0) {  // imported rows start in their own order, with no mass yet
+        st = launched(ctx, launch_h2o_init(h2o_view(ctx, fa_idx), seq, len, ctx->stream), "h2o_init");
+        if (st) return st;
+    }
     return FM_OK;
 }
 
@@ -1033,8 +1107,9 @@ extern "C" fm_status fm_kv_export_fp8(FmCtx *ctx, int fa_idx, int seq, uint8_t *
     FM_CUDA(ctx, cudaSetDevice(c.device));
     const size_t kvd = (size_t)c.num_kv_heads * c.head_dim;
     const KvView kv = kv_view(ctx, fa_idx);
+    const int *order = c.h2o_budget > 0 ? h2o_view(ctx, fa_idx).order + (size_t)seq * ctx->h2o_cap : nullptr;
     if (ctx->ptr_mode == FM_PTR_DEVICE)
-        return launched(ctx, launch_kv_copy_fp8(kv, seq, 0, len, k8, v8, k_scales, v_scales, false, ctx->stream), "kv_export_fp8");
+        return launched(ctx, launch_kv_copy_fp8(kv, seq, 0, len, k8, v8, k_scales, v_scales, false, order, ctx->stream), "kv_export_fp8");
     return staged_rows(ctx, len, kvd, true, [&](int row0, int n, size_t o_v, size_t o_ks, size_t o_vs) -> fm_status {
         char *hs = ctx->h_stage, *ds = ctx->d_stage;
         memcpy(hs, k8 + (size_t)row0 * kvd, (size_t)n * kvd);
@@ -1044,7 +1119,7 @@ extern "C" fm_status fm_kv_export_fp8(FmCtx *ctx, int fa_idx, int seq, uint8_t *
         FM_CUDA(ctx, cudaMemcpyAsync(ds, hs, o_vs + (size_t)n * 4, cudaMemcpyHostToDevice, ctx->stream));
         const fm_status s2 = launched(ctx, launch_kv_copy_fp8(kv, seq, row0, n, reinterpret_cast<uint8_t *>(ds), reinterpret_cast<uint8_t *>(ds + o_v),
                                                               reinterpret_cast<float *>(ds + o_ks), reinterpret_cast<float *>(ds + o_vs), false,
-                                                              ctx->stream), "kv_export_fp8");
+                                                              order, ctx->stream), "kv_export_fp8");
         if (s2) return s2;
         FM_CUDA(ctx, cudaMemcpyAsync(hs, ds, o_vs + (size_t)n * 4, cudaMemcpyDeviceToHost, ctx->stream));
         FM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
@@ -1067,7 +1142,7 @@ extern "C" fm_status fm_kv_import_fp8(FmCtx *ctx, int fa_idx, int seq, const uin
     const KvView kv = kv_view(ctx, fa_idx);
     if (ctx->ptr_mode == FM_PTR_DEVICE)
         return launched(ctx, launch_kv_copy_fp8(kv, seq, 0, len, const_cast<uint8_t *>(k8), const_cast<uint8_t *>(v8), const_cast<float *>(k_scales),
-                                                const_cast<float *>(v_scales), true, ctx->stream), "kv_import_fp8");
+                                                const_cast<float *>(v_scales), true, nullptr, ctx->stream), "kv_import_fp8");
     return staged_rows(ctx, len, kvd, true, [&](int row0, int n, size_t o_v, size_t o_ks, size_t o_vs) -> fm_status {
         char *hs = ctx->h_stage, *ds = ctx->d_stage;
         memcpy(hs, k8 + (size_t)row0 * kvd, (size_t)n * kvd);
@@ -1077,11 +1152,34 @@ extern "C" fm_status fm_kv_import_fp8(FmCtx *ctx, int fa_idx, int seq, const uin
         FM_CUDA(ctx, cudaMemcpyAsync(ds, hs, o_vs + (size_t)n * 4, cudaMemcpyHostToDevice, ctx->stream));
         const fm_status s2 = launched(ctx, launch_kv_copy_fp8(kv, seq, row0, n, reinterpret_cast<uint8_t *>(ds), reinterpret_cast<uint8_t *>(ds + o_v),
                                                               reinterpret_cast<float *>(ds + o_ks), reinterpret_cast<float *>(ds + o_vs), true,
-                                                              ctx->stream), "kv_import_fp8");
+                                                              nullptr, ctx->stream), "kv_import_fp8");
         if (s2) return s2;
         FM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
         return FM_OK;
     });
+}
+
+extern "C" fm_status fm_h2o_export(FmCtx *ctx, int fa_idx, int seq, float *accum, int *token_positions, int max_rows, int *n_out) {
+    if (!ctx) return FM_ERR_INVALID;
+    const FmConfig &c = ctx->cfg;
+    if (c.h2o_budget <= 0) return fail(ctx, FM_ERR_INVALID, "fm_h2o_export: H2O eviction is off");
+    if (fa_idx < 0 || fa_idx >= c.num_full_layers || seq < 0 || seq >= c.max_seqs) return fail(ctx, FM_ERR_INVALID, "fm_h2o_export: bad argument");
+    const int n = rows_kept(c, ctx->kv_len[lidx(ctx, fa_idx, seq)]);
+    if (n_out) *n_out = n;
+    if (n > max_rows) return fail(ctx, FM_ERR_INVALID, "fm_h2o_export: %d rows kept, room for %d", n, max_rows);
+    if (n == 0) return FM_OK;
+    FM_CUDA(ctx, cudaSetDevice(c.device));
+    const H2oView h = h2o_view(ctx, fa_idx);
+    if (ctx->ptr_mode == FM_PTR_DEVICE) return launched(ctx, launch_h2o_gather(h, seq, n, accum, token_positions, ctx->stream), "h2o_gather");
+    if ((size_t)n * 8 + 512 > ctx->stage_bytes) return fail(ctx, FM_ERR_INVALID, "fm_h2o_export: staging buffer too small");
+    float *da = reinterpret_cast<float *>(ctx->d_stage);
+    int *dt = reinterpret_cast<int *>(ctx->d_stage + (((size_t)n * 4 + 255) & ~(size_t)255));
+    const fm_status st = launched(ctx, launch_h2o_gather(h, seq, n, da, dt, ctx->stream), "h2o_gather");
+    if (st) return st;
+    if (accum) FM_CUDA(ctx, cudaMemcpyAsync(accum, da, (size_t)n * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    if (token_positions) FM_CUDA(ctx, cudaMemcpyAsync(token_positions, dt, (size_t)n * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    FM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return FM_OK;
 }
 
 // conv history: the reference keeps [(ks-1)][conv_dim], oldest first; the device keeps a ring of ks
@@ -1183,6 +1281,7 @@ static fm_status xchg_push(FmCtx *ctx, const char *fn, int fa_idx, const int *se
     if (!ctx) return FM_ERR_INVALID;
     *finished = false;
     if (ctx->xchg.nranks < 1) return fail(ctx, FM_ERR_INVALID, "%s: call fm_exchange_attach first", fn);
+    if (ctx->cfg.h2o_budget > 0) return fail(ctx, FM_ERR_UNSUPPORTED, "%s: not with H2O eviction", fn);
     if (!seq || !pos || (!q_proj_out && !q)) return fail(ctx, FM_ERR_INVALID, "%s: null argument", fn);
     if ((k == nullptr) != (v == nullptr)) return fail(ctx, FM_ERR_INVALID, "%s: k and v go together", fn);
     fm_status st = check_layer_seq(ctx, fn, fa_idx, ctx->cfg.num_full_layers, seq, batch);

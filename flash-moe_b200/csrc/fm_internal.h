@@ -84,6 +84,16 @@ struct XchgView {
     long long wait_limit_cycles;
 };
 
+// H2O bookkeeping of one layer as a kernel sees it (attn_h2o.cu): per sequence, `cap` = budget + 1 physical rows.
+struct H2oView {
+    float *accum;           // [seqs][cap] accumulated attention mass, by physical row
+    int *order;             // [seqs][cap] physical row of the i-th row in cache order
+    int *tokpos;            // [seqs][cap] original token index, by physical row
+    int *slot;              // [seqs] physical row the next appended token takes
+    unsigned int *counter;  // [seqs] arrivals of the mass kernel's CTAs (self-resetting)
+    int cap;
+};
+
 struct RopeParams {
     float inv_freq[64];  // rotary_dim / 2 entries, computed on the host exactly as the reference does
     int rotary_dim;
@@ -149,6 +159,13 @@ struct FmCtx {
     void *d_work = nullptr;             // chunked GatedDeltaNet workspace
     size_t work_bytes = 0;
 
+    // H2O eviction: per (layer, sequence) bookkeeping on the device, rows kept on the host
+    float *d_h2o_accum = nullptr;
+    int *d_h2o_order = nullptr, *d_h2o_tokpos = nullptr, *d_h2o_slot = nullptr;
+    unsigned int *d_h2o_counter = nullptr;
+    float *d_h2o_ml = nullptr;  // (max, sum) per (token, head) of the step in flight
+    int h2o_cap = 0;
+
     // cross-GPU exchange of partial results (fm_exchange_attach)
     fm::XchgView xchg = {};
     uint32_t xchg_step = 0;
@@ -186,7 +203,7 @@ int launch_attn_decode_fused(const KvView &kv, const RopeParams &rope, const Tok
                              float *part_o, float *part_ml, int nsplits, const float *k_new, const float *v_new,
                              const uint16_t *k_norm_w, int tail, const float *gate, float *out, float *ml_out,
                              const XchgView *x, uint32_t step, const DecodeScratch &scr, int *err, bool overlap_prev,
-                             cudaStream_t st);
+                             cudaStream_t st, const int *h2o_slot = nullptr);
 constexpr int kDecMaxLastCtaSplits = 24;  // more splits per (KV head, sequence): merged in two levels
 
 // merges [nparts] partials per (token, head) laid out with strides, applies the gate
@@ -198,8 +215,9 @@ int launch_attn_merge(const float *part_o, const float *part_ml, int nparts, lon
 
 // merge of many split partials of (token, head), laid out [tok][H][nparts][..], as a programmatic dependent of the
 // launch that writes them
+// ml_final (may be null): in final mode, also the merged (max, sum) per (token, head)
 int launch_attn_merge_wide(const float *part_o, const float *part_ml, int nparts, int ntok, int H, const float *q_proj_out,
-                           const float *gate, float *out, float *ml_out, cudaStream_t st);
+                           const float *gate, float *out, float *ml_out, cudaStream_t st, float *ml_final = nullptr);
 
 int launch_attn_merge_push(const float *part_o, const float *part_ml, int nsplits, int ntok, int H, const XchgView &x,
                            uint32_t step, unsigned int *done_counter, cudaStream_t st);
@@ -207,11 +225,18 @@ int launch_attn_wait_merge(const XchgView &x, uint32_t step, int ntok, int H, co
                            float *out, int *err, bool overlap_prev, cudaStream_t st);
 
 // rows [row0, row0 + n) of a sequence to / from fp32 [n][Hkv*D] buffers that start at row0
-int launch_kv_export(const KvView &kv, int seq, int row0, int n, float *k, float *v, cudaStream_t st);
+// `order` (may be null): row i of the export is store row order[i] (an H2O store keeps its rows in place and their cache order aside)
+int launch_kv_export(const KvView &kv, int seq, int row0, int n, float *k, float *v, const int *order, cudaStream_t st);
 int launch_kv_import(const KvView &kv, int seq, int row0, int n, const float *k, const float *v, cudaStream_t st);
 // FP8 store: the stored bytes [n][Hkv*D] and per-row scales [n] themselves
 int launch_kv_copy_fp8(const KvView &kv, int seq, int row0, int n, uint8_t *k, uint8_t *v, float *ks, float *vs, bool import,
-                       cudaStream_t st);
+                       const int *order, cudaStream_t st);
+
+int launch_h2o_mass(const KvView &kv, const RopeParams &rope, const TokSpec &toks, const int *token_index, const H2oView &h, int budget, int sinks,
+                    int recent, int H, const float *q_proj_out, const float *q, const uint16_t *q_norm_w, float eps, const float *ml, int max_rows,
+                    cudaStream_t st);
+int launch_h2o_gather(const H2oView &h, int seq, int n, float *accum_out, int *tokpos_out, cudaStream_t st);
+int launch_h2o_init(const H2oView &h, int seq, int n, cudaStream_t st);
 
 struct PrefillWork {
     void *q16, *k16, *v16;

@@ -101,9 +101,9 @@ int launch_kv_append(const KvView &kv, const RopeParams &rope, const TokSpec &to
 // threads; rows not held locally are skipped.  An FP8 store decodes (value * scale) on export and quantises the
 // row the reference's way on import.
 template <bool kImport>
-__global__ void kv_copy_kernel(KvView kv, int seq, int row0, float *__restrict__ k, float *__restrict__ v) {
+__global__ void kv_copy_kernel(KvView kv, int seq, int row0, float *__restrict__ k, float *__restrict__ v, const int *__restrict__ order) {
     __shared__ float sred[32];
-    const int i = blockIdx.x, row = row0 + i, kv_dim = kv.Hkv * kv.D;
+    const int i = blockIdx.x, row = order ? order[row0 + i] : row0 + i, kv_dim = kv.Hkv * kv.D;
     int r = 0;
     unsigned char *pg = kv_row_page(kv, seq, row, r);
     if (pg == nullptr) return;
@@ -140,14 +140,14 @@ __global__ void kv_copy_kernel(KvView kv, int seq, int row0, float *__restrict__
     }
 }
 
-int launch_kv_export(const KvView &kv, int seq, int row0, int n, float *k, float *v, cudaStream_t st) {
+int launch_kv_export(const KvView &kv, int seq, int row0, int n, float *k, float *v, const int *order, cudaStream_t st) {
     if (n <= 0) return 0;
-    kv_copy_kernel<false><<<n, 256, 0, st>>>(kv, seq, row0, k, v);
+    kv_copy_kernel<false><<<n, 256, 0, st>>>(kv, seq, row0, k, v, order);
     return cudaGetLastError() == cudaSuccess ? 1 : -1;
 }
 int launch_kv_import(const KvView &kv, int seq, int row0, int n, const float *k, const float *v, cudaStream_t st) {
     if (n <= 0) return 0;
-    kv_copy_kernel<true><<<n, 256, 0, st>>>(kv, seq, row0, const_cast<float *>(k), const_cast<float *>(v));
+    kv_copy_kernel<true><<<n, 256, 0, st>>>(kv, seq, row0, const_cast<float *>(k), const_cast<float *>(v), nullptr);
     return cudaGetLastError() == cudaSuccess ? 1 : -1;
 }
 
@@ -155,8 +155,8 @@ int launch_kv_import(const KvView &kv, int seq, int row0, int n, const float *k,
 // (metal_infer/layer_forward.h:124-127): bytes [n][Hkv*D], scales [n].  grid (n rows), 128 threads x 4 bytes.
 template <bool kImport>
 __global__ void kv_copy_fp8_kernel(KvView kv, int seq, int row0, uint8_t *__restrict__ k, uint8_t *__restrict__ v,
-                                   float *__restrict__ ks, float *__restrict__ vs) {
-    const int i = blockIdx.x, row = row0 + i, kv_dim = kv.Hkv * kv.D;
+                                   float *__restrict__ ks, float *__restrict__ vs, const int *__restrict__ order) {
+    const int i = blockIdx.x, row = order ? order[row0 + i] : row0 + i, kv_dim = kv.Hkv * kv.D;
     int r = 0;
     unsigned char *pg = kv_row_page(kv, seq, row, r);
     if (pg == nullptr) return;
@@ -174,12 +174,12 @@ __global__ void kv_copy_fp8_kernel(KvView kv, int seq, int row0, uint8_t *__rest
 }
 
 int launch_kv_copy_fp8(const KvView &kv, int seq, int row0, int n, uint8_t *k, uint8_t *v, float *ks, float *vs, bool import,
-                       cudaStream_t st) {
+                       const int *order, cudaStream_t st) {
     if (n <= 0) return 0;
     if (import)
-        kv_copy_fp8_kernel<true><<<n, 128, 0, st>>>(kv, seq, row0, k, v, ks, vs);
+        kv_copy_fp8_kernel<true><<<n, 128, 0, st>>>(kv, seq, row0, k, v, ks, vs, nullptr);
     else
-        kv_copy_fp8_kernel<false><<<n, 128, 0, st>>>(kv, seq, row0, k, v, ks, vs);
+        kv_copy_fp8_kernel<false><<<n, 128, 0, st>>>(kv, seq, row0, k, v, ks, vs, order);
     return cudaGetLastError() == cudaSuccess ? 1 : -1;
 }
 

@@ -100,6 +100,16 @@ typedef struct FmConfig {
      * attention would have read.  The absmax runs over the KV heads THIS CONTEXT holds (all of them on one
      * GPU, as in the reference).  Half the bytes per row of bf16. */
     int kv_dtype;
+    /* Heavy-hitter eviction (H2O) of the KV store at decode: h2o_budget > 0 keeps at most that many rows per
+     * (layer, sequence) -- the first h2o_num_sinks tokens, the last (budget - sinks) / 4 tokens and, of the rest,
+     * those with the largest attention mass accumulated over the steps (softmax weight summed over the query heads).
+     * A step appends its row, attends over budget + 1 rows at most, adds the step's mass and, past the budget, drops
+     * the lightest unprotected row (g_h2o_budget / g_h2o_num_sinks; KVCache fields metal_infer/layer_forward.h:132-140,
+     * kv_cache_h2o_accumulate_scores / kv_cache_evict_h2o :248-383, use in the step :591-727).  It replaces a sliding
+     * window when both are set, as in the reference.  Decode only (the reference's batched prefill ignores it too:
+     * metal_infer/batched_prefill.h:736); not with sequence sharding. */
+    int h2o_budget;
+    int h2o_num_sinks;       /* 4 in the reference */
 } FmConfig;
 
 typedef struct FmCtx FmCtx;
@@ -260,6 +270,10 @@ fm_status fm_kv_export_fp8(FmCtx *ctx, int fa_idx, int seq, uint8_t *k8, uint8_t
                            int max_rows, int *len_out);
 fm_status fm_kv_import_fp8(FmCtx *ctx, int fa_idx, int seq, const uint8_t *k8, const uint8_t *v8, const float *k_scales,
                            const float *v_scales, int len);
+/* H2O bookkeeping of (layer, sequence) in the cache's row order (the order fm_kv_export uses): accum [n] accumulated
+ * attention mass (KVCache.attn_scores_accum), token_positions [n] original token index of each kept row
+ * (KVCache.token_positions); *n_out = rows kept.  Pointers follow the pointer mode. */
+fm_status fm_h2o_export(FmCtx *ctx, int fa_idx, int seq, float *accum, int *token_positions, int max_rows, int *n_out);
 fm_status fm_state_export(FmCtx *ctx, int li, int seq, float *conv, float *ssm);
 fm_status fm_state_import(FmCtx *ctx, int li, int seq, const float *conv, const float *ssm);
 
