@@ -375,6 +375,13 @@ def run_ours(args):
         parity = parity_check(args, pkg, torch, dist, ctx, step, cur, qp, kn, vn, out, dev, world, ss, seq_group, Hl, Hkvl)
 
     extra = {}
+    if world > 1 and not args.no_extra and 16 % world == 0:
+        # GatedDeltaNet decode sharded by value head over the ranks (no exchange inside the path): every rank steps its
+        # 64 / N value heads; the time of a layer step is the slowest rank's
+        ctx.close()
+        ctx = None
+        torch.cuda.empty_cache()
+        extra = _probe_gdn_decode_sharded(pkg, torch, dist, dev, peak, rank, world)
     if rank == 0 and world == 1 and not args.no_extra:
         ctx.close()
         ctx = None
@@ -691,6 +698,56 @@ def _probe_gdn_decode(pkg, torch, dev, peak, gen):
         gdn_bytes = B * (2 * 4194304 + 2 * 147456 + (12288 + 8192 + 128 + 8192) * 4) + 98304 + 768
         res[f"gdn_decode_b{B}"] = {"us_per_layer": us, "state_gbps": gdn_bytes / us / 1e3, "frac_of_peak": gdn_bytes / us / 1e3 / peak,
                                    "algorithmic_bytes_per_layer": gdn_bytes, "layers_cycled": NL}
+        ctx.close()
+        del ctx
+        torch.cuda.empty_cache()
+    return res
+
+
+def _probe_gdn_decode_sharded(pkg, torch, dist, dev, peak, rank, world):
+    res = {}
+    sh = pkg.sharding
+    v0, nv, k0, nk = sh.gdn_head_slice(rank, world)
+    w = pkg.synth.gdn_weights(0)
+    zeros = np.zeros((1, 12288), np.float32)
+    sl = sh.gdn_slice_inputs(rank, world, zeros, np.zeros((1, 8192), np.float32), np.zeros((1, 64), np.float32),
+                             np.zeros((1, 64), np.float32), w["conv_w"], w["A_log"], w["dt_bias"])
+    tw = {k_: torch.from_numpy(v_.view(np.int16) if v_.dtype == np.uint16 else v_).to(dev)
+          for k_, v_ in dict(conv_w=sl["conv_w"], A_log=sl["A_log"], dt_bias=sl["dt_bias"], norm_w=w["norm_w"]).items()}
+    gen = torch.Generator(device=dev); gen.manual_seed(11 + rank)
+    conv_dim = 2 * nk * 128 + nv * 128
+    for B, NL, reps in ((8, 45, 10), (64, 8, 10)):
+        cfg = pkg.default_config(num_full_layers=0, num_linear_layers=NL, max_seqs=B, max_batch_tokens=max(B, 64),
+                                 linear_num_v_heads=nv, linear_num_k_heads=nk, device=dev.index)
+        ctx = pkg.Context(cfg)
+        ctx.set_stream(torch.cuda.current_stream().cuda_stream)
+        qkv = torch.randn((B, conv_dim), device=dev, generator=gen)
+        z = torch.randn((B, nv * 128), device=dev, generator=gen)
+        be = torch.randn((B, nv), device=dev, generator=gen)
+        al = torch.randn((B, nv), device=dev, generator=gen)
+        go = torch.empty((B, nv * 128), device=dev)
+        seq_arr = np.arange(B, dtype=np.int32)
+        calls = [ctx.prepared("fm_gdn_decode", li, seq_arr, B, qkv, z, be, al, tw["conv_w"], tw["A_log"], tw["dt_bias"],
+                              tw["norm_w"], go) for li in range(NL)]
+        for _ in range(3):
+            for f in calls:
+                f()
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            for f in calls:
+                f()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) * 1e3 / (reps * NL)], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        us = float(t.item())
+        gdn_bytes = B * (2 * 4194304 + 2 * 147456 + (12288 + 8192 + 128 + 8192) * 4) + 98304 + 768  # the whole layer, all ranks
+        res[f"gdn_decode_head_sharded_b{B}"] = {"us_per_layer": us, "state_gbps_all_ranks": gdn_bytes / us / 1e3,
+                                                "frac_of_peak_per_gpu": gdn_bytes / us / 1e3 / peak / world,
+                                                "v_heads_per_rank": nv, "layers_cycled": NL}
         ctx.close()
         del ctx
         torch.cuda.empty_cache()

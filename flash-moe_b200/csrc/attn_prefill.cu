@@ -141,10 +141,12 @@ attn_prefill_prep_kernel(KvView kv, RopeParams rope, PrepParams p) {
         }
         const __nv_bfloat16 kb = __float2bfloat16_rn(x), vb = __float2bfloat16_rn(p.v[src]);
         const int gpage = row / kv.page_size, r = row - gpage * kv.page_size;
-        const int page = kv.page_table[(size_t)p.seq * kv.max_slots + gpage];
-        unsigned char *pg = kv_page(kv, page);
-        reinterpret_cast<__nv_bfloat16 *>(pg + kv_tile_offset(kv, 0, kvh))[(size_t)r * kHD + d] = kb;
-        reinterpret_cast<__nv_bfloat16 *>(pg + kv_tile_offset(kv, 1, kvh))[(size_t)r * kHD + d] = vb;
+        if (gpage % kv.shard_count == kv.shard_rank) {  // on a sequence-sharded store the page's owner keeps the row
+            const int page = kv.page_table[(size_t)p.seq * kv.max_slots + gpage / kv.shard_count];
+            unsigned char *pg = kv_page(kv, page);
+            reinterpret_cast<__nv_bfloat16 *>(pg + kv_tile_offset(kv, 0, kvh))[(size_t)r * kHD + d] = kb;
+            reinterpret_cast<__nv_bfloat16 *>(pg + kv_tile_offset(kv, 1, kvh))[(size_t)r * kHD + d] = vb;
+        }
         p.k16[((size_t)row * kv.Hkv + kvh) * kHD + d] = __float2half_rn(clamp_f16(__bfloat162float(kb)));
         p.v16[((size_t)row * kv.Hkv + kvh) * kHD + d] = __float2half_rn(clamp_f16(__bfloat162float(vb)));
         return;

@@ -215,7 +215,7 @@ extern "C" fm_status fm_create(const FmConfig *cfg, FmCtx **out) {
             CREATE_CUDA(cudaMemset(ctx->d_h2o_slot, 0, ns * sizeof(int)));
             CREATE_CUDA(cudaMemset(ctx->d_h2o_counter, 0, ns * sizeof(unsigned int)));
         }
-        if (c.seq_shard_count == 1) {  // prefill needs the whole sequence on one context
+        {
             CREATE_CUDA(cudaMalloc(&ctx->d_pf_q16, (size_t)c.max_batch_tokens * c.num_attn_heads * c.head_dim * 2 * 2));  // hi | lo
             CREATE_CUDA(cudaMalloc(&ctx->d_pf_k16, (size_t)c.max_seq_len * c.num_kv_heads * c.head_dim * 2));
             CREATE_CUDA(cudaMalloc(&ctx->d_pf_v16, (size_t)c.max_seq_len * c.num_kv_heads * c.head_dim * 2));
@@ -854,7 +854,6 @@ extern "C" fm_status fm_attn_prefill(FmCtx *ctx, int fa_idx, int seq, int start_
     const FmConfig &c = ctx->cfg;
     if (fa_idx < 0 || fa_idx >= c.num_full_layers || seq < 0 || seq >= c.max_seqs) return fail(ctx, FM_ERR_INVALID, "fm_attn_prefill: layer %d / seq %d", fa_idx, seq);
     if (n < 0 || n > c.max_batch_tokens) return fail(ctx, FM_ERR_INVALID, "fm_attn_prefill: n=%d exceeds max_batch_tokens=%d", n, c.max_batch_tokens);
-    if (c.seq_shard_count != 1) return fail(ctx, FM_ERR_UNSUPPORTED, "fm_attn_prefill: needs the whole sequence on one context (seq_shard_count=1)");
     if (c.kv_dtype != FM_KV_BF16) return fail(ctx, FM_ERR_UNSUPPORTED, "fm_attn_prefill: the store is FP8; feed the prompt through fm_attn_decode");
     if (c.h2o_budget > 0) return fail(ctx, FM_ERR_UNSUPPORTED, "fm_attn_prefill: H2O eviction works per decode step; feed the prompt through fm_attn_decode");
     if (n == 0) return FM_OK;
@@ -871,6 +870,14 @@ extern "C" fm_status fm_attn_prefill(FmCtx *ctx, int fa_idx, int seq, int start_
     float *d_out = sg.out(out, n * qd, &ok, &w_out);
     if (!ok) return fail(ctx, FM_ERR_INVALID, "fm_attn_prefill: staging buffer too small");
     const int row0 = ctx->kv_len[lidx(ctx, fa_idx, seq)];
+    // Sequence-sharded store: every rank of the sequence group is given the run's k and v (they belong to its KV-head
+    // group), keeps the rows of the pages it owns and attends over the whole sequence out of its operand workspace,
+    // which holds every row that came through fm_attn_prefill.  Rows that came another way (decode steps, imports)
+    // sit on their owners only and are not in the workspace.
+    if (c.seq_shard_count != 1 && row0 > 0 && !(ctx->pf_layer == fa_idx && ctx->pf_seq == seq && ctx->pf_rows == row0))
+        return fail(ctx, FM_ERR_UNSUPPORTED, "fm_attn_prefill: on a sequence-sharded store a prompt has to go through consecutive "
+                    "fm_attn_prefill calls of one (layer, sequence), from its first token (%d rows are cached, %d of them in reach)", row0,
+                    ctx->pf_layer == fa_idx && ctx->pf_seq == seq ? ctx->pf_rows : 0);
     if (c.sliding_window > 0 && row0 + n > c.sliding_window)
         return fail(ctx, FM_ERR_UNSUPPORTED, "fm_attn_prefill: the run would wrap the sliding window (%d + %d > %d); feed it through fm_attn_decode", row0, n, c.sliding_window);
     if (row0 + n > c.max_seq_len) return fail(ctx, FM_ERR_CAPACITY, "KV cache overflow (pos=%d >= cap=%d)", row0 + n - 1, c.max_seq_len);

@@ -133,3 +133,40 @@ def test_reset_and_reference_defaults(pkg, port, synth):
             assert g <= 1e-4
         c.reset(0)
     c.close()
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_head_sharded_contexts_reproduce_the_full_layer(pkg, port, synth, world):
+    """GatedDeltaNet across GPUs shards by value head with no exchange: `world` contexts, each holding 64 / world value
+    heads and 16 / world key heads (pkg.sharding.gdn_head_slice / gdn_slice_inputs), run a chunked prefill and decode
+    steps on their slices; outputs and final states concatenated over the ranks equal the checker's full layer."""
+    from oracle.oracle_py import make_dims
+    sh = pkg.sharding
+    n_pf, n_dec = 150, 5
+    n = n_pf + n_dec
+    dims = make_dims()
+    w = synth.gdn_weights(12)
+    w["dt_bias"] = synth.to_bf16_bits(synth.normal(12, "dtb", (64,), std=0.5))
+    qkv, z, beta, alpha = synth.gdn_step_inputs(12, n, bf16=True)
+    s0 = synth.gdn_state(12)
+    conv_ref = np.zeros((3, 12288), np.float32); ssm_ref = s0.copy()
+    out_ref = port.gdn_run(dims, conv_ref, ssm_ref, qkv, z, beta, alpha, w["conv_w"], w["A_log"], w["dt_bias"], w["norm_w"], threads=16)
+    out = np.empty((n, 8192), np.float32); ssm = np.empty((64, 128, 128), np.float32)
+    for r in range(world):
+        v0, nv, k0, nk = sh.gdn_head_slice(r, world)
+        sl = sh.gdn_slice_inputs(r, world, qkv, z, beta, alpha, w["conv_w"], w["A_log"], w["dt_bias"])
+        c = gdn_ctx(pkg, v_heads=nv, k_heads=nk, max_batch=256)
+        c.state_import(0, 0, None, np.ascontiguousarray(s0[v0:v0 + nv]))
+        o = np.empty((n, nv * 128), np.float32)
+        c.gdn_prefill(0, 0, n_pf, sl["qkv"][:n_pf].copy(), sl["z"][:n_pf].copy(), sl["beta"][:n_pf].copy(), sl["alpha"][:n_pf].copy(),
+                      o[:n_pf], sl["conv_w"], sl["A_log"], sl["dt_bias"], w["norm_w"])
+        for t in range(n_pf, n):
+            c.gdn_decode(0, [0], sl["qkv"][t:t + 1].copy(), sl["z"][t:t + 1].copy(), sl["beta"][t:t + 1].copy(), sl["alpha"][t:t + 1].copy(),
+                         o[t:t + 1], sl["conv_w"], sl["A_log"], sl["dt_bias"], w["norm_w"])
+        c.state_export(0, 0, None, ssm[v0:v0 + nv])
+        c.close()
+        out[:, v0 * 128:(v0 + nv) * 128] = o
+    go, _, _ = rel_errors(out, out_ref)
+    gs, _, _ = rel_errors(ssm, ssm_ref)
+    print("head-sharded over", world, "contexts: out", go, "state", gs)
+    assert go <= TOL_OUT and gs <= TOL_STATE

@@ -111,3 +111,47 @@ def test_gdn_prefill_matches_sequential_steps(pkg, port, synth, sizes):
     g1, _, _ = rel_errors(o1, r1)
     print("gdn prefill", sizes, "state", gs, rs, "out", go, ro, "next step", g1)
     assert gs <= TOL_GDN and go <= TOL_GDN and g1 <= TOL_GDN
+
+
+@pytest.mark.parametrize("shards", [2, 4])
+def test_attn_prefill_on_a_sequence_sharded_store(pkg, port, synth, shards):
+    """A prompt prefilled in three calls on every shard of a sequence-sharded store (each shard is given the run's
+    k and v, keeps the rows of its own pages and attends over the whole prompt): every shard returns the checker's
+    output, the shards' rows put together are the checker's cache, and a decode step whose partial results are merged
+    by log-sum-exp continues from there."""
+    sizes = (130, 64, 107)
+    n = sum(sizes)
+    q, g, k, v = synth.attn_step_inputs(55, n + 1, bf16=True)
+    empty = np.zeros((0, 512), np.float32)
+    ref_out, kc, vc = oracle_attn(port, 32, 2, empty, empty, q, g, k, v, start_pos=0)
+    ctxs = [attn_ctx(pkg, 32, 2, max_seq_len=n + 70, max_batch=256, shard=(r, shards)) for r in range(shards)]
+    ke = np.zeros((n, 512), np.float32); ve = np.zeros_like(ke)
+    for r, c in enumerate(ctxs):
+        out = np.empty((n, 8192), np.float32)
+        t = 0
+        for m in sizes:
+            c.attn_prefill(0, 0, t, m, out[t:t + m], q=q[t:t + m].copy(), gate=g[t:t + m].copy(), k=k[t:t + m].copy(), v=v[t:t + m].copy())
+            t += m
+        gated, _, rr = rel_errors(out, ref_out[:n])
+        print("shard", r, "of", shards, "prefill gated", gated)
+        assert gated <= TOL
+        assert c.kv_len(0, 0) == n
+        c.kv_export(0, 0, ke, ve, n)          # fills the rows this shard owns
+    np.testing.assert_allclose(ke, kc[:n], rtol=2 ** -7, atol=1e-6)
+    np.testing.assert_array_equal(ve, vc[:n])
+    parts_o, parts_ml = [], []
+    for c in ctxs:
+        o = np.empty((1, 32, 256), np.float32); ml = np.empty((1, 32, 2), np.float32)
+        c.attn_decode_partial(0, [0], [n], o, ml, q=q[n:n + 1].copy(), k=k[n:n + 1].copy(), v=v[n:n + 1].copy())
+        parts_o.append(o); parts_ml.append(ml)
+    out1 = np.empty((1, 8192), np.float32)
+    ctxs[0].attn_merge_gate(shards, np.stack(parts_o), np.stack(parts_ml), 1, out1, gate=g[n:n + 1].copy())
+    gated, _, _ = rel_errors(out1, ref_out[n:n + 1])
+    print("decode step after the sharded prefill: gated", gated)
+    assert gated <= TOL
+    # a prompt that does not start at the sequence's first token cannot be served from one shard's rows
+    with pytest.raises(pkg.FmError) as e:
+        ctxs[1].attn_prefill(0, 0, n + 1, 4, np.empty((4, 8192), np.float32), q=q[:4].copy(), gate=g[:4].copy(), k=k[:4].copy(), v=v[:4].copy())
+    assert e.value.status == pkg.binding.FM_ERR_UNSUPPORTED
+    for c in ctxs:
+        c.close()
