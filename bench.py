@@ -496,8 +496,54 @@ def extra_measurements(pkg, torch, dev, peak, only=None):
         res.update(_probe_gdn_decode(pkg, torch, dev, peak, gen))
     if want("gdn_prefill"):
         res.update(_probe_gdn_prefill(pkg, torch, dev, gen))
+    if want("out_proj"):
+        res.update(_probe_out_proj(pkg, torch, dev, peak))
     if want("hybrid"):
         res.update(_probe_hybrid(pkg, torch, dev, peak, gen))
+    return res
+
+
+def _probe_out_proj(pkg, torch, dev, peak):
+    """o_proj / out_proj from the reference's 4-bit format + residual + post-attention norm, 4096 x 8192, cycling 16 weight
+    sets (300 MB) so that the weights come from HBM; bytes = packed weights + scales + biases."""
+    res = {}
+    out_dim, in_dim, nsets = 4096, 8192, 16
+    cfg = pkg.default_config(num_full_layers=1, num_linear_layers=0, max_seq_len=128, max_batch_tokens=64)
+    ctx = pkg.Context(cfg)
+    ctx.set_stream(torch.cuda.current_stream().cuda_stream)
+    rng = np.random.default_rng(0)
+    w = rng.integers(0, 2 ** 32, size=(out_dim, in_dim // 8), dtype=np.uint64).astype(np.uint32)
+    sc = pkg.synth.to_bf16_bits(np.full((out_dim, in_dim // 64), 0.004, np.float32))
+    bi = pkg.synth.to_bf16_bits(np.full((out_dim, in_dim // 64), -0.03, np.float32))
+    sets = [ctx.proj_upload(w, sc, bi) for _ in range(nsets)]
+    nw = torch.ones(out_dim, dtype=torch.bfloat16, device=dev)
+    wbytes = out_dim * in_dim // 2 + 2 * out_dim * (in_dim // 64) * 2
+    for n in (1, 8, 64):
+        x = torch.randn((n, in_dim), device=dev); r = torch.randn((n, out_dim), device=dev)
+        hm = torch.empty((n, out_dim), device=dev); hp = torch.empty_like(hm)
+        import ctypes as C
+        ptr = lambda t_: C.c_void_p(t_.data_ptr())
+        calls = [(C.byref(d), C.c_int(n), ptr(x), ptr(r), ptr(nw), ptr(hm), ptr(hp)) for d in sets]  # arguments converted once
+        fn, h = ctx.lib.fm_out_proj_norm, ctx.h
+
+        def run():
+            for a in calls:
+                fn(h, *a)
+        for _ in range(3):
+            run()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(10):
+            run()
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / (10 * nsets)
+        res[f"out_proj_q4_n{n}"] = {"us": us, "weight_gbps": wbytes / us / 1e3, "frac_of_peak": wbytes / us / 1e3 / peak,
+                                     "weight_bytes": wbytes}
+    for d in sets:
+        ctx.proj_free(d)
+    ctx.close()
     return res
 
 
@@ -800,7 +846,7 @@ def main():
     ap.add_argument("--kv", default="bf16", choices=["bf16", "fp8"], help="element type of the KV store")
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"],
                     help="how sequence shards exchange partial results: the library's peer-memory kernels, or NCCL all-gathers")
-    ap.add_argument("--probe", default=None, choices=["sweep", "prefill", "gdn_decode", "gdn_prefill", "hybrid"],
+    ap.add_argument("--probe", default=None, choices=["sweep", "prefill", "gdn_decode", "gdn_prefill", "hybrid", "out_proj"],
                     help="run only one of the extra measurements and print it (for profiling one kernel)")
     args = ap.parse_args()
     set_kv_dtype(args.kv)

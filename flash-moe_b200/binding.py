@@ -25,7 +25,7 @@ EXPORTS = [
     "fm_state_import", "fm_launch_count", "fm_profile_enable", "fm_profile_read",
     "fm_attn_decode_static", "fm_exchange_bytes", "fm_exchange_attach", "fm_attn_decode_exchange_push",
     "fm_attn_decode_exchange_merge", "fm_attn_decode_exchange", "fm_attn_decode_layers",
-    "fm_kv_export_fp8", "fm_kv_import_fp8", "fm_h2o_export",
+    "fm_kv_export_fp8", "fm_kv_import_fp8", "fm_h2o_export", "fm_proj_upload", "fm_proj_free", "fm_out_proj_norm",
 ]
 
 
@@ -56,6 +56,11 @@ class FmStaticDecodeArgs(C.Structure):
     ]
 
 
+class FmProjWeights(C.Structure):
+    _fields_ = [("format", C.c_int), ("out_dim", C.c_int), ("in_dim", C.c_int), ("group_size", C.c_int),
+                ("w", C.c_void_p), ("scales", C.c_void_p), ("biases", C.c_void_p)]
+
+
 class FmError(RuntimeError):
     def __init__(self, status: int, text: str):
         super().__init__(f"fm status {status}: {text}")
@@ -79,6 +84,7 @@ def load_library() -> C.CDLL:
     lib.fm_default_config.restype = None
     lib.fm_exchange_bytes.restype = C.c_size_t
     lib.fm_exchange_bytes.argtypes = [C.c_void_p, C.c_int]
+    lib.fm_proj_free.restype = None
     return lib
 
 
@@ -302,6 +308,20 @@ class Context:
         self._check(self.lib.fm_h2o_export(self.h, C.c_int(fa_idx), C.c_int(seq), _ptr(accum), _ptr(token_positions),
                                            C.c_int(max_rows), C.byref(n)))
         return n.value
+
+    def proj_upload(self, w, scales, biases) -> "FmProjWeights":
+        """4-bit affine weights (numpy: w uint32 [out][in/8], scales / biases uint16 bf16 bits [out][in/64]) -> device."""
+        out_dim, in_dim = w.shape[0], w.shape[1] * 8
+        host = FmProjWeights(0, out_dim, in_dim, 64, w.ctypes.data, scales.ctypes.data, biases.ctypes.data)
+        dev = FmProjWeights()
+        self._check(self.lib.fm_proj_upload(self.h, C.byref(host), C.byref(dev)))
+        return dev
+
+    def proj_free(self, dev):
+        self.lib.fm_proj_free(self.h, C.byref(dev))
+
+    def out_proj_norm(self, dev, n, x, residual, norm_w, h_mid, h_post):
+        self._check(self.lib.fm_out_proj_norm(self.h, C.byref(dev), C.c_int(n), _ptr(x), _ptr(residual), _ptr(norm_w), _ptr(h_mid), _ptr(h_post)))
 
     def state_export(self, li, seq, conv, ssm):
         self._check(self.lib.fm_state_export(self.h, C.c_int(li), C.c_int(seq), _ptr(conv), _ptr(ssm)))

@@ -235,6 +235,8 @@ extern "C" fm_status fm_create(const FmConfig *cfg, FmCtx **out) {
         ctx->work_bytes = gdn_prefill_work_bytes(g, c.max_batch_tokens, 64);
         if (ctx->work_bytes) CREATE_CUDA(cudaMalloc(&ctx->d_work, ctx->work_bytes));
     }
+    CREATE_CUDA(cudaMalloc(&ctx->d_proj_ssq, 16 * sizeof(float)));
+    CREATE_CUDA(cudaMemset(ctx->d_proj_ssq, 0, 16 * sizeof(float)));
     CREATE_CUDA(cudaMalloc(&ctx->d_err, sizeof(int)));
     CREATE_CUDA(cudaMemset(ctx->d_err, 0, sizeof(int)));
     CREATE_CUDA(cudaMallocHost(&ctx->h_err, sizeof(int)));
@@ -258,6 +260,7 @@ extern "C" void fm_destroy(FmCtx *ctx) {
     if (ctx->h_err) cudaFreeHost(ctx->h_err); cudaFree(ctx->d_work);
     cudaFree(ctx->d_h2o_accum); cudaFree(ctx->d_h2o_order); cudaFree(ctx->d_h2o_tokpos); cudaFree(ctx->d_h2o_slot);
     cudaFree(ctx->d_h2o_counter); cudaFree(ctx->d_h2o_ml);
+    cudaFree(ctx->d_proj_ssq);
     cudaFree(ctx->d_stage);
     cudaFree(ctx->d_lstage);
     if (ctx->h_lstage) cudaFreeHost(ctx->h_lstage);
@@ -900,6 +903,72 @@ extern "C" fm_status fm_attn_prefill(FmCtx *ctx, int fa_idx, int seq, int start_
     if (sg.host) FM_CUDA(ctx, cudaMemcpyAsync(ctx->h_err, ctx->d_err, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
     FM_CUDA(ctx, sg.pull(out, w_out, n * qd));
     if (sg.host) return check_device_error(ctx);
+    return FM_OK;
+}
+
+// ---- output projection + residual + post-attention norm ---------------------------------------
+extern "C" fm_status fm_proj_upload(FmCtx *ctx, const FmProjWeights *h, FmProjWeights *d) {
+    if (!ctx) return FM_ERR_INVALID;
+    if (!h || !d || !h->w || !h->scales || !h->biases) return fail(ctx, FM_ERR_INVALID, "fm_proj_upload: null argument");
+    if (h->format != FM_W_Q4_AFFINE || h->group_size != 64 || h->out_dim < 1 || h->in_dim < 64 || h->in_dim % 64)
+        return fail(ctx, FM_ERR_UNSUPPORTED, "fm_proj_upload: format %d, group size %d, %d x %d", h->format, h->group_size, h->out_dim, h->in_dim);
+    FM_CUDA(ctx, cudaSetDevice(ctx->cfg.device));
+    const size_t wb = (size_t)h->out_dim * (h->in_dim / 8) * 4, sb = (size_t)h->out_dim * (h->in_dim / 64) * 2;
+    char *buf = nullptr;
+    const size_t o_s = (wb + 255) & ~(size_t)255, o_b = o_s + ((sb + 255) & ~(size_t)255);
+    cudaError_t e = cudaMalloc(&buf, o_b + sb);
+    if (e != cudaSuccess) return fail(ctx, FM_ERR_NOMEM, "fm_proj_upload: %s", cudaGetErrorString(e));
+    if ((e = cudaMemcpyAsync(buf, h->w, wb, cudaMemcpyHostToDevice, ctx->stream)) != cudaSuccess ||
+        (e = cudaMemcpyAsync(buf + o_s, h->scales, sb, cudaMemcpyHostToDevice, ctx->stream)) != cudaSuccess ||
+        (e = cudaMemcpyAsync(buf + o_b, h->biases, sb, cudaMemcpyHostToDevice, ctx->stream)) != cudaSuccess ||
+        (e = cudaStreamSynchronize(ctx->stream)) != cudaSuccess) {
+        cudaFree(buf);
+        return fail(ctx, FM_ERR_CUDA, "fm_proj_upload: %s", cudaGetErrorString(e));
+    }
+    *d = *h;
+    d->w = reinterpret_cast<const uint32_t *>(buf);
+    d->scales = reinterpret_cast<const uint16_t *>(buf + o_s);
+    d->biases = reinterpret_cast<const uint16_t *>(buf + o_b);
+    return FM_OK;
+}
+
+extern "C" void fm_proj_free(FmCtx *ctx, FmProjWeights *d) {
+    if (!ctx || !d || !d->w) return;
+    cudaSetDevice(ctx->cfg.device);
+    cudaStreamSynchronize(ctx->stream);
+    cudaFree(const_cast<uint32_t *>(d->w));  // one allocation holds all three arrays
+    d->w = nullptr; d->scales = d->biases = nullptr;
+}
+
+extern "C" fm_status fm_out_proj_norm(FmCtx *ctx, const FmProjWeights *w, int n, const float *x, const float *residual,
+                                      const uint16_t *norm_w, float *h_mid, float *h_post) {
+    if (!ctx) return FM_ERR_INVALID;
+    if (!w || !w->w || !w->scales || !w->biases || !x || !h_mid || n < 0) return fail(ctx, FM_ERR_INVALID, "fm_out_proj_norm: null argument");
+    if (w->format != FM_W_Q4_AFFINE || w->group_size != 64 || w->in_dim % 512 || w->out_dim < 1 || w->in_dim < 512 || w->in_dim > 24576 || w->out_dim % 4)
+        return fail(ctx, FM_ERR_UNSUPPORTED, "fm_out_proj_norm: format %d, group size %d, %d x %d (in a multiple of 512 up to 24576, out of 4)",
+                    w->format, w->group_size, w->out_dim, w->in_dim);
+    if (n == 0) return FM_OK;
+    FM_CUDA(ctx, cudaSetDevice(ctx->cfg.device));
+    const size_t in = (size_t)w->in_dim, out = (size_t)w->out_dim;
+    for (int t0 = 0; t0 < n; t0 += 8) {  // 8 tokens ride along one pass over the weights
+        const int m = std::min(8, n - t0);
+        Stager sg(ctx);
+        bool ok = true;
+        const float *d_x = sg.in(x + t0 * in, m * in, &ok);
+        const float *d_r = sg.in(residual ? residual + t0 * out : nullptr, m * out, &ok);
+        const uint16_t *d_w = sg.in(norm_w, out, &ok);
+        size_t w_mid = 0, w_post = 0;
+        float *d_mid = sg.out(h_mid + t0 * out, m * out, &ok, &w_mid);
+        float *d_post = sg.out(h_post ? h_post + t0 * out : nullptr, m * out, &ok, &w_post);
+        if (!ok) return fail(ctx, FM_ERR_INVALID, "fm_out_proj_norm: staging buffer too small (raise max_batch_tokens)");
+        FM_CUDA(ctx, sg.push());
+        fm_status st = launched(ctx, launch_out_proj_q4(w->w, w->scales, w->biases, w->out_dim, w->in_dim, m, d_x, d_r, d_w, ctx->cfg.rms_norm_eps,
+                                                        d_mid, d_post, ctx->d_proj_ssq, &ctx->proj_parity, ctx->stream), "out_proj");
+        if (st) return st;
+        if (sg.host && h_post) FM_CUDA(ctx, cudaMemcpyAsync(ctx->h_stage + w_post, ctx->d_stage + w_post, m * out * 4, cudaMemcpyDeviceToHost, ctx->stream));
+        FM_CUDA(ctx, sg.pull(h_mid + t0 * out, w_mid, m * out));
+        if (sg.host && h_post) memcpy(h_post + t0 * out, ctx->h_stage + w_post, m * out * 4);
+    }
     return FM_OK;
 }
 

@@ -166,6 +166,9 @@ struct FmCtx {
     float *d_h2o_ml = nullptr;  // (max, sum) per (token, head) of the step in flight
     int h2o_cap = 0;
 
+    float *d_proj_ssq = nullptr;  // per-token sums of squares of the output projection's epilogue, two sets used alternately
+    int proj_parity = 0;
+
     // cross-GPU exchange of partial results (fm_exchange_attach)
     fm::XchgView xchg = {};
     uint32_t xchg_step = 0;
@@ -237,6 +240,12 @@ int launch_h2o_mass(const KvView &kv, const RopeParams &rope, const TokSpec &tok
                     cudaStream_t st);
 int launch_h2o_gather(const H2oView &h, int seq, int n, float *accum_out, int *tokpos_out, cudaStream_t st);
 int launch_h2o_init(const H2oView &h, int seq, int n, cudaStream_t st);
+
+// y = W x from 4-bit affine weights, h_mid = residual + y, h_post = rms-norm(h_mid) * w (out_proj.cu); n <= 8 tokens,
+// ssq: two sets of 8 floats (zero at creation) used alternately, *parity the set of this call.  h_post may be null.
+int launch_out_proj_q4(const uint32_t *w, const uint16_t *scales, const uint16_t *biases, int out_dim, int in_dim, int n, const float *x,
+                       const float *residual, const uint16_t *norm_w, float eps, float *h_mid, float *h_post, float *ssq, int *parity,
+                       cudaStream_t st);
 
 struct PrefillWork {
     void *q16, *k16, *v16;

@@ -86,3 +86,27 @@ void linear_attention_core(const float *qkv, const float *z, const float *beta, 
     if (fm_gdn_decode(g_fm, state->li, &seq0, 1, qkv, z, beta, alpha, conv_w, A_log, dt_bias, gated_norm_w, gated_out) != FM_OK)
         fprintf(stderr, "ERROR: %s\n", fm_last_error(g_fm));
 }
+
+void batched_prefill_full_attention(const float *q_proj_out, const float *k, const float *v, const uint16_t *qnorm_w,
+                                    const uint16_t *knorm_w, KVCache *kv, int cache_start, int n, float *attn_out) {
+    if (!g_fm || !kv) {
+        fprintf(stderr, "ERROR: batched_prefill_full_attention without a context or cache\n");
+        return;
+    }
+    if (fm_attn_prefill(g_fm, kv->fa_idx, 0, cache_start, n, q_proj_out, NULL, NULL, k, v, qnorm_w, knorm_w, attn_out) != FM_OK) {
+        fprintf(stderr, "ERROR: %s\n", fm_last_error(g_fm));
+        return;
+    }
+    kv->len = fm_kv_len(g_fm, kv->fa_idx, 0); /* = cache_start + n (batched_prefill.h:736) */
+}
+
+void batched_prefill_linear_attention(const float *qkv, const float *z, const float *beta, const float *alpha,
+                                      const uint16_t *conv_w, const float *A_log, const uint16_t *dt_bias,
+                                      const uint16_t *gated_norm_w, LinearAttnState *state, int n, float *gated_out) {
+    if (!g_fm || !state) {
+        fprintf(stderr, "ERROR: batched_prefill_linear_attention without a context or state\n");
+        return;
+    }
+    if (fm_gdn_prefill(g_fm, state->li, 0, n, 0, qkv, z, beta, alpha, conv_w, A_log, dt_bias, gated_norm_w, gated_out) != FM_OK)
+        fprintf(stderr, "ERROR: %s\n", fm_last_error(g_fm));
+}

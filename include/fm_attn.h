@@ -277,6 +277,29 @@ fm_status fm_h2o_export(FmCtx *ctx, int fa_idx, int seq, float *accum, int *toke
 fm_status fm_state_export(FmCtx *ctx, int li, int seq, float *conv, float *ssm);
 fm_status fm_state_import(FmCtx *ctx, int li, int seq, const float *conv, const float *ssm);
 
+/* The step behind token mixing: output projection + residual + post-attention RMS-norm, i.e. what the reference
+ * encodes after attention in fused_layer_forward (metal_infer/layer_forward.h:3369-3450): o_proj / out_proj as a
+ * 4-bit dequantising matvec (cpu_dequant_matvec, metal_infer/cpu_kernels.h:199-232; Metal dequant_matvec_4bit*),
+ * residual_add, rms_norm_sum_sq, rms_norm_apply_bf16 (metal_infer/shaders.metal:792-882):
+ *     y = W x;   h_mid = residual + y;   h_post = h_mid * rsqrt(mean(h_mid^2) + rms_norm_eps) * norm_w
+ * Weights in the reference's format: w uint32 [out_dim][in_dim / 8], eight 4-bit values per word, lowest nibble
+ * first; scales, biases bf16 [out_dim][in_dim / group_size], weight = nibble * scale + bias; group_size 64.
+ * Weight pointers are DEVICE pointers in either pointer mode (fm_proj_upload copies a host set to the device once);
+ * x [n][in_dim], residual [n][out_dim] (may be NULL), norm_w bf16 [out_dim] (may be NULL: weight 1), h_mid and
+ * h_post [n][out_dim] (h_post may be NULL) follow the pointer mode.  in_dim a multiple of 512, out_dim of 4. */
+enum { FM_W_Q4_AFFINE = 0 };
+typedef struct FmProjWeights {
+    int format;              /* FM_W_Q4_AFFINE */
+    int out_dim, in_dim;     /* 4096 x 8192 for both o_proj and out_proj of the 397B model */
+    int group_size;          /* 64 */
+    const uint32_t *w;
+    const uint16_t *scales, *biases;
+} FmProjWeights;
+fm_status fm_proj_upload(FmCtx *ctx, const FmProjWeights *host, FmProjWeights *device);
+void fm_proj_free(FmCtx *ctx, FmProjWeights *device);
+fm_status fm_out_proj_norm(FmCtx *ctx, const FmProjWeights *w, int n, const float *x, const float *residual,
+                           const uint16_t *norm_w, float *h_mid, float *h_post);
+
 /* Number of kernels this context has launched since creation (bench bookkeeping). */
 int64_t fm_launch_count(const FmCtx *ctx);
 

@@ -15,6 +15,11 @@
  *   reset_delta_net_state()      metal_ctx.h:599-608       same name
  *   full_attention_forward  :556-735 (after the projections)     full_attention_core()
  *   linear_attention_forward:886-1025 (after the projections)    linear_attention_core()
+ *   batched_prefill(), full-attention layer, after the projection GEMMs, one chunk of <= MAX_PFB_GPU tokens
+ *       (batched_prefill.h:543-740: deinterleave, prefill_q_rope_norm_bf16, prefill_kv_cache_bf16,
+ *       prefill_causal_attn, kv->len = cache_start + n)          batched_prefill_full_attention()
+ *   batched_prefill(), GatedDeltaNet layer, after the projection GEMMs (batched_prefill.h:798-1037:
+ *       conv1d_step_batched ... gated_rms_norm_batched)           batched_prefill_linear_attention()
  */
 #ifndef FM_COMPAT_H
 #define FM_COMPAT_H
@@ -53,6 +58,18 @@ void full_attention_core(const float *q_proj_out, const float *k, const float *v
 void linear_attention_core(const float *qkv, const float *z, const float *beta, const float *alpha,
                            const uint16_t *conv_w, const float *A_log, const uint16_t *dt_bias,
                            const uint16_t *gated_norm_w, LinearAttnState *state, float *gated_out);
+
+/* One chunk of n prompt tokens of a full-attention layer: q_proj_out [n][H][2*D] interleaved q|gate, k, v
+ * [n][Hkv*D]; token t sits at position cache_start + t, its row is appended and it attends to rows
+ * [0, cache_start + t]; attn_out [n][H*D] (already multiplied by the sigmoid gate).  kv->len becomes
+ * cache_start + n.  n is bounded by the context's max_batch_tokens (the reference's MAX_PFB_GPU is 32). */
+void batched_prefill_full_attention(const float *q_proj_out, const float *k, const float *v, const uint16_t *qnorm_w,
+                                    const uint16_t *knorm_w, KVCache *kv, int cache_start, int n, float *attn_out);
+/* One chunk of n prompt tokens of a GatedDeltaNet layer: qkv [n][conv_dim], z [n][Hv*dv], beta, alpha [n][Hv];
+ * gated_out [n][Hv*dv]; the layer's conv history and recurrent state move on by n tokens. */
+void batched_prefill_linear_attention(const float *qkv, const float *z, const float *beta, const float *alpha,
+                                      const uint16_t *conv_w, const float *A_log, const uint16_t *dt_bias,
+                                      const uint16_t *gated_norm_w, LinearAttnState *state, int n, float *gated_out);
 
 #ifdef __cplusplus
 }

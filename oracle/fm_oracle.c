@@ -538,3 +538,34 @@ int fmo_attn_step_cache(const FmoDims *d, FmoCache *c, const float *q_in, const 
     free(k);
     return 0;
 }
+
+/* ------------------------------------------------------------------------ */
+/* 4-bit affine dequantising matvec (metal_infer/cpu_kernels.h:199-232), residual add (a + b, metal_infer/
+   shaders.metal:873-882) and RMS-norm with a bf16 weight (metal_infer/cpu_kernels.h:235-246), in the reference's
+   operation order: one fp32 accumulator per output row, groups and nibbles in ascending order. */
+void fmo_out_proj_norm(const uint32_t *w, const uint16_t *scales, const uint16_t *biases, int out_dim, int in_dim,
+                       int group_size, const float *x, const float *residual, const uint16_t *norm_w, float eps,
+                       float *h_mid, float *h_post) {
+    const int num_groups = in_dim / group_size, packed_per_group = group_size / 8, packed_cols = in_dim / 8;
+    for (int row = 0; row < out_dim; row++) {
+        float acc = 0.0f;
+        const uint32_t *w_row = w + (size_t)row * packed_cols;
+        for (int g = 0; g < num_groups; g++) {
+            const float scale = bf16f(scales[(size_t)row * num_groups + g]), bias = bf16f(biases[(size_t)row * num_groups + g]);
+            for (int p = 0; p < packed_per_group; p++) {
+                const uint32_t packed = w_row[g * packed_per_group + p];
+                const float *xb = x + g * group_size + p * 8;
+                for (int n = 0; n < 8; n++) acc += ((float)((packed >> (n * 4)) & 0xF) * scale + bias) * xb[n];
+            }
+        }
+        h_mid[row] = acc;
+    }
+    if (residual)
+        for (int i = 0; i < out_dim; i++) h_mid[i] = residual[i] + h_mid[i];
+    if (h_post) {
+        float ss = 0.0f;
+        for (int i = 0; i < out_dim; i++) ss += h_mid[i] * h_mid[i];
+        const float inv = 1.0f / sqrtf(ss / out_dim + eps);
+        for (int i = 0; i < out_dim; i++) h_post[i] = h_mid[i] * inv * bf16f(norm_w[i]);
+    }
+}

@@ -96,7 +96,13 @@ typedef struct {
                                 const uint16_t *k_norm_w, int pos, float *out, int threads);     \
     /* FP8 codec on n rows of kv_dim floats: bytes [n][kv_dim], scales [n]. */                   \
     void prefix##fp8_encode_rows(const float *src, int n, int kv_dim, uint8_t *dst, float *scales); \
-    void prefix##fp8_decode_rows(const uint8_t *src, const float *scales, int n, int kv_dim, float *dst);
+    void prefix##fp8_decode_rows(const uint8_t *src, const float *scales, int n, int kv_dim, float *dst); \
+    /* Output projection from 4-bit affine weights + residual + RMS-norm for one token                 \
+       (metal_infer/cpu_kernels.h:199-246; order of use metal_infer/layer_forward.h:3369-3450):         \
+       y = W x, h_mid = residual + y (residual may be NULL), h_post = rms_norm(h_mid) * norm_w. */      \
+    void prefix##out_proj_norm(const uint32_t *w, const uint16_t *scales, const uint16_t *biases, int out_dim, \
+                               int in_dim, int group_size, const float *x, const float *residual,        \
+                               const uint16_t *norm_w, float eps, float *h_mid, float *h_post);
 
 FMO_API(fmo_)
 FMO_API(fmr_)

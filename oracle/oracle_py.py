@@ -114,7 +114,7 @@ class Oracle:
         self.lib = C.CDLL(str(path))
         for name in ("attn_step", "attn_run", "gdn_step", "gdn_run", "attn_step_cache"):
             getattr(self.lib, self.prefix + name).restype = C.c_int
-        for name in ("fp8_encode_rows", "fp8_decode_rows"):
+        for name in ("fp8_encode_rows", "fp8_decode_rows", "out_proj_norm"):
             getattr(self.lib, self.prefix + name).restype = None
 
     # -- cache policies: FP8 store, sliding window, H2O ------------------------
@@ -137,6 +137,23 @@ class Oracle:
             if rc != 0:
                 raise RuntimeError("KV cache overflow in oracle")
         return out
+
+    def out_proj_norm(self, w, scales, biases, x, residual, norm_w, eps=1e-6, group_size=64):
+        """x [n][in], residual [n][out] or None -> (h_mid, h_post) [n][out]."""
+        w = np.ascontiguousarray(w, np.uint32); scales = np.ascontiguousarray(scales, np.uint16)
+        biases = np.ascontiguousarray(biases, np.uint16); norm_w = np.ascontiguousarray(norm_w, np.uint16)
+        x = np.atleast_2d(np.ascontiguousarray(x, np.float32))
+        out_dim, in_dim = w.shape[0], w.shape[1] * 8
+        n = x.shape[0]
+        h_mid = np.empty((n, out_dim), np.float32); h_post = np.empty_like(h_mid)
+        fn = getattr(self.lib, self.prefix + "out_proj_norm")
+        f32p, u16p = C.POINTER(C.c_float), C.POINTER(C.c_uint16)
+        for t in range(n):
+            r = None if residual is None else np.ascontiguousarray(residual[t], np.float32)
+            fn(w.ctypes.data_as(C.POINTER(C.c_uint32)), scales.ctypes.data_as(u16p), biases.ctypes.data_as(u16p), C.c_int(out_dim),
+               C.c_int(in_dim), C.c_int(group_size), x[t].ctypes.data_as(f32p), None if r is None else r.ctypes.data_as(f32p),
+               norm_w.ctypes.data_as(u16p), C.c_float(eps), h_mid[t].ctypes.data_as(f32p), h_post[t].ctypes.data_as(f32p))
+        return h_mid, h_post
 
     def fp8_encode_rows(self, rows):
         rows, rp = _f32(rows)

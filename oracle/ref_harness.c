@@ -214,6 +214,16 @@ void fmr_fp8_decode_rows(const uint8_t *src, const float *scales, int n, int kv_
     for (int i = 0; i < n; i++) fp8_decode_vec(src + (size_t)i * kv_dim, dst + (size_t)i * kv_dim, kv_dim, scales[i]);
 }
 
+/* ---- the step behind attention: o_proj (4-bit dequant matvec) + residual + post-attention RMS-norm ---- */
+void fmr_out_proj_norm(const uint32_t *w, const uint16_t *scales, const uint16_t *biases, int out_dim, int in_dim,
+                       int group_size, const float *x, const float *residual, const uint16_t *norm_w, float eps,
+                       float *h_mid, float *h_post) {
+    cpu_dequant_matvec(w, scales, biases, x, h_mid, out_dim, in_dim, group_size);
+    if (residual)
+        for (int i = 0; i < out_dim; i++) h_mid[i] = residual[i] + h_mid[i];   /* residual_add: a + b */
+    if (h_post) cpu_rms_norm(h_mid, norm_w, h_post, out_dim, eps);
+}
+
 /* ---- GatedDeltaNet ---- */
 static void gdn_body_serial(WeightFile *wf, int layer_idx, LinearAttnState *state, float *qkv,
                             int qkv_dim, float *z, float *beta, float *alpha, float *out) {

@@ -8,7 +8,6 @@
 
 #include "fm_compat.h"
 #include "fm_oracle.h"
-FMO_API(fmo_)
 
 static unsigned long long rng_state = 88172645463325252ULL;
 static float frand(void) { /* xorshift + Box-Muller */
@@ -92,6 +91,42 @@ int main(void) {
         const double e = gated_err(go, gr, HV * DK);
         printf("%s linear_attention_core step %d: err %.3g\n", e <= 5e-3 ? "PASS" : "FAIL", s, e);
         fails += !(e <= 5e-3);
+    }
+    /* ---- batched prefill: a prompt in chunks of 32 tokens (the reference's MAX_PFB_GPU), both layer kinds, against
+     *      sequential checker steps ---- */
+    {
+        enum { NP = 80, CH = 32 };
+        reset_delta_net_state();
+        kv->len = 0;
+        memset(kc, 0, (size_t)CAP * kvd * 4); memset(vc, 0, (size_t)CAP * kvd * 4);
+        memset(conv_state, 0, 3 * CONV * 4); memset(ssm, 0, (size_t)HV * DK * DK * 4);
+        float *pq = malloc((size_t)NP * H * 2 * D * 4), *pk = malloc((size_t)NP * kvd * 4), *pv = malloc((size_t)NP * kvd * 4);
+        float *po = malloc((size_t)NP * qd * 4), *pr = malloc((size_t)NP * qd * 4), *tq = malloc(qd * 4), *tg = malloc(qd * 4);
+        float *lq = malloc((size_t)NP * CONV * 4), *lz = malloc((size_t)NP * HV * DK * 4), *lb = malloc(NP * HV * 4), *la_ = malloc(NP * HV * 4);
+        float *lo = malloc((size_t)NP * HV * DK * 4), *lr = malloc((size_t)NP * HV * DK * 4);
+        for (size_t i = 0; i < (size_t)NP * H * 2 * D; i++) pq[i] = bf16r(frand());
+        for (size_t i = 0; i < (size_t)NP * kvd; i++) { pk[i] = bf16r(frand()); pv[i] = bf16r(frand()); }
+        for (size_t i = 0; i < (size_t)NP * CONV; i++) lq[i] = bf16r(frand());
+        for (size_t i = 0; i < (size_t)NP * HV * DK; i++) lz[i] = bf16r(frand());
+        for (int i = 0; i < NP * HV; i++) { lb[i] = frand(); la_[i] = frand(); }
+        int plen = 0;
+        for (int t = 0; t < NP; t++) {  /* the checker, token by token */
+            for (int h = 0; h < H; h++)
+                for (int d = 0; d < D; d++) { tq[h * D + d] = pq[((size_t)t * H + h) * 2 * D + d]; tg[h * D + d] = pq[((size_t)t * H + h) * 2 * D + D + d]; }
+            fmo_attn_step(&dims, kc, vc, &plen, CAP, tq, tg, pk + (size_t)t * kvd, pv + (size_t)t * kvd, qn, kn, t, pr + (size_t)t * qd, 4);
+            fmo_gdn_step(&dims, conv_state, ssm, lq + (size_t)t * CONV, lz + (size_t)t * HV * DK, lb + t * HV, la_ + t * HV, cw, Alog, dtb, nw,
+                         lr + (size_t)t * HV * DK, 4);
+        }
+        for (int t = 0; t < NP; t += CH) {
+            const int n = NP - t < CH ? NP - t : CH;
+            batched_prefill_full_attention(pq + (size_t)t * H * 2 * D, pk + (size_t)t * kvd, pv + (size_t)t * kvd, qn, kn, kv, t, n, po + (size_t)t * qd);
+            batched_prefill_linear_attention(lq + (size_t)t * CONV, lz + (size_t)t * HV * DK, lb + t * HV, la_ + t * HV, cw, Alog, dtb, nw, la, n,
+                                             lo + (size_t)t * HV * DK);
+        }
+        const double ea = gated_err(po, pr, NP * qd), el = gated_err(lo, lr, NP * HV * DK);
+        printf("%s batched_prefill_full_attention: err %.3g, kv->len %d\n", ea <= 2e-3 && kv->len == NP ? "PASS" : "FAIL", ea, kv->len);
+        printf("%s batched_prefill_linear_attention: err %.3g\n", el <= 5e-3 ? "PASS" : "FAIL", el);
+        fails += !(ea <= 2e-3 && kv->len == NP) + !(el <= 5e-3);
     }
     reset_delta_net_state();
     printf("%s reset_delta_net_state: kv len %d\n", fm_kv_len(fm_compat_ctx(), 0, 0) == 0 ? "PASS" : "FAIL", fm_kv_len(fm_compat_ctx(), 0, 0));

@@ -273,3 +273,18 @@ def test_cache_policy_golden(port, ref, case):
         if int(f["h2o_budget"]):
             np.testing.assert_array_equal(c.token_positions, f["token_positions"])
             np.testing.assert_array_equal(c.accum, f["accum"])
+
+
+def test_port_equals_reference_out_proj_norm(port, ref, synth):
+    """Output projection from the 4-bit affine format + residual + post-attention RMS-norm: bit for bit."""
+    rng = np.random.default_rng(3)
+    out_dim, in_dim = 96, 1024
+    w = rng.integers(0, 2 ** 32, size=(out_dim, in_dim // 8), dtype=np.uint64).astype(np.uint32)
+    scales = synth.to_bf16_bits(np.abs(synth.normal(3, "s", (out_dim, in_dim // 64), std=0.01)) + 0.002)
+    biases = synth.to_bf16_bits(-7.5 * synth.bf16_bits_to_f32(scales) + synth.normal(3, "b", (out_dim, in_dim // 64), std=0.002))
+    x = synth.normal(3, "x", (3, in_dim)); res = synth.normal(3, "r", (3, out_dim))
+    nw = synth.to_bf16_bits(1.0 + synth.normal(3, "nw", (out_dim,), std=0.1))
+    a = ref.out_proj_norm(w, scales, biases, x, res, nw)
+    b = port.out_proj_norm(w, scales, biases, x, res, nw)
+    np.testing.assert_array_equal(a[0], b[0])
+    np.testing.assert_array_equal(a[1], b[1])
