@@ -482,6 +482,9 @@ def parity_check(args, pkg, torch, dist, ctx, step, cur, qp, kn, vn, out, dev, w
 TRAFFIC_NCU_1SEQ_128K = 273.18e6
 
 
+PROBE_REPS = None  # --probe with an explicit --steps: that many timed repetitions (short runs for profiling)
+
+
 def extra_measurements(pkg, torch, dev, peak, only=None):
     """Batch-1 context sweep (us per layer and KV GB/s), prefill attention TFLOP/s, GatedDeltaNet decode
     and chunked prefill.  `only` runs a single one of them (used when profiling one kernel)."""
@@ -529,16 +532,17 @@ def _probe_out_proj(pkg, torch, dev, peak):
         def run():
             for a in calls:
                 fn(h, *a)
+        reps = PROBE_REPS or 10
         for _ in range(3):
             run()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for _ in range(10):
+        for _ in range(reps):
             run()
         e1.record()
         torch.cuda.synchronize()
-        us = e0.elapsed_time(e1) * 1e3 / (10 * nsets)
+        us = e0.elapsed_time(e1) * 1e3 / (reps * nsets)
         res[f"out_proj_q4_n{n}"] = {"us": us, "weight_gbps": wbytes / us / 1e3, "frac_of_peak": wbytes / us / 1e3 / peak,
                                      "weight_bytes": wbytes}
     for d in sets:
@@ -739,11 +743,35 @@ def _probe_gdn_decode(pkg, torch, dev, peak, gen):
             gdn_pass()
         e1.record()
         torch.cuda.synchronize()
-        us = e0.elapsed_time(e1) * 1e3 / (reps * NL)
+        us_host = e0.elapsed_time(e1) * 1e3 / (reps * NL)
+        # the same pass as one CUDA graph (how a serving loop would issue it): at batch 1 a launch per host call is
+        # bounded by the host's call rate, not by the kernel
+        us = us_host
+        graph_note = None
+        try:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                ctx.set_stream(torch.cuda.current_stream().cuda_stream)
+                gdn_pass()
+            ctx.set_stream(torch.cuda.current_stream().cuda_stream)
+            for _ in range(3):
+                g.replay()
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(reps):
+                g.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) * 1e3 / (reps * NL)
+            del g
+        except Exception as exc:  # noqa: BLE001
+            graph_note = f"graph capture failed: {exc}"[:200]
+            ctx.set_stream(torch.cuda.current_stream().cuda_stream)
         # per sequence: state read + written, conv ring rows, inputs and output; weights once per launch
         gdn_bytes = B * (2 * 4194304 + 2 * 147456 + (12288 + 8192 + 128 + 8192) * 4) + 98304 + 768
-        res[f"gdn_decode_b{B}"] = {"us_per_layer": us, "state_gbps": gdn_bytes / us / 1e3, "frac_of_peak": gdn_bytes / us / 1e3 / peak,
-                                   "algorithmic_bytes_per_layer": gdn_bytes, "layers_cycled": NL}
+        res[f"gdn_decode_b{B}"] = {"us_per_layer": us, "us_per_layer_host_launched": us_host, "state_gbps": gdn_bytes / us / 1e3,
+                                   "frac_of_peak": gdn_bytes / us / 1e3 / peak, "algorithmic_bytes_per_layer": gdn_bytes,
+                                   "layers_cycled": NL, "issued_as": graph_note or "one CUDA graph of the layers' launches"}
         ctx.close()
         del ctx
         torch.cuda.empty_cache()
@@ -851,6 +879,9 @@ def main():
     args = ap.parse_args()
     set_kv_dtype(args.kv)
     if args.probe:
+        global PROBE_REPS
+        if any(a == "--steps" or a.startswith("--steps=") for a in sys.argv):
+            PROBE_REPS = args.steps
         import torch
         from __graft_entry__ import load_package
         torch.cuda.set_device(0)

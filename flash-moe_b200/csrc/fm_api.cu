@@ -235,6 +235,8 @@ extern "C" fm_status fm_create(const FmConfig *cfg, FmCtx **out) {
         ctx->work_bytes = gdn_prefill_work_bytes(g, c.max_batch_tokens, 64);
         if (ctx->work_bytes) CREATE_CUDA(cudaMalloc(&ctx->d_work, ctx->work_bytes));
     }
+    if (c.num_linear_layers > 0 && c.linear_key_dim == 128 && c.linear_value_dim == 128)
+        CREATE_CUDA(cudaMalloc(&ctx->d_gdn_scratch, gdn_decode_scratch_bytes(GdnDims{c.linear_num_v_heads, c.linear_num_k_heads, 128, 128, 0, 0, 0.f}, kMaxList)));
     CREATE_CUDA(cudaMalloc(&ctx->d_proj_ssq, 16 * sizeof(float)));
     CREATE_CUDA(cudaMemset(ctx->d_proj_ssq, 0, 16 * sizeof(float)));
     CREATE_CUDA(cudaMalloc(&ctx->d_err, sizeof(int)));
@@ -261,9 +263,16 @@ extern "C" void fm_destroy(FmCtx *ctx) {
     cudaFree(ctx->d_h2o_accum); cudaFree(ctx->d_h2o_order); cudaFree(ctx->d_h2o_tokpos); cudaFree(ctx->d_h2o_slot);
     cudaFree(ctx->d_h2o_counter); cudaFree(ctx->d_h2o_ml);
     cudaFree(ctx->d_proj_ssq);
+    cudaFree(ctx->d_gdn_scratch);
     cudaFree(ctx->d_stage);
     cudaFree(ctx->d_lstage);
     if (ctx->h_lstage) cudaFreeHost(ctx->h_lstage);
+    for (int i = 0; i < 3; i++) {
+        if (ctx->ev_in[i]) cudaEventDestroy(ctx->ev_in[i]);
+        if (ctx->ev_out[i]) cudaEventDestroy(ctx->ev_out[i]);
+    }
+    if (ctx->ev_idle) cudaEventDestroy(ctx->ev_idle);
+    if (ctx->copy_stream) cudaStreamDestroy(ctx->copy_stream);
     for (cudaEvent_t e : ctx->prof_ev) cudaEventDestroy(e);
     if (ctx->h_stage) cudaFreeHost(ctx->h_stage);
     delete ctx;
@@ -978,6 +987,16 @@ static GdnDims gdn_dims(const FmCtx *ctx) {
     return GdnDims{c.linear_num_v_heads, c.linear_num_k_heads, c.linear_key_dim, c.linear_value_dim, c.conv_kernel_size, ctx->conv_dim, c.rms_norm_eps};
 }
 
+// (head, sequence) pairs per launch from which the GatedDeltaNet step takes its persistent form; FM_GDN_STREAM_MIN_PAIRS
+// overrides it (a very large value keeps the cluster kernel everywhere)
+static int gdn_stream_min_pairs() {
+    static const int v = [] {
+        const char *e = getenv("FM_GDN_STREAM_MIN_PAIRS");
+        return e && *e ? atoi(e) : 512;
+    }();
+    return v;
+}
+
 extern "C" fm_status fm_gdn_decode(FmCtx *ctx, int li, const int *seq, int batch, const float *qkv, const float *z,
                                    const float *beta, const float *alpha, const uint16_t *conv_w, const float *A_log,
                                    const uint16_t *dt_bias, const uint16_t *norm_w, float *out) {
@@ -1013,13 +1032,22 @@ extern "C" fm_status fm_gdn_decode(FmCtx *ctx, int li, const int *seq, int batch
             t.set(i, seq[i0 + i], ctx->gdn_steps[lidx(ctx, li, seq[i0 + i])], 0, 0);
         }
         ProfScope prof(ctx);
-        st = launched(ctx, launch_gdn_decode(g, t, ctx->d_conv_state + (size_t)li * c.max_seqs * cn, ctx->d_ssm_state + (size_t)li * c.max_seqs * sn,
-                                             (long long)cn, (long long)sn, d_qkv + (size_t)i0 * ctx->conv_dim, d_z + i0 * vd, d_b + i0 * hv,
-                                             d_a + i0 * hv, d_cw, d_al, d_db, d_nw, d_out + i0 * vd, ctx->stream), "gdn_decode");
+        float *conv_l = ctx->d_conv_state + (size_t)li * c.max_seqs * cn, *ssm_l = ctx->d_ssm_state + (size_t)li * c.max_seqs * sn;
+        // several (head, sequence) pairs per SM: the persistent form that streams the states; else one CTA cluster per pair
+        const bool stream = ctx->d_gdn_scratch != nullptr && g.Hv * t.n >= gdn_stream_min_pairs() && ((uintptr_t)(d_z + i0 * vd) & 15) == 0;
+        if (stream)
+            st = launched(ctx, launch_gdn_decode_stream(g, t, conv_l, ssm_l, (long long)cn, (long long)sn, d_qkv + (size_t)i0 * ctx->conv_dim,
+                                                        d_z + i0 * vd, d_b + i0 * hv, d_a + i0 * hv, d_cw, d_al, d_db, d_nw, d_out + i0 * vd,
+                                                        ctx->d_gdn_scratch, ctx->sm_count, ctx->d_err, ctx->stream), "gdn_decode_stream");
+        else
+            st = launched(ctx, launch_gdn_decode(g, t, conv_l, ssm_l, (long long)cn, (long long)sn, d_qkv + (size_t)i0 * ctx->conv_dim, d_z + i0 * vd,
+                                                 d_b + i0 * hv, d_a + i0 * hv, d_cw, d_al, d_db, d_nw, d_out + i0 * vd, ctx->stream), "gdn_decode");
         if (st) return st;
         for (int i = 0; i < t.n; i++) ctx->gdn_steps[lidx(ctx, li, seq[i0 + i])]++;  // only once the step is queued
     }
+    if (sg.host) FM_CUDA(ctx, cudaMemcpyAsync(ctx->h_err, ctx->d_err, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
     FM_CUDA(ctx, sg.pull(out, w_out, batch * vd));
+    if (sg.host) return check_device_error(ctx);
     return FM_OK;
 }
 
@@ -1477,9 +1505,11 @@ static bool is_pinned(const void *p) {
     return a.type == cudaMemoryTypeHost;
 }
 
-// Host-pointer form: every layer's inputs go to the device in one batch of copies, the layers run
-// back to back on device pointers, the outputs come back in one copy.  Page-locked caller buffers are
-// copied directly; pageable ones pass through the context's own page-locked staging area.
+// Host-pointer form.  The layers' inputs go to the device in three groups (layer 0 | layers 1..3 | the rest) on a copy
+// stream, each group's launches waiting for its event only, so that all but the first small copy run under the earlier
+// layers' kernels; the outputs come back the same way (all but the last four layers | three more | the last), so that
+// only the last layer's rows are copied after the last kernel.  Page-locked caller buffers are copied directly;
+// pageable ones pass through the context's own page-locked staging area.
 static fm_status decode_layers_host(FmCtx *ctx, int first_layer, int n_layers, const int *seq, const int *pos, int batch,
                                     const float *q_proj_out, size_t sq, const float *k, const float *v, size_t skv,
                                     const uint16_t *qnw, const uint16_t *knw, float *out, size_t so, int exchange) {
@@ -1501,37 +1531,85 @@ static fm_status decode_layers_host(FmCtx *ctx, int first_layer, int n_layers, c
         FM_CUDA(ctx, cudaMalloc(&ctx->d_lstage, need));
         ctx->lstage_bytes = need;
     }
+    if (ctx->copy_stream == nullptr) {
+        FM_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking));
+        for (int i = 0; i < 3; i++) {
+            FM_CUDA(ctx, cudaEventCreateWithFlags(&ctx->ev_in[i], cudaEventDisableTiming));
+            FM_CUDA(ctx, cudaEventCreateWithFlags(&ctx->ev_out[i], cudaEventDisableTiming));
+        }
+        FM_CUDA(ctx, cudaEventCreateWithFlags(&ctx->ev_idle, cudaEventDisableTiming));
+    }
+    cudaStream_t cs = ctx->copy_stream;
     char *hs = ctx->h_lstage, *ds = ctx->d_lstage;
-    // host -> device of n_layers blocks of `block` floats, `stride` floats apart at the source
-    auto send = [&](const float *src, size_t stride, size_t block, size_t off) -> cudaError_t {
-        if (src == nullptr || block == 0) return cudaSuccess;
+    // whatever the caller queued on the context's stream before this call (it may still read the staging area)
+    FM_CUDA(ctx, cudaEventRecord(ctx->ev_idle, ctx->stream));
+    FM_CUDA(ctx, cudaStreamWaitEvent(cs, ctx->ev_idle, 0));
+    // host -> device of layers [a, b): blocks of `block` floats, `stride` floats apart at the source
+    auto send = [&](const float *src, size_t stride, size_t block, size_t off, size_t a, size_t b) -> cudaError_t {
+        if (src == nullptr || block == 0 || b <= a) return cudaSuccess;
         if (is_pinned(src))
-            return cudaMemcpy2DAsync(ds + off, block * 4, src, stride * 4, block * 4, nl, cudaMemcpyHostToDevice, ctx->stream);
-        for (size_t l = 0; l < nl; l++) memcpy(hs + off + l * block * 4, src + l * stride, block * 4);
-        return cudaMemcpyAsync(ds + off, hs + off, nl * block * 4, cudaMemcpyHostToDevice, ctx->stream);
+            return cudaMemcpy2DAsync(ds + off + a * block * 4, block * 4, src + a * stride, stride * 4, block * 4, b - a, cudaMemcpyHostToDevice, cs);
+        for (size_t l = a; l < b; l++) memcpy(hs + off + l * block * 4, src + l * stride, block * 4);
+        return cudaMemcpyAsync(ds + off + a * block * 4, hs + off + a * block * 4, (b - a) * block * 4, cudaMemcpyHostToDevice, cs);
     };
     if (qnw) memcpy(hs + o_w, qnw, (size_t)c.head_dim * 2);
     if (knw) memcpy(hs + o_w + 512, knw, (size_t)c.head_dim * 2);
-    if (qnw || knw) FM_CUDA(ctx, cudaMemcpyAsync(ds + o_w, hs + o_w, 1024, cudaMemcpyHostToDevice, ctx->stream));
-    FM_CUDA(ctx, send(q_proj_out, sq, qf, o_q));
-    FM_CUDA(ctx, send(k, skv, kvf, o_k));
-    FM_CUDA(ctx, send(v, skv, kvf, o_v));
-    ctx->ptr_mode = FM_PTR_DEVICE;
-    const fm_status st = fm_attn_decode_layers(ctx, first_layer, n_layers, seq, pos, batch, reinterpret_cast<const float *>(ds + o_q), qf,
-                                               k ? reinterpret_cast<const float *>(ds + o_k) : nullptr,
-                                               v ? reinterpret_cast<const float *>(ds + o_v) : nullptr, kvf,
-                                               qnw ? reinterpret_cast<const uint16_t *>(ds + o_w) : nullptr,
-                                               knw ? reinterpret_cast<const uint16_t *>(ds + o_w + 512) : nullptr,
-                                               reinterpret_cast<float *>(ds + o_out), of, exchange);
-    ctx->ptr_mode = FM_PTR_HOST;
-    if (st) return st;
-    FM_CUDA(ctx, cudaMemcpyAsync(ctx->h_err, ctx->d_err, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+    if (qnw || knw) FM_CUDA(ctx, cudaMemcpyAsync(ds + o_w, hs + o_w, 1024, cudaMemcpyHostToDevice, cs));
+    const size_t in_end[3] = {std::min<size_t>(1, nl), std::min<size_t>(4, nl), nl};
+    const size_t out_end[3] = {nl > 4 ? nl - 4 : 0, nl > 1 ? nl - 1 : 0, nl};
+    for (int g = 0; g < 3; g++) {
+        const size_t a = g ? in_end[g - 1] : 0, b = in_end[g];
+        if (b <= a) continue;
+        FM_CUDA(ctx, send(q_proj_out, sq, qf, o_q, a, b));
+        FM_CUDA(ctx, send(k, skv, kvf, o_k, a, b));
+        FM_CUDA(ctx, send(v, skv, kvf, o_v, a, b));
+        FM_CUDA(ctx, cudaEventRecord(ctx->ev_in[g], cs));
+    }
     const bool direct = is_pinned(out);
-    if (direct)
-        FM_CUDA(ctx, cudaMemcpy2DAsync(out, so * 4, ds + o_out, of * 4, of * 4, nl, cudaMemcpyDeviceToHost, ctx->stream));
-    else
-        FM_CUDA(ctx, cudaMemcpyAsync(hs + o_out, ds + o_out, nl * of * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    // the launches, cut where an input group starts or an output group ends
+    ctx->ptr_mode = FM_PTR_DEVICE;
+    fm_status st = FM_OK;
+    size_t at = 0;
+    while (at < nl && st == FM_OK) {
+        size_t stop = nl;
+        for (int g = 0; g < 3; g++) {
+            if (in_end[g] > at) stop = std::min(stop, in_end[g]);
+            if (out_end[g] > at) stop = std::min(stop, out_end[g]);
+        }
+        cudaError_t e = cudaSuccess;
+        for (int g = 0; g < 3; g++)
+            if ((g ? in_end[g - 1] : 0) == at && in_end[g] > at) e = cudaStreamWaitEvent(ctx->stream, ctx->ev_in[g], 0);
+        if (e != cudaSuccess) { st = fail(ctx, FM_ERR_CUDA, "fm_attn_decode_layers: %s", cudaGetErrorString(e)); break; }
+        st = fm_attn_decode_layers(ctx, first_layer + (int)at, (int)(stop - at), seq, pos, batch, reinterpret_cast<const float *>(ds + o_q) + at * qf, qf,
+                                   k ? reinterpret_cast<const float *>(ds + o_k) + at * kvf : nullptr,
+                                   v ? reinterpret_cast<const float *>(ds + o_v) + at * kvf : nullptr, kvf,
+                                   qnw ? reinterpret_cast<const uint16_t *>(ds + o_w) : nullptr,
+                                   knw ? reinterpret_cast<const uint16_t *>(ds + o_w + 512) : nullptr,
+                                   reinterpret_cast<float *>(ds + o_out) + at * of, of, exchange);
+        if (st) break;
+        for (int g = 0; g < 3 && e == cudaSuccess; g++) {
+            const size_t a = g ? out_end[g - 1] : 0, b = out_end[g];
+            if (b != stop || b <= a) continue;
+            e = cudaEventRecord(ctx->ev_out[g], ctx->stream);
+            if (e == cudaSuccess) e = cudaStreamWaitEvent(cs, ctx->ev_out[g], 0);
+            if (e != cudaSuccess) break;
+            if (direct)
+                e = cudaMemcpy2DAsync(out + a * so, so * 4, ds + o_out + a * of * 4, of * 4, of * 4, b - a, cudaMemcpyDeviceToHost, cs);
+            else
+                e = cudaMemcpyAsync(hs + o_out + a * of * 4, ds + o_out + a * of * 4, (b - a) * of * 4, cudaMemcpyDeviceToHost, cs);
+        }
+        if (e != cudaSuccess) { st = fail(ctx, FM_ERR_CUDA, "fm_attn_decode_layers: %s", cudaGetErrorString(e)); break; }
+        at = stop;
+    }
+    ctx->ptr_mode = FM_PTR_HOST;
+    if (st) {  // leave nothing in flight that touches the caller's buffers
+        cudaStreamSynchronize(cs);
+        cudaStreamSynchronize(ctx->stream);
+        return st;
+    }
+    FM_CUDA(ctx, cudaMemcpyAsync(ctx->h_err, ctx->d_err, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
     FM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    FM_CUDA(ctx, cudaStreamSynchronize(cs));
     if (!direct)
         for (size_t l = 0; l < nl; l++) memcpy(out + l * so, hs + o_out + l * of * 4, of * 4);
     return check_device_error(ctx);

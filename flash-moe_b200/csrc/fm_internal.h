@@ -189,6 +189,10 @@ struct FmCtx {
     // staging of all layers of one fm_attn_decode_layers call in host-pointer mode (grown on demand)
     char *h_lstage = nullptr, *d_lstage = nullptr;
     size_t lstage_bytes = 0;
+    float *d_gdn_scratch = nullptr;  // per-token records of the streaming GatedDeltaNet step (kMaxList tokens)
+    // host-pointer form of the layered decode: copies run on a stream of their own, tied to the launches by events
+    cudaStream_t copy_stream = nullptr;
+    cudaEvent_t ev_in[3] = {nullptr, nullptr, nullptr}, ev_out[3] = {nullptr, nullptr, nullptr}, ev_idle = nullptr;
 };
 
 namespace fm {
@@ -266,6 +270,13 @@ int launch_gdn_decode(const GdnDims &g, const TokSpec &toks, float *conv_state, 
                       const float *z, const float *beta, const float *alpha, const uint16_t *conv_w,
                       const float *A_log, const uint16_t *dt_bias, const uint16_t *norm_w, float *out,
                       cudaStream_t st);
+// The same step as a prep launch + a persistent launch that streams the states (for many (head, sequence) pairs);
+// `scratch` holds gdn_decode_scratch_bytes(g, toks.n) bytes, z must be 16-byte aligned.  Returns the launches made.
+size_t gdn_decode_scratch_bytes(const GdnDims &g, int tokens);
+int launch_gdn_decode_stream(const GdnDims &g, const TokSpec &toks, float *conv_state, float *ssm_state, long long conv_seq_stride,
+                             long long ssm_seq_stride, const float *qkv, const float *z, const float *beta, const float *alpha,
+                             const uint16_t *conv_w, const float *A_log, const uint16_t *dt_bias, const uint16_t *norm_w, float *out,
+                             float *scratch, int sm_count, int *err, cudaStream_t st);
 int launch_gdn_prefill(const GdnDims &g, int n, int chunk, int step0, float *conv_state, float *ssm_state,
                        const float *qkv, const float *z, const float *beta, const float *alpha,
                        const uint16_t *conv_w, const float *A_log, const uint16_t *dt_bias,

@@ -56,7 +56,7 @@ gdn_decode_kernel(GdnDims g, TokSpec toks, float *__restrict__ conv_ring, float 
     __shared__ float s_v[kRows];
     __shared__ float s_o[kRows];
     __shared__ float s_red[8 + W];
-    __shared__ float s_ss;  // this CTA's share of sum(o^2); read by the cluster peers
+    __shared__ float s_share[8];  // sum(o^2) of every CTA of the cluster, each written by its owner into all copies
 
     const int slice = blockIdx.x, vh = blockIdx.y, tok = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -71,6 +71,23 @@ gdn_decode_kernel(GdnDims g, TokSpec toks, float *__restrict__ conv_ring, float 
 #pragma unroll
     for (int i = 0; i < kRowsPerWarp; i++)
         st[i] = *reinterpret_cast<const float4 *>(S0 + (size_t)(warp * kRowsPerWarp + i) * kDk + lane * 4);
+
+    // first phase of the cluster barrier: arrive now, wait just before the first write into a peer's shared memory
+    // (which is only legal once that peer has started); by then everyone has long arrived
+    if (S > 1) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+
+    // ---- everything else the step reads from global memory is requested now as well, so that one memory latency
+    //      covers it all: the gate row, the head's decay / beta inputs, the norm weight ----
+    const bool has_norm = norm_w != nullptr;
+    float z_pre = 0.f, nw_pre = 1.f;
+    if (tid < kRows && has_norm) {
+        const int d = slice * kRows + tid;
+        z_pre = __ldg(z + (size_t)tok * g.Hv * kDv + (size_t)vh * kDv + d);
+        nw_pre = bf16_bits_to_float(__ldg(norm_w + d));
+    }
+    const float alpha_pre = __ldg(alpha + (size_t)tok * g.Hv + vh), beta_pre = __ldg(beta + (size_t)tok * g.Hv + vh);
+    const float bias = dt_bias ? bf16_bits_to_float(__ldg(dt_bias + vh)) : 0.f;
+    const float alog = A_log ? __ldg(A_log + vh) : 0.f;
 
     // ---- conv + SiLU for this head's q, k channels and this slice's v channels ----
     float *ring = conv_ring + (size_t)seq * conv_seq_stride;
@@ -106,59 +123,73 @@ gdn_decode_kernel(GdnDims g, TokSpec toks, float *__restrict__ conv_ring, float 
             s_k[tid - kDk] = my * inv * inv_scale;
     }
     // decay and beta of this head
-    const float bias = dt_bias ? bf16_bits_to_float(dt_bias[vh]) : 0.f;
-    const float A = A_log ? expf(A_log[vh]) : 1.0f;
-    const float sp = logf(1.0f + expf(alpha[(size_t)tok * g.Hv + vh] + bias));
+    const float A = A_log ? expf(alog) : 1.0f;
+    const float sp = logf(1.0f + expf(alpha_pre + bias));
     const float decay = expf(-A * sp);
-    const float bgate = 1.0f / (1.0f + expf(-beta[(size_t)tok * g.Hv + vh]));
+    const float bgate = 1.0f / (1.0f + expf(-beta_pre));
     __syncthreads();
 
-    // ---- delta rule, one warp per row ----
+    // ---- delta rule, one warp per row.  With S the row before the step: mem = decay (S k), delta = (v - mem) beta,
+    // S' = decay S + delta k, o = S' q = decay (S q) + delta (k q).  S k and S q are reduced side by side (one pass of
+    // shuffles over two independent sums instead of two passes one after the other) for all rows of the warp at once.
     const float4 k4 = *reinterpret_cast<const float4 *>(s_k + lane * 4);
     const float4 q4 = *reinterpret_cast<const float4 *>(s_q + lane * 4);
+    const float kq = warp_sum(k4.x * q4.x + k4.y * q4.y + k4.z * q4.z + k4.w * q4.w);
+    float sk[kRowsPerWarp], sq[kRowsPerWarp];
+#pragma unroll
+    for (int i = 0; i < kRowsPerWarp; i++) {
+        const float4 s = st[i];
+        sk[i] = s.x * k4.x + s.y * k4.y + s.z * k4.z + s.w * k4.w;
+        sq[i] = s.x * q4.x + s.y * q4.y + s.z * q4.z + s.w * q4.w;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+        for (int i = 0; i < kRowsPerWarp; i++) {
+            sk[i] += __shfl_xor_sync(0xffffffffu, sk[i], o);
+            sq[i] += __shfl_xor_sync(0xffffffffu, sq[i], o);
+        }
+    }
     float ss_local = 0.f;
 #pragma unroll
     for (int i = 0; i < kRowsPerWarp; i++) {
         const int r = warp * kRowsPerWarp + i;
+        const float delta = (s_v[r] - decay * sk[i]) * bgate;
         float4 s = st[i];
-        s.x *= decay; s.y *= decay; s.z *= decay; s.w *= decay;
-        const float mem = warp_sum(s.x * k4.x + s.y * k4.y + s.z * k4.z + s.w * k4.w);
-        const float delta = (s_v[r] - mem) * bgate;
-        s.x += k4.x * delta; s.y += k4.y * delta; s.z += k4.z * delta; s.w += k4.w * delta;
-        const float o = warp_sum(s.x * q4.x + s.y * q4.y + s.z * q4.z + s.w * q4.w);
+        s.x = s.x * decay + k4.x * delta; s.y = s.y * decay + k4.y * delta;
+        s.z = s.z * decay + k4.z * delta; s.w = s.w * decay + k4.w * delta;
         *reinterpret_cast<float4 *>(S0 + (size_t)r * kDk + lane * 4) = s;
-        if (lane == 0) {
-            s_o[r] = o;
-            ss_local += o * o;
-        }
+        const float o = decay * sq[i] + delta * kq;
+        if (lane == 0) s_o[r] = o;
+        ss_local += o * o;  // the same value in every lane
     }
     if (lane == 0) s_red[8 + warp] = ss_local;
     __syncthreads();
-    if (tid == 0) {
-        float t = 0.f;
-        for (int w = 0; w < W; w++) t += s_red[8 + w];
-        s_ss = t;
-    }
-    float total_ss;
+    float total_ss = 0.f;
     if (S > 1) {
+        // every CTA of the cluster puts its share of sum(o^2) into every peer's shared memory, then one cluster barrier:
+        // after it each CTA reads only its own copy, so nobody depends on a peer that may already have exited
         cg::cluster_group cluster = cg::this_cluster();
-        cluster.sync();  // every CTA's s_ss is written
-        total_ss = 0.f;
-        for (int r = 0; r < S; r++) total_ss += *cluster.map_shared_rank(&s_ss, r);
-        cluster.sync();  // nobody exits while a peer may still read its s_ss
+        asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
+        if (tid < S) {
+            float t = 0.f;
+            for (int w = 0; w < W; w++) t += s_red[8 + w];
+            *cluster.map_shared_rank(&s_share[slice], tid) = t;
+        }
+        cluster.sync();
+#pragma unroll
+        for (int r = 0; r < S; r++) total_ss += s_share[r];
     } else {
-        __syncthreads();
-        total_ss = s_ss;
+        for (int w = 0; w < W; w++) total_ss += s_red[8 + w];
     }
     // ---- gated RMS-norm: o * rsqrt(mean o^2 + eps) * w * silu(z) ----
     if (tid < kRows) {
         const int d = slice * kRows + tid;
         const size_t oi = (size_t)tok * g.Hv * kDv + (size_t)vh * kDv + d;
         float o = s_o[tid];
-        if (norm_w != nullptr) {
+        if (has_norm) {
             const float inv = 1.0f / sqrtf(total_ss / kDv + g.eps);
-            const float zz = z[oi];
-            o = o * inv * bf16_bits_to_float(norm_w[d]) * (zz / (1.0f + expf(-zz)));
+            o = o * inv * nw_pre * (z_pre / (1.0f + expf(-z_pre)));
         }
         out[oi] = o;
     }

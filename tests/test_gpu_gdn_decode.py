@@ -115,6 +115,40 @@ def test_large_batch_whole_head_variant(pkg, port, synth):
     c.close()
 
 
+@pytest.mark.parametrize("B,defaults", [(24, False), (8, True), (64, False)])
+def test_streamed_states_many_pairs(pkg, port, synth, B, defaults):
+    """64 heads x B >= 512 (head, sequence) pairs: the persistent form that streams the states through shared memory.
+    Several steps per sequence (ring slots and stages are reused, 1536 pairs do not divide by the SM count), outputs of
+    every step and the final recurrent and conv states against the checker; once with the reference's defaults for
+    absent A_log / dt_bias / norm weight."""
+    n = 5 if B < 64 else 2
+    dims = make_dims()
+    w = synth.gdn_weights(11)
+    wa = (w["conv_w"], None, None, None) if defaults else (w["conv_w"], w["A_log"], w["dt_bias"], w["norm_w"])
+    c = gdn_ctx(pkg, max_seqs=B)
+    refs, states, convs = [], [], []
+    ins = [synth.gdn_step_inputs(300 + s, n) for s in range(B)]
+    for s in range(B):
+        conv = np.zeros((3, 12288), np.float32); ssm = synth.gdn_state(300 + s).copy()
+        c.state_import(0, s, None, ssm)
+        refs.append(port.gdn_run(dims, conv, ssm, *ins[s], *wa, threads=8))
+        states.append(ssm); convs.append(conv)
+    for t in range(n):
+        pack = lambda j: np.ascontiguousarray(np.stack([ins[s][j][t] for s in range(B)]))
+        out = np.empty((B, 8192), np.float32)
+        c.gdn_decode(0, list(range(B)), pack(0), pack(1), pack(2), pack(3), out, *wa)
+        for s in range(B):
+            g, _, _ = rel_errors(out[s], refs[s][t])
+            assert g <= 1e-4, (t, s, g)
+    for s in range(0, B, max(1, B // 8)):
+        ssm = np.empty((64, 128, 128), np.float32); conv = np.empty((3, 12288), np.float32)
+        c.state_export(0, s, conv, ssm)
+        g, _, _ = rel_errors(ssm, states[s])
+        assert g <= 1e-4
+        assert np.array_equal(conv, convs[s])
+    c.close()
+
+
 def test_reset_and_reference_defaults(pkg, port, synth):
     """NULL A_log / dt_bias / norm weight mean A = 1, bias 0, no output norm, as in the reference;
     fm_reset returns the layer to the zero state."""
