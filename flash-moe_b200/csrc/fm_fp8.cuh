@@ -50,15 +50,37 @@ __device__ __forceinline__ float fp8_e4m3_decode_ref(uint8_t b, float scale) {
     return __fmul_rn(val, scale);
 }
 
-// Two E4M3 bytes of `r`, picked by a byte-permute selector that puts them in the high byte of each 16-bit lane,
-// as two fp16 numbers worth value * 2^-8: the byte's exponent and mantissa bits are simply placed in the fp16
+// Two E4M3 bytes of `r` (selector: a byte-permute selector that puts them in the high byte of each 16-bit lane; the
+// low bytes are zero) as two fp16 numbers.  The hardware conversion gives the exact values; E4M3's NaN codes come out as
+// NaN, and the maximum with -480 turns them into -480 (max returns its other operand for a NaN, and every other
+// value is above -448): that is what the reference's decoder makes of 0xFF (it knows only 0x7F as NaN; 0x7F is never
+// produced from finite data, and reads as -480 here).
+#ifndef FM_FP8_HW_CVT
+#define FM_FP8_HW_CVT 1
+#endif
+#if FM_FP8_HW_CVT
+__device__ __forceinline__ uint32_t fp8x2_cvt(uint32_t pair16) {
+    uint32_t d;
+    asm("{\n\t.reg .b16 p;\n\tcvt.u16.u32 p, %1;\n\tcvt.rn.f16x2.e4m3x2 %0, p;\n\tmax.f16x2 %0, %0, %2;\n\t}\n" : "=r"(d) : "r"(pair16), "r"(0xDF80DF80u));
+    return d;
+}
+__device__ __forceinline__ uint32_t fp8x2_to_f16x2_scaled(uint32_t r, uint32_t selector) {
+    // the same byte pairs as the permute form below, as the two bytes of a 16-bit word
+    if (selector == 0x1404u) return fp8x2_cvt(r & 0xffffu);
+    if (selector == 0x3424u) return fp8x2_cvt(r >> 16);
+    return fp8x2_cvt(__byte_perm(r, 0u, selector == 0x2404u ? 0x4420u : 0x4431u));
+}
+constexpr float kFp8HalfScale = 1.0f;
+#else
+// Without the conversion instruction: the byte's exponent and mantissa bits are simply placed in the fp16
 // exponent / mantissa fields (E4M3 normal -> fp16 normal, E4M3 subnormal -> fp16 subnormal, both short by the
 // same factor 2^-8 because the biases differ by 8), and the sign is moved up by one bit.  0xFF comes out as
-// -480 * 2^-8, matching the reference's decoder; 0x7F (NaN in, never produced from finite data) as +480 * 2^-8.
+// -480 * 2^-8, matching the reference's decoder; 0x7F as +480 * 2^-8.
 __device__ __forceinline__ uint32_t fp8x2_to_f16x2_scaled(uint32_t r, uint32_t selector) {
     const uint32_t t = __byte_perm(r, 0u, selector) >> 1;  // per lane: bit 14 sign, bits 13..7 exponent | mantissa
     return t + (t & 0x40004000u);                          // carry the sign into bit 15
 }
-constexpr float kFp8HalfScale = 256.0f;  // what fp8x2_to_f16x2_scaled leaves out
+constexpr float kFp8HalfScale = 256.0f;  // what this form leaves out
+#endif
 
 }  // namespace fm
