@@ -477,9 +477,9 @@ def parity_check(args, pkg, torch, dist, ctx, step, cur, qp, kn, vn, out, dev, w
 # DRAM bytes (read + write) of one attn_decode_kernel launch for ONE sequence at 131073 rows, from
 # the committed ncu capture (profiles/attn_decode_kernel_b1_ctx128k_ncu.md): 268.76 MB + 4.43 MB.
 # Traffic grows in proportion to rows x sequences, so the bench launch is scaled from it.  Captured on the kernel
-# as of commit 9d09feb (two-level merge with a warp merging its two heads together); refresh when the kernel's
-# memory behaviour changes.
-TRAFFIC_NCU_1SEQ_128K = 273.18e6
+# as of commit 946021c (wide merges as a dependent launch; its own traffic, a few hundred KB, is not included); refresh
+# when the kernel's memory behaviour changes.
+TRAFFIC_NCU_1SEQ_128K = 272.57e6
 
 
 PROBE_REPS = None  # --probe with an explicit --steps: that many timed repetitions (short runs for profiling)
