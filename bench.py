@@ -217,6 +217,8 @@ def run_ours(args):
             V = torch.randn((L, Hkvl * D), device=dev, generator=gen).bfloat16().float()
             ctx.kv_import(layer, s, K, V, L)
     del K, V
+    # the step's inputs are those of the head group: the same on every rank of a sequence group
+    gen = torch.Generator(device=dev); gen.manual_seed(99991 + my_hg)
     qp = torch.randn((NL, B, Hl * 2 * D), device=dev, generator=gen)
     kn = torch.randn((NL, B, Hkvl * D), device=dev, generator=gen)
     vn = torch.randn((NL, B, Hkvl * D), device=dev, generator=gen)
