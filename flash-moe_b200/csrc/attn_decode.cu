@@ -608,7 +608,7 @@ __device__ __forceinline__ void attn_decode_body(const KvView &kv, const RopePar
                 f.ml_out[((size_t)tk * H + head) * 2 + 1] = lt;
             }
         } else {
-            const size_t row = ((((size_t)(f.step & 1) * f.x.nranks + f.x.me) * f.x.cap + tk) * H + head) * (kD + 2);
+            const size_t row = ((((size_t)(f.step & (f.x.ring - 1)) * f.x.nranks + f.x.me) * f.x.cap + tk) * H + head) * (kD + 2);
             for (int r = 0; r < f.x.nranks; r++) {
                 float *dst = f.x.peer[r] + row;
                 *reinterpret_cast<float2 *>(dst + d) = make_float2(acc.x, acc.y);
@@ -618,10 +618,10 @@ __device__ __forceinline__ void attn_decode_body(const KvView &kv, const RopePar
         }
     };
     const bool direct = kFused && nsplits == 1;  // this CTA is the only split: finish the rows here
-    // The exchange tails write slots that the previous launch's peers may still be reading: wait for the previous
-    // launch to complete.  (Partials, counters and outputs are per layer, and a launch is only ever overlapped with
-    // another layer's; those tails wait at the end of the CTA instead, see attn_decode_kernel.)
-    if (kFused && f.tail >= 3) dep_wait();
+    // Nothing written from here on is shared with the launch this one may overlap: partials, counters and outputs
+    // are per layer, and the exchange tails write the slot set of their own step (a ring deep enough that a set is
+    // only reused after every rank has read it, see fm_exchange_attach).  The wait the overlap owes is at the end
+    // of the CTA (attn_decode_kernel).
     for (int r = warp; r < group; r += kDecWarps) {
         float mw[4], M = kNegBig;
 #pragma unroll
@@ -759,7 +759,7 @@ __device__ __forceinline__ void attn_decode_body(const KvView &kv, const RopePar
     if (f.tail == 4) {
         // ---- this CTA has stored the unit's rows into every rank's buffer: publish, wait, merge ----
         __shared__ int s_ok;
-        const int nr = f.x.nranks, par = f.step & 1;
+        const int nr = f.x.nranks, par = f.step & (f.x.ring - 1);
         const int nunits = f.x.cap * kv.Hkv, unit = tok * kv.Hkv + kvh;
         if (tid == 0) s_ok = 1;
         __threadfence_system();
@@ -826,7 +826,7 @@ __device__ __forceinline__ void attn_decode_body(const KvView &kv, const RopePar
                 __threadfence_system();
                 for (int r = 0; r < f.x.nranks; r++) {
                     uint32_t *flags = reinterpret_cast<uint32_t *>(f.x.peer[r] + f.x.flag_offset_floats);
-                    st_release_sys(flags + (f.step & 1) * f.x.nranks + f.x.me, f.step);
+                    st_release_sys(flags + (f.step & (f.x.ring - 1)) * f.x.nranks + f.x.me, f.step);
                 }
             }
         }
@@ -1104,7 +1104,7 @@ __global__ void attn_merge_push_kernel(const float *__restrict__ part_o, const f
         const float4 v = *reinterpret_cast<const float4 *>(o0 + (size_t)j * D + d);
         acc.x += w * v.x; acc.y += w * v.y; acc.z += w * v.z; acc.w += w * v.w;
     }
-    const int par = step & 1;
+    const int par = step & (x.ring - 1);
     const size_t row = (((size_t)par * x.nranks + x.me) * x.cap + tok) * H + head;
     for (int r = 0; r < x.nranks; r++) {
         float *dst = x.peer[r] + row * (D + 2);
@@ -1133,7 +1133,7 @@ __global__ void attn_wait_merge_kernel(XchgView x, uint32_t step, int H, const f
     constexpr int D = kD;
     __shared__ int s_ok;
     const int head = blockIdx.x, tok = blockIdx.y, d = threadIdx.x * 4;
-    const int par = step & 1;
+    const int par = step & (x.ring - 1);
     const float *mine = x.peer[x.me];
     dep_launch_dependents();
     if (threadIdx.x == 0) {

@@ -1335,16 +1335,29 @@ extern "C" fm_status fm_state_import(FmCtx *ctx, int li, int seq, const float *c
 
 // ---- cross-GPU exchange of decode partials over peer memory ------------------------------------
 static int xchg_cap(const FmCtx *ctx) { return std::min(ctx->cfg.max_batch_tokens, kMaxList); }
-static size_t xchg_slot_floats(const FmCtx *ctx, int nranks) {
-    return (size_t)2 * nranks * xchg_cap(ctx) * ctx->cfg.num_attn_heads * (ctx->cfg.head_dim + 2);
+// Slot sets of the exchange: step s uses set s & (ring - 1).  Within one fm_attn_decode_layers call up to
+// num_full_layers launches are in flight at once (each a programmatic dependent of the one before, all complete in
+// order, the first one behind everything earlier in the stream), and nothing orders a launch's push behind the
+// earlier launches' reads.  A rank that pushes step s has completed every call before the current one, i.e. every
+// step <= s - n (n = num_full_layers); completing a step means every peer has pushed it, and a peer that has pushed
+// step x has itself completed every step <= x - n, reads included.  So when step s is pushed, every rank has read all
+// steps <= s - 2n: a ring of at least 2n sets is never overwritten while in use.
+static int xchg_ring(const FmCtx *ctx) {
+    int r = 2;
+    while (r < 2 * ctx->cfg.num_full_layers) r <<= 1;
+    return r;
 }
+static size_t xchg_slot_floats(const FmCtx *ctx, int nranks) {
+    return (size_t)xchg_ring(ctx) * nranks * xchg_cap(ctx) * ctx->cfg.num_attn_heads * (ctx->cfg.head_dim + 2);
+}
+static size_t xchg_step_flag_bytes(const FmCtx *ctx, int nranks) { return ((size_t)xchg_ring(ctx) * nranks * 4 + 255) & ~(size_t)255; }
 
 extern "C" size_t fm_exchange_bytes(const FmCtx *ctx, int nranks) {
     if (!ctx || nranks < 1 || nranks > kMaxXchgRanks) return 0;
     const size_t slots = (xchg_slot_floats(ctx, nranks) * sizeof(float) + 255) & ~(size_t)255;
-    // after the slots: step flags [2][nranks], then flags per (token, KV head) [2][nranks][cap * Hkv], 32 bits each
-    const size_t unit_flags = ((size_t)2 * nranks * xchg_cap(ctx) * ctx->cfg.num_kv_heads * 4 + 255) & ~(size_t)255;
-    return slots + 256 + unit_flags;
+    // after the slots: step flags [ring][nranks], then flags per (token, KV head) [ring][nranks][cap * Hkv], 32 bits each
+    const size_t unit_flags = ((size_t)xchg_ring(ctx) * nranks * xchg_cap(ctx) * ctx->cfg.num_kv_heads * 4 + 255) & ~(size_t)255;
+    return slots + xchg_step_flag_bytes(ctx, nranks) + unit_flags;
 }
 
 extern "C" fm_status fm_exchange_attach(FmCtx *ctx, int nranks, int my_index, void *const *peer_bufs) {
@@ -1364,8 +1377,9 @@ extern "C" fm_status fm_exchange_attach(FmCtx *ctx, int nranks, int my_index, vo
     x.nranks = nranks;
     x.me = my_index;
     x.cap = xchg_cap(ctx);
+    x.ring = xchg_ring(ctx);
     x.flag_offset_floats = (long long)(((xchg_slot_floats(ctx, nranks) * sizeof(float) + 255) & ~(size_t)255) / sizeof(float));
-    x.unit_flag_offset_floats = x.flag_offset_floats + 64;
+    x.unit_flag_offset_floats = x.flag_offset_floats + (long long)(xchg_step_flag_bytes(ctx, nranks) / sizeof(float));
     int khz = 0;
     cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, ctx->cfg.device);
     x.wait_limit_cycles = (long long)(khz > 0 ? khz : 1900000) * 500;  // about half a second of SM clock

@@ -79,8 +79,9 @@ struct XchgView {
     float *peer[kMaxXchgRanks];  // every rank's buffer, addressable from this GPU; peer[me] is the local one
     int nranks, me;
     int cap;                     // token capacity of a slot
-    long long flag_offset_floats;       // step flags [2][nranks]
-    long long unit_flag_offset_floats;  // flags per (token, KV head) [2][nranks][cap * Hkv]
+    int ring;                    // slot sets, a power of two: exchange step s uses set s & (ring - 1)
+    long long flag_offset_floats;       // step flags [ring][nranks]
+    long long unit_flag_offset_floats;  // flags per (token, KV head) [ring][nranks][cap * Hkv]
     long long wait_limit_cycles;
 };
 
