@@ -679,10 +679,18 @@ int launch_gdn_prefill(const GdnDims &g, int n, int chunk, int step0, float *con
     (void)chunk;
     GdnWork w;
     if (carve(g, n, work, &w) > work_bytes) return -1;
+    // the prep kernel's shared memory grows with conv_dim: the limit is raised whenever a context needs more than
+    // any earlier one on the same device did
+    static int prep_smem_set[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
+    if (g.conv_dim * 4 > prep_smem_set[dev]) {
+        if (cudaFuncSetAttribute(gdn_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, g.conv_dim * 4) != cudaSuccess) return -1;
+        prep_smem_set[dev] = g.conv_dim * 4;
+    }
     static unsigned long long configured = 0;  // one bit per device
     if (first_use_on_device(&configured)) {
-        if (cudaFuncSetAttribute(gdn_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, g.conv_dim * 4) != cudaSuccess ||
-            cudaFuncSetAttribute(gdn_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kChunkSmem) != cudaSuccess ||
+        if (cudaFuncSetAttribute(gdn_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kChunkSmem) != cudaSuccess ||
             cudaFuncSetAttribute(gdn_kk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kKkSmem) != cudaSuccess ||
             cudaFuncSetAttribute(gdn_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kScSmem) != cudaSuccess)
             return -1;
