@@ -679,7 +679,26 @@ static int pick_splits(const FmCtx *ctx, int batch, int max_len, bool exchange =
         // have to wait for their turn holds its SMs meanwhile: measured at batch 8 x 128K, full width is better
         // at 57 tiles per CTA (4 GPUs: 91 vs 101 us per layer), a quarter at 29 (8 GPUs: 56 vs 64).
         const int tiles_full = (slots + want - 1) / want;
-        if (tiles_full < (exchange ? 40 : 64)) want = std::max(1, std::min(want / 4, (slots + 7) / 8));
+        if (tiles_full < (exchange ? 40 : 64)) {
+            const int full = want;
+            want = std::max(1, std::min(want / 4, (slots + 7) / 8));
+            // The CTAs of the call's layers fill the SMs in waves; a width whose CTA count over all layers just
+            // misses a whole number of waves pays for a nearly empty one (8 GPUs, batch 8 x 128K: 15 layers x 32 CTAs
+            // = 3.2 waves of 129 tiles cost 4; 48 CTAs per layer = 4.9 waves of 86 tiles cost 5: 55 -> 47 us per
+            // layer expected).  Cost of a width: waves x (tiles per CTA + a CTA's fixed cost, about 6 tiles' time);
+            // the quarter width stays unless another one is clearly cheaper.
+            if (ctx->overlap_nlayers > 1 && batch >= 4) {
+                auto cost = [&](int w) {
+                    const long long ctas = (long long)ctx->overlap_nlayers * units * w;
+                    const long long waves = (ctas + ctx->sm_count - 1) / ctx->sm_count;
+                    return waves * ((slots + w - 1) / w + 6);
+                };
+                int best = want;
+                for (int w = want + 1; w <= full; w++)
+                    if ((slots + w - 1) / w >= 8 && cost(w) * 100 < cost(best) * 95) best = w;
+                want = best;
+            }
+        }
     }
     want = std::min(want, kDecGroup * kDecMaxGroups);
     if (batch > ctx->dec_scr.group_tokens) want = std::min(want, kDecMaxLastCtaSplits);  // no second-level scratch for that many tokens
@@ -1651,6 +1670,7 @@ extern "C" fm_status fm_attn_decode_layers(FmCtx *ctx, int first_layer, int n_la
     // (layers whose outputs would alias are kept in full stream order)
     const bool distinct = layer_stride_out >= (size_t)std::max(batch, 0) * ctx->cfg.num_attn_heads * ctx->cfg.head_dim;
     ctx->overlap_layers = !ctx->prof_on && n_layers > 1 && distinct;
+    ctx->overlap_nlayers = n_layers;
     for (int l = 0; l < n_layers; l++) {
         ctx->overlap_prev = l > 0 && ctx->overlap_layers;
         ctx->overlap_merge = !ctx->prof_on;

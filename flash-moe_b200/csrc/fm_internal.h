@@ -180,6 +180,7 @@ struct FmCtx {
     // set by fm_attn_decode_layers between layers: the next decode launch may start while the previous
     // layer's kernel drains (different layers touch different pages, inputs and outputs)
     bool overlap_prev = false, overlap_merge = false, overlap_layers = false;
+    int overlap_nlayers = 0;  // layers of the fm_attn_decode_layers call in progress (valid while overlap_layers)
     std::vector<cudaEvent_t> prof_ev;  // pairs (start, stop)
     size_t prof_used = 0;
 
