@@ -1538,12 +1538,11 @@ static bool is_pinned(const void *p) {
     return a.type == cudaMemoryTypeHost;
 }
 
-// Host-pointer form.  The layers' inputs go to the device in two groups (layer 0 | the rest) on a copy stream, each
-// group's launches waiting for its event only, so that all but the first small copy run under layer 0's kernel; the
-// outputs come back in two as well (all but the last layer | the last), so that only the last layer's rows are copied
-// after the last kernel.  Every cut costs the overlap between two layers' launches, and a run of a few layers between
-// two cuts would be launched narrow with too few neighbours to fill the machine (measured: a middle group of two
-// layers cost 0.3 ms per step at 96 us per layer), hence a single long middle run.  Page-locked caller buffers are copied directly;
+// Host-pointer form.  The layers' inputs go to the device in two groups (the first three layers | the rest) on a copy
+// stream, each group's launches waiting for its event only, so that all but the first small copy run under the first
+// layers' kernels; the outputs come back in two as well (all but the last layer | the last), so that only the last
+// layer's rows are copied after the last kernel.  Every cut costs the overlap between two layers' launches, hence so
+// few; the launches of a run between two cuts pick their width for that run's number of layers (pick_splits).  Page-locked caller buffers are copied directly;
 // pageable ones pass through the context's own page-locked staging area.
 static fm_status decode_layers_host(FmCtx *ctx, int first_layer, int n_layers, const int *seq, const int *pos, int batch,
                                     const float *q_proj_out, size_t sq, const float *k, const float *v, size_t skv,
@@ -1590,7 +1589,8 @@ static fm_status decode_layers_host(FmCtx *ctx, int first_layer, int n_layers, c
     if (qnw) memcpy(hs + o_w, qnw, (size_t)c.head_dim * 2);
     if (knw) memcpy(hs + o_w + 512, knw, (size_t)c.head_dim * 2);
     if (qnw || knw) FM_CUDA(ctx, cudaMemcpyAsync(ds + o_w, hs + o_w, 1024, cudaMemcpyHostToDevice, cs));
-    const size_t in_end[3] = {std::min<size_t>(1, nl), std::min<size_t>(1, nl), nl};
+    const size_t first = 3;  // layers whose inputs go first: their kernels cover the copy of the rest
+    const size_t in_end[3] = {std::min(first, nl), std::min(first, nl), nl};
     const size_t out_end[3] = {0, nl > 1 ? nl - 1 : 0, nl};
     for (int g = 0; g < 3; g++) {
         const size_t a = g ? in_end[g - 1] : 0, b = in_end[g];
