@@ -503,6 +503,8 @@ def extra_measurements(pkg, torch, dev, peak, only=None):
         res.update(_probe_gdn_prefill(pkg, torch, dev, gen))
     if want("out_proj"):
         res.update(_probe_out_proj(pkg, torch, dev, peak))
+    if want("kv_policies"):
+        res.update(_probe_kv_policies(pkg, torch, dev, peak, gen))
     if want("hybrid"):
         res.update(_probe_hybrid(pkg, torch, dev, peak, gen))
     return res
@@ -572,6 +574,56 @@ def _probe_out_proj(pkg, torch, dev, peak):
         ctx.proj_free(d)
     ctx.close()
     return res
+
+
+def _probe_kv_policies(pkg, torch, dev, peak, gen):
+    """The decode step under the reference's cache policies, batch 8, 32768 rows attended, 8 layers cycled (the bf16 store
+    is 4.3 GB per pass: far more than L2), one fm_attn_decode call per layer: the bf16 store as the yardstick, the FP8
+    store, a sliding window of 32768 rows (circular store, already wrapped), and H2O eviction with a budget of 32768
+    rows (every step evicts; the figure includes the mass / eviction launch)."""
+    res = {}
+    B, L, NL = 8, 32768, 8
+    K = torch.randn((L, HKV * D), device=dev, generator=gen).bfloat16().float()
+    qp = torch.randn((NL, B, H * 2 * D), device=dev, generator=gen)
+    kn = torch.randn((NL, B, HKV * D), device=dev, generator=gen)
+    out = torch.empty((NL, B, H * D), device=dev)
+    seq_arr = np.arange(B, dtype=np.int32)
+    pos_arr = np.zeros(B, dtype=np.int32)
+    variants = (("bf16", {}, 2048), ("fp8", {"kv_dtype": pkg.binding.FM_KV_FP8_E4M3}, 1032),
+                ("sliding_window", {"sliding_window": L}, 2048), ("h2o", {"h2o_budget": L, "h2o_num_sinks": 4}, 2048))
+    for name, extra_cfg, row_bytes in variants:
+        cfg = pkg.default_config(num_full_layers=NL, num_linear_layers=0, max_seqs=B, max_seq_len=L + 256, max_batch_tokens=64, **extra_cfg)
+        ctx = pkg.Context(cfg)
+        ctx.set_stream(torch.cuda.current_stream().cuda_stream)
+        for layer in range(NL):
+            for s_ in range(B):
+                ctx.kv_import(layer, s_, K, K, L - 1 if name == "h2o" else L)
+        calls = [ctx.prepared("fm_attn_decode", l, seq_arr, pos_arr, B, qp[l], None, None, kn[l], kn[l], None, None, out[l]) for l in range(NL)]
+        pos = L
+        launches0 = ctx.launch_count()
+
+        def token():
+            pos_arr[:] = pos
+            for f in calls:
+                f()
+        for _ in range(3):
+            token(); pos += 1
+        torch.cuda.synchronize()
+        reps = PROBE_REPS or 10
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            token(); pos += 1
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / (reps * NL)
+        rows_bytes = B * L * row_bytes
+        res[name] = {"us_per_layer": us, "kv_gbps": rows_bytes / us / 1e3, "frac_of_peak": rows_bytes / us / 1e3 / peak,
+                     "launches_per_layer": (ctx.launch_count() - launches0) / ((reps + 3) * NL)}
+        ctx.close()
+        del ctx
+        torch.cuda.empty_cache()
+    return {"decode_b8_32k_cache_policies": res}
 
 
 def _probe_hybrid(pkg, torch, dev, peak, gen):
@@ -897,7 +949,7 @@ def main():
     ap.add_argument("--kv", default="bf16", choices=["bf16", "fp8"], help="element type of the KV store")
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"],
                     help="how sequence shards exchange partial results: the library's peer-memory kernels, or NCCL all-gathers")
-    ap.add_argument("--probe", default=None, choices=["sweep", "prefill", "gdn_decode", "gdn_prefill", "hybrid", "out_proj"],
+    ap.add_argument("--probe", default=None, choices=["sweep", "prefill", "gdn_decode", "gdn_prefill", "hybrid", "out_proj", "kv_policies"],
                     help="run only one of the extra measurements and print it (for profiling one kernel)")
     args = ap.parse_args()
     set_kv_dtype(args.kv)

@@ -134,7 +134,7 @@ struct DecodeFused {
     unsigned int *group_counters;  // [tokens*Hkv][kDecMaxGroups] arrivals per group of splits (many splits only)
     float *group_o, *group_ml;     // [tokens][H][kDecMaxGroups][D] / [..][2]: the groups' merged partials
     int *err;                // tail 4: device error word (a peer never published)
-    const int *h2o_slot;     // H2O store: [seqs] the physical row the new token takes (overrides the token list's row)
+    H2oStep h2o;             // H2O store (slot != null): where the new row goes, and where the step's softmax weights are left
 };
 
 // kFp8: the store holds E4M3 bytes with one scale per row (fm_fp8.cuh).  The bytes go through the MMAs as fp16
@@ -165,7 +165,7 @@ __device__ __forceinline__ void attn_decode_body(const KvView &kv, const RopePar
 
     int seq, pos, row_new;
     tok_get(toks, tok, seq, pos, row_new);
-    if (kFused && f.h2o_slot != nullptr) row_new = f.h2o_slot[seq];
+    if (kFused && f.h2o.slot != nullptr) row_new = f.h2o.slot[seq];
     const int L = tok_rows(toks, tok);  // rows attended, the new one included (row_new + 1 unless the window wrapped)
 
     // ---- which page slots this CTA walks ----
@@ -508,6 +508,24 @@ __device__ __forceinline__ void attn_decode_body(const KvView &kv, const RopePar
         }
         l_sum[0] += p[0][0] + p[0][1] + p[1][0] + p[1][1];
         l_sum[1] += p[0][2] + p[0][3] + p[1][2] + p[1][3];
+        if (kFused && f.h2o.w != nullptr && hs == 0) {
+            // H2O: the un-normalised weights of this slice's 16 rows x 16 heads, and the maximum they refer to; the mass
+            // pass turns them into softmax weights once the step's final (max, sum) of every head is known
+            const int g = lane >> 2, tq = lane & 3;
+            const size_t rstride = (size_t)kv.Hkv * 16;
+            float *wr = f.h2o.w + (((size_t)tok * f.h2o.rows_pad + p0) * kv.Hkv + kvh) * 16 + g;
+#pragma unroll
+            for (int nt = 0; nt < 2; nt++) {
+                float *w0 = wr + (size_t)(nt * 8 + 2 * tq) * rstride;
+                w0[0] = p[nt][0]; w0[rstride] = p[nt][1];
+                w0[8] = p[nt][2]; w0[rstride + 8] = p[nt][3];
+            }
+            if (tq == 0) {
+                float *mr = f.h2o.mref + ((((size_t)tok * f.h2o.tiles + gpage) * kv.Hkv + kvh) * 4 + pw) * 16;
+                mr[g] = m_ref[0];
+                mr[g + 8] = m_ref[1];
+            }
+        }
         if (!kFp8) {
             // weights as two bf16 terms; O += P V on this warp's output dims
             uint32_t ph[4], pl[4];
@@ -876,7 +894,7 @@ int launch_attn_decode_fused(const KvView &kv, const RopeParams &rope, const Tok
                              float *part_o, float *part_ml, int nsplits, const float *k_new, const float *v_new,
                              const uint16_t *k_norm_w, int tail, const float *gate, float *out, float *ml_out,
                              const XchgView *x, uint32_t step, const DecodeScratch &scr, int *err, bool overlap_prev,
-                             cudaStream_t st, const int *h2o_slot) {
+                             cudaStream_t st, const H2oStep *h2o) {
     if (!(kv.fp8 ? configure_decode<true, true>() : configure_decode<true, false>())) return -1;
     if (tail != 0 && nsplits > kDecMaxLastCtaSplits && (toks.n > scr.group_tokens || nsplits > kDecGroup * kDecMaxGroups)) return -1;
     if (kv.fp8 && k_new != nullptr && kv.Hkv > 8) return -1;
@@ -891,7 +909,7 @@ int launch_attn_decode_fused(const KvView &kv, const RopeParams &rope, const Tok
     f.group_o = scr.group_o;
     f.group_ml = scr.group_ml;
     f.err = err;
-    f.h2o_slot = h2o_slot;
+    if (h2o) f.h2o = *h2o;
     // overlap_prev: the caller vouches that this launch reads nothing the previous kernel in the
     // stream writes except through the scratch the kernel guards itself (another layer's step).
     // Its CTAs then take SMs as the previous grid's CTAs retire instead of after the grid drains.

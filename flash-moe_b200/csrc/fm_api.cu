@@ -108,8 +108,8 @@ extern "C" fm_status fm_create(const FmConfig *cfg, FmCtx **out) {
             return fail(nullptr, FM_ERR_INVALID, "fm_create: h2o_budget %d / h2o_num_sinks %d", c.h2o_budget, c.h2o_num_sinks);
         if (c.h2o_budget > 0 && c.seq_shard_count != 1)
             return fail(nullptr, FM_ERR_UNSUPPORTED, "fm_create: H2O eviction needs the whole sequence on one context (seq_shard_count=1)");
-        if (c.h2o_budget > 0 && (size_t)c.num_attn_heads * c.head_dim * sizeof(float) > 96 * 1024)
-            return fail(nullptr, FM_ERR_UNSUPPORTED, "fm_create: H2O eviction takes at most 96 query heads per context (%d)", c.num_attn_heads);
+        if (c.h2o_budget > 0 && c.num_kv_heads > 8)
+            return fail(nullptr, FM_ERR_UNSUPPORTED, "fm_create: H2O eviction takes at most 8 KV heads per context (%d)", c.num_kv_heads);
         if (c.kv_dtype == FM_KV_FP8_E4M3 && c.num_kv_heads > 8)
             return fail(nullptr, FM_ERR_UNSUPPORTED, "fm_create: an FP8 store takes at most 8 KV heads per context (%d)", c.num_kv_heads);
     }
@@ -209,6 +209,13 @@ extern "C" fm_status fm_create(const FmConfig *cfg, FmCtx **out) {
             CREATE_CUDA(cudaMalloc(&ctx->d_h2o_slot, ns * sizeof(int)));
             CREATE_CUDA(cudaMalloc(&ctx->d_h2o_counter, ns * sizeof(unsigned int)));
             CREATE_CUDA(cudaMalloc(&ctx->d_h2o_ml, (size_t)kMaxList * c.num_attn_heads * 2 * sizeof(float)));
+            // the decode launch's per-(row, head) weights of one step, consumed by the mass pass right after it
+            const size_t ntok = (size_t)std::min(kMaxList, std::max(1, c.max_batch_tokens));
+            ctx->h2o_tiles = (ctx->h2o_cap + c.page_size - 1) / c.page_size;
+            ctx->h2o_rows_pad = ctx->h2o_tiles * c.page_size;
+            CREATE_CUDA(cudaMalloc(&ctx->d_h2o_w, ntok * ctx->h2o_rows_pad * c.num_kv_heads * 16 * sizeof(float)));
+            CREATE_CUDA(cudaMalloc(&ctx->d_h2o_mref, ntok * ctx->h2o_tiles * c.num_kv_heads * 64 * sizeof(float)));
+            CREATE_CUDA(cudaMalloc(&ctx->d_h2o_cand, ntok * ctx->h2o_tiles * 4 * sizeof(float)));
             CREATE_CUDA(cudaMemset(ctx->d_h2o_accum, 0, ne * sizeof(float)));
             CREATE_CUDA(cudaMemset(ctx->d_h2o_order, 0, ne * sizeof(int)));
             CREATE_CUDA(cudaMemset(ctx->d_h2o_tokpos, 0, ne * sizeof(int)));
@@ -261,7 +268,7 @@ extern "C" void fm_destroy(FmCtx *ctx) {
     cudaFree(ctx->d_part_o); cudaFree(ctx->d_part_ml); cudaFree(ctx->d_dec_counters); cudaFree(ctx->d_xchg_counter); cudaFree(ctx->d_pf_q16); cudaFree(ctx->d_pf_k16); cudaFree(ctx->d_pf_v16); cudaFree(ctx->d_err);
     if (ctx->h_err) cudaFreeHost(ctx->h_err); cudaFree(ctx->d_work);
     cudaFree(ctx->d_h2o_accum); cudaFree(ctx->d_h2o_order); cudaFree(ctx->d_h2o_tokpos); cudaFree(ctx->d_h2o_slot);
-    cudaFree(ctx->d_h2o_counter); cudaFree(ctx->d_h2o_ml);
+    cudaFree(ctx->d_h2o_counter); cudaFree(ctx->d_h2o_ml); cudaFree(ctx->d_h2o_w); cudaFree(ctx->d_h2o_mref); cudaFree(ctx->d_h2o_cand);
     cudaFree(ctx->d_proj_ssq);
     cudaFree(ctx->d_gdn_scratch);
     cudaFree(ctx->d_stage);
@@ -773,10 +780,11 @@ static fm_status decode_core(FmCtx *ctx, int fa_idx, const int *seq, const int *
         const LayerScratch ls = layer_scratch(ctx, fa_idx);
         const bool wide = ns > kDecMaxLastCtaSplits;
         const H2oView hv = h2o ? h2o_view(ctx, fa_idx) : H2oView{};
+        const H2oStep hstep = {hv.slot, ctx->d_h2o_w, ctx->d_h2o_mref, ctx->h2o_rows_pad, ctx->h2o_tiles};
         fm_status st = launched(ctx, launch_attn_decode_fused(kv, ctx->rope, t, H, qp, qq, qnw, c.rms_norm_eps, ls.part_o, ls.part_ml, ns,
                                                               k ? k + i0 * kvd : nullptr, v ? v + i0 * kvd : nullptr, knw, wide ? 0 : (out ? 1 : 2),
                                                               gp, op, h2o ? ctx->d_h2o_ml : mlp, nullptr, 0, ls.scr, ctx->d_err,
-                                                              ctx->overlap_prev && i0 == 0 && !sg_host(ctx), ctx->stream, h2o ? hv.slot : nullptr),
+                                                              ctx->overlap_prev && i0 == 0 && !sg_host(ctx), ctx->stream, h2o ? &hstep : nullptr),
                                 "attn_decode");
         if (st) return st;
         if (wide) {
@@ -787,8 +795,8 @@ static fm_status decode_core(FmCtx *ctx, int fa_idx, const int *seq, const int *
         if (h2o) {
             // the step's attention mass per cache row, and the eviction if the budget is exceeded (attn_h2o.cu)
             const int recent = (c.h2o_budget - c.h2o_num_sinks) / 4;  // kv_cache_new(), metal_infer/layer_forward.h:203
-            st = launched(ctx, launch_h2o_mass(kv, ctx->rope, t, tok_index.data() + i0, hv, c.h2o_budget, c.h2o_num_sinks, recent, H, qp, qq, qnw,
-                                               c.rms_norm_eps, ctx->d_h2o_ml, max_len, ctx->stream), "h2o_mass");
+            st = launched(ctx, launch_h2o_mass(t, tok_index.data() + i0, hv, c.h2o_budget, c.h2o_num_sinks, recent, H, c.num_kv_heads, ctx->d_h2o_ml,
+                                               hstep, ctx->d_h2o_cand, max_len, ctx->stream), "h2o_mass");
             if (st) return st;
         }
     }
@@ -1136,6 +1144,13 @@ static fm_status kv_export_check(FmCtx *ctx, const char *fn, int fa_idx, int seq
     return FM_OK;
 }
 
+// The cache order of an H2O store is rebuilt from the token positions when something is exported (attn_h2o.cu).
+static fm_status h2o_refresh_order(FmCtx *ctx, int fa_idx, int seq) {
+    if (ctx->cfg.h2o_budget <= 0) return FM_OK;
+    return launched(ctx, launch_h2o_order(h2o_view(ctx, fa_idx), seq, rows_held(ctx->cfg, ctx->kv_len[lidx(ctx, fa_idx, seq)]), ctx->stream),
+                    "h2o_order");
+}
+
 extern "C" fm_status fm_kv_export(FmCtx *ctx, int fa_idx, int seq, float *k, float *v, int max_rows, int *len_out) {
     if (!ctx) return FM_ERR_INVALID;
     const FmConfig &c = ctx->cfg;
@@ -1146,6 +1161,7 @@ extern "C" fm_status fm_kv_export(FmCtx *ctx, int fa_idx, int seq, float *k, flo
     const size_t kvd = (size_t)c.num_kv_heads * c.head_dim;
     const KvView kv = kv_view(ctx, fa_idx);
     const int *order = c.h2o_budget > 0 ? h2o_view(ctx, fa_idx).order + (size_t)seq * ctx->h2o_cap : nullptr;  // cache order of an H2O store
+    if ((st = h2o_refresh_order(ctx, fa_idx, seq)) != FM_OK) return st;
     if (ctx->ptr_mode == FM_PTR_DEVICE)
         return launched(ctx, launch_kv_export(kv, seq, 0, len, k, v, order, ctx->stream), "kv_export");
     return staged_rows(ctx, len, kvd * 4, false, [&](int row0, int n, size_t o_v, size_t, size_t) -> fm_status {
@@ -1231,6 +1247,7 @@ extern "C" fm_status fm_kv_export_fp8(FmCtx *ctx, int fa_idx, int seq, uint8_t *
     const size_t kvd = (size_t)c.num_kv_heads * c.head_dim;
     const KvView kv = kv_view(ctx, fa_idx);
     const int *order = c.h2o_budget > 0 ? h2o_view(ctx, fa_idx).order + (size_t)seq * ctx->h2o_cap : nullptr;
+    if ((st = h2o_refresh_order(ctx, fa_idx, seq)) != FM_OK) return st;
     if (ctx->ptr_mode == FM_PTR_DEVICE)
         return launched(ctx, launch_kv_copy_fp8(kv, seq, 0, len, k8, v8, k_scales, v_scales, false, order, ctx->stream), "kv_export_fp8");
     return staged_rows(ctx, len, kvd, true, [&](int row0, int n, size_t o_v, size_t o_ks, size_t o_vs) -> fm_status {
@@ -1293,6 +1310,10 @@ extern "C" fm_status fm_h2o_export(FmCtx *ctx, int fa_idx, int seq, float *accum
     if (n == 0) return FM_OK;
     FM_CUDA(ctx, cudaSetDevice(c.device));
     const H2oView h = h2o_view(ctx, fa_idx);
+    {
+        const fm_status so = h2o_refresh_order(ctx, fa_idx, seq);
+        if (so) return so;
+    }
     if (ctx->ptr_mode == FM_PTR_DEVICE) return launched(ctx, launch_h2o_gather(h, seq, n, accum, token_positions, ctx->stream), "h2o_gather");
     if ((size_t)n * 8 + 512 > ctx->stage_bytes) return fail(ctx, FM_ERR_INVALID, "fm_h2o_export: staging buffer too small");
     float *da = reinterpret_cast<float *>(ctx->d_stage);

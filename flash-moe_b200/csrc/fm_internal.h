@@ -95,6 +95,16 @@ struct H2oView {
     int cap;
 };
 
+// What the decode launch of an H2O store needs besides the attention itself: where the step's row goes, and where
+// to leave the un-normalised softmax weights of every (row, head) for the mass pass (attn_h2o.cu).
+struct H2oStep {
+    const int *slot;   // [seqs] physical row the new token takes
+    float *w;          // [tokens][rows_pad][Hkv][16] weights exp2(score - mref) of the step's rows
+    float *mref;       // [tokens][tiles][Hkv][4][16] the maximum those weights refer to, per 16-row slice of a 64-row tile
+    int rows_pad;      // rows per token in `w` (the capacity rounded up to whole tiles)
+    int tiles;         // tiles per token in `mref`
+};
+
 struct RopeParams {
     float inv_freq[64];  // rotary_dim / 2 entries, computed on the host exactly as the reference does
     int rotary_dim;
@@ -191,6 +201,8 @@ struct FmCtx {
     // staging of all layers of one fm_attn_decode_layers call in host-pointer mode (grown on demand)
     char *h_lstage = nullptr, *d_lstage = nullptr;
     size_t lstage_bytes = 0;
+    float *d_h2o_w = nullptr, *d_h2o_mref = nullptr, *d_h2o_cand = nullptr;  // the decode launch's weights for the H2O mass pass (H2oStep)
+    int h2o_rows_pad = 0, h2o_tiles = 0;
     float *d_gdn_scratch = nullptr;  // per-token records of the streaming GatedDeltaNet step (kMaxList tokens)
     // host-pointer form of the layered decode: copies run on a stream of their own, tied to the launches by events
     cudaStream_t copy_stream = nullptr;
@@ -212,7 +224,7 @@ int launch_attn_decode_fused(const KvView &kv, const RopeParams &rope, const Tok
                              float *part_o, float *part_ml, int nsplits, const float *k_new, const float *v_new,
                              const uint16_t *k_norm_w, int tail, const float *gate, float *out, float *ml_out,
                              const XchgView *x, uint32_t step, const DecodeScratch &scr, int *err, bool overlap_prev,
-                             cudaStream_t st, const int *h2o_slot = nullptr);
+                             cudaStream_t st, const H2oStep *h2o = nullptr);
 constexpr int kDecMaxLastCtaSplits = 24;  // more splits per (KV head, sequence): merged in two levels
 
 // merges [nparts] partials per (token, head) laid out with strides, applies the gate
@@ -241,9 +253,9 @@ int launch_kv_import(const KvView &kv, int seq, int row0, int n, const float *k,
 int launch_kv_copy_fp8(const KvView &kv, int seq, int row0, int n, uint8_t *k, uint8_t *v, float *ks, float *vs, bool import,
                        const int *order, cudaStream_t st);
 
-int launch_h2o_mass(const KvView &kv, const RopeParams &rope, const TokSpec &toks, const int *token_index, const H2oView &h, int budget, int sinks,
-                    int recent, int H, const float *q_proj_out, const float *q, const uint16_t *q_norm_w, float eps, const float *ml, int max_rows,
-                    cudaStream_t st);
+int launch_h2o_mass(const TokSpec &toks, const int *token_index, const H2oView &h, int budget, int sinks, int recent, int H, int Hkv,
+                    const float *ml, const H2oStep &step, float *cand, int max_rows, cudaStream_t st);
+int launch_h2o_order(const H2oView &h, int seq, int n, cudaStream_t st);  // rebuilds h.order for rows [0, n) of a sequence
 int launch_h2o_gather(const H2oView &h, int seq, int n, float *accum_out, int *tokpos_out, cudaStream_t st);
 int launch_h2o_init(const H2oView &h, int seq, int n, cudaStream_t st);
 

@@ -13,9 +13,13 @@ H, HKV, D = 32, 2, 256
 
 
 @pytest.mark.parametrize("lens,layers,steps,host", [((3000, 1200, 4500), 6, 4, False), ((64,), 3, 3, False),
-                                                    ((20000,), 4, 2, False), ((700, 2100), 5, 3, True)])
+                                                    ((20000,), 4, 2, False), ((700, 2100), 5, 3, True),
+                                                    ((700, 2100), 5, 2, "pinned"), ((900,), 1, 2, "pinned"),
+                                                    ((900, 100), 2, 2, True), ((300,), 9, 2, "pinned")])
 def test_layers_call_matches_layer_by_layer_checker(pkg, port, synth, lens, layers, steps, host):
-    """host=True: the same call with pageable host arrays (inputs of all layers staged in one batch)."""
+    """host=True: the same call with pageable host arrays (staged through the library's page-locked buffer);
+    host="pinned": page-locked caller arrays, copied directly.  Either way the copies run on the library's copy stream
+    in groups (first layers | rest; all but the last layer's outputs | last), whatever the number of layers."""
     import torch
     dev = torch.device("cuda:0")
     B = len(lens)
@@ -45,6 +49,10 @@ def test_layers_call_matches_layer_by_layer_checker(pkg, port, synth, lens, laye
         if host:
             c.set_pointer_mode(pkg.binding.FM_PTR_HOST)
             out = np.empty((layers, B, H * D), np.float32)
+            if host == "pinned":
+                pin = lambda a: torch.empty(a.shape, dtype=torch.float32, pin_memory=True).copy_(torch.from_numpy(a)).numpy()
+                qp, kk, vv = pin(qp), pin(kk), pin(vv)
+                out = torch.empty((layers, B, H * D), dtype=torch.float32, pin_memory=True).numpy()
             c.attn_decode_layers(0, layers, list(range(B)), [L + st for L in lens], out, qp, kk, vv, sq, skv, so)
             c.set_pointer_mode(pkg.binding.FM_PTR_DEVICE)
         else:
