@@ -819,6 +819,19 @@ def _probe_gdn_decode(pkg, torch, dev, peak, gen):
         e1.record()
         torch.cuda.synchronize()
         us_host = e0.elapsed_time(e1) * 1e3 / (reps * NL)
+        # host-launched once more with fm_set_layer_overlap (consecutive calls step different layers: a step may be
+        # launched under the previous one's tail)
+        ctx.set_layer_overlap(True)
+        for _ in range(3):
+            gdn_pass()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(reps):
+            gdn_pass()
+        e1.record()
+        torch.cuda.synchronize()
+        us_host_overlap = e0.elapsed_time(e1) * 1e3 / (reps * NL)
+        ctx.set_layer_overlap(False)
         # the same pass as one CUDA graph (how a serving loop would issue it): at batch 1 a launch per host call is
         # bounded by the host's call rate, not by the kernel
         us = us_host
@@ -844,7 +857,8 @@ def _probe_gdn_decode(pkg, torch, dev, peak, gen):
             ctx.set_stream(torch.cuda.current_stream().cuda_stream)
         # per sequence: state read + written, conv ring rows, inputs and output; weights once per launch
         gdn_bytes = B * (2 * 4194304 + 2 * 147456 + (12288 + 8192 + 128 + 8192) * 4) + 98304 + 768
-        res[f"gdn_decode_b{B}"] = {"us_per_layer": us, "us_per_layer_host_launched": us_host, "state_gbps": gdn_bytes / us / 1e3,
+        res[f"gdn_decode_b{B}"] = {"us_per_layer": us, "us_per_layer_host_launched": us_host,
+                                   "us_per_layer_host_launched_layer_overlap": us_host_overlap, "state_gbps": gdn_bytes / us / 1e3,
                                    "frac_of_peak": gdn_bytes / us / 1e3 / peak, "algorithmic_bytes_per_layer": gdn_bytes,
                                    "layers_cycled": NL, "issued_as": graph_note or "one CUDA graph of the layers' launches"}
         ctx.close()

@@ -19,7 +19,7 @@ FM_KV_BF16, FM_KV_FP8_E4M3 = 0, 1
 
 EXPORTS = [
     "fm_default_config", "fm_create", "fm_destroy", "fm_last_error", "fm_set_stream",
-    "fm_set_pointer_mode", "fm_synchronize", "fm_reset", "fm_seq_fork", "fm_kv_free_pages", "fm_kv_len", "fm_kv_append_rope",
+    "fm_set_pointer_mode", "fm_set_layer_overlap", "fm_synchronize", "fm_reset", "fm_seq_fork", "fm_kv_free_pages", "fm_kv_len", "fm_kv_append_rope",
     "fm_attn_decode", "fm_attn_decode_partial", "fm_attn_merge_gate", "fm_attn_prefill",
     "fm_gdn_decode", "fm_gdn_prefill", "fm_kv_export", "fm_kv_import", "fm_state_export",
     "fm_state_import", "fm_launch_count", "fm_profile_enable", "fm_profile_read",
@@ -151,6 +151,9 @@ class Context:
 
     def set_stream(self, stream_ptr: int):
         self._check(self.lib.fm_set_stream(self.h, C.c_void_p(stream_ptr)))
+
+    def set_layer_overlap(self, on: bool):
+        self._check(self.lib.fm_set_layer_overlap(self.h, C.c_int(1 if on else 0)))
 
     def set_pointer_mode(self, mode: int):
         self._check(self.lib.fm_set_pointer_mode(self.h, C.c_int(mode)))

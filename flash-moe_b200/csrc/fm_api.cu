@@ -315,6 +315,11 @@ extern "C" fm_status fm_synchronize(FmCtx *ctx) {
     FM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     return check_device_error(ctx);
 }
+extern "C" fm_status fm_set_layer_overlap(FmCtx *ctx, int on) {
+    if (!ctx) return FM_ERR_INVALID;
+    ctx->layer_overlap = on != 0;
+    return FM_OK;
+}
 extern "C" int64_t fm_launch_count(const FmCtx *ctx) { return ctx ? ctx->launches : 0; }
 
 // ---- event bracketing of the dominant kernels --------------------------------------------------
@@ -1068,7 +1073,8 @@ extern "C" fm_status fm_gdn_decode(FmCtx *ctx, int li, const int *seq, int batch
                                                         ctx->d_gdn_scratch, ctx->sm_count, ctx->d_err, ctx->stream), "gdn_decode_stream");
         else
             st = launched(ctx, launch_gdn_decode(g, t, conv_l, ssm_l, (long long)cn, (long long)sn, d_qkv + (size_t)i0 * ctx->conv_dim, d_z + i0 * vd,
-                                                 d_b + i0 * hv, d_a + i0 * hv, d_cw, d_al, d_db, d_nw, d_out + i0 * vd, ctx->stream), "gdn_decode");
+                                                 d_b + i0 * hv, d_a + i0 * hv, d_cw, d_al, d_db, d_nw, d_out + i0 * vd, ctx->layer_overlap && !sg.host,
+                                                 ctx->stream), "gdn_decode");
         if (st) return st;
         for (int i = 0; i < t.n; i++) ctx->gdn_steps[lidx(ctx, li, seq[i0 + i])]++;  // only once the step is queued
     }

@@ -190,7 +190,8 @@ struct FmCtx {
     // set by fm_attn_decode_layers between layers: the next decode launch may start while the previous
     // layer's kernel drains (different layers touch different pages, inputs and outputs)
     bool overlap_prev = false, overlap_merge = false, overlap_layers = false;
-    int overlap_nlayers = 0;  // layers of the fm_attn_decode_layers call in progress (valid while overlap_layers)
+    int overlap_nlayers = 0;
+    bool layer_overlap = false;  // fm_set_layer_overlap: consecutive decode calls touch different layers' state  // layers of the fm_attn_decode_layers call in progress (valid while overlap_layers)
     std::vector<cudaEvent_t> prof_ev;  // pairs (start, stop)
     size_t prof_used = 0;
 
@@ -283,7 +284,7 @@ int launch_gdn_decode(const GdnDims &g, const TokSpec &toks, float *conv_state, 
                       long long conv_seq_stride, long long ssm_seq_stride, const float *qkv,
                       const float *z, const float *beta, const float *alpha, const uint16_t *conv_w,
                       const float *A_log, const uint16_t *dt_bias, const uint16_t *norm_w, float *out,
-                      cudaStream_t st);
+                      bool overlap_prev, cudaStream_t st);
 // The same step as a prep launch + a persistent launch that streams the states (for many (head, sequence) pairs);
 // `scratch` holds gdn_decode_scratch_bytes(g, toks.n) bytes, z must be 16-byte aligned.  Returns the launches made.
 size_t gdn_decode_scratch_bytes(const GdnDims &g, int tokens);

@@ -65,6 +65,11 @@ gdn_decode_kernel(GdnDims g, TokSpec toks, float *__restrict__ conv_ring, float 
     int seq, step, unused;
     tok_get(toks, tok, seq, step, unused);
 
+    // Launched as a programmatic dependent (the caller vouched that the previous launch in the stream does not touch
+    // this layer's state, fm_set_layer_overlap): the next such launch may start, and this one requests its state before
+    // it waits for the previous launch -- whose results its other inputs may be -- to complete.  Without the launch
+    // attribute both instructions do nothing.
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     // ---- start the state loads first: they are the long pole ----
     float *S0 = ssm + (size_t)seq * ssm_seq_stride + ((size_t)vh * kDv + slice * kRows) * kDk;
     float4 st[kRowsPerWarp];
@@ -72,6 +77,7 @@ gdn_decode_kernel(GdnDims g, TokSpec toks, float *__restrict__ conv_ring, float 
     for (int i = 0; i < kRowsPerWarp; i++)
         st[i] = *reinterpret_cast<const float4 *>(S0 + (size_t)(warp * kRowsPerWarp + i) * kDk + lane * 4);
 
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
     // first phase of the cluster barrier: arrive now, wait just before the first write into a peer's shared memory
     // (which is only legal once that peer has started); by then everyone has long arrived
     if (S > 1) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
@@ -200,19 +206,21 @@ static int launch_gdn_decode_s(const GdnDims &g, const TokSpec &toks, float *con
                                long long conv_seq_stride, long long ssm_seq_stride, const float *qkv,
                                const float *z, const float *beta, const float *alpha,
                                const uint16_t *conv_w, const float *A_log, const uint16_t *dt_bias,
-                               const uint16_t *norm_w, float *out, cudaStream_t st) {
+                               const uint16_t *norm_w, float *out, bool overlap_prev, cudaStream_t st) {
     cudaLaunchConfig_t lc = {};
     lc.gridDim = dim3(S, g.Hv, toks.n);
     lc.blockDim = dim3(32 * W);
     lc.dynamicSmemBytes = 0;
     lc.stream = st;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = S;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     lc.attrs = attr;
-    lc.numAttrs = 1;
+    lc.numAttrs = overlap_prev ? 2 : 1;
     cudaError_t e = cudaLaunchKernelEx(&lc, gdn_decode_kernel<S, W>, g, toks, conv_state, ssm_state,
                                        conv_seq_stride, ssm_seq_stride, qkv, z, beta, alpha, conv_w,
                                        A_log, dt_bias, norm_w, out);
@@ -223,18 +231,18 @@ int launch_gdn_decode(const GdnDims &g, const TokSpec &toks, float *conv_state, 
                       long long conv_seq_stride, long long ssm_seq_stride, const float *qkv,
                       const float *z, const float *beta, const float *alpha, const uint16_t *conv_w,
                       const float *A_log, const uint16_t *dt_bias, const uint16_t *norm_w, float *out,
-                      cudaStream_t st) {
+                      bool overlap_prev, cudaStream_t st) {
     if (toks.n <= 0) return 0;
     // enough CTAs to cover the machine at small batch, whole heads per CTA at large batch
     const int ctas_whole = g.Hv * toks.n;
     if (ctas_whole >= 512)
         return launch_gdn_decode_s<1, 16>(g, toks, conv_state, ssm_state, conv_seq_stride, ssm_seq_stride, qkv, z,
-                                      beta, alpha, conv_w, A_log, dt_bias, norm_w, out, st);
+                                      beta, alpha, conv_w, A_log, dt_bias, norm_w, out, overlap_prev, st);
     if (ctas_whole >= 256)
         return launch_gdn_decode_s<2, 8>(g, toks, conv_state, ssm_state, conv_seq_stride, ssm_seq_stride, qkv, z,
-                                      beta, alpha, conv_w, A_log, dt_bias, norm_w, out, st);
+                                      beta, alpha, conv_w, A_log, dt_bias, norm_w, out, overlap_prev, st);
     return launch_gdn_decode_s<4, 8>(g, toks, conv_state, ssm_state, conv_seq_stride, ssm_seq_stride, qkv, z,
-                                  beta, alpha, conv_w, A_log, dt_bias, norm_w, out, st);
+                                  beta, alpha, conv_w, A_log, dt_bias, norm_w, out, overlap_prev, st);
 }
 
 }  // namespace fm

@@ -300,6 +300,15 @@ void fm_proj_free(FmCtx *ctx, FmProjWeights *device);
 fm_status fm_out_proj_norm(FmCtx *ctx, const FmProjWeights *w, int n, const float *x, const float *residual,
                            const uint16_t *norm_w, float *h_mid, float *h_post);
 
+/* Off by default.  On: the caller vouches that the launch that precedes a fm_gdn_decode call in the stream does not
+ * touch the state of the layer that call steps (in a model loop it never does: the previous launch belongs to another
+ * layer or to a projection).  The step is then launched as a programmatic dependent of whatever precedes it: it
+ * requests its recurrent state at once and waits for the previous launch to complete before it reads qkv, z, beta,
+ * alpha or writes anything, so its start-up and the state's trip from HBM hide behind the previous kernel's tail.
+ * Device-pointer mode, batches that take the one-launch form (fewer than 512 (head, sequence) pairs).  Two consecutive
+ * steps of the SAME layer must not be issued with this on. */
+fm_status fm_set_layer_overlap(FmCtx *ctx, int on);
+
 /* Number of kernels this context has launched since creation (bench bookkeeping). */
 int64_t fm_launch_count(const FmCtx *ctx);
 

@@ -149,6 +149,47 @@ def test_streamed_states_many_pairs(pkg, port, synth, B, defaults):
     c.close()
 
 
+def test_steps_of_different_layers_may_overlap(pkg, port, synth):
+    """fm_set_layer_overlap: with device pointers, the steps of three layers are issued round-robin, each launch a
+    programmatic dependent of the previous one (it fetches its state before the previous launch has finished and waits
+    for it before touching its inputs).  Every layer's outputs and final state against the checker."""
+    import torch
+    dev = torch.device("cuda:0")
+    layers, n = 3, 6
+    dims = make_dims()
+    cfg = pkg.default_config(num_full_layers=0, num_linear_layers=layers, max_seqs=1, max_batch_tokens=64)
+    c = pkg.Context(cfg)
+    c.set_stream(torch.cuda.current_stream().cuda_stream)
+    c.set_layer_overlap(True)
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a.view(np.int16) if a.dtype == np.uint16 else a)).to(dev)
+    ws = [synth.gdn_weights(20 + l) for l in range(layers)]
+    wd = [{k: t(v) for k, v in w.items()} for w in ws]
+    ins = [synth.gdn_step_inputs(400 + l, n) for l in range(layers)]
+    refs, states = [], []
+    for l in range(layers):
+        conv = np.zeros((3, 12288), np.float32); ssm = synth.gdn_state(400 + l).copy()
+        c.state_import(l, 0, None, t(ssm))
+        refs.append(port.gdn_run(dims, conv, ssm, *ins[l], ws[l]["conv_w"], ws[l]["A_log"], ws[l]["dt_bias"], ws[l]["norm_w"], threads=8))
+        states.append(ssm)
+    dins = [[t(a) for a in ins[l]] for l in range(layers)]
+    outs = [[torch.empty((1, 8192), device=dev) for _ in range(n)] for _ in range(layers)]
+    for st in range(n):
+        for l in range(layers):
+            qkv, z, beta, alpha = (a[st:st + 1] for a in dins[l])
+            c.gdn_decode(l, [0], qkv, z, beta, alpha, outs[l][st], wd[l]["conv_w"], wd[l]["A_log"], wd[l]["dt_bias"], wd[l]["norm_w"])
+    c.synchronize()
+    for l in range(layers):
+        for st in range(n):
+            g, _, _ = rel_errors(outs[l][st].cpu().numpy(), refs[l][st])
+            assert g <= 1e-4, (l, st, g)
+        ssm = torch.empty((64, 128, 128), device=dev)
+        c.state_export(l, 0, None, ssm)
+        c.synchronize()
+        g, _, _ = rel_errors(ssm.cpu().numpy(), states[l])
+        assert g <= 1e-4
+    c.close()
+
+
 def test_reset_and_reference_defaults(pkg, port, synth):
     """NULL A_log / dt_bias / norm weight mean A = 1, bias 0, no output norm, as in the reference;
     fm_reset returns the layer to the zero state."""
