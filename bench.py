@@ -638,6 +638,7 @@ def _probe_hybrid(pkg, torch, dev, peak, gen):
                                  max_batch_tokens=max(B, 64))
         ctx = pkg.Context(cfg)
         ctx.set_stream(torch.cuda.current_stream().cuda_stream)
+        ctx.set_layer_overlap(True)  # consecutive calls step different layers, as in the model
         K = torch.randn((L, HKV * D), device=dev, generator=gen).bfloat16().float()
         for layer in range(15):
             for s in range(B):
