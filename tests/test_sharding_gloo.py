@@ -1,5 +1,6 @@
 """Multi-rank host logic on CPU (gloo, world size 2 and 4): the mesh, page ownership and the
-log-sum-exp merge of per-shard partial results reproduce the single-rank CPU checker."""
+log-sum-exp merge of per-shard partial results reproduce the single-rank CPU checker; GatedDeltaNet layers sliced by
+value head (each rank steps its heads, no exchange) reproduce the whole layer."""
 import os
 import socket
 import sys
@@ -110,3 +111,45 @@ def test_mesh_and_ownership(pkg):
     assert sh.gdn_head_slice(3, 8) == (24, 8, 6, 2)
     with pytest.raises(ValueError):
         sh.mesh_for(3)
+
+
+def _gdn_worker(rank, world, port, steps, out_file):
+    sys.path.insert(0, str(ROOT))
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from __graft_entry__ import load_package
+    from oracle.oracle_py import Oracle, make_dims
+    pkg = load_package()
+    synth, sh = pkg.synth, pkg.sharding
+    w = synth.gdn_weights(9)
+    qkv, z, beta, alpha = synth.gdn_step_inputs(9, steps)
+    v0, nv, k0, nk = sh.gdn_head_slice(rank, world)
+    mine = sh.gdn_slice_inputs(rank, world, qkv, z, beta, alpha, w["conv_w"], w["A_log"], w["dt_bias"])
+    dims = make_dims(linear_num_v_heads=nv, linear_num_k_heads=nk)
+    conv = np.zeros((3, 2 * nk * 128 + nv * 128), np.float32)
+    ssm = np.ascontiguousarray(synth.gdn_state(9)[v0:v0 + nv])
+    out = Oracle("port").gdn_run(dims, conv, ssm, mine["qkv"], mine["z"], mine["beta"], mine["alpha"], mine["conv_w"],
+                                 mine["A_log"], mine["dt_bias"], w["norm_w"])
+    outs = [torch.zeros(steps, nv * 128) for _ in range(world)]
+    states = [torch.zeros(nv, 128, 128) for _ in range(world)]
+    dist.all_gather(outs, torch.from_numpy(np.ascontiguousarray(out, dtype=np.float32)))
+    dist.all_gather(states, torch.from_numpy(ssm))
+    if rank == 0:
+        np.savez(out_file, out=np.concatenate([o.numpy() for o in outs], axis=1), ssm=np.concatenate([s_.numpy() for s_ in states]))
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_gdn_layers_sliced_by_value_head_reproduce_the_whole_layer(tmp_path, port, synth, world):
+    from oracle.oracle_py import make_dims
+    steps = 3
+    out_file = str(tmp_path / "gdn.npz")
+    mp.spawn(_gdn_worker, args=(world, _free_port(), steps, out_file), nprocs=world, join=True)
+    got = np.load(out_file)
+    w = synth.gdn_weights(9)
+    qkv, z, beta, alpha = synth.gdn_step_inputs(9, steps)
+    conv = np.zeros((3, 12288), np.float32); ssm = synth.gdn_state(9).copy()
+    want = port.gdn_run(make_dims(), conv, ssm, qkv, z, beta, alpha, w["conv_w"], w["A_log"], w["dt_bias"], w["norm_w"])
+    np.testing.assert_array_equal(got["out"], np.asarray(want, dtype=np.float32))   # heads never mix: bit for bit
+    np.testing.assert_array_equal(got["ssm"], ssm)
