@@ -197,20 +197,30 @@ gdn_decode_stream_kernel(GdnDims g, TokSpec toks, float *__restrict__ ssm, long 
             int tok, vh;
             item_of(j, tok, vh);
             const unsigned char *stg = st_smem + s * kStageBytes;
-            if (lane == 0) {
-                float *dst = state_of(tok, vh);
-#pragma unroll
-                for (int c = 0; c < 4; c++) bulk_s2g(dst + c * (kStateBytes / 16), sbase + s * kStageBytes + c * (kStateBytes / 4), kStateBytes / 4);
-                bulk_commit();
-            }
-            // gated RMS-norm of the pair's output: o * rsqrt(mean o^2 + eps) * w * silu(z)
+            // what the output needs leaves the stage first, so that the stage is written back and re-armed before the
+            // output is computed (batch 64: 104.5 -> 97.7 us per layer)
             const float *ssp = reinterpret_cast<const float *>(stg + kOffSS);
             float total_ss = 0.f;
 #pragma unroll
             for (int w = 0; w < kStWarps; w++) total_ss += ssp[w];
             float4 o = *reinterpret_cast<const float4 *>(stg + kOffO + lane * 16);
+            float4 zz = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (has_norm) zz = *reinterpret_cast<const float4 *>(stg + kOffZ + lane * 16);
+            __syncwarp();
+            if (lane == 0) {
+                float *dst = state_of(tok, vh);
+#pragma unroll
+                for (int c = 0; c < 4; c++) bulk_s2g(dst + c * (kStateBytes / 16), sbase + s * kStageBytes + c * (kStateBytes / 4), kStateBytes / 4);
+                bulk_commit();
+                if (j + kStStages < n_my) {
+                    bulk_wait_read0();  // the store has read the stage
+                    fetch_state(j + kStStages);
+                    fetch_small(j + kStStages);
+                    armed = j + kStStages + 1;
+                }
+            }
+            // gated RMS-norm of the pair's output: o * rsqrt(mean o^2 + eps) * w * silu(z)
             if (has_norm) {
-                const float4 zz = *reinterpret_cast<const float4 *>(stg + kOffZ + lane * 16);
                 const float inv = 1.0f / sqrtf(total_ss / kSDv + g.eps);
                 o.x = o.x * inv * nw[0] * (zz.x / (1.0f + expf(-zz.x)));
                 o.y = o.y * inv * nw[1] * (zz.y / (1.0f + expf(-zz.y)));
@@ -218,13 +228,6 @@ gdn_decode_stream_kernel(GdnDims g, TokSpec toks, float *__restrict__ ssm, long 
                 o.w = o.w * inv * nw[3] * (zz.w / (1.0f + expf(-zz.w)));
             }
             *reinterpret_cast<float4 *>(out + ((size_t)tok * g.Hv + vh) * kSDv + lane * 4) = o;
-            __syncwarp();
-            if (lane == 0 && j + kStStages < n_my) {
-                bulk_wait_read0();  // the store has read the stage
-                fetch_state(j + kStStages);
-                fetch_small(j + kStStages);
-                armed = j + kStStages + 1;
-            }
         }
         if (lane == 0) {
             if (!ok) {
