@@ -449,6 +449,7 @@ extern "C" int fm_kv_len(const FmCtx *ctx, int fa_idx, int seq) {
 
 extern "C" fm_status fm_reset(FmCtx *ctx, int seq) {
     if (!ctx) return FM_ERR_INVALID;
+    ctx->last_state_li = -1;  // the next GatedDeltaNet step is not launched under this call's tail
     const FmConfig &c = ctx->cfg;
     if (seq < -1 || seq >= c.max_seqs) return fail(ctx, FM_ERR_INVALID, "fm_reset: seq %d", seq);
     FM_CUDA(ctx, cudaSetDevice(c.device));
@@ -1073,10 +1074,13 @@ extern "C" fm_status fm_gdn_decode(FmCtx *ctx, int li, const int *seq, int batch
                                                         ctx->d_gdn_scratch, ctx->sm_count, ctx->d_err, ctx->stream), "gdn_decode_stream");
         else
             st = launched(ctx, launch_gdn_decode(g, t, conv_l, ssm_l, (long long)cn, (long long)sn, d_qkv + (size_t)i0 * ctx->conv_dim, d_z + i0 * vd,
-                                                 d_b + i0 * hv, d_a + i0 * hv, d_cw, d_al, d_db, d_nw, d_out + i0 * vd, ctx->layer_overlap && !sg.host,
+                                                 d_b + i0 * hv, d_a + i0 * hv, d_cw, d_al, d_db, d_nw, d_out + i0 * vd,
+                                                 // not behind a step of the same layer, nor behind a prefill, import or reset
+                                                 ctx->layer_overlap && !sg.host && ctx->last_state_li >= 0 && ctx->last_state_li != li,
                                                  ctx->stream), "gdn_decode");
         if (st) return st;
         for (int i = 0; i < t.n; i++) ctx->gdn_steps[lidx(ctx, li, seq[i0 + i])]++;  // only once the step is queued
+        ctx->last_state_li = li;
     }
     if (sg.host) FM_CUDA(ctx, cudaMemcpyAsync(ctx->h_err, ctx->d_err, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
     FM_CUDA(ctx, sg.pull(out, w_out, batch * vd));
@@ -1088,6 +1092,7 @@ extern "C" fm_status fm_gdn_prefill(FmCtx *ctx, int li, int seq, int n, int chun
                                     const float *beta, const float *alpha, const uint16_t *conv_w, const float *A_log,
                                     const uint16_t *dt_bias, const uint16_t *norm_w, float *out) {
     if (!ctx) return FM_ERR_INVALID;
+    ctx->last_state_li = -1;  // the next GatedDeltaNet step is not launched under this call's tail
     if (!qkv || !z || !beta || !alpha || !out) return fail(ctx, FM_ERR_INVALID, "fm_gdn_prefill: null argument");
     const FmConfig &c = ctx->cfg;
     if (li < 0 || li >= c.num_linear_layers || seq < 0 || seq >= c.max_seqs) return fail(ctx, FM_ERR_INVALID, "fm_gdn_prefill: layer %d / seq %d", li, seq);
@@ -1362,6 +1367,7 @@ extern "C" fm_status fm_state_export(FmCtx *ctx, int li, int seq, float *conv, f
 
 extern "C" fm_status fm_state_import(FmCtx *ctx, int li, int seq, const float *conv, const float *ssm) {
     if (!ctx) return FM_ERR_INVALID;
+    ctx->last_state_li = -1;  // the next GatedDeltaNet step is not launched under this call's tail
     const FmConfig &c = ctx->cfg;
     if (li < 0 || li >= c.num_linear_layers || seq < 0 || seq >= c.max_seqs) return fail(ctx, FM_ERR_INVALID, "fm_state_import: bad argument");
     FM_CUDA(ctx, cudaSetDevice(c.device));

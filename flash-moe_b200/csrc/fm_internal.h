@@ -191,7 +191,8 @@ struct FmCtx {
     // layer's kernel drains (different layers touch different pages, inputs and outputs)
     bool overlap_prev = false, overlap_merge = false, overlap_layers = false;
     int overlap_nlayers = 0;
-    bool layer_overlap = false;  // fm_set_layer_overlap: consecutive decode calls touch different layers' state  // layers of the fm_attn_decode_layers call in progress (valid while overlap_layers)
+    bool layer_overlap = false;  // fm_set_layer_overlap: consecutive decode calls touch different layers' state
+    int last_state_li = -1;      // GatedDeltaNet layer the last decode step updated; -1 after anything else that writes state  // layers of the fm_attn_decode_layers call in progress (valid while overlap_layers)
     std::vector<cudaEvent_t> prof_ev;  // pairs (start, stop)
     size_t prof_used = 0;
 

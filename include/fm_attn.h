@@ -305,8 +305,9 @@ fm_status fm_out_proj_norm(FmCtx *ctx, const FmProjWeights *w, int n, const floa
  * layer or to a projection).  The step is then launched as a programmatic dependent of whatever precedes it: it
  * requests its recurrent state at once and waits for the previous launch to complete before it reads qkv, z, beta,
  * alpha or writes anything, so its start-up and the state's trip from HBM hide behind the previous kernel's tail.
- * Device-pointer mode, batches that take the one-launch form (fewer than 512 (head, sequence) pairs).  Two consecutive
- * steps of the SAME layer must not be issued with this on. */
+ * Device-pointer mode, batches that take the one-launch form (fewer than 512 (head, sequence) pairs).  The library
+ * itself keeps a step of the layer it stepped last, or one that follows its own prefill, import or reset, in plain
+ * stream order; launches it does not know about are the caller's to vouch for. */
 fm_status fm_set_layer_overlap(FmCtx *ctx, int on);
 
 /* Number of kernels this context has launched since creation (bench bookkeeping). */
