@@ -384,6 +384,9 @@ def run_ours(args):
         ctx = None
         torch.cuda.empty_cache()
         extra = _probe_gdn_decode_sharded(pkg, torch, dist, dev, peak, rank, world)
+        if ss == 1:
+            # batch 64 x 131072 rows does not fit one GPU (258 GB of bf16 KV); split by KV head it does
+            extra.update(_probe_attn_b64_head_sharded(pkg, torch, dist, dev, peak, rank, world, Hl, Hkvl))
     if rank == 0 and world == 1 and not args.no_extra:
         ctx.close()
         ctx = None
@@ -939,6 +942,58 @@ def _probe_gdn_decode_sharded(pkg, torch, dist, dev, peak, rank, world):
         del ctx
         torch.cuda.empty_cache()
     return res
+
+
+def _probe_attn_b64_head_sharded(pkg, torch, dist, dev, peak, rank, world, Hl, Hkvl):
+    """The largest cell of the hybrid configuration, batch 64 x context 131072: each rank holds one KV-head group (no
+    exchange inside the path).  Three layers are filled and stepped in one call (26 GB of rows per rank and step, far
+    more than L2; all 15 would take minutes to fill); the time is the slowest rank's, per layer and times 15."""
+    B, L, NL = 64, 131072, 3
+    need = B * (L + 128) * NL * Hkvl * D * 2 * 2 + (8 << 30)
+    free, _ = torch.cuda.mem_get_info(dev)
+    if free < need:
+        return {"decode_b64_ctx131072_head_sharded": f"skipped: {need >> 30} GiB needed, {free >> 30} GiB free"}
+    cfg = pkg.default_config(num_attn_heads=Hl, num_kv_heads=Hkvl, num_full_layers=NL, num_linear_layers=0, max_seqs=B,
+                             max_seq_len=L + 64, max_batch_tokens=64, device=dev.index,
+                             kv_dtype=pkg.binding.FM_KV_FP8_E4M3 if KV_DTYPE == "fp8" else pkg.binding.FM_KV_BF16)
+    ctx = pkg.Context(cfg)
+    ctx.set_stream(torch.cuda.current_stream().cuda_stream)
+    gen = torch.Generator(device=dev); gen.manual_seed(4321 + rank)
+    K = torch.randn((L, Hkvl * D), device=dev, generator=gen).bfloat16().float()
+    for layer in range(NL):
+        for s_ in range(B):
+            ctx.kv_import(layer, s_, K, K, L)
+    del K
+    qp = torch.randn((NL, B, Hl * 2 * D), device=dev, generator=gen)
+    kn = torch.randn((NL, B, Hkvl * D), device=dev, generator=gen)
+    out = torch.empty((NL, B, Hl * D), device=dev)
+    sq, skv, so = B * Hl * 2 * D, B * Hkvl * D, B * Hl * D
+    seqs = list(range(B))
+    pos = L
+
+    def token(p_):
+        ctx.attn_decode_layers(0, NL, seqs, [p_] * B, out, qp, kn, kn, sq, skv, so)
+    for _ in range(2):
+        token(pos); pos += 1
+    torch.cuda.synchronize()
+    dist.barrier()
+    reps = 3
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        token(pos); pos += 1
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / reps], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    kv_bytes = NL * B * (L + 3) * KV_BYTES_PER_ROW  # whole job: both KV heads
+    ctx.close()
+    del ctx
+    torch.cuda.empty_cache()
+    return {"decode_b64_ctx131072_head_sharded": {"ms_per_layer": ms / NL, "ms_per_token_15_layers": ms / NL * 15, "layers_stepped": NL,
+                                                  "kv_gbps_all_ranks": kv_bytes / ms / 1e6,
+                                                  "frac_of_peak_per_gpu": kv_bytes / ms / 1e6 / world / peak, "ranks": world}}
 
 
 def _probe_gdn_prefill(pkg, torch, dev, gen):
